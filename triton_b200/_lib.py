@@ -1,0 +1,87 @@
+"""ctypes binding of ``libtriton_b200.so`` (the C ABI declared in ``include/triton_b200.h``).
+
+There is no CPU fallback: if the shared library is missing or a call fails, the wrappers
+raise. ``lib()`` loads the library on first use.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_void_p
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "libtriton_b200.so"
+
+OK = 0
+ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_CUDA, ERR_TIMEOUT, ERR_TMAP, ERR_TOO_LARGE = -1, -2, -3, -4, -5, -6
+
+BF16, F16, F32, E4M3, E5M2 = 0, 1, 2, 3, 4
+
+
+class Tb200Error(RuntimeError):
+    def __init__(self, code: int, what: str):
+        self.code = code
+        super().__init__(f"{what}: {error_string(code)} (code {code})")
+
+
+class GemmArgs(Structure):
+    _fields_ = [
+        ("a", c_void_p), ("b", c_void_p), ("c", c_void_p),
+        ("m", c_int64), ("n", c_int64), ("k", c_int64),
+        ("lda", c_int64), ("ldb", c_int64), ("ldc", c_int64),
+        ("in_dtype", c_int32), ("out_dtype", c_int32),
+        ("a_k_major", c_int32), ("b_k_major", c_int32),
+        ("split_k", c_int32), ("block_n", c_int32),
+        ("workspace", c_void_p), ("workspace_bytes", c_size_t),
+        ("scale_a", c_void_p), ("scale_b", c_void_p),
+    ]
+
+
+_lib = None
+
+
+def _declare(l: ctypes.CDLL) -> None:
+    l.tb200_version.restype = c_int
+    l.tb200_version.argtypes = []
+    l.tb200_error_string.restype = c_char_p
+    l.tb200_error_string.argtypes = [c_int]
+    l.tb200_check.restype = c_int
+    l.tb200_check.argtypes = [c_void_p]
+    l.tb200_last_status_code.restype = c_int
+    l.tb200_last_status_code.argtypes = []
+    l.tb200_gemm.restype = c_int
+    l.tb200_gemm.argtypes = [POINTER(GemmArgs), c_void_p]
+    l.tb200_gemm_workspace_bytes.restype = c_size_t
+    l.tb200_gemm_workspace_bytes.argtypes = [POINTER(GemmArgs)]
+
+
+def lib() -> ctypes.CDLL:
+    """Returns the loaded library; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m triton_b200.build` "
+                "(triton_b200 has no CPU or PyTorch fallback)")
+        l = ctypes.CDLL(str(LIB_PATH))
+        _declare(l)
+        _lib = l
+    return _lib
+
+
+def error_string(code: int) -> str:
+    return lib().tb200_error_string(code).decode()
+
+
+def check(rc: int, what: str) -> None:
+    if rc != OK:
+        raise Tb200Error(rc, what)
+
+
+def current_stream_ptr(device=None) -> int:
+    import torch
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def sync_check(device=None) -> None:
+    """Synchronises the current stream and raises if a device-side wait timed out."""
+    check(lib().tb200_check(c_void_p(current_stream_ptr(device))), "tb200_check")
