@@ -1,0 +1,298 @@
+#!/usr/bin/env python
+"""Benchmark driver.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+Default workload (the configuration the headline metric is quoted on): the bf16 persistent
+warp-specialised GEMM, M=N=K=8192, A row-major, B supplied K-major, entries N(0,1)/sqrt(K) from
+seed 1, fp32 accumulation, bf16 output. One "step" is one GEMM over resident inputs. With N GPUs
+every rank owns one 8192-column block of a K x (8192*N) B (no collective on the data path; weak
+scaling) and the reported value is the whole job's TFLOP/s with the time taken as the max over
+ranks.
+
+One JSON line is printed by rank 0. Keys beyond the base contract:
+  roofline      tensor-pipe roofline of the GEMM kernel: achieved = 2MNK / mean CUDA-event duration
+                of the launches in the timed region, peak = measured cuBLAS bf16 figure from
+                MEASURED_PEAKS.json (burst figure when the timed region is shorter than 0.5 s,
+                else the sustained one), traffic = DRAM bytes per launch from the committed ncu
+                capture (profiles/), or null.
+  e2e           same metric through the public Python entry point with HOST (pinned) inputs and a
+                host result: H2D copies of A and B and the D2H copy of C are inside the timed region.
+  cpu_baseline  the CPU oracle (torch CPU fp32 matmul, all host threads) timed on a bounded sample.
+  clocks        SM clock / throttle reasons sampled through NVML during the timed region.
+
+`--impl reference` times the reference's CPU path for this workload (the oracle port: the
+reference's own kernels need a GPU and its compiler, which cannot be built offline) on a bounded
+sample per step with all host threads.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+M = N = K = 8192
+WORKLOAD = "bf16 GEMM M=N=K=8192, A row-major, B K-major (transposed), N(0,1)/sqrt(K) seed 1, fp32 acc, bf16 out"
+
+# DRAM bytes per launch of gemm_kernel<256,4> at 8192^3 from the committed ncu capture
+# (profiles/gemm_bf16_8192.md); None until a capture exists.
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def read_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"bf16_burst": float(p["bf16_tflops"]), "bf16_sustained": float(p["bf16_tflops_sustained"]),
+                "hbm": float(p["hbm_gbs"]), "source": "measured"}
+    return {"bf16_burst": 1590.0, "bf16_sustained": 1400.0, "hbm": 6650.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Polls NVML for SM clock and throttle reasons while the timed region runs (read-only)."""
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thr = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def sample(self):
+        if not self.nv:
+            return
+        try:
+            nv = self.nv
+            self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+            r = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h) if hasattr(
+                nv, "nvmlDeviceGetCurrentClocksEventReasons") else nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+            names = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown",
+                     0x4: "sw_power_cap", 0x80: "hw_power_brake_slowdown"}
+            for bit, name in names.items():
+                if r & bit:
+                    self.reasons.add(name)
+        except Exception:
+            pass
+
+    def _run(self):
+        while not self._stop.is_set():
+            self.sample()
+            time.sleep(0.01)
+
+    def start(self):
+        if self.nv:
+            self._thr = threading.Thread(target=self._run, daemon=True)
+            self._thr.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._thr:
+            self._thr.join()
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None,
+                "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def make_inputs(rank: int, device):
+    import torch
+    g = torch.Generator(device="cpu").manual_seed(1 + 1000 * rank)
+    a = (torch.randn(M, K, generator=g) / K ** 0.5).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) / K ** 0.5).to(torch.bfloat16)
+    return a, w
+
+
+def cpu_baseline(budget_s: float = 20.0):
+    """Times the CPU oracle (torch fp32 matmul, all threads) on the largest cube of the workload's
+    family that fits the time budget; returns the cpu_baseline object."""
+    import torch
+    from oracle import gemm as o_gemm
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    g = torch.Generator().manual_seed(1)
+    best = None
+    rate = None
+    for s in (1024, 2048, 4096, 8192):
+        flops = 2.0 * s ** 3
+        if rate is not None and flops / rate > budget_s:
+            break
+        a = (torch.randn(s, s, generator=g) / s ** 0.5).to(torch.bfloat16)
+        w = (torch.randn(s, s, generator=g) / s ** 0.5).to(torch.bfloat16)
+        o_gemm.gemm_ref(a[:256], w.t())  # warm the thread pool
+        t0 = time.perf_counter()
+        o_gemm.gemm_ref(a, w.t())
+        dt = time.perf_counter() - t0
+        rate = flops / dt
+        best = (s, rate)
+    s, rate = best
+    return {"value": rate / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+            "sample": f"torch CPU fp32 matmul of bf16 inputs, M=N=K={s} (one pass, all host threads)"}
+
+
+def run_reference(args, rank: int, world: int):
+    """Reference arm: the CPU path of the workload (oracle port) with all host threads; each step is
+    a 256-row band of the 8192^3 GEMM."""
+    if rank != 0:
+        return
+    import torch
+    from oracle import gemm as o_gemm
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    g = torch.Generator().manual_seed(1)
+    rows = 256
+    a = (torch.randn(rows, K, generator=g) / K ** 0.5).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) / K ** 0.5).to(torch.bfloat16)
+    for _ in range(max(1, min(args.warmup, 2))):
+        o_gemm.gemm_ref(a, w.t())
+    steps = max(1, min(args.steps, 10))
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        o_gemm.gemm_ref(a, w.t())
+    dt = (time.perf_counter() - t0) / steps
+    val = 2.0 * rows * N * K / dt / 1e12
+    sample = f"{rows}-row band of the 8192^3 GEMM per step, torch CPU fp32 matmul, {steps} timed steps"
+    print(json.dumps({
+        "impl": "reference", "metric": "bf16 GEMM throughput", "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "reference_path": "CPU (oracle port of the reference's torch check); "
+                   "the reference's TLX kernels need its own compiler build and a GPU"},
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import torch
+    import torch.distributed as dist
+    from triton_b200 import _lib
+    from triton_b200.tutorials.blackwell_gemm_ws import matmul
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: triton_b200 has no CPU path")
+    _lib.lib()  # fail loudly if the extension is missing
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    warmup = max(args.warmup, 3)
+    steps = max(args.steps, 1)
+    a_h, w_h = make_inputs(rank, dev)
+    a_pin, w_pin = a_h.pin_memory(), w_h.pin_memory()
+    a = a_pin.to(dev, non_blocking=True)
+    w = w_pin.to(dev, non_blocking=True)
+    b = w.t()  # logical (K, N), K-major in memory
+    c_pin = torch.empty(M, N, dtype=torch.bfloat16).pin_memory()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---------------------------------------------------------------- device-resident timing
+    for _ in range(warmup):
+        c = matmul(a, b)
+    barrier()
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    t_all0 = torch.cuda.Event(enable_timing=True)
+    t_all1 = torch.cuda.Event(enable_timing=True)
+    t_all0.record()
+    for i in range(steps):
+        starts[i].record()
+        c = matmul(a, b)
+        ends[i].record()
+    t_all1.record()
+    sampler.sample()
+    barrier()
+    clocks = sampler.stop()
+    _lib.sync_check(dev)
+    total_ms = t_all0.elapsed_time(t_all1)
+    kernel_ms = statistics.mean(s.elapsed_time(e) for s, e in zip(starts, ends))
+
+    # ---------------------------------------------------------------- end to end (host buffers)
+    e2e_steps = max(3, min(steps, 10))
+    for _ in range(2):
+        c_pin.copy_(matmul(a_pin.to(dev, non_blocking=True), w_pin.to(dev, non_blocking=True).t()), non_blocking=True)
+    barrier()
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(e2e_steps):
+        a_d = a_pin.to(dev, non_blocking=True)
+        w_d = w_pin.to(dev, non_blocking=True)
+        c_pin.copy_(matmul(a_d, w_d.t()), non_blocking=True)
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1) / e2e_steps
+
+    if world > 1:
+        t = torch.tensor([total_ms, kernel_ms, e2e_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms, kernel_ms, e2e_ms = t.tolist()
+
+    if rank == 0:
+        flops = 2.0 * M * N * K
+        ms_per_step = total_ms / steps
+        value = world * flops / (ms_per_step * 1e-3) / 1e12
+        peaks = read_peaks()
+        sustained = total_ms > 500.0
+        peak = peaks["bf16_sustained"] if sustained else peaks["bf16_burst"]
+        achieved = flops / (kernel_ms * 1e-3) / 1e12
+        out = {
+            "metric": "bf16 GEMM throughput", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": steps,
+            "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "sharding": "one 8192-column block of B per GPU, no collective",
+                       "l2": "inputs (256 MiB) and output (128 MiB) exceed the 126 MB L2; no flush"},
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                         "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+                         "peak_kind": ("sustained" if sustained else "burst") + " cuBLAS bf16, " + peaks["source"],
+                         "frac_of_nominal_2250": achieved / 2250.0, "kernel": "gemm_kernel<256,4>"},
+            "e2e": {"value": world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                    "h2d_bytes_per_step": 2 * M * K * 2, "d2h_bytes_per_step": M * N * 2, "steps": e2e_steps},
+            "gpu_launches": steps * world,
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            out["cpu_baseline"] = cpu_baseline()
+        print(json.dumps(out))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,33 @@
+"""Oracle for flash-attention forward (test infrastructure only).
+
+The reference checks its kernel against ``F.scaled_dot_product_attention(q, k, v, scale=sm_scale,
+is_causal=causal)`` (``third_party/tlx/tutorials/testing/test_correctness.py:425-435``). Its
+kernel also produces the row statistic ``M = m * sm_scale * log2(e) + log2(l)``
+(``blackwell_fa_ws_pipelined_persistent.py:886-894``), i.e. the base-2 log-sum-exp of the scaled
+scores. Both are restated here in fp32, one (batch, head) at a time to bound memory.
+"""
+import math
+
+import torch
+
+
+def attention_ref(q, k, v, sm_scale: float, causal: bool):
+    """q, k, v: (B, H, S, D). Returns (o in q.dtype, lse2 fp32 (B, H, S))."""
+    q32, k32, v32 = (t.detach().cpu().float() for t in (q, k, v))
+    B, H, S, D = q32.shape
+    Sk = k32.shape[2]
+    o = torch.empty(B, H, S, v32.shape[3], dtype=torch.float32)
+    lse2 = torch.empty(B, H, S, dtype=torch.float32)
+    mask = None
+    if causal:
+        mask = torch.ones(S, Sk, dtype=torch.bool).tril(diagonal=Sk - S)
+    for b in range(B):
+        for h in range(H):
+            s = (q32[b, h] @ k32[b, h].t()) * sm_scale
+            if mask is not None:
+                s = s.masked_fill(~mask, float("-inf"))
+            lse = torch.logsumexp(s, dim=-1)
+            p = torch.exp(s - lse[:, None])
+            o[b, h] = p @ v32[b, h]
+            lse2[b, h] = lse * math.log2(math.e)
+    return o.to(q.dtype), lse2

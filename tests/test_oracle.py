@@ -1,0 +1,130 @@
+"""Pins the CPU oracle against the reference's own golden material (no GPU needed)."""
+import os
+
+import numpy as np
+import torch
+
+from oracle import attention as o_attn
+from oracle import gemm as o_gemm
+from oracle import moe as o_moe
+from oracle import mxfp8 as o_mx
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def test_gemm_oracle_matches_reference_interpreter_fixture():
+    """tests/golden/gemm_interp_512.npz holds rows of C produced by the reference's tutorial-03
+    Triton kernel under TRITON_INTERPRET=1 (fp16 inputs, seed 0). fp16 output: tolerance 2 fp16
+    ulps of the row magnitude (the kernel accumulates K in blocks of 32, the oracle in one go)."""
+    fx = np.load(os.path.join(GOLDEN, "gemm_interp_512.npz"))
+    torch.manual_seed(int(fx["seed"]))
+    a = torch.randn(512, 512).to(torch.float16)
+    b = torch.randn(512, 512).to(torch.float16)
+    c = o_gemm.gemm_ref(a, b)
+    rows = fx["rows"].tolist()
+    got = c[rows].float().numpy()
+    want = fx["c_rows"].astype(np.float32)
+    np.testing.assert_allclose(got, want, rtol=2e-3, atol=0.0625)
+    assert abs(float(c.double().sum()) - float(fx["c_sum"])) < 1e-3 * float(fx["c_abs_sum"])
+
+
+def test_bitmatrix_metadata_docstring_example():
+    # reference: tensor_details/bitmatrix.py:10-19
+    bm = np.array([[0, 0, 1, 0, 1, 1, 0], [0, 1, 0, 0, 0, 1, 0], [1, 1, 1, 0, 0, 0, 1], [0, 0, 1, 0, 1, 0, 0]])
+    flat = np.concatenate([np.nonzero(r)[0] for r in bm])
+    md = o_moe.bitmatrix_metadata_ref(flat, 7)
+    assert md.col_sum.tolist() == [1, 2, 3, 0, 2, 2, 1]
+    assert md.col_sorted_indx.tolist() == [5, 3, 6, 0, 7, 9, 1, 10, 2, 4, 8]
+    assert md.row_sorted_indx.tolist() == [3, 6, 8, 1, 9, 0, 2, 4, 10, 5, 7]
+
+
+def test_ragged_metadata_docstring_example():
+    # reference: tensor_details/ragged_tensor.py:14-30 (block_offs are the self-consistent part of
+    # that example: slice_offs' last entry and the schedule rows in it do not add up)
+    md = o_moe.ragged_metadata_ref([15, 17, 0, 127], 159)
+    assert md.slice_offs.tolist()[:4] == [0, 15, 32, 32]
+    assert md.block_offs_data.tolist() == [[0, 1, 3, 3, 11], [0, 1, 2, 2, 6], [0, 1, 2, 2, 4], [0, 1, 2, 2, 3]]
+    s128 = md.block_schedule_data[3]
+    assert s128[:3].tolist() == [(0 << 16) | 0, (0 << 16) | 1, (0 << 16) | 3]
+    assert (s128[3:] == -1).all()
+    s16 = md.block_schedule_data[0]
+    assert s16[:4].tolist() == [0, 1, (1 << 16) | 1, 3] and s16[10] == (7 << 16) | 3
+
+
+def test_n_blocks_formula():
+    # reference: RaggedTensorMetadata.n_blocks, ragged_tensor.py:73-77 — an upper bound on the
+    # number of blocks of any split of n rows into n_slices slices
+    rng = np.random.default_rng(0)
+    for _ in range(200):
+        E = int(rng.integers(1, 40))
+        n = int(rng.integers(0, 3000))
+        bs = int(rng.choice([16, 32, 64, 128]))
+        cuts = np.sort(rng.integers(0, n + 1, E - 1))
+        sizes = np.diff(np.concatenate([[0], cuts, [n]]))
+        assert int(np.sum((sizes + bs - 1) // bs)) <= o_moe.n_blocks(E, n, bs)
+
+
+def test_remap_ragged_metadata():
+    md = o_moe.ragged_metadata_ref([15, 17, 0, 127], 159)
+    r = o_moe.remap_ragged_metadata_ref(md, np.array([-1, 0, 1, -1]))
+    assert r.slice_sizes.tolist() == [17, 0, -1, -1]
+    assert r.block_offs_data[0].tolist() == [1, 3, 2, -1, -1]
+    assert r.block_schedule_data[0][:3].tolist() == [0, (1 << 16) | 0, -1]
+
+
+def test_topk_ties_and_order():
+    x = torch.tensor([[1.0, 3.0, 3.0, 2.0, 0.0], [5.0, 5.0, 5.0, 5.0, 5.0]])
+    vals, indx, bits = o_moe.topk_ref(x, 2, apply_softmax=False)
+    assert indx.tolist() == [[1, 2], [0, 1]]
+    assert vals.tolist() == [[3.0, 3.0], [5.0, 5.0]]
+    assert bits.view(torch.int32)[:, 0].tolist() == [0b110, 0b11]
+    vals, indx, _ = o_moe.topk_ref(x, 3, apply_softmax=True)
+    np.testing.assert_allclose(vals.sum(1).numpy(), 1.0, rtol=1e-6)
+
+
+def test_scale_swizzle_roundtrip_and_atom_order():
+    rows, ks = 256, 8
+    s = torch.arange(rows * ks, dtype=torch.int32).remainder(251).to(torch.uint8).reshape(rows, ks)
+    flat = o_mx.swizzle_scales(s)
+    assert torch.equal(o_mx.unswizzle_scales(flat, rows, ks), s)
+    # 512-byte atom = [row % 32][row // 32 % 4][k % 4] (blackwell_scale.py:119-122)
+    r, kk = 128 + 37, 6
+    atom = ((r // 128) * (ks // 4) + kk // 4) * 512
+    assert flat[atom + (r % 32) * 16 + ((r % 128) // 32) * 4 + kk % 4] == s[r, kk]
+
+
+def test_mxfp8_dequant_known_values():
+    q = torch.full((128, 32), 1.5).to(torch.float8_e4m3fn)
+    s = torch.full((128, 1), 127 + 3, dtype=torch.uint8)
+    s4 = torch.cat([s, s, s, s], dim=1)
+    d = o_mx.dequantize(torch.cat([q, q, q, q], dim=1), o_mx.swizzle_scales(s4))
+    assert torch.all(d == 12.0)
+
+
+def test_attention_oracle_matches_sdpa():
+    torch.manual_seed(0)
+    q, k, v = (torch.randn(1, 2, 96, 32) for _ in range(3))
+    for causal in (False, True):
+        o, lse2 = o_attn.attention_ref(q, k, v, 0.3, causal)
+        want = torch.nn.functional.scaled_dot_product_attention(q, k, v, scale=0.3, is_causal=causal)
+        torch.testing.assert_close(o, want, atol=1e-5, rtol=1e-5)
+        s = (q @ k.transpose(-1, -2)) * 0.3
+        if causal:
+            s = s.masked_fill(~torch.ones(96, 96, dtype=torch.bool).tril(), float("-inf"))
+        torch.testing.assert_close(lse2, torch.logsumexp(s, -1) * 1.4426950408889634, atol=1e-5, rtol=1e-5)
+
+
+def test_moe_layer_oracle_is_dense_mixture():
+    """With k = E every expert sees every token: the layer equals the dense gate-weighted sum."""
+    torch.manual_seed(1)
+    T, D, F, E = 24, 16, 8, 4
+    x = torch.randn(T, D)
+    logits = torch.randn(T, E)
+    w1 = torch.randn(E, D, 2 * F) * 0.2
+    w2 = torch.randn(E, F, D) * 0.2
+    got = o_moe.moe_layer_ref(x, logits, w1, w2, k=E, alpha=1.0, limit=None)
+    gate = torch.softmax(logits, -1)
+    want = torch.zeros(T, D)
+    for e in range(E):
+        want += gate[:, e:e + 1] * (o_moe.swiglu_ref(x @ w1[e], 1.0) @ w2[e])
+    torch.testing.assert_close(got, want, atol=1e-5, rtol=1e-5)

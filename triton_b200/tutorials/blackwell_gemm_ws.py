@@ -55,6 +55,8 @@ def matmul(a: torch.Tensor, b: torch.Tensor, config=None) -> torch.Tensor:
     c = torch.empty((M, N), device=a.device, dtype=a.dtype)
     if M == 0 or N == 0:
         return c
+    if K == 0:
+        return c.zero_()
 
     a, a_k_major, lda = _operand(a)
     # For B (K, N): contiguous rows mean N is the fast axis, i.e. not K-major.
