@@ -90,7 +90,7 @@ typedef struct {
   int32_t a_k_major;
   int32_t b_k_major;
   int32_t split_k;
-  int32_t block_n; /* 0 = choose; else 64, 128 or 256 */
+  int32_t block_n; /* 0 = choose; 64, 128 or 256 = one CTA per 128 x block_n tile; 512 = CTA pair per 256 x 256 tile */
   void* workspace;
   size_t workspace_bytes;
   const float* scale_a;

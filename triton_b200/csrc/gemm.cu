@@ -1,15 +1,37 @@
 // Dense GEMM for sm_100a: persistent, warp-specialised, TMA -> shared-memory ring ->
 // tcgen05.mma with the accumulator double-buffered in tensor memory -> epilogue warps.
 //
-// Roles (192 threads): warp 0 = TMA producer (one elected lane), warp 1 = MMA issuer (one
-// lane; the warp also owns the TMEM allocation), warps 2..5 = epilogue (each reads its own
-// 32-lane quarter of TMEM). Tile = 128 x BN, K step = 128 bytes of K per row (64 16-bit or
-// 128 8-bit elements). The same kernel serves bf16/fp16 (kind::f16) and e4m3/e5m2
-// (kind::f8f6f4): operand geometry, instruction descriptor and output mode are parameters.
+// Roles (192 threads): warp 0 = TMA producer (one lane), warp 1 = MMA issuer (one lane; the warp
+// also owns the TMEM allocation), warps 2..5 = epilogue (each reads its own 32-lane quarter of
+// TMEM). K step = 128 bytes of K per operand row (64 16-bit or 128 8-bit elements) = 4 MMAs.
+// The same kernel serves bf16/fp16 (kind::f16) and e4m3/e5m2 (kind::f8f6f4).
+//
+// Two tilings:
+//   single CTA : 128 x BN tile per CTA, BN in {64, 128, 256}.
+//   CTA pair   : a 2-CTA cluster shares one 256 x 256 tile. CTA r loads A rows [m0+128r, +128)
+//                and B rows (N) [n0+128r, +128); the leader (rank 0) issues
+//                tcgen05.mma.cta_group::2 with M = 256, which reads A from each CTA's own shared
+//                memory and the two halves of B from both, and leaves rows 128r..128r+127 of the
+//                accumulator in CTA r's tensor memory. Per CTA a K step lands 32 KB instead of
+//                48 KB, which keeps the TMA engine (measured ~75 B/clk/SM) under the MMA rate.
+//                Signalling: TMA bytes of both CTAs count on the leader's `full` barrier; the
+//                leader issues one tcgen05.commit per CTA onto that CTA's `empty` / `tfull` barrier
+//                (two plain commits, no multicast); epilogue warps of both CTAs arrive on the
+//                leader's `tempty`.
+//
+// The issue loops are kept lean on purpose: measured on B200, tcgen05.mma issue blocks the issuing
+// thread until the tensor pipe accepts the instruction, so every other instruction in the MMA
+// thread's loop is exposed tensor-pipe idle time. All loop-invariant parameters are copied to
+// registers first (inline asm with a memory clobber otherwise forces re-loads from the parameter
+// bank), descriptors advance by integer adds, stage/phase are running counters, and the commit
+// and the wait of each K step are placed between its MMAs.
 //
 // Counterpart in the reference: matmul_kernel_tma_ws_blackwell,
 // third_party/tlx/tutorials/blackwell_gemm_ws.py:1168-1483 (producer :961-1088, MMA :840-957,
 // epilogue :680-836) and the tensorwise path of blackwell_scaled_mm_ws.py:51-378.
+#include <stdlib.h>
+#include <string.h>
+
 #include "common.cuh"
 #include "host_common.h"
 
@@ -43,35 +65,113 @@ struct GemmParams {
   int bk_elems;  // K elements per stage
   int group_m;
   int out_mode;  // 0 bf16, 1 fp16, 2 fp32 to c, 3 fp32 partial to ws
-  int is_f8;
   uint32_t idesc;
   OperandGeom ga, gb;
 };
 
-template <int BN, int STAGES>
+// BNC = B rows (N) staged per CTA; the tile is 128 x BNC (single) or 256 x 256 (pair, BNC = 128).
+template <int BNC, int STAGES>
 struct GemmSmem {
   static constexpr int A_BYTES = BM * STAGE_K_BYTES;
-  static constexpr int B_BYTES = BN * STAGE_K_BYTES;
+  static constexpr int B_BYTES = BNC * STAGE_K_BYTES;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
   static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 4) * 8 + 16 + 1024;  // + alignment slack
 };
 
-__device__ __forceinline__ void unit_to_tile(const GemmParams& p, int unit, int& pid_m, int& pid_n, int& ks) {
-  int tile = unit / p.split_k;
-  ks = unit - tile * p.split_k;
-  const int group = p.group_m * p.tiles_n;
+struct TileCoord {
+  int pid_m, pid_n, ks;
+};
+
+__device__ __forceinline__ TileCoord unit_to_tile(int unit, int split_k, int group_m, int tiles_m, int tiles_n) {
+  TileCoord t;
+  const int tile = unit / split_k;
+  t.ks = unit - tile * split_k;
+  const int group = group_m * tiles_n;
   const int gid = tile / group;
-  const int first_m = gid * p.group_m;
-  const int gsz = min(p.tiles_m - first_m, p.group_m);
+  const int first_m = gid * group_m;
+  const int gsz = min(tiles_m - first_m, group_m);
   const int r = tile - gid * group;
-  pid_m = first_m + (r % gsz);
-  pid_n = r / gsz;
+  t.pid_m = first_m + (r % gsz);
+  t.pid_n = r / gsz;
+  return t;
 }
 
-template <int BN, int STAGES>
+// Writes 32 consecutive columns of one output row (fp32 accumulators in v) in the output mode.
+__device__ __forceinline__ void store_chunk(void* c, float* ws, long long ldc, int m, int n, int out_mode,
+                                            const uint32_t (&v)[32], int row, int col, int ks, float alpha) {
+  if (row >= m || col >= n) return;
+  const bool full = col + 32 <= n;
+  if (out_mode <= 1) {
+    uint16_t* dst = reinterpret_cast<uint16_t*>(c) + (long long)row * ldc + col;
+    if (full && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint32_t w[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const float lo = __uint_as_float(v[j * 8 + 2 * t]) * alpha;
+          const float hi = __uint_as_float(v[j * 8 + 2 * t + 1]) * alpha;
+          w[t] = (out_mode == 0) ? pack_bf16x2(lo, hi) : pack_f16x2(lo, hi);
+        }
+        reinterpret_cast<uint4*>(dst)[j] = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    } else {
+      const int cnt = n - col;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        if (j < cnt) {
+          const float x = __uint_as_float(v[j]) * alpha;
+          if (out_mode == 0) {
+            __nv_bfloat16 h = __float2bfloat16_rn(x);
+            dst[j] = *reinterpret_cast<uint16_t*>(&h);
+          } else {
+            __half h = __float2half_rn(x);
+            dst[j] = *reinterpret_cast<uint16_t*>(&h);
+          }
+        }
+      }
+    }
+  } else {
+    float* dst = (out_mode == 2) ? reinterpret_cast<float*>(c) + (long long)row * ldc + col
+                                 : ws + ((long long)ks * m + row) * (long long)n + col;
+    if (full && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        reinterpret_cast<float4*>(dst)[j] =
+            make_float4(__uint_as_float(v[4 * j]) * alpha, __uint_as_float(v[4 * j + 1]) * alpha,
+                        __uint_as_float(v[4 * j + 2]) * alpha, __uint_as_float(v[4 * j + 3]) * alpha);
+      }
+    } else {
+      const int cnt = n - col;
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j < cnt) dst[j] = __uint_as_float(v[j]) * alpha;
+    }
+  }
+}
+
+template <bool PAIR, bool F8>
+__device__ __forceinline__ void issue_mma(uint32_t tmem_d, uint64_t ad, uint64_t bd, uint32_t idesc, uint32_t accum) {
+  if constexpr (PAIR) {
+    if constexpr (F8)
+      umma_f8_ss_pair(tmem_d, ad, bd, idesc, accum);
+    else
+      umma_f16_ss_pair(tmem_d, ad, bd, idesc, accum);
+  } else {
+    if constexpr (F8)
+      umma_f8_ss(tmem_d, ad, bd, idesc, accum);
+    else
+      umma_f16_ss(tmem_d, ad, bd, idesc, accum);
+  }
+}
+
+template <int BNC, int STAGES, bool PAIR, bool F8>
 __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const __grid_constant__ GemmParams p) {
-  using L = GemmSmem<BN, STAGES>;
+  using L = GemmSmem<BNC, STAGES>;
+  constexpr int BN = PAIR ? 256 : BNC;        // accumulator columns per tile
+  constexpr int TILE_M = PAIR ? 256 : BM;     // output rows per scheduling unit
+  constexpr uint32_t TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET);
@@ -82,7 +182,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const __grid_cons
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  constexpr uint32_t TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
+  const int worker = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int num_workers = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
 
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&p.tma);
@@ -93,101 +195,158 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const __grid_cons
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&tfull[i], 1);
-      mbar_init(&tempty[i], 4);
+      mbar_init(&tempty[i], PAIR ? 8 : 4);
     }
     mbar_init_fence();
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, TMEM_COLS);
-    tmem_relinquish();
+    if constexpr (PAIR) {
+      tmem_alloc_pair(tmem_slot, TMEM_COLS);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(tmem_slot, TMEM_COLS);
+      tmem_relinquish();
+    }
   }
   tc_fence_before_sync();
-  __syncthreads();
+  if constexpr (PAIR) cluster_sync_all(); else __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+
+  // loop-invariant scheduling parameters in registers
+  const int units = p.units, split_k = p.split_k, group_m = p.group_m, tiles_m = p.tiles_m, tiles_n = p.tiles_n;
+  const int k_blocks = p.k_blocks, kb_per_split = p.kb_per_split;
+  int* const status = p.status;
+  const uint32_t smem_a = smem_u32(smem);
+  const uint32_t full_a = smem_u32(full), empty_a = smem_u32(empty);
 
   if (warp == 0) {
     // ------------------------------------------------------------- producer
     if (lane == 0) {
       const uint64_t pol = policy_evict_last();
-      uint32_t it = 0;
+      const int bk_elems = p.bk_elems;
+      const uint32_t a_boxes = p.ga.boxes, a_box_bytes = p.ga.box_bytes, a_box_mn = p.ga.box_mn, a_mn = p.ga.mn_major;
+      const uint32_t b_boxes = p.gb.boxes, b_box_bytes = p.gb.box_bytes, b_box_mn = p.gb.box_mn, b_mn = p.gb.mn_major;
+      const uint32_t leader_full = PAIR ? mapa_shared(full_a, 0) : full_a;
+      uint32_t s = 0, ph = 0;
       bool ok = true;
-      for (int unit = blockIdx.x; unit < p.units && ok; unit += gridDim.x) {
-        int pid_m, pid_n, ks;
-        unit_to_tile(p, unit, pid_m, pid_n, ks);
-        const int m0 = pid_m * BM, n0 = pid_n * BN;
-        const int kb0 = ks * p.kb_per_split;
-        const int kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
-        for (int kb = kb0; kb < kb1; ++kb, ++it) {
-          const uint32_t s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
-          if (!mbar_wait(&empty[s], ph ^ 1, p.status, WAIT_SMEM_EMPTY)) {
+      for (int unit = worker; unit < units && ok; unit += num_workers) {
+        const TileCoord t = unit_to_tile(unit, split_k, group_m, tiles_m, tiles_n);
+        const int m0 = t.pid_m * TILE_M + (int)rank * BM;
+        const int n0 = t.pid_n * BN + (int)rank * BNC * (PAIR ? 1 : 0);
+        const int kb0 = t.ks * kb_per_split;
+        const int kb1 = min(k_blocks, kb0 + kb_per_split);
+        int kx = kb0 * bk_elems;
+        for (int kb = kb0; kb < kb1; ++kb, kx += bk_elems) {
+          if (!mbar_wait_a(empty_a + s * 8, ph ^ 1, status, WAIT_SMEM_EMPTY)) {
             ok = false;
             break;
           }
-          mbar_expect_tx(&full[s], L::STAGE_BYTES);
-          uint8_t* sa = smem + s * L::STAGE_BYTES;
-          uint8_t* sb = sa + L::A_BYTES;
-          const int kx = kb * p.bk_elems;
-          for (uint32_t i = 0; i < p.ga.boxes; ++i) {
-            if (p.ga.mn_major)
-              tma_load_2d(sa + i * p.ga.box_bytes, &p.tma, &full[s], m0 + (int)(i * p.ga.box_mn), kx, pol);
-            else
-              tma_load_2d(sa + i * p.ga.box_bytes, &p.tma, &full[s], kx, m0 + (int)(i * p.ga.box_mn), pol);
+          if constexpr (PAIR) {
+            // the leader's barrier counts both CTAs' bytes
+            if (rank == 0) mbar_expect_tx_a(full_a + s * 8, 2 * L::STAGE_BYTES);
+          } else {
+            mbar_expect_tx_a(full_a + s * 8, L::STAGE_BYTES);
           }
-          for (uint32_t i = 0; i < p.gb.boxes; ++i) {
-            if (p.gb.mn_major)
-              tma_load_2d(sb + i * p.gb.box_bytes, &p.tmb, &full[s], n0 + (int)(i * p.gb.box_mn), kx, pol);
+          const uint32_t bar = leader_full + s * 8;
+          const uint32_t sa = smem_a + s * L::STAGE_BYTES;
+          const uint32_t sb = sa + L::A_BYTES;
+          for (uint32_t i = 0; i < a_boxes; ++i) {
+            const int mn = m0 + (int)(i * a_box_mn);
+            if constexpr (PAIR)
+              tma_load_2d_pair(sa + i * a_box_bytes, &p.tma, bar, a_mn ? mn : kx, a_mn ? kx : mn, pol);
             else
-              tma_load_2d(sb + i * p.gb.box_bytes, &p.tmb, &full[s], kx, n0 + (int)(i * p.gb.box_mn), pol);
+              tma_load_2d_a(sa + i * a_box_bytes, &p.tma, bar, a_mn ? mn : kx, a_mn ? kx : mn, pol);
+          }
+          for (uint32_t i = 0; i < b_boxes; ++i) {
+            const int mn = n0 + (int)(i * b_box_mn);
+            if constexpr (PAIR)
+              tma_load_2d_pair(sb + i * b_box_bytes, &p.tmb, bar, b_mn ? mn : kx, b_mn ? kx : mn, pol);
+            else
+              tma_load_2d_a(sb + i * b_box_bytes, &p.tmb, bar, b_mn ? mn : kx, b_mn ? kx : mn, pol);
+          }
+          if (++s == STAGES) {
+            s = 0;
+            ph ^= 1;
           }
         }
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
-      uint32_t it = 0, tcount = 0;
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = p.idesc;
+      const uint64_t ak = (uint64_t)(p.ga.kstep >> 4), bk = (uint64_t)(p.gb.kstep >> 4);
+      const uint64_t adesc0 = make_smem_desc(smem_a, p.ga.lbo, p.ga.sbo, SWIZZLE_128B);
+      const uint64_t bdesc0 = make_smem_desc(smem_a + L::A_BYTES, p.gb.lbo, p.gb.sbo, SWIZZLE_128B);
+      const uint32_t tfull_a = smem_u32(tfull), tempty_a = smem_u32(tempty);
+      const uint32_t tfull_peer = PAIR ? mapa_shared(tfull_a, 1) : 0u;
+      // shared::cluster address of the peer's copy of a barrier = own address + peer_delta
+      const uint32_t peer_delta = PAIR ? (mapa_shared(empty_a, 1) - empty_a) : 0u;
+      uint32_t s = 0, ph = 0, tcount = 0;
       bool ok = true;
-      const uint64_t sw = SWIZZLE_128B;
-      for (int unit = blockIdx.x; unit < p.units && ok; unit += gridDim.x, ++tcount) {
-        int pid_m, pid_n, ks;
-        unit_to_tile(p, unit, pid_m, pid_n, ks);
-        const int kb0 = ks * p.kb_per_split;
-        const int kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
+      for (int unit = worker; unit < units && ok; unit += num_workers, ++tcount) {
+        const TileCoord t = unit_to_tile(unit, split_k, group_m, tiles_m, tiles_n);
+        const int kb0 = t.ks * kb_per_split;
+        const int nkb = min(k_blocks, kb0 + kb_per_split) - kb0;
         const uint32_t acc = tcount & 1;
         const uint32_t aph = (tcount >> 1) & 1;
-        if (!mbar_wait(&tempty[acc], aph ^ 1, p.status, WAIT_TMEM_EMPTY)) {
+        if (!mbar_wait_a(tempty_a + acc * 8, aph ^ 1, status, WAIT_TMEM_EMPTY)) {
           ok = false;
           break;
         }
         tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + acc * BN;
-        for (int kb = kb0; kb < kb1; ++kb, ++it) {
-          const uint32_t s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
-          if (!mbar_wait(&full[s], ph, p.status, WAIT_SMEM_FULL)) {
-            ok = false;
-            break;
-          }
-          tc_fence_after_sync();
-          const uint32_t sa = smem_u32(smem + s * L::STAGE_BYTES);
-          const uint32_t sb = sa + L::A_BYTES;
-          const uint64_t adesc = make_smem_desc(sa, p.ga.lbo, p.ga.sbo, sw);
-          const uint64_t bdesc = make_smem_desc(sb, p.gb.lbo, p.gb.sbo, sw);
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const uint64_t ad = adesc + (uint64_t)((k * p.ga.kstep) >> 4);
-            const uint64_t bd = bdesc + (uint64_t)((k * p.gb.kstep) >> 4);
-            const uint32_t accum = (kb > kb0 || k > 0) ? 1u : 0u;
-            if (p.is_f8)
-              umma_f8_ss(tmem_d, ad, bd, p.idesc, accum);
-            else
-              umma_f16_ss(tmem_d, ad, bd, p.idesc, accum);
-          }
-          umma_commit(&empty[s]);
+        // Loop shape: every non-MMA instruction sits between two MMAs of the same K step, where it
+        // overlaps with tensor-pipe work already queued: the commit that frees the previous stage
+        // comes after this step's first MMA, the wait for the next stage after the second.
+        if (!mbar_wait_a(full_a + s * 8, ph, status, WAIT_SMEM_FULL)) {
+          ok = false;
+          break;
         }
-        if (ok) umma_commit(&tfull[acc]);
+        tc_fence_after_sync();
+        uint32_t accum = 0;
+        uint32_t prev_empty = 0;  // barrier address of the stage whose release is still owed
+        for (int i = 0; i < nkb; ++i) {
+          const uint64_t ad = adesc0 + (uint64_t)(s * (L::STAGE_BYTES >> 4));
+          const uint64_t bd = bdesc0 + (uint64_t)(s * (L::STAGE_BYTES >> 4));
+          issue_mma<PAIR, F8>(tmem_d, ad, bd, idesc, accum);
+          accum = 1u;
+          if (prev_empty) {
+            if constexpr (PAIR) {
+              umma_commit_pair(prev_empty);
+              umma_commit_pair(prev_empty + peer_delta);
+            } else {
+              umma_commit_a(prev_empty);
+            }
+          }
+          prev_empty = empty_a + s * 8;
+          issue_mma<PAIR, F8>(tmem_d, ad + ak, bd + bk, idesc, 1u);
+          if (++s == STAGES) {
+            s = 0;
+            ph ^= 1;
+          }
+          if (i + 1 < nkb) {
+            if (!mbar_wait_a(full_a + s * 8, ph, status, WAIT_SMEM_FULL)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after_sync();
+          }
+          issue_mma<PAIR, F8>(tmem_d, ad + 2 * ak, bd + 2 * bk, idesc, 1u);
+          issue_mma<PAIR, F8>(tmem_d, ad + 3 * ak, bd + 3 * bk, idesc, 1u);
+        }
+        if (ok) {
+          if constexpr (PAIR) {
+            umma_commit_pair(prev_empty);
+            umma_commit_pair(prev_empty + peer_delta);
+            umma_commit_pair(tfull_a + acc * 8);
+            umma_commit_pair(tfull_peer + acc * 8);
+          } else {
+            umma_commit_a(prev_empty);
+            umma_commit_a(tfull_a + acc * 8);
+          }
+        }
       }
     }
   } else {
@@ -196,15 +355,19 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const __grid_cons
     float alpha = 1.0f;
     if (p.scale_a) alpha *= __ldg(p.scale_a);
     if (p.scale_b) alpha *= __ldg(p.scale_b);
+    void* const c = p.c;
+    float* const ws = p.ws;
+    const long long ldc = p.ldc;
+    const int m = p.m, n = p.n, out_mode = p.out_mode;
+    const uint32_t tempty_leader = PAIR ? mapa_shared(smem_u32(tempty), 0) : smem_u32(tempty);
     uint32_t tcount = 0;
     bool ok = true;
-    for (int unit = blockIdx.x; unit < p.units && ok; unit += gridDim.x, ++tcount) {
-      int pid_m, pid_n, ks;
-      unit_to_tile(p, unit, pid_m, pid_n, ks);
-      const int m0 = pid_m * BM, n0 = pid_n * BN;
+    for (int unit = worker; unit < units && ok; unit += num_workers, ++tcount) {
+      const TileCoord t = unit_to_tile(unit, split_k, group_m, tiles_m, tiles_n);
+      const int m0 = t.pid_m * TILE_M + (int)rank * BM, n0 = t.pid_n * BN;
       const uint32_t acc = tcount & 1;
       const uint32_t aph = (tcount >> 1) & 1;
-      if (!mbar_wait(&tfull[acc], aph, p.status, WAIT_TMEM_FULL)) {
+      if (!mbar_wait(&tfull[acc], aph, status, WAIT_TMEM_FULL)) {
         ok = false;
         break;
       }
@@ -212,73 +375,31 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const __grid_cons
       const int row = m0 + q * 32 + lane;
       const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + acc * BN;
 #pragma unroll 1
-      for (int c = 0; c < BN; c += 32) {
+      for (int cc = 0; cc < BN; cc += 32) {
         uint32_t v[32];
-        tmem_ld_32x32b_x32(taddr + c, v);
+        tmem_ld_32x32b_x32(taddr + cc, v);
         tmem_ld_wait();
-        const int col = n0 + c;
-        if (row < p.m && col < p.n) {
-          if (p.out_mode <= 1) {
-            uint16_t* dst = reinterpret_cast<uint16_t*>(p.c) + (long long)row * p.ldc + col;
-            const bool vec = (col + 32 <= p.n) && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
-            if (vec) {
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                uint4 o;
-                uint32_t w[4];
-#pragma unroll
-                for (int t = 0; t < 4; ++t) {
-                  float lo = __uint_as_float(v[j * 8 + 2 * t]) * alpha;
-                  float hi = __uint_as_float(v[j * 8 + 2 * t + 1]) * alpha;
-                  w[t] = (p.out_mode == 0) ? pack_bf16x2(lo, hi) : pack_f16x2(lo, hi);
-                }
-                o.x = w[0]; o.y = w[1]; o.z = w[2]; o.w = w[3];
-                reinterpret_cast<uint4*>(dst)[j] = o;
-              }
-            } else {
-              for (int j = 0; j < 32 && col + j < p.n; ++j) {
-                float x = __uint_as_float(v[j]) * alpha;
-                if (p.out_mode == 0) {
-                  __nv_bfloat16 h = __float2bfloat16_rn(x);
-                  dst[j] = *reinterpret_cast<uint16_t*>(&h);
-                } else {
-                  __half h = __float2half_rn(x);
-                  dst[j] = *reinterpret_cast<uint16_t*>(&h);
-                }
-              }
-            }
-          } else {
-            float* dst = (p.out_mode == 2)
-                             ? reinterpret_cast<float*>(p.c) + (long long)row * p.ldc + col
-                             : p.ws + ((long long)ks * p.m + row) * (long long)p.n + col;
-            const bool vec = (col + 32 <= p.n) && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
-            if (vec) {
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                float4 o;
-                o.x = __uint_as_float(v[4 * j]) * alpha;
-                o.y = __uint_as_float(v[4 * j + 1]) * alpha;
-                o.z = __uint_as_float(v[4 * j + 2]) * alpha;
-                o.w = __uint_as_float(v[4 * j + 3]) * alpha;
-                reinterpret_cast<float4*>(dst)[j] = o;
-              }
-            } else {
-              for (int j = 0; j < 32 && col + j < p.n; ++j) dst[j] = __uint_as_float(v[j]) * alpha;
-            }
-          }
-        }
+        store_chunk(c, ws, ldc, m, n, out_mode, v, row, n0 + cc, t.ks, alpha);
       }
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&tempty[acc]);
+      if (lane == 0) {
+        if constexpr (PAIR)
+          mbar_arrive_cluster(tempty_leader + acc * 8);
+        else
+          mbar_arrive_a(tempty_leader + acc * 8);
+      }
     }
   }
 
   tc_fence_before_sync();
-  __syncthreads();
+  if constexpr (PAIR) cluster_sync_all(); else __syncthreads();
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, TMEM_COLS);
+    if constexpr (PAIR)
+      tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    else
+      tmem_dealloc(tmem_base, TMEM_COLS);
   }
 }
 
@@ -318,6 +439,7 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ ws, void* __restr
 // ------------------------------------------------------------------------------- host
 
 struct GemmPlan {
+  int pair;  // 1: CTA-pair kernel, 256 x 256 tile per cluster
   int bn;
   int split_k;
   int kb_per_split;
@@ -342,24 +464,41 @@ static bool plan_gemm(const tb200_gemm_args* a, int sms, GemmPlan* plan) {
   const long long kb = (a->k + bk - 1) / bk;
   const long long tm = (a->m + BM - 1) / BM;
   int bn = a->block_n;
-  if (bn == 0) {
-    // Pick the widest tile whose estimated time (waves x per-tile cost) is smallest.
+  int pair = 0;
+  long long tm_eff = tm;
+  if (bn == 512) {
+    pair = 1;
+    bn = 256;
+  } else if (bn == 0) {
+    // Estimated time = waves x per-tile cost; one SM handles a 128 x bn tile in ~(bn + 48) units.
     long long best = -1;
     const int cands[3] = {256, 128, 64};
     for (int i = 0; i < 3; ++i) {
       const int cbn = cands[i];
       const long long tiles = tm * ((a->n + cbn - 1) / cbn);
       const long long waves = (tiles + sms - 1) / sms;
-      const long long cost = waves * (cbn + 48);
+      const long long cost = waves * (cbn + 48) * 4;
       if (best < 0 || cost < best) {
         best = cost;
         bn = cbn;
       }
     }
+    // CTA pair: two SMs share a 256 x 256 tile; each still computes 128 x 256 but stages a third
+    // less data per K step, which is worth ~25% once the grid is full.
+    if (a->m > BM && sms >= 2) {
+      const long long tiles2 = ((a->m + 255) / 256) * ((a->n + 255) / 256);
+      const long long waves2 = (tiles2 + sms / 2 - 1) / (sms / 2);
+      const long long cost2 = waves2 * (256 + 48) * 3;
+      if (cost2 <= best) {
+        pair = 1;
+        bn = 256;
+      }
+    }
   }
   if (bn != 64 && bn != 128 && bn != 256) return false;
+  if (pair) tm_eff = (a->m + 255) / 256;
   const long long tn = (a->n + bn - 1) / bn;
-  const long long tiles = tm * tn;
+  const long long tiles = tm_eff * tn * (pair ? 2 : 1);
   long long split = a->split_k;
   if (split <= 0) {
     split = 1;
@@ -374,24 +513,40 @@ static bool plan_gemm(const tb200_gemm_args* a, int sms, GemmPlan* plan) {
   if (split > kb) split = kb > 0 ? kb : 1;
   long long per = kb > 0 ? (kb + split - 1) / split : 0;
   if (per > 0) split = (kb + per - 1) / per;
+  plan->pair = pair;
   plan->bn = bn;
   plan->split_k = (int)split;
   plan->kb_per_split = (int)per;
   plan->k_blocks = (int)kb;
-  plan->tiles_m = (int)tm;
+  plan->tiles_m = (int)tm_eff;
   plan->tiles_n = (int)tn;
   return true;
 }
 
-template <int BN, int STAGES>
-static int launch_gemm(const GemmParams& p, int grid, cudaStream_t stream) {
-  using L = GemmSmem<BN, STAGES>;
-  auto kfn = gemm_kernel<BN, STAGES>;
+template <int BNC, int STAGES, bool PAIR, bool F8>
+static int launch_one(const GemmParams& p, int grid, cudaStream_t stream) {
+  using L = GemmSmem<BNC, STAGES>;
+  auto kfn = gemm_kernel<BNC, STAGES, PAIR, F8>;
   cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
   if (e != cudaSuccess) return TB200_ERR_CUDA;
-  kfn<<<grid, GEMM_THREADS, L::TOTAL, stream>>>(p);
-  return cuda_err(cudaGetLastError());
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(GEMM_THREADS);
+  cfg.dynamicSmemBytes = L::TOTAL;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = PAIR ? 2 : 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cuda_err(cudaLaunchKernelEx(&cfg, kfn, p));
 }
+
+template <bool F8>
+static int launch_gemm(const GemmParams& p, const struct GemmPlan& plan, int sms, cudaStream_t stream);
 
 static int set_operand(OperandGeom* g, CUtensorMap* tm, const void* base, long long rows_mn, long long k, long long ld,
                        int k_major, int eb, int tile_mn, CUtensorMapDataType dt) {
@@ -440,6 +595,20 @@ static int validate(const tb200_gemm_args* a) {
   return TB200_OK;
 }
 
+template <bool F8>
+static int launch_gemm(const GemmParams& p, const GemmPlan& plan, int sms, cudaStream_t stream) {
+  if (plan.pair) {
+    const int clusters = p.units < sms / 2 ? p.units : sms / 2;
+    return launch_one<128, 7, true, F8>(p, 2 * clusters, stream);
+  }
+  const int grid = p.units < sms ? p.units : sms;
+  switch (plan.bn) {
+    case 256: return launch_one<256, 4, false, F8>(p, grid, stream);
+    case 128: return launch_one<128, 6, false, F8>(p, grid, stream);
+    default: return launch_one<64, 8, false, F8>(p, grid, stream);
+  }
+}
+
 }  // namespace tb200
 
 using namespace tb200;
@@ -477,7 +646,7 @@ extern "C" int tb200_gemm(const tb200_gemm_args* a, void* stream_) {
                                                            : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
   rc = set_operand(&p.ga, &p.tma, a->a, a->m, a->k, a->lda, a->a_k_major, eb, BM, dt);
   if (rc != TB200_OK) return rc;
-  rc = set_operand(&p.gb, &p.tmb, a->b, a->n, a->k, a->ldb, a->b_k_major, eb, plan.bn, dt);
+  rc = set_operand(&p.gb, &p.tmb, a->b, a->n, a->k, a->ldb, a->b_k_major, eb, plan.pair ? 128 : plan.bn, dt);
   if (rc != TB200_OK) return rc;
 
   uint32_t fmt;
@@ -485,8 +654,7 @@ extern "C" int tb200_gemm(const tb200_gemm_args* a, void* stream_) {
     fmt = a->in_dtype == TB200_E4M3 ? 0u : 1u;
   else
     fmt = a->in_dtype == TB200_F16 ? 0u : 1u;
-  p.idesc = make_idesc(fmt, fmt, p.ga.mn_major, p.gb.mn_major, BM, plan.bn);
-  p.is_f8 = f8 ? 1 : 0;
+  p.idesc = make_idesc(fmt, fmt, p.ga.mn_major, p.gb.mn_major, plan.pair ? 256 : BM, plan.bn);
   p.c = a->c;
   p.ldc = a->ldc;
   p.m = (int)a->m;
@@ -514,12 +682,7 @@ extern "C" int tb200_gemm(const tb200_gemm_args* a, void* stream_) {
   } else {
     p.out_mode = final_mode;
   }
-  const int grid = p.units < sms ? p.units : sms;
-  switch (plan.bn) {
-    case 256: rc = launch_gemm<256, 4>(p, grid, stream); break;
-    case 128: rc = launch_gemm<128, 6>(p, grid, stream); break;
-    default: rc = launch_gemm<64, 8>(p, grid, stream); break;
-  }
+  rc = f8 ? launch_gemm<true>(p, plan, sms, stream) : launch_gemm<false>(p, plan, sms, stream);
   if (rc != TB200_OK) return rc;
   if (plan.split_k > 1) {
     // scale factors were already applied to the partial sums
