@@ -101,6 +101,33 @@ int tb200_gemm(const tb200_gemm_args* args, void* stream);
 /* Bytes of workspace tb200_gemm needs for these args (0 when no split-K is used). */
 size_t tb200_gemm_workspace_bytes(const tb200_gemm_args* args);
 
+/* ---------------------------------------------------------------- MXFP8 GEMM ------- */
+
+/*
+ * C[M,N] (bf16) = dq(A) * dq(B)^T with A [M,K] and B [N,K] contiguous float8_e4m3fn and one e8m0
+ * scale per 1x32 block along K (value = element * 2^(scale - 127)), fp32 accumulation.
+ * Stands behind: third_party/tlx/tutorials/blackwell_gemm_ws_mxfp8.py:1135
+ *   matmul(a, b, a_scale, b_scale, config=None)   (kernel _gemm_mxfp8_ws_kernel :759).
+ * a_scale / b_scale: rows*K/32 bytes each in the Blackwell 512-byte-atom order the reference
+ *   reshapes to [1, rows/128, K/128, 2, 256] (:1038-1041): atom (row/128, k/128), byte
+ *   (row%32)*16 + (row/32%4)*4 + (k/32)%4.
+ * M, N and K must be multiples of 128 (as the reference asserts, :1167-1168); all four input
+ * pointers 16-byte aligned. block_n: 0 = choose, else 128 or 256.
+ */
+typedef struct {
+  const void* a;
+  const void* b;
+  const void* a_scale;
+  const void* b_scale;
+  void* c;
+  int64_t m, n, k;
+  int64_t ldc;
+  int32_t block_n;
+  int32_t reserved;
+} tb200_gemm_mxfp8_args;
+
+int tb200_gemm_mxfp8(const tb200_gemm_mxfp8_args* args, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,101 @@
+"""Parity of the FP8 paths against the CPU oracle: tensorwise-scaled e4m3 GEMM (tolerance of the
+reference's own test, atol 0.1 / rtol 0.05, test_correctness.py:554-562) and the MXFP8 block-scaled
+GEMM (BASELINE: rtol 3e-2; the reference's test uses atol 0.1, rtol 0.01 on N(0, 0.5) inputs)."""
+import pytest
+import torch
+
+from oracle import gemm as o_gemm
+from oracle import mxfp8 as o_mx
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("shape", [(1024, 1024, 1024), (2048, 2048, 2048), (384, 256, 640)])
+@pytest.mark.parametrize("num_ctas", [1, 2])
+def test_scaled_mm_tensorwise(cuda, shape, num_ctas):
+    from triton_b200.tutorials.blackwell_scaled_mm_ws import blackwell_scaled_mm_ws
+    M, N, K = shape
+    torch.manual_seed(0)
+    a = (torch.randn(M, K) * 0.1).to(torch.float8_e4m3fn)
+    b = (torch.randn(N, K) * 0.1).to(torch.float8_e4m3fn)
+    sa, sb = torch.rand(1), torch.rand(1)
+    out = blackwell_scaled_mm_ws(a.to(cuda), b.to(cuda), sa.to(cuda), sb.to(cuda), scale_mode="tensorwise",
+                                 NUM_CTAS=num_ctas)
+    ref = o_gemm.scaled_mm_tensorwise_ref(a, b, sa, sb)
+    torch.testing.assert_close(out.cpu().float(), ref.float(), atol=0.1, rtol=0.05)
+    # tighter: within bf16 rounding of the fp32 result
+    torch.testing.assert_close(out.cpu().float(), ref.float(), atol=1e-3, rtol=1e-2)
+
+
+def test_scaled_mm_other_modes_raise(cuda):
+    from triton_b200.tutorials.blackwell_scaled_mm_ws import blackwell_scaled_mm_ws
+    a = torch.zeros(128, 128, device=cuda).to(torch.float8_e4m3fn)
+    s = torch.ones(1, device=cuda)
+    with pytest.raises(NotImplementedError):
+        blackwell_scaled_mm_ws(a, a, s, s, scale_mode="rowwise")
+    with pytest.raises(AssertionError):
+        blackwell_scaled_mm_ws(a[:, :64].contiguous(), a[:, :64].contiguous(), s, s, scale_mode="tensorwise")
+
+
+def _mx_case(cuda, M, N, K, bn, seed=3):
+    from triton_b200.tutorials.blackwell_gemm_ws_mxfp8 import matmul
+    g = torch.Generator().manual_seed(seed)
+    a, sa = o_mx.make_mxfp8_operand(M, K, g)
+    b, sb = o_mx.make_mxfp8_operand(N, K, g)
+    out = matmul(a.to(cuda), b.to(cuda), sa.to(cuda).view(torch.float8_e8m0fnu), sb.to(cuda).view(torch.float8_e8m0fnu),
+                 {"BLOCK_SIZE_N": bn} if bn else None)
+    ref = o_mx.dequantize(a, sa) @ o_mx.dequantize(b, sb).t()
+    # rtol 3e-2 (BASELINE) on entries, with an absolute floor of 3e-2 x the mean magnitude
+    torch.testing.assert_close(out.cpu().float(), ref, rtol=3e-2, atol=3e-2 * float(ref.abs().mean()))
+
+
+@pytest.mark.parametrize("shape", [(128, 128, 128), (256, 256, 256), (384, 256, 512), (384, 384, 1024)])
+@pytest.mark.parametrize("bn", [0, 128, 256])
+def test_mxfp8_reference_test_shapes(cuda, shape, bn):
+    """Shapes of the reference's Mxfp8Gemm.SHAPES (test_correctness.py:446-450) plus a ragged-N tile."""
+    _mx_case(cuda, *shape, bn)
+
+
+def test_mxfp8_scale_layout_known_answer(cuda):
+    """All-ones operands with scales that differ per row (A) and per K block (B): every output is
+    an exact power-of-two sum, so any mistake in the 512-byte-atom addressing shows up exactly."""
+    from triton_b200.tutorials.blackwell_gemm_ws_mxfp8 import matmul
+    M, N, K = 256, 384, 512
+    a = torch.ones(M, K).to(torch.float8_e4m3fn)
+    b = torch.ones(N, K).to(torch.float8_e4m3fn)
+    sa = (127 + (torch.arange(M)[:, None] % 5) - 2).to(torch.uint8).expand(M, K // 32).contiguous()
+    sb = (127 + (torch.arange(K // 32)[None, :] % 3) + (torch.arange(N)[:, None] % 2)).to(torch.uint8)
+    fa, fb = o_mx.swizzle_scales(sa), o_mx.swizzle_scales(sb)
+    out = matmul(a.to(cuda), b.to(cuda), fa.to(cuda).view(torch.float8_e8m0fnu), fb.to(cuda).view(torch.float8_e8m0fnu))
+    ref = o_mx.dequantize(a, fa) @ o_mx.dequantize(b, fb).t()
+    assert torch.equal(out.cpu().float(), ref.to(torch.bfloat16).float())
+
+
+def test_mxfp8_2048_and_linearity_at_full_size(cuda):
+    _mx_case(cuda, 2048, 2048, 2048, 0)
+    # BASELINE config 4 size (8192^3): the CPU oracle is too slow; use exactness instead — with
+    # all-ones data and power-of-two scales every product is exact, so C = K/32 * sum of 2^(ea+eb).
+    from triton_b200.tutorials.blackwell_gemm_ws_mxfp8 import matmul
+    n = 8192
+    a = torch.ones(n, n, device=cuda).to(torch.float8_e4m3fn)
+    ea = (torch.arange(n, device=cuda) % 4).to(torch.uint8)      # per-row exponent of A
+    eb = (torch.arange(n, device=cuda) % 3).to(torch.uint8)      # per-row exponent of B
+    sa = (127 + ea)[:, None].expand(n, n // 32).contiguous()
+    sb = (127 + eb)[:, None].expand(n, n // 32).contiguous()
+    fa = o_mx.swizzle_scales(sa.cpu()).to(cuda).view(torch.float8_e8m0fnu)
+    fb = o_mx.swizzle_scales(sb.cpu()).to(cuda).view(torch.float8_e8m0fnu)
+    out = matmul(a, a, fa, fb)
+    want = (n * torch.pow(2.0, ea.float())[:, None] * torch.pow(2.0, eb.float())[None, :]).to(torch.bfloat16)
+    assert torch.equal(out, want)
+
+
+def test_mxfp8_asserts(cuda):
+    from triton_b200.tutorials.blackwell_gemm_ws_mxfp8 import matmul
+    a = torch.zeros(128, 128, device=cuda).to(torch.float8_e4m3fn)
+    s = torch.zeros(128 * 4, dtype=torch.uint8, device=cuda).view(torch.float8_e8m0fnu)
+    with pytest.raises(AssertionError):
+        matmul(a.to(torch.bfloat16), a, s, s)
+    with pytest.raises(AssertionError):
+        matmul(a[:, :64].contiguous(), a[:, :64].contiguous(), s, s)
+    with pytest.raises(AssertionError):
+        matmul(a, a, s[:100], s)

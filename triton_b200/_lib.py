@@ -36,6 +36,14 @@ class GemmArgs(Structure):
     ]
 
 
+class GemmMxfp8Args(Structure):
+    _fields_ = [
+        ("a", c_void_p), ("b", c_void_p), ("a_scale", c_void_p), ("b_scale", c_void_p), ("c", c_void_p),
+        ("m", c_int64), ("n", c_int64), ("k", c_int64), ("ldc", c_int64),
+        ("block_n", c_int32), ("reserved", c_int32),
+    ]
+
+
 _lib = None
 
 
@@ -52,6 +60,8 @@ def _declare(l: ctypes.CDLL) -> None:
     l.tb200_gemm.argtypes = [POINTER(GemmArgs), c_void_p]
     l.tb200_gemm_workspace_bytes.restype = c_size_t
     l.tb200_gemm_workspace_bytes.argtypes = [POINTER(GemmArgs)]
+    l.tb200_gemm_mxfp8.restype = c_int
+    l.tb200_gemm_mxfp8.argtypes = [POINTER(GemmMxfp8Args), c_void_p]
 
 
 def lib() -> ctypes.CDLL:

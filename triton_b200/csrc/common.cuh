@@ -128,7 +128,7 @@ __device__ __forceinline__ bool mbar_try_wait_a(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-__device__ __noinline__ bool mbar_wait_slow_a(uint32_t bar, uint32_t parity, int* status, int code) {
+static __device__ __noinline__ bool mbar_wait_slow_a(uint32_t bar, uint32_t parity, int* status, int code) {
   uint64_t t0 = 0;
   uint32_t spins = 0;
   for (;;) {

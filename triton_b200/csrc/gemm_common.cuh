@@ -1,0 +1,80 @@
+// Pieces shared by the GEMM kernels: tile scheduling order and the epilogue's row-chunk store.
+#pragma once
+#include "common.cuh"
+
+namespace tb200 {
+
+struct TileCoord {
+  int pid_m, pid_n, ks;
+};
+
+__device__ __forceinline__ TileCoord unit_to_tile(int unit, int split_k, int group_m, int tiles_m, int tiles_n) {
+  TileCoord t;
+  const int tile = unit / split_k;
+  t.ks = unit - tile * split_k;
+  const int group = group_m * tiles_n;
+  const int gid = tile / group;
+  const int first_m = gid * group_m;
+  const int gsz = min(tiles_m - first_m, group_m);
+  const int r = tile - gid * group;
+  t.pid_m = first_m + (r % gsz);
+  t.pid_n = r / gsz;
+  return t;
+}
+
+// Writes 32 consecutive columns of one output row (fp32 accumulators in v) in the output mode.
+__device__ __forceinline__ void store_chunk(void* c, float* ws, long long ldc, int m, int n, int out_mode,
+                                            const uint32_t (&v)[32], int row, int col, int ks, float alpha) {
+  if (row >= m || col >= n) return;
+  const bool full = col + 32 <= n;
+  if (out_mode <= 1) {
+    uint16_t* dst = reinterpret_cast<uint16_t*>(c) + (long long)row * ldc + col;
+    if (full && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint32_t w[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const float lo = __uint_as_float(v[j * 8 + 2 * t]) * alpha;
+          const float hi = __uint_as_float(v[j * 8 + 2 * t + 1]) * alpha;
+          w[t] = (out_mode == 0) ? pack_bf16x2(lo, hi) : pack_f16x2(lo, hi);
+        }
+        reinterpret_cast<uint4*>(dst)[j] = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    } else {
+      const int cnt = n - col;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        if (j < cnt) {
+          const float x = __uint_as_float(v[j]) * alpha;
+          if (out_mode == 0) {
+            __nv_bfloat16 h = __float2bfloat16_rn(x);
+            dst[j] = *reinterpret_cast<uint16_t*>(&h);
+          } else {
+            __half h = __float2half_rn(x);
+            dst[j] = *reinterpret_cast<uint16_t*>(&h);
+          }
+        }
+      }
+    }
+  } else {
+    float* dst = (out_mode == 2) ? reinterpret_cast<float*>(c) + (long long)row * ldc + col
+                                 : ws + ((long long)ks * m + row) * (long long)n + col;
+    if (full && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        reinterpret_cast<float4*>(dst)[j] =
+            make_float4(__uint_as_float(v[4 * j]) * alpha, __uint_as_float(v[4 * j + 1]) * alpha,
+                        __uint_as_float(v[4 * j + 2]) * alpha, __uint_as_float(v[4 * j + 3]) * alpha);
+      }
+    } else {
+      const int cnt = n - col;
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j < cnt) dst[j] = __uint_as_float(v[j]) * alpha;
+    }
+  }
+}
+
+
+}  // namespace tb200

@@ -1,0 +1,58 @@
+"""``blackwell_scaled_mm_ws(a, b, scale_a, scale_b, ...)`` — counterpart of the reference's FP8
+scaled matmul, ``third_party/tlx/tutorials/blackwell_scaled_mm_ws.py:392``.
+
+``a`` [M, K] and ``b`` [N, K] are ``float8_e4m3fn`` (row-major; computes ``A @ B^T``), the result is
+``out_dtype`` (bf16 by default). ``scale_mode="tensorwise"`` (one fp32 scalar per operand, applied
+once after the K loop) is the mode built here; ``"blockwise"`` and ``"rowwise"`` raise
+``NotImplementedError``. The tiling arguments (``BLOCK_M``, ``BLOCK_N``, ``NUM_CTAS``, ``USE_CLC``,
+``EPI_SUB``, ``persistent``) are accepted for call compatibility; the kernel picks its own tiling
+(``NUM_CTAS=2`` forces the CTA-pair tiling). Same shape assertions as the reference (``:408``).
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from .. import _lib
+
+_OUT = {torch.bfloat16: _lib.BF16, torch.float16: _lib.F16, torch.float32: _lib.F32}
+_IN = {torch.float8_e4m3fn: _lib.E4M3, torch.float8_e5m2: _lib.E5M2}
+
+
+def blackwell_scaled_mm_ws(a, b, scale_a, scale_b, out_dtype=torch.bfloat16, BLOCK_M=None, BLOCK_N=128, NUM_CTAS=1,
+                           USE_CLC=False, EPI_SUB=2, persistent=True, scale_mode="blockwise"):
+    if scale_mode not in ("blockwise", "rowwise", "tensorwise"):
+        raise KeyError(scale_mode)
+    if scale_mode != "tensorwise":
+        raise NotImplementedError(f"scale_mode={scale_mode!r}: only 'tensorwise' is implemented")
+    if not a.is_cuda:
+        raise RuntimeError("blackwell_scaled_mm_ws needs CUDA tensors (there is no CPU path)")
+    M, K = a.shape
+    N, Kb = b.shape
+    assert K == Kb and K % 128 == 0 and N % 128 == 0
+    assert a.dtype in _IN and b.dtype == a.dtype, "fp8 operands of the same dtype"
+    assert out_dtype in _OUT
+    a = a.contiguous()
+    b = b.contiguous()
+    scale_a = scale_a.reshape(-1).contiguous().to(torch.float32)
+    scale_b = scale_b.reshape(-1).contiguous().to(torch.float32)
+    assert scale_a.numel() == 1 and scale_b.numel() == 1, (
+        f"tensorwise expects scalar scale_a/scale_b; got {scale_a.numel()}, {scale_b.numel()}")
+    c = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    if M == 0:
+        return c
+    args = _lib.GemmArgs()
+    args.a, args.b, args.c = a.data_ptr(), b.data_ptr(), c.data_ptr()
+    args.m, args.n, args.k = M, N, K
+    args.lda, args.ldb, args.ldc = K, K, c.stride(0)
+    args.in_dtype = _IN[a.dtype]
+    args.out_dtype = _OUT[out_dtype]
+    args.a_k_major = args.b_k_major = 1
+    args.split_k = 1
+    args.block_n = 512 if NUM_CTAS == 2 else 0
+    args.scale_a, args.scale_b = scale_a.data_ptr(), scale_b.data_ptr()
+    with torch.cuda.device(a.device):
+        rc = _lib.lib().tb200_gemm(ctypes.byref(args), ctypes.c_void_p(_lib.current_stream_ptr(a.device)))
+    _lib.check(rc, "tb200_gemm")
+    return c
