@@ -128,6 +128,34 @@ typedef struct {
 
 int tb200_gemm_mxfp8(const tb200_gemm_mxfp8_args* args, void* stream);
 
+/* ---------------------------------------------------------------- attention -------- */
+
+/*
+ * Flash-attention forward: o = softmax(q k^T * sm_scale [+ causal mask]) v, and optionally
+ * lse[b,h,i] = log2(sum_j exp(s_ij)) with s the scaled (masked) scores, i.e. the reference's
+ * M = m*sm_scale*log2(e) + log2(l).
+ * Stands behind: third_party/tlx/tutorials/blackwell_fa_ws_pipelined_persistent.py:3491
+ *   attention(q, k, v, sm_scale, causal, config=None)   (kernel _attn_fwd_ws :600, forward :3288).
+ * q, o: [batch, heads, seq_q, head_dim] contiguous; k, v: [batch, heads, seq_kv, head_dim]
+ * contiguous; dtype TB200_BF16 or TB200_F16; head_dim 64 or 128; lse (may be NULL):
+ * float [batch, heads, seq_q]. causal requires seq_q == seq_kv (as in the reference).
+ * Any sequence length >= 1 is accepted (the tail is masked). Base pointers 16-byte aligned.
+ */
+typedef struct {
+  const void* q;
+  const void* k;
+  const void* v;
+  void* o;
+  float* lse;
+  int64_t batch, heads, seq_q, seq_kv;
+  int32_t head_dim;
+  int32_t dtype;
+  int32_t causal;
+  float sm_scale;
+} tb200_attention_args;
+
+int tb200_attention_fwd(const tb200_attention_args* args, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -44,6 +44,14 @@ class GemmMxfp8Args(Structure):
     ]
 
 
+class AttentionArgs(Structure):
+    _fields_ = [
+        ("q", c_void_p), ("k", c_void_p), ("v", c_void_p), ("o", c_void_p), ("lse", c_void_p),
+        ("batch", c_int64), ("heads", c_int64), ("seq_q", c_int64), ("seq_kv", c_int64),
+        ("head_dim", c_int32), ("dtype", c_int32), ("causal", c_int32), ("sm_scale", c_float),
+    ]
+
+
 _lib = None
 
 
@@ -60,6 +68,8 @@ def _declare(l: ctypes.CDLL) -> None:
     l.tb200_gemm.argtypes = [POINTER(GemmArgs), c_void_p]
     l.tb200_gemm_workspace_bytes.restype = c_size_t
     l.tb200_gemm_workspace_bytes.argtypes = [POINTER(GemmArgs)]
+    l.tb200_attention_fwd.restype = c_int
+    l.tb200_attention_fwd.argtypes = [POINTER(AttentionArgs), c_void_p]
     l.tb200_gemm_mxfp8.restype = c_int
     l.tb200_gemm_mxfp8.argtypes = [POINTER(GemmMxfp8Args), c_void_p]
 

@@ -1,0 +1,54 @@
+"""``attention(q, k, v, sm_scale, causal, config=None)`` — counterpart of the reference's Blackwell
+flash-attention forward, ``third_party/tlx/tutorials/blackwell_fa_ws_pipelined_persistent.py:3491``.
+
+q, k, v: ``[B, H, S, D]`` fp16 or bf16 CUDA tensors with equal head dims; returns ``o`` with the shape
+and dtype of ``q``. Forward only: the result carries no autograd graph (the reference wraps its
+kernel in an autograd Function whose backward is a separate kernel). The reference keeps the row
+statistic ``M = m*sm_scale*log2(e) + log2(l)`` (base-2 log-sum-exp, ``:886-894``) internal;
+``attention_with_lse`` returns it as a second fp32 ``[B, H, S]`` tensor without changing the
+signature of ``attention``. ``config`` is accepted for call compatibility (the tiling is fixed:
+256 query rows per CTA as two groups of 128, KV blocks of 128).
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from .. import _lib
+
+_DT = {torch.bfloat16: _lib.BF16, torch.float16: _lib.F16}
+
+
+def attention_with_lse(q, k, v, sm_scale, causal, config=None):
+    HEAD_DIM_Q, HEAD_DIM_K, HEAD_DIM_V = q.shape[-1], k.shape[-1], v.shape[-1]
+    assert HEAD_DIM_Q == HEAD_DIM_K and HEAD_DIM_K == HEAD_DIM_V
+    assert HEAD_DIM_K in {16, 32, 64, 128, 256}
+    if HEAD_DIM_K not in (64, 128):
+        raise NotImplementedError(f"head_dim {HEAD_DIM_K}: this kernel is built for 64 and 128")
+    if not q.is_cuda:
+        raise RuntimeError("triton_b200 attention needs CUDA tensors (there is no CPU path)")
+    assert q.dim() == 4 and k.dim() == 4 and v.dim() == 4
+    assert q.dtype in _DT and k.dtype == q.dtype and v.dtype == q.dtype
+    assert k.shape == v.shape and q.shape[:2] == k.shape[:2]
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    B, H, S, D = q.shape
+    o = torch.empty_like(q)
+    M = torch.empty((B, H, S), device=q.device, dtype=torch.float32)
+    if q.numel() == 0:
+        return o, M
+    args = _lib.AttentionArgs()
+    args.q, args.k, args.v, args.o, args.lse = q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), M.data_ptr()
+    args.batch, args.heads, args.seq_q, args.seq_kv = B, H, S, k.shape[2]
+    args.head_dim = D
+    args.dtype = _DT[q.dtype]
+    args.causal = 1 if causal else 0
+    args.sm_scale = float(sm_scale)
+    with torch.cuda.device(q.device):
+        rc = _lib.lib().tb200_attention_fwd(ctypes.byref(args), ctypes.c_void_p(_lib.current_stream_ptr(q.device)))
+    _lib.check(rc, "tb200_attention_fwd")
+    return o, M
+
+
+def attention(q, k, v, sm_scale, causal, config=None):
+    return attention_with_lse(q, k, v, sm_scale, causal, config)[0]
