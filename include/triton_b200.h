@@ -156,6 +156,156 @@ typedef struct {
 
 int tb200_attention_fwd(const tb200_attention_args* args, void* stream);
 
+/* ---------------------------------------------------------------- MoE routing ------ */
+/* Paths below are inside python/triton_kernels/triton_kernels/ of the reference. */
+
+/*
+ * Per-row top-k over n_cols expert logits.
+ * Stands behind: topk.py:106 topk(x, k, apply_softmax=True, dim=1, y_indx=None, n_rows=None, ...)
+ *   (kernel _topk_forward, topk_details/_topk_forward.py:87-147; torch twin topk_torch topk.py:144).
+ * Selection: k largest per row, ties to the smaller column; values in descending order; softmax
+ * (fp32) over the k selected values when apply_softmax. Rows in [n_rows, rows_alloc) get index -1,
+ * values x[row, :k] and no mask bits, as the torch twin does.
+ * x: [rows_alloc, n_cols] of dtype (F32/BF16/F16), row stride stride_x elements.
+ * y_vals: same dtype [rows_alloc, k]; y_indx: int16 [rows_alloc, k]; both with row stride stride_y.
+ * bitmatrix: uint32 words; word w of row r lives at r*bits_stride_row + w*bits_stride_word
+ *   (the reference stores it transposed: bits_stride_row = 1).
+ * use_provided_indx: y_indx is an input (values are gathered, the mask is built from it).
+ * n_cols <= 1024, k <= 32.
+ */
+typedef struct {
+  const void* x;
+  void* y_vals;
+  void* y_indx;
+  void* bitmatrix;
+  int64_t rows_alloc, n_rows, n_cols;
+  int64_t stride_x, stride_y;
+  int64_t bits_stride_row, bits_stride_word;
+  int32_t k;
+  int32_t dtype;
+  int32_t apply_softmax;
+  int32_t use_provided_indx;
+} tb200_topk_args;
+int tb200_topk(const tb200_topk_args* args, void* stream);
+
+/*
+ * Expert histogram and the two index permutations of the routing bitmatrix.
+ * Stands behind: tensor_details/bitmatrix.py:110 make_bitmatrix_metadata(nonzero_indx, bitmatrix)
+ *   (torch twin make_bitmatrix_metadata_torch :157).
+ * indx: [n_entries] expert index per (token, slot) in row-major order, int16 or int32, -1 = none.
+ * col_sum int32[n_cols]; col_sorted_indx int32[n_entries]: entry ids grouped by expert, stable
+ * ("combine" order); row_sorted_indx int32[n_entries]: position of each entry in that order
+ * ("dispatch"); unused tail entries are -1. workspace: tb200_bitmatrix_metadata_workspace_bytes().
+ */
+typedef struct {
+  const void* indx;
+  int32_t* col_sum;
+  int32_t* col_sorted_indx;
+  int32_t* row_sorted_indx;
+  void* workspace;
+  size_t workspace_bytes;
+  int64_t n_entries;
+  int32_t n_cols;
+  int32_t indx_is_int16;
+} tb200_bitmatrix_metadata_args;
+int tb200_bitmatrix_metadata(const tb200_bitmatrix_metadata_args* args, void* stream);
+size_t tb200_bitmatrix_metadata_workspace_bytes(int64_t n_entries, int32_t n_cols);
+
+/*
+ * Ragged-tensor metadata for block sizes 16, 32, 64, 128.
+ * Stands behind: tensor_details/ragged_tensor.py:183 make_ragged_tensor_metadata(slice_sizes, n_total_rows)
+ *   (torch twin make_ragged_tensor_metadata_torch :217).
+ * slice_offs int32[n_slices+1]; block_offs int32[4, n_slices+1]; block_schedule int32[4, max_n_blocks]
+ * with entries (block_in_slice << 16) | slice, -1 padded. max_n_blocks is the caller's bound
+ * (RaggedTensorMetadata.max_n_blocks, :79-81).
+ */
+typedef struct {
+  const int32_t* slice_sizes;
+  int32_t* slice_offs;
+  int32_t* block_offs;
+  int32_t* block_schedule;
+  int32_t n_slices;
+  int32_t max_n_blocks;
+} tb200_ragged_metadata_args;
+int tb200_ragged_metadata(const tb200_ragged_metadata_args* args, void* stream);
+
+/*
+ * y[t, :] = sum over the k slots of x[t, j, :] (optionally masked / scaled per (t, j)), fp32 sum.
+ * Stands behind: reduce.py:1135 reduce(x, dim, mask=None, scale=None, ...) for the MoE combine
+ *   `reduce(y.view(-1, k, d), dim=1)` (torch twin reduce_torch :1173).
+ * x: [n_tokens, k, d] contiguous BF16/F16, d % 8 == 0; mask: uint8 [n_tokens, k] or NULL;
+ * scale: float [n_tokens, k] or NULL; y: [n_tokens, d].
+ */
+typedef struct {
+  const void* x;
+  const uint8_t* mask;
+  const float* scale;
+  void* y;
+  int64_t n_tokens;
+  int64_t d;
+  int32_t k;
+  int32_t dtype;
+} tb200_reduce_k_args;
+int tb200_reduce_k(const tb200_reduce_k_args* args, void* stream);
+
+/*
+ * out[r, j] = g * sigmoid(alpha * g) * (l + 1), g = a[r, 2j] (clamped to <= limit),
+ * l = a[r, 2j+1] (clamped to [-limit, limit]) when has_limit.
+ * Stands behind: swiglu.py swiglu(a, alpha, precision_config) (torch twin swiglu_torch :89-100).
+ */
+typedef struct {
+  const void* a;
+  void* out;
+  int64_t rows, n_in;
+  int64_t lda, ldo;
+  float alpha, limit;
+  int32_t has_limit;
+  int32_t dtype;
+} tb200_swiglu_args;
+int tb200_swiglu(const tb200_swiglu_args* args, void* stream);
+
+/* ---------------------------------------------------------------- MoE grouped GEMM - */
+
+/*
+ * Per-expert GEMM over expert-sorted rows with fused gather / bias / SwiGLU / gate scale / scatter:
+ *   for r in [slice_offs[e], slice_offs[e+1]):
+ *     acc = x[gather_indx[r], :] @ w[e] (+ bias[e]);  if swiglu: acc = swiglu(acc) (N -> N/2 columns)
+ *     y[scatter_indx[r], :] = acc * gammas[r]          (scatter_indx[r] == -1: row dropped)
+ * Stands behind: python/triton_kernels/triton_kernels/matmul.py:243
+ *   matmul(a, b, bias, a_ragged_metadata, ..., gather_indx, scatter_indx, ..., gammas, ..., fused_activation)
+ *   (kernel _p_matmul, matmul_details/_p_matmul.py:62; torch twin matmul_torch matmul.py:823).
+ * x: [rows_x, k] row-major (ldx elements between rows), BF16/F16.
+ * w: n_experts matrices, w_n_major = 1: [E, K, N] with N contiguous; 0: [E, N, K] with K contiguous.
+ * bias: float [E, N] or NULL. gammas: float [R] or NULL. gather_indx / scatter_indx: int32 [R] or
+ * NULL (identity). slice_offs: int32 [E+1]; block_schedule: the 128-row schedule of the ragged
+ * metadata, int32 [n_sched], entries (block << 16) | expert or -1.
+ * y: [rows_y, N or N/2], ldy elements between rows; rows that no sorted row maps to are untouched.
+ * k % 8 == 0, ldx % 8 == 0 (and n % 8 == 0 when w_n_major); n even when swiglu.
+ */
+typedef struct {
+  const void* x;
+  const void* w;
+  const float* bias;
+  void* y;
+  const int32_t* slice_offs;
+  const int32_t* block_schedule;
+  const int32_t* gather_indx;
+  const int32_t* scatter_indx;
+  const float* gammas;
+  int64_t n_experts, k, n;
+  int64_t rows_x, rows_y;
+  int64_t ldx, ldy;
+  int32_t n_sched;
+  int32_t w_n_major;
+  int32_t dtype;
+  int32_t swiglu;
+  float swiglu_alpha;
+  float swiglu_limit;
+  int32_t swiglu_has_limit;
+  int32_t reserved;
+} tb200_moe_gemm_args;
+int tb200_moe_gemm(const tb200_moe_gemm_args* args, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -52,6 +52,57 @@ class AttentionArgs(Structure):
     ]
 
 
+class TopkArgs(Structure):
+    _fields_ = [
+        ("x", c_void_p), ("y_vals", c_void_p), ("y_indx", c_void_p), ("bitmatrix", c_void_p),
+        ("rows_alloc", c_int64), ("n_rows", c_int64), ("n_cols", c_int64),
+        ("stride_x", c_int64), ("stride_y", c_int64),
+        ("bits_stride_row", c_int64), ("bits_stride_word", c_int64),
+        ("k", c_int32), ("dtype", c_int32), ("apply_softmax", c_int32), ("use_provided_indx", c_int32),
+    ]
+
+
+class BitmatrixMetadataArgs(Structure):
+    _fields_ = [
+        ("indx", c_void_p), ("col_sum", c_void_p), ("col_sorted_indx", c_void_p), ("row_sorted_indx", c_void_p),
+        ("workspace", c_void_p), ("workspace_bytes", c_size_t),
+        ("n_entries", c_int64), ("n_cols", c_int32), ("indx_is_int16", c_int32),
+    ]
+
+
+class RaggedMetadataArgs(Structure):
+    _fields_ = [
+        ("slice_sizes", c_void_p), ("slice_offs", c_void_p), ("block_offs", c_void_p), ("block_schedule", c_void_p),
+        ("n_slices", c_int32), ("max_n_blocks", c_int32),
+    ]
+
+
+class ReduceKArgs(Structure):
+    _fields_ = [
+        ("x", c_void_p), ("mask", c_void_p), ("scale", c_void_p), ("y", c_void_p),
+        ("n_tokens", c_int64), ("d", c_int64), ("k", c_int32), ("dtype", c_int32),
+    ]
+
+
+class SwigluArgs(Structure):
+    _fields_ = [
+        ("a", c_void_p), ("out", c_void_p), ("rows", c_int64), ("n_in", c_int64), ("lda", c_int64), ("ldo", c_int64),
+        ("alpha", c_float), ("limit", c_float), ("has_limit", c_int32), ("dtype", c_int32),
+    ]
+
+
+class MoeGemmArgs(Structure):
+    _fields_ = [
+        ("x", c_void_p), ("w", c_void_p), ("bias", c_void_p), ("y", c_void_p),
+        ("slice_offs", c_void_p), ("block_schedule", c_void_p),
+        ("gather_indx", c_void_p), ("scatter_indx", c_void_p), ("gammas", c_void_p),
+        ("n_experts", c_int64), ("k", c_int64), ("n", c_int64),
+        ("rows_x", c_int64), ("rows_y", c_int64), ("ldx", c_int64), ("ldy", c_int64),
+        ("n_sched", c_int32), ("w_n_major", c_int32), ("dtype", c_int32), ("swiglu", c_int32),
+        ("swiglu_alpha", c_float), ("swiglu_limit", c_float), ("swiglu_has_limit", c_int32), ("reserved", c_int32),
+    ]
+
+
 _lib = None
 
 
@@ -70,6 +121,14 @@ def _declare(l: ctypes.CDLL) -> None:
     l.tb200_gemm_workspace_bytes.argtypes = [POINTER(GemmArgs)]
     l.tb200_attention_fwd.restype = c_int
     l.tb200_attention_fwd.argtypes = [POINTER(AttentionArgs), c_void_p]
+    for name, typ in (("tb200_topk", TopkArgs), ("tb200_bitmatrix_metadata", BitmatrixMetadataArgs),
+                      ("tb200_ragged_metadata", RaggedMetadataArgs), ("tb200_reduce_k", ReduceKArgs),
+                      ("tb200_swiglu", SwigluArgs), ("tb200_moe_gemm", MoeGemmArgs)):
+        fn = getattr(l, name)
+        fn.restype = c_int
+        fn.argtypes = [POINTER(typ), c_void_p]
+    l.tb200_bitmatrix_metadata_workspace_bytes.restype = c_size_t
+    l.tb200_bitmatrix_metadata_workspace_bytes.argtypes = [c_int64, c_int32]
     l.tb200_gemm_mxfp8.restype = c_int
     l.tb200_gemm_mxfp8.argtypes = [POINTER(GemmMxfp8Args), c_void_p]
 

@@ -1,0 +1,442 @@
+// Grouped (per-expert) GEMM for MoE layers on sm_100a with the routing gather fused into the TMA
+// load and the scatter / gate scaling / SwiGLU fused into the epilogue:
+//
+//   for each expert e and each sorted row r in [slice_offs[e], slice_offs[e+1]):
+//       acc      = X[gather[r], :] @ W[e]            (+ bias[e])
+//       acc      = swiglu(acc)                        (optional; interleaved gate / linear columns)
+//       Y[scatter[r], :] = acc * gammas[r]            (scatter[r] == -1: dropped)
+//
+// Work units are (block-schedule entry, N tile): the schedule lists the 128-row blocks of every
+// non-empty expert as (block << 16) | expert, padded with -1, so a tile never straddles experts.
+// The A tile is fetched with `cp.async.bulk.tensor.2d.tile::gather4`: each of the 32 lanes of the
+// producer warp owns 4 of the tile's 128 rows and issues one gather4 per K step; rows past the end
+// of the expert's slice use an out-of-range row coordinate and arrive as zeros. W[e] is read
+// through a 3-D tensor map (expert is the outermost coordinate) either K-major or N-major.
+// MMA issue, TMEM double buffering and the lean single-thread loops are those of the dense kernel.
+//
+// Counterpart in the reference: _p_matmul, python/triton_kernels/triton_kernels/matmul_details/
+// _p_matmul.py:62-790 (gather :343-344, bias/activation/gammas :561-622, scatter :733-737), host
+// entry triton_kernels/matmul.py:243.
+#include <string.h>
+
+#include "common.cuh"
+#include "gemm_common.cuh"
+#include "host_common.h"
+
+namespace tb200 {
+
+static constexpr int MOE_THREADS = 192;
+static constexpr int MOE_BM = 128;
+static constexpr int MOE_BN = 256;
+static constexpr int MOE_STAGES = 4;
+
+struct MoeParams {
+  CUtensorMap tmx;  // X: (K, rows_x), box (64, 1): gather4 source
+  CUtensorMap tmw;  // W: K-major (K, N, E) box (64, BN, 1); N-major (N, K, E) box (64, 64, 1)
+  const int* slice_offs;
+  const int* sched;
+  const int* gather;
+  const int* scatter;
+  const float* gammas;
+  const float* bias;
+  void* y;
+  int* status;
+  long long ldy;
+  int n_sched, tiles_n, units;
+  int n, k, k_blocks, rows_x, rows_y;
+  int w_n_major;
+  int swiglu, has_limit, out_f16;
+  float alpha, limit;
+  uint32_t idesc;
+};
+
+struct MoeSmem {
+  static constexpr int A_BYTES = MOE_BM * 128;
+  static constexpr int B_BYTES = MOE_BN * 128;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int BAR_OFFSET = MOE_STAGES * STAGE_BYTES;
+  static constexpr int TOTAL = BAR_OFFSET + (2 * MOE_STAGES + 4) * 8 + 16 + 1024;
+};
+
+__device__ __forceinline__ void tma_gather4(uint32_t dst, const CUtensorMap* tmap, uint32_t bar, int col, int r0, int r1,
+                                            int r2, int r3, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%3, %4, %5, %6, %7}], [%2], %8;"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(col), "r"(r0), "r"(r1), "r"(r2), "r"(r3),
+      "l"(policy)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_a(uint32_t dst, const CUtensorMap* tmap, uint32_t bar, int x, int y, int z,
+                                              uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%3, %4, %5}], [%2], %6;"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(x), "r"(y), "r"(z), "l"(policy)
+      : "memory");
+}
+
+__device__ __forceinline__ float moe_swiglu(float g, float l, float alpha, float limit, int has_limit) {
+  if (has_limit) {
+    g = fminf(g, limit);
+    l = fminf(fmaxf(l, -limit), limit);
+  }
+  return g / (1.f + __expf(-alpha * g)) * (l + 1.f);
+}
+
+__global__ void __launch_bounds__(MOE_THREADS, 1) moe_gemm_kernel(const __grid_constant__ MoeParams p) {
+  using L = MoeSmem;
+  constexpr int BN = MOE_BN;
+  constexpr int STAGES = MOE_STAGES;
+  constexpr uint32_t TMEM_COLS = 512;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET);
+  uint64_t* empty = full + STAGES;
+  uint64_t* tfull = empty + STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&p.tmx);
+    tma_prefetch_desc(&p.tmw);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tfull[i], 1);
+      mbar_init(&tempty[i], 4);
+    }
+    mbar_init_fence();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+
+  const int units = p.units, tiles_n = p.tiles_n, k_blocks = p.k_blocks;
+  const int* const sched = p.sched;
+  const int* const slice_offs = p.slice_offs;
+  int* const status = p.status;
+  const uint32_t smem_a = smem_u32(smem);
+  const uint32_t full_a = smem_u32(full), empty_a = smem_u32(empty);
+
+  if (warp == 0) {
+    // ------------------------------------------------------------- producer (whole warp)
+    const uint64_t pol_x = policy_evict_normal();
+    const uint64_t pol_w = policy_evict_last();
+    const int* const gather = p.gather;
+    const int rows_x = p.rows_x;
+    const int w_n_major = p.w_n_major;
+    uint32_t s = 0, ph = 0;
+    bool ok = true;
+    for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x) {
+      const int si = unit / tiles_n;
+      const int entry = __ldg(sched + si);
+      if (entry < 0) continue;
+      const int e = entry & 0xFFFF;
+      const int n0 = (unit - si * tiles_n) * BN;
+      const int row0 = __ldg(slice_offs + e) + (entry >> 16) * MOE_BM;
+      const int row_end = __ldg(slice_offs + e + 1);
+      int r[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int sr = row0 + lane * 4 + i;
+        int src = rows_x;  // out of range -> zero fill
+        if (sr < row_end) {
+          src = gather ? __ldg(gather + sr) : sr;
+          if (src < 0 || src >= rows_x) src = rows_x;
+        }
+        r[i] = src;
+      }
+      for (int kb = 0; kb < k_blocks; ++kb) {
+        int good = 1;
+        if (lane == 0) {
+          good = mbar_wait_a(empty_a + s * 8, ph ^ 1, status, WAIT_SMEM_EMPTY) ? 1 : 0;
+          if (good) mbar_expect_tx_a(full_a + s * 8, L::STAGE_BYTES);
+        }
+        good = __shfl_sync(0xffffffffu, good, 0);
+        if (!good) {
+          ok = false;
+          break;
+        }
+        const uint32_t bar = full_a + s * 8;
+        const uint32_t sa = smem_a + s * L::STAGE_BYTES;
+        const int kx = kb * 64;
+        tma_gather4(sa + lane * 512, &p.tmx, bar, kx, r[0], r[1], r[2], r[3], pol_x);
+        if (lane == 0) {
+          const uint32_t sb = sa + L::A_BYTES;
+          if (w_n_major) {
+#pragma unroll
+            for (int i = 0; i < BN / 64; ++i) tma_load_3d_a(sb + i * 8192, &p.tmw, bar, n0 + i * 64, kx, e, pol_w);
+          } else {
+            tma_load_3d_a(sb, &p.tmw, bar, kx, n0, e, pol_w);
+          }
+        }
+        if (++s == STAGES) {
+          s = 0;
+          ph ^= 1;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = p.idesc;
+      const uint32_t b_lbo = p.w_n_major ? 8192u : 16u;
+      const uint64_t bk = p.w_n_major ? (uint64_t)(2048 >> 4) : (uint64_t)(32 >> 4);
+      const uint64_t adesc0 = make_smem_desc(smem_a, 16, 1024, SWIZZLE_128B);
+      const uint64_t bdesc0 = make_smem_desc(smem_a + L::A_BYTES, b_lbo, 1024, SWIZZLE_128B);
+      const uint32_t tfull_a = smem_u32(tfull), tempty_a = smem_u32(tempty);
+      uint32_t s = 0, ph = 0, tcount = 0;
+      bool ok = true;
+      for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x) {
+        const int si = unit / tiles_n;
+        if (__ldg(sched + si) < 0) continue;
+        const uint32_t acc = tcount & 1;
+        const uint32_t aph = (tcount >> 1) & 1;
+        ++tcount;
+        if (!mbar_wait_a(tempty_a + acc * 8, aph ^ 1, status, WAIT_TMEM_EMPTY)) break;
+        if (!mbar_wait_a(full_a + s * 8, ph, status, WAIT_SMEM_FULL)) break;
+        tc_fence_after_sync();
+        const uint32_t tmem_d = tmem_base + acc * BN;
+        uint32_t accum = 0;
+        uint32_t prev_empty = 0;
+        for (int i = 0; i < k_blocks; ++i) {
+          const uint64_t ad = adesc0 + (uint64_t)(s * (L::STAGE_BYTES >> 4));
+          const uint64_t bd = bdesc0 + (uint64_t)(s * (L::STAGE_BYTES >> 4));
+          umma_f16_ss(tmem_d, ad, bd, idesc, accum);
+          accum = 1u;
+          if (prev_empty) umma_commit_a(prev_empty);
+          prev_empty = empty_a + s * 8;
+          umma_f16_ss(tmem_d, ad + 2, bd + bk, idesc, 1u);
+          if (++s == STAGES) {
+            s = 0;
+            ph ^= 1;
+          }
+          if (i + 1 < k_blocks) {
+            if (!mbar_wait_a(full_a + s * 8, ph, status, WAIT_SMEM_FULL)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after_sync();
+          }
+          umma_f16_ss(tmem_d, ad + 4, bd + 2 * bk, idesc, 1u);
+          umma_f16_ss(tmem_d, ad + 6, bd + 3 * bk, idesc, 1u);
+        }
+        if (ok) {
+          umma_commit_a(prev_empty);
+          umma_commit_a(tfull_a + acc * 8);
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------- epilogue
+    const int q = warp & 3;
+    const int* const scatter = p.scatter;
+    const float* const gammas = p.gammas;
+    const float* const bias = p.bias;
+    const int n = p.n, swiglu = p.swiglu, has_limit = p.has_limit, out_f16 = p.out_f16, rows_y = p.rows_y;
+    const float alpha = p.alpha, limit = p.limit;
+    const long long ldy = p.ldy;
+    uint16_t* const y = reinterpret_cast<uint16_t*>(p.y);
+    const uint32_t tempty_a = smem_u32(tempty);
+    uint32_t tcount = 0;
+    for (int unit = blockIdx.x; unit < units; unit += gridDim.x) {
+      const int si = unit / tiles_n;
+      const int entry = __ldg(sched + si);
+      if (entry < 0) continue;
+      const int e = entry & 0xFFFF;
+      const int n0 = (unit - si * tiles_n) * BN;
+      const int row0 = __ldg(slice_offs + e) + (entry >> 16) * MOE_BM;
+      const int row_end = __ldg(slice_offs + e + 1);
+      const uint32_t acc = tcount & 1;
+      const uint32_t aph = (tcount >> 1) & 1;
+      ++tcount;
+      if (!mbar_wait(&tfull[acc], aph, status, WAIT_TMEM_FULL)) break;
+      tc_fence_after_sync();
+      const int sr = row0 + q * 32 + lane;  // sorted row handled by this thread
+      int out_row = -1;
+      float gamma = 1.f;
+      if (sr < row_end) {
+        out_row = scatter ? __ldg(scatter + sr) : sr;
+        if (out_row >= rows_y) out_row = -1;
+        if (gammas) gamma = __ldg(gammas + sr);
+      }
+      const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + acc * BN;
+      const float* brow = bias ? bias + (long long)e * n : nullptr;
+#pragma unroll 1
+      for (int cc = 0; cc < BN; cc += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(taddr + cc, v);
+        tmem_ld_wait();
+        const int col = n0 + cc;
+        if (out_row < 0 || col >= n) continue;
+        float f[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          f[j] = __uint_as_float(v[j]);
+          if (brow && col + j < n) f[j] += __ldg(brow + col + j);
+        }
+        if (swiglu) {
+          // 32 accumulator columns -> 16 outputs at column (col / 2)
+          uint16_t* dst = y + (long long)out_row * ldy + (col >> 1);
+          const int cnt = min(16, (n - col) >> 1);
+          float o[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) o[j] = moe_swiglu(f[2 * j], f[2 * j + 1], alpha, limit, has_limit) * gamma;
+          if (cnt == 16 && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+              uint32_t w[4];
+#pragma unroll
+              for (int t = 0; t < 4; ++t)
+                w[t] = out_f16 ? pack_f16x2(o[j * 8 + 2 * t], o[j * 8 + 2 * t + 1])
+                               : pack_bf16x2(o[j * 8 + 2 * t], o[j * 8 + 2 * t + 1]);
+              reinterpret_cast<uint4*>(dst)[j] = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              if (j < cnt) {
+                if (out_f16) {
+                  __half h = __float2half_rn(o[j]);
+                  dst[j] = *reinterpret_cast<uint16_t*>(&h);
+                } else {
+                  __nv_bfloat16 h = __float2bfloat16_rn(o[j]);
+                  dst[j] = *reinterpret_cast<uint16_t*>(&h);
+                }
+              }
+            }
+          }
+        } else {
+          uint16_t* dst = y + (long long)out_row * ldy + col;
+          const int cnt = min(32, n - col);
+          if (cnt == 32 && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint32_t w[4];
+#pragma unroll
+              for (int t = 0; t < 4; ++t) {
+                const float lo = f[j * 8 + 2 * t] * gamma, hi = f[j * 8 + 2 * t + 1] * gamma;
+                w[t] = out_f16 ? pack_f16x2(lo, hi) : pack_bf16x2(lo, hi);
+              }
+              reinterpret_cast<uint4*>(dst)[j] = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (j < cnt) {
+                const float x = f[j] * gamma;
+                if (out_f16) {
+                  __half h = __float2half_rn(x);
+                  dst[j] = *reinterpret_cast<uint16_t*>(&h);
+                } else {
+                  __nv_bfloat16 h = __float2bfloat16_rn(x);
+                  dst[j] = *reinterpret_cast<uint16_t*>(&h);
+                }
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_a(tempty_a + acc * 8);
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+}  // namespace tb200
+
+using namespace tb200;
+
+extern "C" int tb200_moe_gemm(const tb200_moe_gemm_args* a, void* stream_) {
+  if (!a || !a->x || !a->w || !a->y || !a->slice_offs || !a->block_schedule) return TB200_ERR_BAD_ARG;
+  if (a->n_experts <= 0 || a->n_experts > 65535 || a->k <= 0 || a->n <= 0 || a->n_sched < 0) return TB200_ERR_BAD_ARG;
+  if (a->rows_x < 0 || a->rows_y < 0) return TB200_ERR_BAD_ARG;
+  if (a->dtype != TB200_BF16 && a->dtype != TB200_F16) return TB200_ERR_UNSUPPORTED;
+  if (a->swiglu && (a->n & 1)) return TB200_ERR_BAD_ARG;
+  if ((a->k % 8) || (a->ldx % 8) || (a->w_n_major && (a->n % 8))) return TB200_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(a->x) & 15) || (reinterpret_cast<uintptr_t>(a->w) & 15)) return TB200_ERR_BAD_ARG;
+  if (a->rows_x > INT32_MAX - 1 || a->rows_y > INT32_MAX || a->k > INT32_MAX || a->n > INT32_MAX)
+    return TB200_ERR_UNSUPPORTED;
+  if (a->n_sched == 0 || a->rows_x == 0) return TB200_OK;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const int sms = sm_count();
+  if (sms <= 0) return TB200_ERR_CUDA;
+
+  MoeParams p;
+  memset(&p, 0, sizeof(p));
+  const CUtensorMapDataType dt =
+      a->dtype == TB200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  {
+    const uint64_t dims[2] = {(uint64_t)a->k, (uint64_t)a->rows_x};
+    const uint64_t strides[1] = {(uint64_t)a->ldx * 2};
+    const uint32_t box[2] = {64, 1};
+    int rc = encode_tmap(&p.tmx, dt, 2, a->x, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != TB200_OK) return rc;
+  }
+  if (a->w_n_major) {
+    const uint64_t dims[3] = {(uint64_t)a->n, (uint64_t)a->k, (uint64_t)a->n_experts};
+    const uint64_t strides[2] = {(uint64_t)a->n * 2, (uint64_t)a->n * a->k * 2};
+    const uint32_t box[3] = {64, 64, 1};
+    int rc = encode_tmap(&p.tmw, dt, 3, a->w, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != TB200_OK) return rc;
+  } else {
+    const uint64_t dims[3] = {(uint64_t)a->k, (uint64_t)a->n, (uint64_t)a->n_experts};
+    const uint64_t strides[2] = {(uint64_t)a->k * 2, (uint64_t)a->n * a->k * 2};
+    const uint32_t box[3] = {64, (uint32_t)MOE_BN, 1};
+    int rc = encode_tmap(&p.tmw, dt, 3, a->w, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != TB200_OK) return rc;
+  }
+  p.slice_offs = a->slice_offs;
+  p.sched = a->block_schedule;
+  p.gather = a->gather_indx;
+  p.scatter = a->scatter_indx;
+  p.gammas = a->gammas;
+  p.bias = a->bias;
+  p.y = a->y;
+  p.ldy = a->ldy;
+  p.status = status_ptr();
+  if (!p.status) return TB200_ERR_CUDA;
+  p.n_sched = a->n_sched;
+  p.tiles_n = (int)((a->n + MOE_BN - 1) / MOE_BN);
+  const long long units = (long long)a->n_sched * p.tiles_n;
+  if (units > INT32_MAX) return TB200_ERR_UNSUPPORTED;
+  p.units = (int)units;
+  p.n = (int)a->n;
+  p.k = (int)a->k;
+  p.k_blocks = (int)((a->k + 63) / 64);
+  p.rows_x = (int)a->rows_x;
+  p.rows_y = (int)a->rows_y;
+  p.w_n_major = a->w_n_major ? 1 : 0;
+  p.swiglu = a->swiglu ? 1 : 0;
+  p.has_limit = a->swiglu_has_limit ? 1 : 0;
+  p.alpha = a->swiglu_alpha;
+  p.limit = a->swiglu_limit;
+  p.out_f16 = a->dtype == TB200_F16 ? 1 : 0;
+  const uint32_t fmt = a->dtype == TB200_F16 ? 0u : 1u;
+  p.idesc = make_idesc(fmt, fmt, 0u, p.w_n_major ? 1u : 0u, MOE_BM, MOE_BN);
+  auto kfn = moe_gemm_kernel;
+  if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, MoeSmem::TOTAL) != cudaSuccess)
+    return TB200_ERR_CUDA;
+  const int grid = p.units < sms ? p.units : sms;
+  kfn<<<grid, MOE_THREADS, MoeSmem::TOTAL, stream>>>(p);
+  return cuda_err(cudaGetLastError());
+}

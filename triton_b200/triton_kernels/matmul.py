@@ -1,0 +1,158 @@
+"""``matmul(a, b, bias, a_ragged_metadata=None, ..., gather_indx=None, scatter_indx=None, ...,
+gammas=None, ..., fused_activation=None, ...)`` — counterpart of ``triton_kernels/matmul.py:243`` in
+the reference for the bf16/fp16 MoE subset: per-expert GEMM over expert-sorted rows with the row
+gather fused into the load and bias, SwiGLU, per-row gammas and row scatter fused into the epilogue.
+Unsupported combinations (MX / flexpoint precision, batched input, ragged K, fused communication,
+accumulator input, betas, out_alpha, custom epilogues) raise ``NotImplementedError``, as the
+reference does for combinations it cannot serve (``:288,437-447,467``)."""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+
+import torch
+
+from .. import _lib
+from .swiglu import swiglu_fn
+from .tensor import RaggedTensorMetadata, make_ragged_tensor_metadata
+
+_DT = {torch.bfloat16: _lib.BF16, torch.float16: _lib.F16}
+
+
+@dataclass(frozen=True)
+class FnSpecs:
+    name: str
+    fn: object
+    fn_arg_names: tuple = tuple()
+    fn_arg_do_not_specialize: tuple = tuple()
+    reduction_n: int = 1
+
+    @staticmethod
+    def default():
+        return FnSpecs("dflt", None, tuple())
+
+
+@dataclass(frozen=True)
+class FusedActivation:
+    specs: FnSpecs = FnSpecs.default()
+    fn_args: tuple = tuple()
+
+
+@dataclass(frozen=True)
+class Epilogue:
+    specs: FnSpecs = FnSpecs.default()
+    fn_arg_values_matmul: tuple = tuple()
+    fn_arg_values_finalize: tuple = tuple()
+    effective_itemsize: float | None = None
+
+
+@dataclass
+class PrecisionConfig:
+    max_num_imprecise_acc: int | None = None
+    allow_tf32: bool = True
+    acc_scale: float = 1.0
+    out_dtype: torch.dtype | None = None
+    a_mx_scale: object = None
+    b_mx_scale: object = None
+    c_mx_scale: object = None
+
+
+def swiglu_activation(alpha: float = 1.0, limit: float | None = None) -> FusedActivation:
+    """The fused SwiGLU spec the reference builds as
+    ``FusedActivation(FnSpecs("swiglu", swiglu_fn, ("alpha", "limit"), reduction_n=2), (alpha, limit))``."""
+    return FusedActivation(FnSpecs("swiglu", swiglu_fn, ("alpha", "limit"), reduction_n=2), (alpha, limit))
+
+
+def matmul(a, b, bias, a_ragged_metadata: RaggedTensorMetadata | None = None, b_ragged_metadata=None,
+           gather_indx=None, scatter_indx=None, precision_config: PrecisionConfig | None = None, betas=None,
+           gammas=None, out_alpha=None, c=None, fused_comm=None, fused_activation: FusedActivation | None = None,
+           epilogue: Epilogue | None = None, c_acc_in=None):
+    if b_ragged_metadata is not None:
+        raise NotImplementedError("matmul: ragged K (b_ragged_metadata) is not implemented")
+    if betas is not None or out_alpha is not None or fused_comm is not None or c_acc_in is not None:
+        raise NotImplementedError("matmul: betas / out_alpha / fused_comm / c_acc_in are not implemented")
+    if epilogue is not None and epilogue.specs.name != "dflt":
+        raise NotImplementedError("matmul: custom epilogues are not implemented")
+    if precision_config is not None and (precision_config.a_mx_scale is not None
+                                         or precision_config.b_mx_scale is not None
+                                         or precision_config.c_mx_scale is not None):
+        raise NotImplementedError("matmul: MX precision configs are not implemented")
+    if not isinstance(a, torch.Tensor) or not isinstance(b, torch.Tensor):
+        raise NotImplementedError("matmul: wrapped Tensor operands (MX / layouts) are not implemented")
+    if a.ndim != 2:
+        raise NotImplementedError("matmul: batched input is not implemented")
+    if not a.is_cuda:
+        raise RuntimeError("triton_b200 matmul needs CUDA tensors (there is no CPU path)")
+    if a.dtype not in _DT or b.dtype != a.dtype:
+        raise NotImplementedError(f"matmul: dtype {a.dtype}/{b.dtype} (bf16 and fp16 are implemented)")
+    dev = a.device
+    if b.ndim == 2:
+        b = b.unsqueeze(0)
+    E, K, N = b.shape
+    assert a.shape[1] == K, "inner dimensions differ"
+    if a.stride(1) != 1:
+        a = a.contiguous()
+    # weight layout: [E, K, N] with N contiguous, or K contiguous (the reference's benches store W
+    # column-major per expert)
+    if b.stride(2) == 1 and b.stride(1) == N and b.stride(0) == K * N:
+        w_n_major = 1
+    elif b.stride(1) == 1 and b.stride(2) == K and b.stride(0) == K * N:
+        w_n_major = 0
+    else:
+        b = b.contiguous()
+        w_n_major = 1
+
+    swiglu, alpha, limit = 0, 1.0, None
+    if fused_activation is not None and fused_activation.specs.name != "dflt":
+        if fused_activation.specs.name != "swiglu":
+            raise NotImplementedError(f"matmul: fused activation {fused_activation.specs.name!r}")
+        swiglu = 1
+        alpha = float(fused_activation.fn_args[0])
+        limit = fused_activation.fn_args[1] if len(fused_activation.fn_args) > 1 else None
+    n_out = N // 2 if swiglu else N
+
+    R = a.shape[0] if gather_indx is None else gather_indx.shape[0]
+    if a_ragged_metadata is None:
+        assert E == 1, "several weight matrices need a_ragged_metadata"
+        a_ragged_metadata = make_ragged_tensor_metadata(torch.tensor([R], dtype=torch.int32, device=dev), R)
+    md = a_ragged_metadata
+    sched = md.block_schedule(128)
+    rows_y = R if scatter_indx is None else scatter_indx.shape[0]
+    out_dtype = a.dtype
+    if precision_config is not None and precision_config.out_dtype not in (None, a.dtype):
+        raise NotImplementedError("matmul: out_dtype different from the input dtype")
+    if c is None:
+        # rows no sorted row maps to stay zero, as in the torch twin (matmul.py:902-906)
+        c = (torch.zeros if scatter_indx is not None else torch.empty)((rows_y, n_out), dtype=out_dtype, device=dev)
+    else:
+        assert c.shape == (rows_y, n_out) and c.dtype == out_dtype and c.stride(1) == 1
+
+    def i32(t):
+        return None if t is None else t.to(torch.int32).contiguous()
+
+    gi, si = i32(gather_indx), i32(scatter_indx)
+    gm = None if gammas is None else gammas.float().contiguous()
+    bs = None
+    if bias is not None:
+        bs = bias.float().reshape(E, N).contiguous()
+    args = _lib.MoeGemmArgs()
+    args.x, args.w, args.y = a.data_ptr(), b.data_ptr(), c.data_ptr()
+    args.bias = bs.data_ptr() if bs is not None else None
+    args.slice_offs, args.block_schedule = md.slice_offs.data_ptr(), sched.data_ptr()
+    args.gather_indx = gi.data_ptr() if gi is not None else None
+    args.scatter_indx = si.data_ptr() if si is not None else None
+    args.gammas = gm.data_ptr() if gm is not None else None
+    args.n_experts, args.k, args.n = E, K, N
+    args.rows_x, args.rows_y = a.shape[0], rows_y
+    args.ldx, args.ldy = a.stride(0), c.stride(0)
+    args.n_sched = sched.shape[0]
+    args.w_n_major = w_n_major
+    args.dtype = _DT[a.dtype]
+    args.swiglu = swiglu
+    args.swiglu_alpha = alpha
+    args.swiglu_limit = float(limit) if limit is not None else 0.0
+    args.swiglu_has_limit = 1 if limit is not None else 0
+    with torch.cuda.device(dev):
+        rc = _lib.lib().tb200_moe_gemm(ctypes.byref(args), ctypes.c_void_p(_lib.current_stream_ptr(dev)))
+    _lib.check(rc, "tb200_moe_gemm")
+    return c

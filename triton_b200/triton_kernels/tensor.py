@@ -1,0 +1,172 @@
+"""Routing data structures: ``Bitmatrix``, ``BitmatrixMetadata``, ``RaggedTensorMetadata``,
+``SparseMatrix`` and their builders. Counterparts of ``triton_kernels/tensor.py:203-210``,
+``tensor_details/bitmatrix.py:8-25,110-150`` and ``tensor_details/ragged_tensor.py:12-94,183-210``
+in the reference; field names and dtypes are the reference's (all index tensors int32)."""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+
+import torch
+
+from .. import _lib
+
+
+@dataclass
+class Bitmatrix:
+    """(rows x cols) bit mask packed into 32-bit words; ``data[r, w]`` holds columns 32w..32w+31
+    of row r. The reference stores it transposed in memory (``data.stride(0) == 1``)."""
+    data: torch.Tensor
+    shape: list
+    shape_max: list | None = None
+
+    @property
+    def device(self):
+        return self.data.device
+
+
+@dataclass
+class BitmatrixMetadata:
+    col_sum: torch.Tensor          # entries per column (tokens per expert)
+    col_sorted_indx: torch.Tensor  # row-major entry ids grouped by column ("combine" order)
+    row_sorted_indx: torch.Tensor  # position of each row-major entry in column order ("dispatch")
+
+
+def make_bitmatrix_metadata(nonzero_indx: torch.Tensor, bitmatrix: Bitmatrix) -> BitmatrixMetadata:
+    assert nonzero_indx.ndim == 2
+    assert nonzero_indx.dtype in (torch.int16, torch.int32)
+    nonzero_indx = nonzero_indx.contiguous()
+    dev = nonzero_indx.device
+    n = nonzero_indx.numel()
+    n_cols = int(bitmatrix.shape[1])
+    col_sum = torch.empty(n_cols, dtype=torch.int32, device=dev)
+    combined = torch.empty(2 * n, dtype=torch.int32, device=dev)
+    col_sorted, row_sorted = combined[:n], combined[n:]
+    l = _lib.lib()
+    need = l.tb200_bitmatrix_metadata_workspace_bytes(n, n_cols)
+    ws = torch.empty(max(need, 4), dtype=torch.uint8, device=dev)
+    args = _lib.BitmatrixMetadataArgs()
+    args.indx = nonzero_indx.data_ptr()
+    args.col_sum, args.col_sorted_indx, args.row_sorted_indx = col_sum.data_ptr(), col_sorted.data_ptr(), row_sorted.data_ptr()
+    args.workspace, args.workspace_bytes = ws.data_ptr(), need
+    args.n_entries, args.n_cols = n, n_cols
+    args.indx_is_int16 = 1 if nonzero_indx.dtype == torch.int16 else 0
+    with torch.cuda.device(dev):
+        rc = l.tb200_bitmatrix_metadata(ctypes.byref(args), ctypes.c_void_p(_lib.current_stream_ptr(dev)))
+    _lib.check(rc, "tb200_bitmatrix_metadata")
+    return BitmatrixMetadata(col_sum=col_sum, col_sorted_indx=col_sorted, row_sorted_indx=row_sorted)
+
+
+@dataclass
+class RaggedTensorMetadata:
+    slice_sizes: torch.Tensor
+    slice_offs: torch.Tensor
+    block_offs_data: torch.Tensor
+    block_schedule_data: torch.Tensor
+    expected_slice_size: int | None = None
+    slice_sizes_divisibility: int = None
+
+    def __post_init__(self):
+        assert self.block_offs_data.shape[0] == len(RaggedTensorMetadata.block_sizes())
+        assert self.block_schedule_data.shape[0] == len(RaggedTensorMetadata.block_sizes())
+        assert self.block_offs_data.dtype == torch.int32
+        assert self.block_schedule_data.dtype == torch.int32
+        if self.slice_sizes is not None:
+            assert self.slice_sizes.dtype == torch.int32
+        if self.slice_offs is not None:
+            assert self.slice_offs.dtype == torch.int32
+
+    @property
+    def n_slices(self):
+        return self.slice_sizes.shape[0]
+
+    def block_offs(self, block_size):
+        return self.block_offs_data[RaggedTensorMetadata.block_sizes().index(block_size)]
+
+    def block_schedule(self, block_size):
+        return self.block_schedule_data[RaggedTensorMetadata.block_sizes().index(block_size)]
+
+    @staticmethod
+    def n_blocks(n_slices, n_total_rows, block_size):
+        if n_total_rows <= n_slices:
+            return n_total_rows
+        return n_slices - 1 - ((n_slices - n_total_rows - 1) // block_size)
+
+    @staticmethod
+    def max_n_blocks(n_slices, n_total_rows):
+        return RaggedTensorMetadata.n_blocks(n_slices, n_total_rows, min(RaggedTensorMetadata.block_sizes()))
+
+    @staticmethod
+    def block_sizes_log2():
+        return range(4, 8)
+
+    @staticmethod
+    def block_sizes():
+        return [2**x for x in RaggedTensorMetadata.block_sizes_log2()]
+
+
+def make_ragged_tensor_metadata(slice_sizes: torch.Tensor, n_total_rows: int) -> RaggedTensorMetadata:
+    assert slice_sizes.ndim == 1
+    slice_sizes = slice_sizes.to(torch.int32).contiguous()
+    dev = slice_sizes.device
+    n_slices = slice_sizes.shape[0]
+    nbs = len(RaggedTensorMetadata.block_sizes())
+    max_n_blocks = RaggedTensorMetadata.max_n_blocks(n_slices, n_total_rows)
+    slice_offs = torch.empty(n_slices + 1, dtype=torch.int32, device=dev)
+    block_offs = torch.empty((nbs, n_slices + 1), dtype=torch.int32, device=dev)
+    block_schedule = torch.empty((nbs, max_n_blocks), dtype=torch.int32, device=dev)
+    args = _lib.RaggedMetadataArgs()
+    args.slice_sizes, args.slice_offs = slice_sizes.data_ptr(), slice_offs.data_ptr()
+    args.block_offs, args.block_schedule = block_offs.data_ptr(), block_schedule.data_ptr()
+    args.n_slices, args.max_n_blocks = n_slices, max_n_blocks
+    with torch.cuda.device(dev):
+        rc = _lib.lib().tb200_ragged_metadata(ctypes.byref(args), ctypes.c_void_p(_lib.current_stream_ptr(dev)))
+    _lib.check(rc, "tb200_ragged_metadata")
+    return RaggedTensorMetadata(slice_sizes, slice_offs, block_offs, block_schedule)
+
+
+def remap_ragged_tensor_metadata(md: RaggedTensorMetadata, slice_map: torch.Tensor) -> RaggedTensorMetadata:
+    """Metadata of the ragged tensor that keeps slice i iff ``slice_map[i] != -1`` (renumbered to
+    ``slice_map[i]``); dropped entries are compacted to the end as -1
+    (``tensor_details/ragged_tensor.py:348-381``). Tiny index bookkeeping, done with device-side
+    tensor ops."""
+    assert slice_map.ndim == 1 and slice_map.shape[0] == md.slice_sizes.shape[0]
+    sm = slice_map.to(torch.int64)
+    dev = sm.device
+    keep = sm != -1
+    keep1 = torch.cat([keep, torch.zeros(1, dtype=torch.bool, device=dev)])
+
+    def compact(vals, cond):
+        pad = torch.full((int((~cond).sum().item()), ), -1, dtype=vals.dtype, device=dev)
+        return torch.cat([vals[cond], pad])
+
+    ss = compact(md.slice_sizes, keep)
+    so = compact(md.slice_offs, keep1)
+    bo, bs = [], []
+    for i in range(md.block_offs_data.shape[0]):
+        o = compact(md.block_offs_data[i], keep1)
+        sch = md.block_schedule_data[i]
+        sid = (sch & 0xFFFF).to(torch.int64)
+        valid = sid != 0xFFFF
+        cond = torch.zeros_like(valid)
+        cond[valid] = sm[sid[valid]] != -1
+        s2 = compact(sch, cond)
+        sid2 = (s2 & 0xFFFF).to(torch.int64)
+        v2 = sid2 != 0xFFFF
+        out = s2.clone()
+        out[v2] = ((s2[v2].to(torch.int64) & 0xFFFF0000) | sm[sid2[v2]]).to(torch.int32)
+        first = int((o == -1).nonzero()[0].item())
+        o[first] = int((out != -1).sum().item())
+        bo.append(o)
+        bs.append(out)
+    return RaggedTensorMetadata(ss, so, torch.stack(bo), torch.stack(bs))
+
+
+@dataclass
+class SparseMatrix:
+    indx: torch.Tensor
+    vals: torch.Tensor
+    mask: Bitmatrix
+
+    def __post_init__(self):
+        self.mask_metadata = make_bitmatrix_metadata(self.indx, self.mask)
