@@ -107,6 +107,127 @@ class ClockSampler:
                 "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
 
 
+def build_workload(name: str, rank: int, dev):
+    """Returns (step, flops_per_step, hbm_bytes_per_step, description, kernel, bound) for an extra
+    workload (`--workload`); the default GEMM workload is handled in main()."""
+    import math
+    import torch
+    g = torch.Generator(device="cpu").manual_seed(2 + 1000 * rank)
+    if name in ("attn", "attn_causal", "attn_short", "attn_short_causal"):
+        from triton_b200.tutorials.blackwell_fa_ws_pipelined_persistent import attention_with_lse
+        causal = name.endswith("causal")
+        B, H, S, D = (32, 32, 1024, 128) if "short" in name else (4, 32, 8192, 128)
+        q, k, v = (torch.randn(B, H, S, D, generator=g).to(torch.bfloat16).to(dev) for _ in range(3))
+        sc = 1.0 / math.sqrt(D)
+        fl = 4.0 * B * H * D * (S * (S + 1) / 2 if causal else S * S)
+        return (lambda: attention_with_lse(q, k, v, sc, causal), fl, 4.0 * B * H * S * D * 2,
+                f"flash-attention fwd bf16 [B={B},H={H},S={S},D={D}] causal={causal}, seed 2", "attention_fwd_kernel<128>",
+                "tensor")
+    if name in ("fp8", "mxfp8"):
+        n = 8192
+        a = (torch.randn(n, n, generator=g) * 0.1).to(torch.float8_e4m3fn).to(dev)
+        b = (torch.randn(n, n, generator=g) * 0.1).to(torch.float8_e4m3fn).to(dev)
+        if name == "fp8":
+            from triton_b200.tutorials.blackwell_scaled_mm_ws import blackwell_scaled_mm_ws
+            sa, sb = torch.rand(1, generator=g).to(dev), torch.rand(1, generator=g).to(dev)
+            return (lambda: blackwell_scaled_mm_ws(a, b, sa, sb, scale_mode="tensorwise"), 2.0 * n ** 3, 3.0 * n * n,
+                    "per-tensor-scaled e4m3 GEMM 8192^3, bf16 out", "gemm_kernel<128,7,pair,f8>", "tensor")
+        from triton_b200.tutorials.blackwell_gemm_ws_mxfp8 import matmul as mx_matmul
+        u = torch.randint(-4, 5, (n * n // 32, ), generator=g)
+        sc = (u + 127).to(torch.uint8).to(dev).view(torch.float8_e8m0fnu)
+        return (lambda: mx_matmul(a, b, sc, sc), 2.0 * n ** 3, 3.0 * n * n + 2 * n * n / 32,
+                "MXFP8 block-scaled GEMM 8192^3 (e8m0 scales 2^u, u in [-4,4]), bf16 out", "gemm_mxfp8_kernel<256,4>",
+                "tensor")
+    if name in ("moe", "moe_decode"):
+        from triton_b200.triton_kernels.matmul import matmul as moe_matmul, swiglu_activation
+        from triton_b200.triton_kernels.reduce import reduce
+        from triton_b200.triton_kernels.tensor import make_ragged_tensor_metadata
+        from triton_b200.triton_kernels.topk import topk
+        T, D, F, E, k = (64 if name == "moe_decode" else 16384), 4096, 1536, 128, 4
+        g4 = torch.Generator(device="cpu").manual_seed(4 + 1000 * rank)
+        x = torch.randn(T, D, generator=g4).to(torch.bfloat16).to(dev)
+        logits = torch.randn(T, E, generator=g4).to(dev)
+        w1 = (0.02 * torch.randn(E, D, 2 * F, generator=g4)).to(torch.bfloat16).to(dev)
+        w2 = (0.02 * torch.randn(E, F, D, generator=g4)).to(torch.bfloat16).to(dev)
+        act = swiglu_activation(1.0, None)
+        y = torch.empty(T * k, D, dtype=torch.bfloat16, device=dev)
+
+        def step():
+            sm = topk(logits, k)
+            mm = sm.mask_metadata
+            rg = make_ragged_tensor_metadata(mm.col_sum, T * k)
+            combine = mm.col_sorted_indx
+            gather = torch.div(combine, k, rounding_mode="trunc")
+            gam = sm.vals.float().reshape(-1)[combine.long()]
+            h = moe_matmul(x, w1, None, rg, gather_indx=gather, fused_activation=act)
+            moe_matmul(h, w2, None, rg, scatter_indx=combine, gammas=gam, c=y)
+            return reduce(y.view(T, k, D), dim=1)[0]
+        R = T * k
+        fl = 2.0 * R * D * 2 * F + 2.0 * R * F * D
+        active = min(E, R)
+        by = active * (D * 2 * F + F * D) * 2.0 + R * (D + F) * 2.0 + R * (F + D) * 2.0
+        return (step, fl, by, f"MoE layer: {T} tokens, d_model {D}, E={E}, top-{k}, W1 [{D},{2*F}] SwiGLU W2 [{F},{D}], "
+                "gate-weighted combine, seed 4", "moe_gemm_kernel", "hbm" if name == "moe_decode" else "tensor")
+    raise SystemExit(f"unknown workload {name}")
+
+
+def run_extra_workload(args, rank, local_rank, world):
+    """Times one of the non-headline workloads on each rank (independent replicas of the sharded
+    unit: (batch, head) groups for attention, N blocks for GEMMs, expert groups for MoE) and prints
+    one JSON line with the same keys as the headline line."""
+    import torch
+    import torch.distributed as dist
+    from triton_b200 import _lib
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    step, fl, by, desc, kernel, bound = build_workload(args.workload, rank, dev)
+    warmup, steps = max(args.warmup, 3), max(args.steps, 1)
+    for _ in range(warmup):
+        step()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    sampler.sample()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    _lib.sync_check(dev)
+    ms = e0.elapsed_time(e1) / steps
+    if world > 1:
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    if rank == 0:
+        peaks = read_peaks()
+        tf = world * fl / (ms * 1e-3) / 1e12
+        if bound == "hbm":
+            ach, peak, unit = by / (ms * 1e-3) / 1e9, peaks["hbm"], "GB/s"
+        else:
+            ach, peak, unit = fl / (ms * 1e-3) / 1e12, peaks["bf16_burst"], "TFLOP/s"
+        print(json.dumps({
+            "metric": f"{args.workload} throughput", "value": tf, "unit": "TFLOP/s", "n_gpus": world, "steps": steps,
+            "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "e4m3" if args.workload in ("fp8", "mxfp8") else "bf16", "data": "synthetic",
+            "config": {"workload": desc},
+            "roofline": {"bound": bound, "achieved": ach, "peak": peak, "unit": unit, "frac": ach / peak,
+                         "traffic": None, "kernel": kernel,
+                         "peak_kind": ("copy bandwidth" if bound == "hbm" else "burst cuBLAS bf16") + ", " + peaks["source"]},
+            "gpu_launches": None, "clocks": clocks}))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def make_inputs(rank: int, device):
     import torch
     g = torch.Generator(device="cpu").manual_seed(1 + 1000 * rank)
@@ -182,6 +303,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="gemm",
+                    help="gemm (headline, default) | attn | attn_causal | attn_short | attn_short_causal | fp8 | mxfp8 | "
+                         "moe | moe_decode")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -190,6 +314,9 @@ def main():
 
     if args.impl == "reference":
         run_reference(args, rank, world)
+        return
+    if args.workload != "gemm":
+        run_extra_workload(args, rank, local_rank, world)
         return
 
     import torch
