@@ -245,8 +245,18 @@ typedef struct {
   int64_t d;
   int32_t k;
   int32_t dtype;
+  const int32_t* row_indx; /* optional int32 [n_tokens*k]: slot (t, j) reads row row_indx[t*k+j] of x (< 0 = skip) */
 } tb200_reduce_k_args;
 int tb200_reduce_k(const tb200_reduce_k_args* args, void* stream);
+
+/*
+ * Row gather (scatter = 0: dst[i] = src[indx[i]]) or scatter (scatter = 1: dst[indx[i]] = src[i]) of
+ * rows of row_bytes bytes (multiple of 16; pitches and bases 16-byte aligned); indx[i] < 0 skips.
+ * Stands behind the local row moves around the expert-parallel exchange,
+ * distributed.py:176-283 (convert_dp_to_ep / convert_ep_to_dp store rows at indexed positions).
+ */
+int tb200_move_rows(const void* src, int64_t src_pitch_bytes, void* dst, int64_t dst_pitch_bytes,
+                    const int32_t* indx, int64_t n_indx, int64_t row_bytes, int32_t scatter, void* stream);
 
 /*
  * out[r, j] = g * sigmoid(alpha * g) * (l + 1), g = a[r, 2j] (clamped to <= limit),
@@ -303,6 +313,7 @@ typedef struct {
   float swiglu_limit;
   int32_t swiglu_has_limit;
   int32_t reserved;
+  const int32_t* slice_sizes; /* optional int32 [E]: rows of expert e (needed for remapped metadata, whose slice_offs are not cumulative); NULL = slice_offs[e+1] - slice_offs[e] */
 } tb200_moe_gemm_args;
 int tb200_moe_gemm(const tb200_moe_gemm_args* args, void* stream);
 

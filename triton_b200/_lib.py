@@ -80,7 +80,7 @@ class RaggedMetadataArgs(Structure):
 class ReduceKArgs(Structure):
     _fields_ = [
         ("x", c_void_p), ("mask", c_void_p), ("scale", c_void_p), ("y", c_void_p),
-        ("n_tokens", c_int64), ("d", c_int64), ("k", c_int32), ("dtype", c_int32),
+        ("n_tokens", c_int64), ("d", c_int64), ("k", c_int32), ("dtype", c_int32), ("row_indx", c_void_p),
     ]
 
 
@@ -100,6 +100,7 @@ class MoeGemmArgs(Structure):
         ("rows_x", c_int64), ("rows_y", c_int64), ("ldx", c_int64), ("ldy", c_int64),
         ("n_sched", c_int32), ("w_n_major", c_int32), ("dtype", c_int32), ("swiglu", c_int32),
         ("swiglu_alpha", c_float), ("swiglu_limit", c_float), ("swiglu_has_limit", c_int32), ("reserved", c_int32),
+        ("slice_sizes", c_void_p),
     ]
 
 
@@ -127,6 +128,8 @@ def _declare(l: ctypes.CDLL) -> None:
         fn = getattr(l, name)
         fn.restype = c_int
         fn.argtypes = [POINTER(typ), c_void_p]
+    l.tb200_move_rows.restype = c_int
+    l.tb200_move_rows.argtypes = [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int32, c_void_p]
     l.tb200_bitmatrix_metadata_workspace_bytes.restype = c_size_t
     l.tb200_bitmatrix_metadata_workspace_bytes.argtypes = [c_int64, c_int32]
     l.tb200_gemm_mxfp8.restype = c_int

@@ -38,6 +38,7 @@ struct MoeParams {
   CUtensorMap tmx_tile;  // X: (K, rows_x), box (64, 128): contiguous-row source (no gather)
   CUtensorMap tmw;  // W: K-major (K, N, E) box (64, BN, 1); N-major (N, K, E) box (64, 64, 1)
   const int* slice_offs;
+  const int* slice_sizes;  // optional: rows of expert e = slice_sizes[e] (else slice_offs[e+1] - slice_offs[e])
   const int* sched;
   const int* gather;
   const int* scatter;
@@ -131,6 +132,7 @@ __global__ void __launch_bounds__(MOE_THREADS, 1) moe_gemm_kernel(const __grid_c
   const int units = p.units, tiles_n = p.tiles_n, k_blocks = p.k_blocks;
   const int* const sched = p.sched;
   const int* const slice_offs = p.slice_offs;
+  const int* const slice_sizes = p.slice_sizes;
   int* const status = p.status;
   const uint32_t smem_a = smem_u32(smem);
   const uint32_t full_a = smem_u32(full), empty_a = smem_u32(empty);
@@ -202,7 +204,7 @@ __global__ void __launch_bounds__(MOE_THREADS, 1) moe_gemm_kernel(const __grid_c
         if (entry < 0) continue;
         const int e = entry & 0xFFFF;
         const int row0 = __ldg(slice_offs + e) + (entry >> 16) * MOE_BM;
-        const int row_end = __ldg(slice_offs + e + 1);
+        const int row_end = slice_sizes ? __ldg(slice_offs + e) + __ldg(slice_sizes + e) : __ldg(slice_offs + e + 1);
         const uint16_t* src[8];
         uint32_t dst_off[8];
 #pragma unroll
@@ -326,7 +328,7 @@ __global__ void __launch_bounds__(MOE_THREADS, 1) moe_gemm_kernel(const __grid_c
       const int e = entry & 0xFFFF;
       const int n0 = (unit - si * tiles_n) * BN;
       const int row0 = __ldg(slice_offs + e) + (entry >> 16) * MOE_BM;
-      const int row_end = __ldg(slice_offs + e + 1);
+      const int row_end = slice_sizes ? __ldg(slice_offs + e) + __ldg(slice_sizes + e) : __ldg(slice_offs + e + 1);
       const uint32_t acc = tcount & 1;
       const uint32_t aph = (tcount >> 1) & 1;
       ++tcount;
@@ -475,6 +477,7 @@ extern "C" int tb200_moe_gemm(const tb200_moe_gemm_args* a, void* stream_) {
     if (rc != TB200_OK) return rc;
   }
   p.slice_offs = a->slice_offs;
+  p.slice_sizes = a->slice_sizes;
   p.sched = a->block_schedule;
   p.gather = a->gather_indx;
   p.scatter = a->scatter_indx;

@@ -255,10 +255,12 @@ __global__ void ragged_metadata_kernel(const int* __restrict__ slice_sizes, int 
 
 // ------------------------------------------------------------------------------- k-way reduce
 
-// y[t, d] = sum_j (mask[t, j] ? x[t, j, d] * scale[t, j] : 0), fp32 accumulation, 8 columns per thread
+// y[t, d] = sum_j (mask[t, j] ? x[row(t, j), d] * scale[t, j] : 0), fp32 accumulation, 8 columns per
+// thread; row(t, j) = row_indx[t*k + j] when an index is given (negative = skip), else t*k + j.
 template <typename T>
 __global__ void reduce_k_kernel(const T* __restrict__ x, const uint8_t* __restrict__ mask,
-                                const float* __restrict__ scale, T* __restrict__ y, long long n_tok, int k, int d) {
+                                const float* __restrict__ scale, const int* __restrict__ row_indx,
+                                T* __restrict__ y, long long n_tok, int k, int d) {
   const int d8 = d >> 3;
   const long long total = n_tok * d8;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
@@ -269,7 +271,12 @@ __global__ void reduce_k_kernel(const T* __restrict__ x, const uint8_t* __restri
     for (int j = 0; j < k; ++j) {
       if (mask && !mask[t * k + j]) continue;
       const float s = scale ? scale[t * k + j] : 1.f;
-      const uint4 raw = *reinterpret_cast<const uint4*>(x + ((t * k + j) * (long long)d + c));
+      long long row = t * k + j;
+      if (row_indx) {
+        row = row_indx[row];
+        if (row < 0) continue;
+      }
+      const uint4 raw = *reinterpret_cast<const uint4*>(x + (row * (long long)d + c));
       const T* e = reinterpret_cast<const T*>(&raw);
 #pragma unroll
       for (int u = 0; u < 8; ++u) acc[u] += to_f32<T>(e[u]) * s;
@@ -279,6 +286,25 @@ __global__ void reduce_k_kernel(const T* __restrict__ x, const uint8_t* __restri
 #pragma unroll
     for (int u = 0; u < 8; ++u) o[u] = from_f32<T>(acc[u]);
     *reinterpret_cast<uint4*>(y + (t * (long long)d + c)) = out;
+  }
+}
+
+// ---------------------------------------------------------------------------------- row mover
+
+// gather: dst[i] = src[indx[i]];  scatter: dst[indx[i]] = src[i];  indx < 0 skips the row.
+// One warp per row, 16 bytes per lane per step.
+__global__ void move_rows_kernel(const uint8_t* __restrict__ src, long long src_pitch, uint8_t* __restrict__ dst,
+                                 long long dst_pitch, const int* __restrict__ indx, long long n, int row_bytes,
+                                 int scatter) {
+  const long long warp = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long i = warp; i < n; i += nwarps) {
+    const int j = indx[i];
+    if (j < 0) continue;
+    const uint8_t* s = src + (scatter ? i : (long long)j) * src_pitch;
+    uint8_t* d = dst + (scatter ? (long long)j : i) * dst_pitch;
+    for (int b = lane * 16; b < row_bytes; b += 512) *reinterpret_cast<uint4*>(d + b) = *reinterpret_cast<const uint4*>(s + b);
   }
 }
 
@@ -411,13 +437,32 @@ extern "C" int tb200_reduce_k(const tb200_reduce_k_args* a, void* stream_) {
   if (blocks > (long long)sms * 16) blocks = (long long)sms * 16;
   if (a->dtype == TB200_BF16)
     reduce_k_kernel<__nv_bfloat16><<<(int)blocks, 256, 0, stream>>>(
-        static_cast<const __nv_bfloat16*>(a->x), a->mask, a->scale, static_cast<__nv_bfloat16*>(a->y), a->n_tokens,
-        a->k, (int)a->d);
+        static_cast<const __nv_bfloat16*>(a->x), a->mask, a->scale, a->row_indx, static_cast<__nv_bfloat16*>(a->y),
+        a->n_tokens, a->k, (int)a->d);
   else if (a->dtype == TB200_F16)
     reduce_k_kernel<__half><<<(int)blocks, 256, 0, stream>>>(static_cast<const __half*>(a->x), a->mask, a->scale,
-                                                            static_cast<__half*>(a->y), a->n_tokens, a->k, (int)a->d);
+                                                            a->row_indx, static_cast<__half*>(a->y), a->n_tokens, a->k,
+                                                            (int)a->d);
   else
     return TB200_ERR_UNSUPPORTED;
+  return cuda_err(cudaGetLastError());
+}
+
+extern "C" int tb200_move_rows(const void* src, int64_t src_pitch_bytes, void* dst, int64_t dst_pitch_bytes,
+                               const int32_t* indx, int64_t n_indx, int64_t row_bytes, int32_t scatter, void* stream_) {
+  if (n_indx < 0 || row_bytes < 0) return TB200_ERR_BAD_ARG;
+  if (n_indx == 0 || row_bytes == 0) return TB200_OK;
+  if (!src || !dst || !indx) return TB200_ERR_BAD_ARG;
+  if ((row_bytes % 16) || (src_pitch_bytes % 16) || (dst_pitch_bytes % 16) || row_bytes > INT32_MAX)
+    return TB200_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(src) & 15) || (reinterpret_cast<uintptr_t>(dst) & 15)) return TB200_ERR_BAD_ARG;
+  int sms = sm_count();
+  if (sms <= 0) sms = 148;
+  long long blocks = (n_indx + 7) / 8;  // 8 warps per block
+  if (blocks > (long long)sms * 16) blocks = (long long)sms * 16;
+  move_rows_kernel<<<(int)blocks, 256, 0, static_cast<cudaStream_t>(stream_)>>>(
+      static_cast<const uint8_t*>(src), src_pitch_bytes, static_cast<uint8_t*>(dst), dst_pitch_bytes, indx, n_indx,
+      (int)row_bytes, scatter ? 1 : 0);
   return cuda_err(cudaGetLastError());
 }
 

@@ -139,6 +139,7 @@ def matmul(a, b, bias, a_ragged_metadata: RaggedTensorMetadata | None = None, b_
     args.x, args.w, args.y = a.data_ptr(), b.data_ptr(), c.data_ptr()
     args.bias = bs.data_ptr() if bs is not None else None
     args.slice_offs, args.block_schedule = md.slice_offs.data_ptr(), sched.data_ptr()
+    args.slice_sizes = md.slice_sizes.data_ptr()
     args.gather_indx = gi.data_ptr() if gi is not None else None
     args.scatter_indx = si.data_ptr() if si is not None else None
     args.gammas = gm.data_ptr() if gm is not None else None
