@@ -44,7 +44,7 @@ WORKLOAD = "bf16 GEMM M=N=K=8192, A row-major, B K-major (transposed), N(0,1)/sq
 
 # DRAM bytes per launch of gemm_kernel<256,4> at 8192^3 from the committed ncu capture
 # (profiles/gemm_bf16_8192.md); None until a capture exists.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 1.19e9
 
 
 def read_peaks():
@@ -168,6 +168,25 @@ def build_workload(name: str, rank: int, dev):
         by = active * (D * 2 * F + F * D) * 2.0 + R * (D + F) * 2.0 + R * (F + D) * 2.0
         return (step, fl, by, f"MoE layer: {T} tokens, d_model {D}, E={E}, top-{k}, W1 [{D},{2*F}] SwiGLU W2 [{F},{D}], "
                 "gate-weighted combine, seed 4", "moe_gemm_kernel", "hbm" if name == "moe_decode" else "tensor")
+    if name == "moe_ep":
+        import torch.distributed as dist
+        from triton_b200.triton_kernels.distributed import (EpGroup, make_expt_assignment, make_expt_dict_uniform,
+                                                            moe_layer_ep)
+        world = dist.get_world_size() if dist.is_initialized() else 1
+        T, D, F, E, k = 16384, 4096, 1536, 128, 4
+        tl, per = T // world, E // world
+        g4 = torch.Generator(device="cpu").manual_seed(4 + 1000 * rank)
+        x = torch.randn(tl, D, generator=g4).to(torch.bfloat16).to(dev)
+        logits = torch.randn(tl, E, generator=g4).to(dev)
+        w1 = (0.02 * torch.randn(per, D, 2 * F, generator=g4)).to(torch.bfloat16).to(dev)
+        w2 = (0.02 * torch.randn(per, F, D, generator=g4)).to(torch.bfloat16).to(dev)
+        ea = make_expt_assignment(world, E, make_expt_dict_uniform(world, E), dev)
+        ep = EpGroup()
+        R = T * k
+        fl = (2.0 * R * D * 2 * F + 2.0 * R * F * D) / world  # per rank; the line reports world * this
+        return (lambda: moe_layer_ep(x, logits, w1, w2, k, ea, ep), fl, 0.0,
+                f"expert-parallel MoE layer: {T} tokens total ({tl}/GPU), E={E} ({per}/GPU), top-{k}, d_model {D}, "
+                "NCCL all-to-all dispatch/combine inside the timed region; strong scaling", "moe_gemm_kernel", "tensor")
     raise SystemExit(f"unknown workload {name}")
 
 
@@ -216,7 +235,8 @@ def run_extra_workload(args, rank, local_rank, world):
             ach, peak, unit = fl / (ms * 1e-3) / 1e12, peaks["bf16_burst"], "TFLOP/s"
         print(json.dumps({
             "metric": f"{args.workload} throughput", "value": tf, "unit": "TFLOP/s", "n_gpus": world, "steps": steps,
-            "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "warmup": warmup, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "strong" if args.workload == "moe_ep" else "weak", "vs_baseline": None,
             "dtype": "e4m3" if args.workload in ("fp8", "mxfp8") else "bf16", "data": "synthetic",
             "config": {"workload": desc},
             "roofline": {"bound": bound, "achieved": ach, "peak": peak, "unit": unit, "frac": ach / peak,
@@ -407,7 +427,7 @@ def main():
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                          "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
                          "peak_kind": ("sustained" if sustained else "burst") + " cuBLAS bf16, " + peaks["source"],
-                         "frac_of_nominal_2250": achieved / 2250.0, "kernel": "gemm_kernel<256,4>"},
+                         "frac_of_nominal_2250": achieved / 2250.0, "kernel": "gemm_kernel<128,7,PAIR,bf16>"},
             "e2e": {"value": world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                     "h2d_bytes_per_step": 2 * M * K * 2, "d2h_bytes_per_step": M * N * 2, "steps": e2e_steps},
             "gpu_launches": steps * world,
