@@ -212,6 +212,23 @@ int tb200_bitmatrix_metadata(const tb200_bitmatrix_metadata_args* args, void* st
 size_t tb200_bitmatrix_metadata_workspace_bytes(int64_t n_entries, int32_t n_cols);
 
 /*
+ * Same result as tb200_bitmatrix_metadata, but without a workspace argument: the scratch lives in
+ * a fixed device array inside the library (about 1 MiB per GPU, resident until exit). This entry
+ * point has no counterpart in the reference; it exists for callers that cannot allocate device
+ * memory at call time and have none to lend — processes that freeze their GPU memory plan at
+ * start-up, or runtimes that forbid cudaMalloc (a device-wide stall) on the request path.
+ * Limit: ceil(n_entries / 1024) * n_cols + n_cols <= 263168 (e.g. 262144 entries x 1024 columns,
+ * or 65536 entries x 4096 columns); beyond that the call returns TB200_ERR_TOO_LARGE and launches
+ * nothing. The first call on each device looks up the array's device address (make that call
+ * outside stream capture). Calls on the same GPU share the array: run them on one stream or order
+ * them yourself — kernels of two calls that overlap in time corrupt each other's scratch.
+ * No call here allocates or frees memory.
+ */
+int tb200_bitmatrix_metadata_static(const void* indx, int32_t indx_is_int16, int64_t n_entries, int32_t n_cols,
+                                    int32_t* col_sum, int32_t* col_sorted_indx, int32_t* row_sorted_indx,
+                                    void* stream);
+
+/*
  * Ragged-tensor metadata for block sizes 16, 32, 64, 128.
  * Stands behind: tensor_details/ragged_tensor.py:183 make_ragged_tensor_metadata(slice_sizes, n_total_rows)
  *   (torch twin make_ragged_tensor_metadata_torch :217).

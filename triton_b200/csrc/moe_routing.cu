@@ -15,6 +15,8 @@
 // These are HBM- or launch-bound integer/elementwise kernels: plain coalesced loads, no tensor cores.
 #include <string.h>
 
+#include <mutex>
+
 #include "common.cuh"
 #include "host_common.h"
 
@@ -408,6 +410,63 @@ extern "C" int tb200_bitmatrix_metadata(const tb200_bitmatrix_metadata_args* a, 
   return bitmatrix_metadata_launch(a->indx, a->indx_is_int16, a->n_entries, a->n_cols, a->col_sum, a->col_sorted_indx,
                                    a->row_sorted_indx, static_cast<int*>(a->workspace),
                                    static_cast<cudaStream_t>(stream_));
+}
+
+// ------------------------------------------------------------------ fixed-scratch variant
+// tb200_bitmatrix_metadata_static: the same three kernels as tb200_bitmatrix_metadata, with the
+// per-block histograms and the column offsets kept in a device array that is part of this library
+// instead of in a caller-provided workspace. It is for callers whose device memory is fully
+// planned before they start calling into the library and who therefore have no buffer to lend and
+// no permission to create one: a serving process that carves up the GPU at start-up and treats
+// any later allocation as a fault, or a host runtime in which cudaMalloc (which stalls the whole
+// device) is banned on the request path.
+//
+// Capacity: TB200_STATIC_SCRATCH_INTS 32-bit words (a little over 1 MiB). The array exists once per
+// GPU that loads the library and stays resident until the process exits. A call needs
+// ceil(n_entries / 1024) * n_cols + n_cols words; larger problems are refused with
+// TB200_ERR_TOO_LARGE before anything is launched.
+//
+// `g_static_scratch` below is a device symbol. In host code that name is only a handle: taking
+// its address on the host does not give a pointer a kernel can use. The device address is fetched
+// once per device with cudaGetSymbolAddress (with that device current) and cached; this happens
+// inside the first call made on each device, so make that first call outside of any stream
+// capture. Nothing in the scratch has to start out as zero: every call overwrites the part it uses
+// (histograms, then prefix sums) before reading it. All calls on one GPU share the one array, so
+// two calls whose kernels may run at the same time (different streams) corrupt each other; issue
+// them on one stream or order them with events.
+#define TB200_STATIC_SCRATCH_INTS (256 * 1024 + 1024)
+static __device__ __align__(256) int g_static_scratch[TB200_STATIC_SCRATCH_INTS];
+
+namespace tb200 {
+static int* g_static_scratch_ptr[64] = {};
+static std::mutex g_static_scratch_mu;
+
+// Device address of g_static_scratch on the current device (nullptr on failure).
+static int* static_scratch_ptr() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(g_static_scratch_mu);
+  if (!g_static_scratch_ptr[dev]) {
+    int* ptr = nullptr;
+    if (cudaGetSymbolAddress((void**)&ptr, g_static_scratch) != cudaSuccess) return nullptr;
+    g_static_scratch_ptr[dev] = ptr;
+  }
+  return g_static_scratch_ptr[dev];
+}
+}  // namespace tb200
+
+extern "C" int tb200_bitmatrix_metadata_static(const void* indx, int32_t indx_is_int16, int64_t n_entries,
+                                               int32_t n_cols, int32_t* col_sum, int32_t* col_sorted_indx,
+                                               int32_t* row_sorted_indx, void* stream_) {
+  if (!col_sum || (n_entries > 0 && (!indx || !col_sorted_indx || !row_sorted_indx))) return TB200_ERR_BAD_ARG;
+  if (n_entries < 0 || n_cols <= 0) return TB200_ERR_BAD_ARG;
+  if (n_cols > 8192 || n_entries > INT32_MAX) return TB200_ERR_UNSUPPORTED;
+  const long long n_blocks = (n_entries + BM_BLOCK - 1) / BM_BLOCK;
+  if (n_blocks * n_cols + n_cols > (long long)TB200_STATIC_SCRATCH_INTS) return TB200_ERR_TOO_LARGE;
+  int* scratch = static_scratch_ptr();
+  if (!scratch) return TB200_ERR_CUDA;
+  return bitmatrix_metadata_launch(indx, indx_is_int16, n_entries, n_cols, col_sum, col_sorted_indx, row_sorted_indx,
+                                   scratch, static_cast<cudaStream_t>(stream_));
 }
 
 extern "C" int tb200_ragged_metadata(const tb200_ragged_metadata_args* a, void* stream_) {
