@@ -64,6 +64,32 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+template <int N>
+__device__ __forceinline__ void reg_dealloc() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void reg_alloc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+
+// 32 columns of this thread's TMEM lane into s[OFF .. OFF+31] (no wait)
+template <int OFF>
+__device__ __forceinline__ void tmem_ld_row32(uint32_t taddr, uint32_t (&s)[128]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(s[OFF + 0]), "=r"(s[OFF + 1]), "=r"(s[OFF + 2]), "=r"(s[OFF + 3]), "=r"(s[OFF + 4]), "=r"(s[OFF + 5]),
+        "=r"(s[OFF + 6]), "=r"(s[OFF + 7]), "=r"(s[OFF + 8]), "=r"(s[OFF + 9]), "=r"(s[OFF + 10]), "=r"(s[OFF + 11]),
+        "=r"(s[OFF + 12]), "=r"(s[OFF + 13]), "=r"(s[OFF + 14]), "=r"(s[OFF + 15]), "=r"(s[OFF + 16]),
+        "=r"(s[OFF + 17]), "=r"(s[OFF + 18]), "=r"(s[OFF + 19]), "=r"(s[OFF + 20]), "=r"(s[OFF + 21]),
+        "=r"(s[OFF + 22]), "=r"(s[OFF + 23]), "=r"(s[OFF + 24]), "=r"(s[OFF + 25]), "=r"(s[OFF + 26]),
+        "=r"(s[OFF + 27]), "=r"(s[OFF + 28]), "=r"(s[OFF + 29]), "=r"(s[OFF + 30]), "=r"(s[OFF + 31])
+      : "r"(taddr)
+      : "memory");
+}
+
 struct AttnTile {
   int bh, q0, nkv;
 };
@@ -134,8 +160,13 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_fwd_kernel(const __g
   const int units = p.units;
   const uint32_t smem_a = smem_u32(smem);
 
+  // Register re-partition: the load / MMA warpgroup needs few registers, the softmax warpgroups hold
+  // a whole 128-column score row per thread.
+  // (each role branch starts with its own setmaxnreg so that the instruction dominates the code it
+  // governs; the four warps of the first warpgroup all execute the same decrease)
   if (warp == 0) {
     // ------------------------------------------------------------------ loader
+    reg_dealloc<104>();
     if (lane == 0) {
       const uint64_t pol_q = policy_evict_first();
       const uint64_t pol_kv = policy_evict_last();
@@ -172,6 +203,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_fwd_kernel(const __g
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
+    reg_dealloc<104>();
     if (lane == 0) {
       const uint32_t idesc_qk = make_idesc(1u, 1u, 0u, 0u, ATT_BM, ATT_BN);  // bf16 x bf16, both K-major
       const uint32_t idesc_pv = make_idesc(1u, 1u, 0u, 1u, ATT_BM, D);       // B (= V) MN-major
@@ -268,8 +300,11 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_fwd_kernel(const __g
         }
       }
     }
-  } else if (warp >= 4) {
+  } else if (warp < 4) {
+    reg_dealloc<104>();  // warps 2 and 3 only take part in the warpgroup-wide register release
+  } else {
     // ------------------------------------------------------------------ softmax / correction / epilogue
+    reg_alloc<192>();
     const int g = (warp - 4) >> 2;
     const int q = warp & 3;
     const int row_in_group = q * 32 + lane;
@@ -292,23 +327,27 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_fwd_kernel(const __g
         // a block needs masking when it crosses the causal diagonal of this group or the KV tail
         const bool need_mask = (k0 + ATT_BN > s_kv) || (causal && (k0 + ATT_BN - 1 > t.q0 + g * ATT_BM));
         const int limit = causal ? min(s_kv - 1, qrow) : (s_kv - 1);  // last visible column
-        // ---- pass 1: row max
-        float mx = -INFINITY;
-#pragma unroll 1
-        for (int c = 0; c < ATT_BN; c += 32) {
-          uint32_t v[32];
-          tmem_ld_32x32b_x32(t_s + c, v);
-          tmem_ld_wait();
-          if (need_mask) {
+        // ---- the whole score row of this thread in registers: four loads in flight, one wait
+        uint32_t sv[128];
+        tmem_ld_row32<0>(t_s, sv);
+        tmem_ld_row32<32>(t_s + 32, sv);
+        tmem_ld_row32<64>(t_s + 64, sv);
+        tmem_ld_row32<96>(t_s + 96, sv);
+        tmem_ld_wait();
+        if (need_mask) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (k0 + c + i <= limit) mx = fmaxf(mx, __uint_as_float(v[i]));
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
-          }
+          for (int i = 0; i < 128; ++i)
+            if (k0 + i > limit) sv[i] = 0xff800000u;  // -inf: contributes exp2(-inf) = 0
         }
-        const float m_blk = mx * scale;  // scale > 0
+        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < 128; i += 4) {
+          mx0 = fmaxf(mx0, __uint_as_float(sv[i]));
+          mx1 = fmaxf(mx1, __uint_as_float(sv[i + 1]));
+          mx2 = fmaxf(mx2, __uint_as_float(sv[i + 2]));
+          mx3 = fmaxf(mx3, __uint_as_float(sv[i + 3]));
+        }
+        const float m_blk = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale;  // scale > 0
         float alpha = 1.f;
         if (j == 0) {
           m = m_blk;
@@ -332,28 +371,24 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_fwd_kernel(const __g
           }
           tmem_st_wait();
         }
-        // ---- pass 2: P = exp2(S * scale - m), row sum, bf16 into the first half of S's columns
+        // ---- P = exp2(S * scale - m), row sum, packed 16-bit into the first half of S's columns
         const float neg_m = -m;
-        float sum = 0.f;
-#pragma unroll 1
-        for (int c = 0; c < ATT_BN; c += 32) {
-          uint32_t v[32];
-          tmem_ld_32x32b_x32(t_s + c, v);
-          tmem_ld_wait();
+        float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+        for (int c = 0; c < 128; c += 32) {
           uint32_t pk[16];
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
-            float e0 = fast_exp2(fmaf(__uint_as_float(v[i]), scale, neg_m));
-            float e1 = fast_exp2(fmaf(__uint_as_float(v[i + 1]), scale, neg_m));
-            if (need_mask) {
-              if (k0 + c + i > limit) e0 = 0.f;
-              if (k0 + c + i + 1 > limit) e1 = 0.f;
-            }
-            sum += e0 + e1;
+            const float x0 = fmaf(__uint_as_float(sv[c + i]), scale, neg_m);
+            const float x1 = fmaf(__uint_as_float(sv[c + i + 1]), scale, neg_m);
+            const float e0 = fast_exp2(x0), e1 = fast_exp2(x1);
+            sum0 += e0;
+            sum1 += e1;
             pk[i >> 1] = p.out_f16 ? pack_f16x2(e0, e1) : pack_bf16x2(e0, e1);
           }
           tmem_st_32x32b_x16(t_s + (c >> 1), pk);
         }
+        const float sum = sum0 + sum1;
         l += sum;
         tmem_st_wait();
         tc_fence_before_sync();
