@@ -6,7 +6,11 @@
 //   warp 0       TMA loads: Q0, Q1 once per tile; K(j), V(j) through a 4-deep ring.
 //   warp 1       one thread issues every tcgen05.mma, in the fixed order
 //                QK0(0) QK1(0) | PV0(j) QK0(j+1) PV1(j) QK1(j+1) | ...   so that while one group's
-//                softmax runs the tensor pipe works for the other group.
+//                softmax runs the tensor pipe works for the other group. PV_g(j) goes out in four
+//                slices as the softmax publishes P in 32-column chunks, overlapping its tail.
+//                (Measured alternatives that lost: one issuing thread per group, 715 vs 900
+//                TFLOP/s - MMAs of two streams interleave one by one; a Cody-Waite + cubic exp2
+//                on the FMA pipe for 25-50 % of the elements, 5-20 % slower - issue-bound.)
 //                S_g = Q_g K^T : SS MMA, 128 x 128 x D.    O_g += P_g V : TS MMA, P read from TMEM,
 //                V is the MN-major B operand straight from its row-major tile.
 //   warps 4-7    softmax + correction + epilogue for group 0;  warps 8-11 the same for group 1.
@@ -54,7 +58,7 @@ struct AttnSmem {
   static constexpr int Q_OFFSET = 0;
   static constexpr int KV_OFFSET = 2 * TILE_BYTES;
   static constexpr int BAR_OFFSET = KV_OFFSET + ATT_KV_STAGES * TILE_BYTES;
-  static constexpr int NUM_BARS = 4 + 2 * ATT_KV_STAGES + 8;
+  static constexpr int NUM_BARS = 4 + 2 * ATT_KV_STAGES + 14;
   static constexpr int TOTAL = BAR_OFFSET + NUM_BARS * 8 + 16 + 1024;
 };
 
@@ -62,6 +66,26 @@ __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+// packed f32x2 arithmetic (two fp32 lanes in one 64-bit register, one issue slot)
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
 }
 
 template <int N>
@@ -122,8 +146,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_fwd_kernel(const __g
   uint64_t* kv_full = bars + 4;                 // [KV]
   uint64_t* kv_empty = kv_full + ATT_KV_STAGES; // [KV]
   uint64_t* s_full = kv_empty + ATT_KV_STAGES;  // [2] MMA -> softmax: S_g ready
-  uint64_t* p_full = s_full + 2;                // [2] softmax -> MMA: P_g written (128 arrivals)
-  uint64_t* pv_done = p_full + 2;               // [2] MMA -> softmax: PV_g complete
+  uint64_t* p_full = s_full + 2;                // [2][4] softmax -> MMA: 32-column chunk c of P_g written (128 arrivals)
+  uint64_t* pv_done = p_full + 8;               // [2] MMA -> softmax: PV_g complete
   uint64_t* o_free = pv_done + 2;               // [2] softmax -> MMA: O_g read out (128 arrivals)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_free + 2);
 
@@ -138,7 +162,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_fwd_kernel(const __g
       mbar_init(&q_full[i], 1);
       mbar_init(&q_empty[i], 1);
       mbar_init(&s_full[i], 1);
-      mbar_init(&p_full[i], 128);
+      for (int c = 0; c < 4; ++c) mbar_init(&p_full[i * 4 + c], 128);
       mbar_init(&pv_done[i], 1);
       mbar_init(&o_free[i], 128);
     }
@@ -228,15 +252,22 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_fwd_kernel(const __g
         }
         umma_commit(&s_full[g]);
       };
-      auto issue_pv = [&](int g, uint32_t vstage, uint32_t accum) {
+      // PV_g in four slices: slice c (two MMAs, 32 kv rows) goes out as soon as the softmax has
+      // published chunk c of P_g, so the MMA overlaps the tail of the softmax
+      auto issue_pv = [&](int g, uint32_t vstage, uint32_t accum, uint32_t iph) -> bool {
         const uint64_t vd = vdesc0 + (uint64_t)((vstage * L::TILE_BYTES) >> 4);
         const uint32_t d_o = tmem_base + O_COL0 + g * D;
         const uint32_t a_p = tmem_base + g * S_COLS;
 #pragma unroll
-        for (int k = 0; k < ATT_BN / 16; ++k) {
-          umma_f16_ts(d_o, a_p + k * 8, vd + (uint64_t)((k * 16 * 128) >> 4), idp, (k > 0) ? 1u : accum);
+        for (int c = 0; c < 4; ++c) {
+          if (!mbar_wait(&p_full[g * 4 + c], iph, status, WAIT_ATTN)) return false;
+          tc_fence_after_sync();
+#pragma unroll
+          for (int k = 2 * c; k < 2 * c + 2; ++k)
+            umma_f16_ts(d_o, a_p + k * 8, vd + (uint64_t)((k * 16 * 128) >> 4), idp, (k > 0) ? 1u : accum);
         }
         umma_commit(&pv_done[g]);
+        return true;
       };
       auto advance = [&]() {
         if (++kvs == ATT_KV_STAGES) {
@@ -277,9 +308,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_fwd_kernel(const __g
           // PV0(j)
           if (!mbar_wait(&kv_full[vcur], vcur_ph, status, WAIT_SMEM_FULL)) { ok = false; break; }
           if (j == 0 && !mbar_wait(&o_free[0], tph ^ 1, status, WAIT_ATTN)) { ok = false; break; }
-          if (!mbar_wait(&p_full[0], iph, status, WAIT_ATTN)) { ok = false; break; }
-          tc_fence_after_sync();
-          issue_pv(0, vcur, j > 0 ? 1u : 0u);
+          if (!issue_pv(0, vcur, j > 0 ? 1u : 0u, iph)) { ok = false; break; }
           if (more) {
             if (!mbar_wait(&kv_full[knext], knext_ph, status, WAIT_SMEM_FULL)) { ok = false; break; }
             tc_fence_after_sync();
@@ -288,9 +317,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_fwd_kernel(const __g
           }
           // PV1(j)
           if (j == 0 && !mbar_wait(&o_free[1], tph ^ 1, status, WAIT_ATTN)) { ok = false; break; }
-          if (!mbar_wait(&p_full[1], iph, status, WAIT_ATTN)) { ok = false; break; }
-          tc_fence_after_sync();
-          issue_pv(1, vcur, j > 0 ? 1u : 0u);
+          if (!issue_pv(1, vcur, j > 0 ? 1u : 0u, iph)) { ok = false; break; }
           umma_commit(&kv_empty[vcur]);
           if (more) {
             issue_qk(1, knext);
@@ -372,27 +399,36 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_fwd_kernel(const __g
           tmem_st_wait();
         }
         // ---- P = exp2(S * scale - m), row sum, packed 16-bit into the first half of S's columns
-        const float neg_m = -m;
-        float sum0 = 0.f, sum1 = 0.f;
+        const uint64_t scale2 = pack2(scale, scale);
+        const uint64_t negm2 = pack2(-m, -m);
+        uint64_t sum2 = pack2(0.f, 0.f);
 #pragma unroll
         for (int c = 0; c < 128; c += 32) {
           uint32_t pk[16];
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
-            const float x0 = fmaf(__uint_as_float(sv[c + i]), scale, neg_m);
-            const float x1 = fmaf(__uint_as_float(sv[c + i + 1]), scale, neg_m);
+            const uint64_t x = fma2(pack2(__uint_as_float(sv[c + i]), __uint_as_float(sv[c + i + 1])), scale2, negm2);
+            float x0, x1;
+            unpack2(x, x0, x1);
             const float e0 = fast_exp2(x0), e1 = fast_exp2(x1);
-            sum0 += e0;
-            sum1 += e1;
+            sum2 = add2(sum2, pack2(e0, e1));
             pk[i >> 1] = p.out_f16 ? pack_f16x2(e0, e1) : pack_bf16x2(e0, e1);
+          }
+          if (c > 0) {
+            // the previous chunk's store has had this chunk's arithmetic to land: publish it
+            tmem_st_wait();
+            tc_fence_before_sync();
+            mbar_arrive(&p_full[g * 4 + (c >> 5) - 1]);
           }
           tmem_st_32x32b_x16(t_s + (c >> 1), pk);
         }
-        const float sum = sum0 + sum1;
+        float sum_lo, sum_hi;
+        unpack2(sum2, sum_lo, sum_hi);
+        const float sum = sum_lo + sum_hi;
         l += sum;
         tmem_st_wait();
         tc_fence_before_sync();
-        mbar_arrive(&p_full[g]);
+        mbar_arrive(&p_full[g * 4 + 3]);
       }
       if (!ok) break;
       // ---- epilogue: wait for the last PV_g, normalise, store O and the base-2 LSE
