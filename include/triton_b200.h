@@ -112,7 +112,8 @@ size_t tb200_gemm_workspace_bytes(const tb200_gemm_args* args);
  *   reshapes to [1, rows/128, K/128, 2, 256] (:1038-1041): atom (row/128, k/128), byte
  *   (row%32)*16 + (row/32%4)*4 + (k/32)%4.
  * M, N and K must be multiples of 128 (as the reference asserts, :1167-1168); all four input
- * pointers 16-byte aligned. block_n: 0 = choose, else 128 or 256.
+ * pointers 16-byte aligned. block_n: 0 = choose; 128 or 256 = one CTA per 128 x block_n tile;
+ * 512 = CTA pair per 256 x 256 tile.
  */
 typedef struct {
   const void* a;

@@ -414,6 +414,21 @@ __device__ __forceinline__ void umma_f8_ss_pair(uint32_t tmem_d, uint64_t adesc,
       ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// CTA-pair forms of the block-scaled MMA and of the scale copy (issued by the leader for both CTAs)
+__device__ __forceinline__ void umma_mxf8_ss_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                  uint32_t tmem_sfa, uint32_t tmem_sfb, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t"
+      "}\n"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_cp_32x128b_warpx4_pair(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
 // Arrives (once) on the mbarrier at a shared::cluster address when all prior tcgen05 ops of this
 // thread, in both CTAs of the pair, have completed.
 __device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
