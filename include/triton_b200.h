@@ -62,7 +62,7 @@ int tb200_last_status_code(void);
  * Stands behind: third_party/tlx/tutorials/blackwell_gemm_ws.py:1486  matmul(a, b, config=None)
  *   (kernel matmul_kernel_tma_ws_blackwell :1168, split-K reduction _reduce_k_kernel :1098)
  * and, with dtype TB200_E4M3 and scale pointers, behind
- *   third_party/tlx/tutorials/blackwell_scaled_mm_ws.py:392  blackwell_scaled_mm_ws(..., scale_mode="tensorwise").
+ *   third_party/tlx/tutorials/blackwell_scaled_mm_ws.py:392  blackwell_scaled_mm_ws(..., scale_mode="tensorwise" | "rowwise").
  *
  * a_k_major = 1: A stored [M,K] with K contiguous (row-major), lda = elements between rows.
  * a_k_major = 0: A stored [K,M] with M contiguous (column-major A), lda = elements between k rows.
@@ -95,6 +95,8 @@ typedef struct {
   size_t workspace_bytes;
   const float* scale_a;
   const float* scale_b;
+  int32_t scale_mode; /* 0: scale_a / scale_b point to one float each (tensorwise); 1: rowwise, scale_a is float[M] (per row of A), scale_b float[N] (per row of B): C[m,n] = acc * scale_a[m] * scale_b[n] */
+  int32_t reserved;
 } tb200_gemm_args;
 
 int tb200_gemm(const tb200_gemm_args* args, void* stream);

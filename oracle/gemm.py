@@ -21,3 +21,10 @@ def scaled_mm_tensorwise_ref(a, b, scale_a, scale_b, out_dtype=torch.bfloat16):
     af, bf = a.detach().cpu().float(), b.detach().cpu().float()
     prod = af @ bf.t()
     return (prod * scale_a.detach().cpu().float().reshape(()) * scale_b.detach().cpu().float().reshape(())).to(out_dtype)
+
+
+def scaled_mm_rowwise_ref(a, b, scale_a, scale_b, out_dtype=torch.bfloat16):
+    """a (M, K), b (N, K) fp8; scale_a [M], scale_b [N]: out = (a @ b.T) * scale_a[:, None] * scale_b[None, :]
+    (ScaledMM.get_reference, rowwise branch, test_correctness.py:548-551)."""
+    prod = a.detach().cpu().float() @ b.detach().cpu().float().t()
+    return (prod * scale_a.detach().cpu().float()[:, None] * scale_b.detach().cpu().float()[None, :]).to(out_dtype)

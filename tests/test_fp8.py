@@ -27,12 +27,27 @@ def test_scaled_mm_tensorwise(cuda, shape, num_ctas):
     torch.testing.assert_close(out.cpu().float(), ref.float(), atol=1e-3, rtol=1e-2)
 
 
+@pytest.mark.parametrize("shape", [(1024, 1024, 1024), (384, 256, 640)])
+def test_scaled_mm_rowwise(cuda, shape):
+    """out[m, n] = (a @ b.T)[m, n] * scale_a[m] * scale_b[n] — ScaledMM.get_reference, rowwise branch
+    (test_correctness.py:548-551)."""
+    from triton_b200.tutorials.blackwell_scaled_mm_ws import blackwell_scaled_mm_ws
+    M, N, K = shape
+    torch.manual_seed(0)
+    a = (torch.randn(M, K) * 0.1).to(torch.float8_e4m3fn)
+    b = (torch.randn(N, K) * 0.1).to(torch.float8_e4m3fn)
+    sa, sb = torch.rand(M), torch.rand(N)
+    out = blackwell_scaled_mm_ws(a.to(cuda), b.to(cuda), sa.to(cuda), sb.to(cuda), scale_mode="rowwise")
+    ref = o_gemm.scaled_mm_rowwise_ref(a, b, sa, sb)
+    torch.testing.assert_close(out.cpu().float(), ref.float(), atol=1e-3, rtol=1e-2)
+
+
 def test_scaled_mm_other_modes_raise(cuda):
     from triton_b200.tutorials.blackwell_scaled_mm_ws import blackwell_scaled_mm_ws
     a = torch.zeros(128, 128, device=cuda).to(torch.float8_e4m3fn)
     s = torch.ones(1, device=cuda)
     with pytest.raises(NotImplementedError):
-        blackwell_scaled_mm_ws(a, a, s, s, scale_mode="rowwise")
+        blackwell_scaled_mm_ws(a, a, s, s, scale_mode="blockwise")
     with pytest.raises(AssertionError):
         blackwell_scaled_mm_ws(a[:, :64].contiguous(), a[:, :64].contiguous(), s, s, scale_mode="tensorwise")
 

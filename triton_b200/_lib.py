@@ -33,6 +33,7 @@ class GemmArgs(Structure):
         ("split_k", c_int32), ("block_n", c_int32),
         ("workspace", c_void_p), ("workspace_bytes", c_size_t),
         ("scale_a", c_void_p), ("scale_b", c_void_p),
+        ("scale_mode", c_int32), ("reserved", c_int32),
     ]
 
 

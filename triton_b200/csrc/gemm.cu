@@ -66,6 +66,7 @@ struct GemmParams {
   int bk_elems;  // K elements per stage
   int group_m;
   int out_mode;  // 0 bf16, 1 fp16, 2 fp32 to c, 3 fp32 partial to ws
+  int scale_mode;  // 0: scale_a / scale_b are scalars; 1: per-row (M) and per-column (N) vectors
   uint32_t idesc;
   OperandGeom ga, gb;
 };
@@ -281,9 +282,14 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const __grid_cons
   } else {
     // ------------------------------------------------------------- epilogue
     const int q = warp & 3;  // TMEM lane quarter this warp may read
+    const bool rowwise = p.scale_mode == 1;
     float alpha = 1.0f;
-    if (p.scale_a) alpha *= __ldg(p.scale_a);
-    if (p.scale_b) alpha *= __ldg(p.scale_b);
+    if (!rowwise) {
+      if (p.scale_a) alpha *= __ldg(p.scale_a);
+      if (p.scale_b) alpha *= __ldg(p.scale_b);
+    }
+    const float* const row_scale = rowwise ? p.scale_a : nullptr;
+    const float* const col_scale = rowwise ? p.scale_b : nullptr;
     void* const c = p.c;
     float* const ws = p.ws;
     const long long ldc = p.ldc;
@@ -303,12 +309,13 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const __grid_cons
       tc_fence_after_sync();
       const int row = m0 + q * 32 + lane;
       const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + acc * BN;
+      if (row_scale) alpha = row < m ? __ldg(row_scale + row) : 0.f;
 #pragma unroll 1
       for (int cc = 0; cc < BN; cc += 32) {
         uint32_t v[32];
         tmem_ld_32x32b_x32(taddr + cc, v);
         tmem_ld_wait();
-        store_chunk(c, ws, ldc, m, n, out_mode, v, row, n0 + cc, t.ks, alpha);
+        store_chunk(c, ws, ldc, m, n, out_mode, v, row, n0 + cc, t.ks, alpha, col_scale);
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -599,6 +606,9 @@ extern "C" int tb200_gemm(const tb200_gemm_args* a, void* stream_) {
   p.group_m = 8;
   p.scale_a = a->scale_a;
   p.scale_b = a->scale_b;
+  p.scale_mode = a->scale_mode;
+  if (a->scale_mode == 1 && (!a->scale_a || !a->scale_b)) return TB200_ERR_BAD_ARG;
+  if (a->scale_mode != 0 && a->scale_mode != 1) return TB200_ERR_UNSUPPORTED;
   p.status = status_ptr();
   if (!p.status) return TB200_ERR_CUDA;
   const int final_mode = a->out_dtype == TB200_BF16 ? 0 : (a->out_dtype == TB200_F16 ? 1 : 2);

@@ -24,9 +24,15 @@ __device__ __forceinline__ TileCoord unit_to_tile(int unit, int split_k, int gro
 
 // Writes 32 consecutive columns of one output row (fp32 accumulators in v) in the output mode.
 __device__ __forceinline__ void store_chunk(void* c, float* ws, long long ldc, int m, int n, int out_mode,
-                                            const uint32_t (&v)[32], int row, int col, int ks, float alpha) {
+                                            uint32_t (&v)[32], int row, int col, int ks, float alpha,
+                                            const float* col_scale = nullptr) {
   if (row >= m || col >= n) return;
   const bool full = col + 32 <= n;
+  if (col_scale) {  // per-column factors (row-wise scaled GEMM); alpha then carries the row's factor
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (full || col + j < n) v[j] = __float_as_uint(__uint_as_float(v[j]) * __ldg(col_scale + col + j));
+  }
   if (out_mode <= 1) {
     uint16_t* dst = reinterpret_cast<uint16_t*>(c) + (long long)row * ldc + col;
     if (full && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {

@@ -2,8 +2,9 @@
 scaled matmul, ``third_party/tlx/tutorials/blackwell_scaled_mm_ws.py:392``.
 
 ``a`` [M, K] and ``b`` [N, K] are ``float8_e4m3fn`` (row-major; computes ``A @ B^T``), the result is
-``out_dtype`` (bf16 by default). ``scale_mode="tensorwise"`` (one fp32 scalar per operand, applied
-once after the K loop) is the mode built here; ``"blockwise"`` and ``"rowwise"`` raise
+``out_dtype`` (bf16 by default). ``scale_mode="tensorwise"`` (one fp32 scalar per operand) and
+``"rowwise"`` (``scale_a`` [M] per row of A, ``scale_b`` [N] per row of B), both applied once after the
+K loop, are built here; ``"blockwise"`` (128-wide K groups promoted in registers) raises
 ``NotImplementedError``. The tiling arguments (``BLOCK_M``, ``BLOCK_N``, ``NUM_CTAS``, ``USE_CLC``,
 ``EPI_SUB``, ``persistent``) are accepted for call compatibility; the kernel picks its own tiling
 (``NUM_CTAS=2`` forces the CTA-pair tiling). Same shape assertions as the reference (``:408``).
@@ -24,8 +25,8 @@ def blackwell_scaled_mm_ws(a, b, scale_a, scale_b, out_dtype=torch.bfloat16, BLO
                            USE_CLC=False, EPI_SUB=2, persistent=True, scale_mode="blockwise"):
     if scale_mode not in ("blockwise", "rowwise", "tensorwise"):
         raise KeyError(scale_mode)
-    if scale_mode != "tensorwise":
-        raise NotImplementedError(f"scale_mode={scale_mode!r}: only 'tensorwise' is implemented")
+    if scale_mode == "blockwise":
+        raise NotImplementedError("scale_mode='blockwise' is not implemented ('tensorwise' and 'rowwise' are)")
     if not a.is_cuda:
         raise RuntimeError("blackwell_scaled_mm_ws needs CUDA tensors (there is no CPU path)")
     M, K = a.shape
@@ -37,8 +38,12 @@ def blackwell_scaled_mm_ws(a, b, scale_a, scale_b, out_dtype=torch.bfloat16, BLO
     b = b.contiguous()
     scale_a = scale_a.reshape(-1).contiguous().to(torch.float32)
     scale_b = scale_b.reshape(-1).contiguous().to(torch.float32)
-    assert scale_a.numel() == 1 and scale_b.numel() == 1, (
-        f"tensorwise expects scalar scale_a/scale_b; got {scale_a.numel()}, {scale_b.numel()}")
+    if scale_mode == "rowwise":
+        assert scale_a.numel() == M and scale_b.numel() == N, (
+            f"rowwise expects scale_a [M]={M}, scale_b [N]={N}; got {scale_a.numel()}, {scale_b.numel()}")
+    else:
+        assert scale_a.numel() == 1 and scale_b.numel() == 1, (
+            f"tensorwise expects scalar scale_a/scale_b; got {scale_a.numel()}, {scale_b.numel()}")
     c = torch.empty((M, N), dtype=out_dtype, device=a.device)
     if M == 0:
         return c
@@ -52,6 +57,7 @@ def blackwell_scaled_mm_ws(a, b, scale_a, scale_b, out_dtype=torch.bfloat16, BLO
     args.split_k = 1
     args.block_n = 512 if NUM_CTAS == 2 else 0
     args.scale_a, args.scale_b = scale_a.data_ptr(), scale_b.data_ptr()
+    args.scale_mode = 1 if scale_mode == "rowwise" else 0
     with torch.cuda.device(a.device):
         rc = _lib.lib().tb200_gemm(ctypes.byref(args), ctypes.c_void_p(_lib.current_stream_ptr(a.device)))
     _lib.check(rc, "tb200_gemm")
