@@ -332,7 +332,7 @@ typedef struct {
   float swiglu_alpha;
   float swiglu_limit;
   int32_t swiglu_has_limit;
-  int32_t reserved;
+  int32_t moe_tile_mode; /* 0 = choose; 1 = one CTA per 128-row block; 2 = CTA pair per two consecutive blocks */
   const int32_t* slice_sizes; /* optional int32 [E]: rows of expert e (needed for remapped metadata, whose slice_offs are not cumulative); NULL = slice_offs[e+1] - slice_offs[e] */
 } tb200_moe_gemm_args;
 int tb200_moe_gemm(const tb200_moe_gemm_args* args, void* stream);

@@ -100,7 +100,7 @@ class MoeGemmArgs(Structure):
         ("n_experts", c_int64), ("k", c_int64), ("n", c_int64),
         ("rows_x", c_int64), ("rows_y", c_int64), ("ldx", c_int64), ("ldy", c_int64),
         ("n_sched", c_int32), ("w_n_major", c_int32), ("dtype", c_int32), ("swiglu", c_int32),
-        ("swiglu_alpha", c_float), ("swiglu_limit", c_float), ("swiglu_has_limit", c_int32), ("reserved", c_int32),
+        ("swiglu_alpha", c_float), ("swiglu_limit", c_float), ("swiglu_has_limit", c_int32), ("moe_tile_mode", c_int32),
         ("slice_sizes", c_void_p),
     ]
 

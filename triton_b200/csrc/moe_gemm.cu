@@ -29,10 +29,8 @@
 namespace tb200 {
 
 static constexpr int MOE_THREADS = 320;  // TMA warp, MMA warp, 4 epilogue warps, 4 gather warps
-static constexpr int MOE_GATHER_LOOKAHEAD = 2;  // K steps a gather warp keeps in flight (< stages)
 static constexpr int MOE_BM = 128;
 static constexpr int MOE_BN = 256;
-static constexpr int MOE_STAGES = 4;
 
 struct MoeParams {
   CUtensorMap tmx_tile;  // X: (K, rows_x), box (64, 128): contiguous-row source (no gather)
@@ -57,14 +55,6 @@ struct MoeParams {
   uint32_t idesc;
 };
 
-struct MoeSmem {
-  static constexpr int A_BYTES = MOE_BM * 128;
-  static constexpr int B_BYTES = MOE_BN * 128;
-  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int BAR_OFFSET = MOE_STAGES * STAGE_BYTES;
-  static constexpr int TOTAL = BAR_OFFSET + (2 * MOE_STAGES + 4) * 8 + 16 + 1024;
-};
-
 // 16-byte asynchronous copy global -> shared (LDGSTS); src_bytes = 0 writes zeros.
 __device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, uint32_t src_bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
@@ -83,6 +73,15 @@ __device__ __forceinline__ void tma_load_3d_a(uint32_t dst, const CUtensorMap* t
       : "memory");
 }
 
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* tmap, uint32_t bar_cluster_addr, int x,
+                                                 int y, int z, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%3, %4, %5}], [%2], %6;"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar_cluster_addr), "r"(x), "r"(y), "r"(z), "l"(policy)
+      : "memory");
+}
+
 __device__ __forceinline__ float moe_swiglu(float g, float l, float alpha, float limit, int has_limit) {
   if (has_limit) {
     g = fminf(g, limit);
@@ -91,10 +90,28 @@ __device__ __forceinline__ float moe_swiglu(float g, float l, float alpha, float
   return g / (1.f + __expf(-alpha * g)) * (l + 1.f);
 }
 
+// BNC = W rows (N) staged per CTA. Single: 128 x 256 tile per CTA, 4 stages. Pair: a 2-CTA cluster
+// shares a 256-row x 256-column tile (two consecutive 128-row blocks of one expert; schedule entries
+// with an odd block index are covered by their even neighbour), CTA r stages rows block+r of A
+// and W rows [n0 + 128 r, +128), the leader issues tcgen05.mma.cta_group::2: 32 KB per K step per
+// CTA instead of 48 KB and a 6-deep ring.
+template <bool PAIR>
+struct MoeCfg {
+  static constexpr int BNC = PAIR ? 128 : 256;
+  static constexpr int STAGES = PAIR ? 6 : 4;
+  static constexpr int A_BYTES = MOE_BM * 128;
+  static constexpr int B_BYTES = BNC * 128;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 4) * 8 + 16 + 1024;
+  static constexpr int LOOKAHEAD = PAIR ? 3 : 2;  // K steps a gather warp keeps in flight (< stages)
+};
+
+template <bool PAIR>
 __global__ void __launch_bounds__(MOE_THREADS, 1) moe_gemm_kernel(const __grid_constant__ MoeParams p) {
-  using L = MoeSmem;
+  using L = MoeCfg<PAIR>;
   constexpr int BN = MOE_BN;
-  constexpr int STAGES = MOE_STAGES;
+  constexpr int STAGES = L::STAGES;
   constexpr uint32_t TMEM_COLS = 512;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -106,26 +123,36 @@ __global__ void __launch_bounds__(MOE_THREADS, 1) moe_gemm_kernel(const __grid_c
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
+  const int worker = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int num_workers = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+  const bool gathered = p.gather != nullptr;
 
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&p.tmx_tile);
     tma_prefetch_desc(&p.tmw);
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&full[s], p.gather ? 5 : 1);  // B's expect_tx arrival (+ one per gather warp)
+      // the expect_tx arrival, plus one arrival per gather warp (of both CTAs in pair mode)
+      mbar_init(&full[s], gathered ? (PAIR ? 9 : 5) : 1);
       mbar_init(&empty[s], 1);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&tfull[i], 1);
-      mbar_init(&tempty[i], 4);
+      mbar_init(&tempty[i], PAIR ? 8 : 4);
     }
     mbar_init_fence();
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, TMEM_COLS);
-    tmem_relinquish();
+    if constexpr (PAIR) {
+      tmem_alloc_pair(tmem_slot, TMEM_COLS);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(tmem_slot, TMEM_COLS);
+      tmem_relinquish();
+    }
   }
   tc_fence_before_sync();
-  __syncthreads();
+  if constexpr (PAIR) cluster_sync_all(); else __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
 
@@ -136,42 +163,52 @@ __global__ void __launch_bounds__(MOE_THREADS, 1) moe_gemm_kernel(const __grid_c
   int* const status = p.status;
   const uint32_t smem_a = smem_u32(smem);
   const uint32_t full_a = smem_u32(full), empty_a = smem_u32(empty);
+  const uint32_t leader_full = PAIR ? mapa_shared(full_a, 0) : full_a;
+
+  // A schedule entry is worked on iff it is valid and (pair mode) names an even block.
+  auto entry_active = [&](int entry) -> bool { return entry >= 0 && (!PAIR || (((entry >> 16) & 1) == 0)); };
 
   if (warp == 0) {
     // ------------------------------------------------------------- TMA producer (one lane)
     if (lane == 0) {
       const uint64_t pol_x = policy_evict_normal();
       const uint64_t pol_w = policy_evict_last();
-      const bool gathered = p.gather != nullptr;
       const int w_n_major = p.w_n_major;
-      const uint32_t tx_bytes = gathered ? L::B_BYTES : L::STAGE_BYTES;
+      const uint32_t tx_bytes = (gathered ? L::B_BYTES : L::STAGE_BYTES) * (PAIR ? 2 : 1);
       uint32_t s = 0, ph = 0;
       bool ok = true;
-      for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x) {
+      for (int unit = worker; unit < units && ok; unit += num_workers) {
         const int si = unit / tiles_n;
         const int entry = __ldg(sched + si);
-        if (entry < 0) continue;
+        if (!entry_active(entry)) continue;
         const int e = entry & 0xFFFF;
-        const int n0 = (unit - si * tiles_n) * BN;
-        const int row0 = __ldg(slice_offs + e) + (entry >> 16) * MOE_BM;
+        const int n0 = (unit - si * tiles_n) * BN + (int)rank * L::BNC * (PAIR ? 1 : 0);
+        const int row0 = __ldg(slice_offs + e) + ((entry >> 16) + (int)rank) * MOE_BM;
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!mbar_wait_a(empty_a + s * 8, ph ^ 1, status, WAIT_SMEM_EMPTY)) {
             ok = false;
             break;
           }
-          const uint32_t bar = full_a + s * 8;
-          mbar_expect_tx_a(bar, tx_bytes);
+          if (rank == 0) mbar_expect_tx_a(full_a + s * 8, tx_bytes);
+          const uint32_t bar = leader_full + s * 8;
           const uint32_t sa = smem_a + s * L::STAGE_BYTES;
           const int kx = kb * 64;
           // Without a gather the sorted rows are contiguous: one tiled box (rows past the slice end
           // belong to the next expert; their products are never stored).
-          if (!gathered) tma_load_2d_a(sa, &p.tmx_tile, bar, kx, row0, pol_x);
+          if (!gathered) {
+            if constexpr (PAIR) tma_load_2d_pair(sa, &p.tmx_tile, bar, kx, row0, pol_x);
+            else tma_load_2d_a(sa, &p.tmx_tile, bar, kx, row0, pol_x);
+          }
           const uint32_t sb = sa + L::A_BYTES;
           if (w_n_major) {
 #pragma unroll
-            for (int i = 0; i < BN / 64; ++i) tma_load_3d_a(sb + i * 8192, &p.tmw, bar, n0 + i * 64, kx, e, pol_w);
+            for (int i = 0; i < L::BNC / 64; ++i) {
+              if constexpr (PAIR) tma_load_3d_pair(sb + i * 8192, &p.tmw, bar, n0 + i * 64, kx, e, pol_w);
+              else tma_load_3d_a(sb + i * 8192, &p.tmw, bar, n0 + i * 64, kx, e, pol_w);
+            }
           } else {
-            tma_load_3d_a(sb, &p.tmw, bar, kx, n0, e, pol_w);
+            if constexpr (PAIR) tma_load_3d_pair(sb, &p.tmw, bar, kx, n0, e, pol_w);
+            else tma_load_3d_a(sb, &p.tmw, bar, kx, n0, e, pol_w);
           }
           if (++s == STAGES) {
             s = 0;
@@ -185,9 +222,9 @@ __global__ void __launch_bounds__(MOE_THREADS, 1) moe_gemm_kernel(const __grid_c
     // 128 threads copy the 128 x 128-byte A tile of each K step with 16-byte LDGSTS copies straight
     // into the 128-byte-swizzled layout the MMA descriptor expects (chunk c of row r lands at
     // r * 128 + ((c ^ (r & 7)) << 4)); rows past the expert's slice are zero-filled. Each thread
-    // keeps MOE_GATHER_LOOKAHEAD K steps in flight; when a step has landed it fences the writes
-    // for the async proxy and its warp arrives on the stage's `full` barrier.
-    if (p.gather != nullptr) {
+    // keeps LOOKAHEAD K steps in flight; when a step has landed it fences the writes for the async
+    // proxy and its warp arrives on the stage's `full` barrier (the leader's, in pair mode).
+    if (gathered) {
       const int gt = threadIdx.x - 192;
       const int chunk = gt & 7, rsub = gt >> 3;
       const int* const gather = p.gather;
@@ -198,12 +235,20 @@ __global__ void __launch_bounds__(MOE_THREADS, 1) moe_gemm_kernel(const __grid_c
       uint32_t s_old = 0;          // oldest stage issued but not yet signalled
       uint32_t pending = 0;        // K steps issued but not yet signalled
       bool ok = true;
-      for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x) {
+      auto signal_oldest = [&]() {
+        if (lane == 0) {
+          if constexpr (PAIR) mbar_arrive_cluster(leader_full + s_old * 8);
+          else mbar_arrive_a(full_a + s_old * 8);
+        }
+        if (++s_old == STAGES) s_old = 0;
+        --pending;
+      };
+      for (int unit = worker; unit < units && ok; unit += num_workers) {
         const int si = unit / tiles_n;
         const int entry = __ldg(sched + si);
-        if (entry < 0) continue;
+        if (!entry_active(entry)) continue;
         const int e = entry & 0xFFFF;
-        const int row0 = __ldg(slice_offs + e) + (entry >> 16) * MOE_BM;
+        const int row0 = __ldg(slice_offs + e) + ((entry >> 16) + (int)rank) * MOE_BM;
         const int row_end = slice_sizes ? __ldg(slice_offs + e) + __ldg(slice_sizes + e) : __ldg(slice_offs + e + 1);
         const uint16_t* src[8];
         uint32_t dst_off[8];
@@ -238,13 +283,11 @@ __global__ void __launch_bounds__(MOE_THREADS, 1) moe_gemm_kernel(const __grid_c
             s = 0;
             ph ^= 1;
           }
-          if (pending > MOE_GATHER_LOOKAHEAD) {
-            cp_async_wait<MOE_GATHER_LOOKAHEAD>();
+          if (pending > L::LOOKAHEAD) {
+            cp_async_wait<L::LOOKAHEAD>();
             fence_proxy_async_smem();
             __syncwarp();
-            if (lane == 0) mbar_arrive_a(full_a + s_old * 8);
-            if (++s_old == STAGES) s_old = 0;
-            --pending;
+            signal_oldest();
           }
         }
       }
@@ -252,26 +295,35 @@ __global__ void __launch_bounds__(MOE_THREADS, 1) moe_gemm_kernel(const __grid_c
       cp_async_wait<0>();
       fence_proxy_async_smem();
       __syncwarp();
-      while (pending > 0) {
-        if (lane == 0) mbar_arrive_a(full_a + s_old * 8);
-        if (++s_old == STAGES) s_old = 0;
-        --pending;
-      }
+      while (pending > 0) signal_oldest();
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
+    if (lane == 0 && rank == 0) {
       const uint32_t idesc = p.idesc;
       const uint32_t b_lbo = p.w_n_major ? 8192u : 16u;
       const uint64_t bk = p.w_n_major ? (uint64_t)(2048 >> 4) : (uint64_t)(32 >> 4);
       const uint64_t adesc0 = make_smem_desc(smem_a, 16, 1024, SWIZZLE_128B);
       const uint64_t bdesc0 = make_smem_desc(smem_a + L::A_BYTES, b_lbo, 1024, SWIZZLE_128B);
       const uint32_t tfull_a = smem_u32(tfull), tempty_a = smem_u32(tempty);
+      const uint32_t peer_delta = PAIR ? (mapa_shared(empty_a, 1) - empty_a) : 0u;
       uint32_t s = 0, ph = 0, tcount = 0;
       bool ok = true;
-      for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x) {
+      auto mma = [&](uint32_t d, uint64_t a, uint64_t b, uint32_t acc) {
+        if constexpr (PAIR) umma_f16_ss_pair(d, a, b, idesc, acc);
+        else umma_f16_ss(d, a, b, idesc, acc);
+      };
+      auto commit = [&](uint32_t bar) {
+        if constexpr (PAIR) {
+          umma_commit_pair(bar);
+          umma_commit_pair(bar + peer_delta);
+        } else {
+          umma_commit_a(bar);
+        }
+      };
+      for (int unit = worker; unit < units && ok; unit += num_workers) {
         const int si = unit / tiles_n;
-        if (__ldg(sched + si) < 0) continue;
+        if (!entry_active(__ldg(sched + si))) continue;
         const uint32_t acc = tcount & 1;
         const uint32_t aph = (tcount >> 1) & 1;
         ++tcount;
@@ -284,11 +336,11 @@ __global__ void __launch_bounds__(MOE_THREADS, 1) moe_gemm_kernel(const __grid_c
         for (int i = 0; i < k_blocks; ++i) {
           const uint64_t ad = adesc0 + (uint64_t)(s * (L::STAGE_BYTES >> 4));
           const uint64_t bd = bdesc0 + (uint64_t)(s * (L::STAGE_BYTES >> 4));
-          umma_f16_ss(tmem_d, ad, bd, idesc, accum);
+          mma(tmem_d, ad, bd, accum);
           accum = 1u;
-          if (prev_empty) umma_commit_a(prev_empty);
+          if (prev_empty) commit(prev_empty);
           prev_empty = empty_a + s * 8;
-          umma_f16_ss(tmem_d, ad + 2, bd + bk, idesc, 1u);
+          mma(tmem_d, ad + 2, bd + bk, 1u);
           if (++s == STAGES) {
             s = 0;
             ph ^= 1;
@@ -300,16 +352,16 @@ __global__ void __launch_bounds__(MOE_THREADS, 1) moe_gemm_kernel(const __grid_c
             }
             tc_fence_after_sync();
           }
-          umma_f16_ss(tmem_d, ad + 4, bd + 2 * bk, idesc, 1u);
-          umma_f16_ss(tmem_d, ad + 6, bd + 3 * bk, idesc, 1u);
+          mma(tmem_d, ad + 4, bd + 2 * bk, 1u);
+          mma(tmem_d, ad + 6, bd + 3 * bk, 1u);
         }
         if (ok) {
-          umma_commit_a(prev_empty);
-          umma_commit_a(tfull_a + acc * 8);
+          commit(prev_empty);
+          commit(tfull_a + acc * 8);
         }
       }
     }
-  } else {
+  } else if (warp >= 2) {
     // ------------------------------------------------------------- epilogue
     const int q = warp & 3;
     const int* const scatter = p.scatter;
@@ -319,15 +371,15 @@ __global__ void __launch_bounds__(MOE_THREADS, 1) moe_gemm_kernel(const __grid_c
     const float alpha = p.alpha, limit = p.limit;
     const long long ldy = p.ldy;
     uint16_t* const y = reinterpret_cast<uint16_t*>(p.y);
-    const uint32_t tempty_a = smem_u32(tempty);
+    const uint32_t tempty_leader = PAIR ? mapa_shared(smem_u32(tempty), 0) : smem_u32(tempty);
     uint32_t tcount = 0;
-    for (int unit = blockIdx.x; unit < units; unit += gridDim.x) {
+    for (int unit = worker; unit < units; unit += num_workers) {
       const int si = unit / tiles_n;
       const int entry = __ldg(sched + si);
-      if (entry < 0) continue;
+      if (!entry_active(entry)) continue;
       const int e = entry & 0xFFFF;
       const int n0 = (unit - si * tiles_n) * BN;
-      const int row0 = __ldg(slice_offs + e) + (entry >> 16) * MOE_BM;
+      const int row0 = __ldg(slice_offs + e) + ((entry >> 16) + (int)rank) * MOE_BM;
       const int row_end = slice_sizes ? __ldg(slice_offs + e) + __ldg(slice_sizes + e) : __ldg(slice_offs + e + 1);
       const uint32_t acc = tcount & 1;
       const uint32_t aph = (tcount >> 1) & 1;
@@ -421,16 +473,44 @@ __global__ void __launch_bounds__(MOE_THREADS, 1) moe_gemm_kernel(const __grid_c
       }
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive_a(tempty_a + acc * 8);
+      if (lane == 0) {
+        if constexpr (PAIR) mbar_arrive_cluster(tempty_leader + acc * 8);
+        else mbar_arrive_a(tempty_leader + acc * 8);
+      }
     }
   }
 
   tc_fence_before_sync();
-  __syncthreads();
+  if constexpr (PAIR) cluster_sync_all(); else __syncthreads();
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, TMEM_COLS);
+    if constexpr (PAIR) tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    else tmem_dealloc(tmem_base, TMEM_COLS);
   }
+}
+
+template <bool PAIR>
+static int launch_moe(const MoeParams& p, int sms, cudaStream_t stream) {
+  using L = MoeCfg<PAIR>;
+  auto kfn = moe_gemm_kernel<PAIR>;
+  if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL) != cudaSuccess)
+    return TB200_ERR_CUDA;
+  const int workers_max = PAIR ? sms / 2 : sms;
+  const int workers = p.units < workers_max ? p.units : workers_max;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(PAIR ? 2 * workers : workers);
+  cfg.blockDim = dim3(MOE_THREADS);
+  cfg.dynamicSmemBytes = L::TOTAL;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = PAIR ? 2 : 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cuda_err(cudaLaunchKernelEx(&cfg, kfn, p));
 }
 
 }  // namespace tb200
@@ -452,6 +532,10 @@ extern "C" int tb200_moe_gemm(const tb200_moe_gemm_args* a, void* stream_) {
   const int sms = sm_count();
   if (sms <= 0) return TB200_ERR_CUDA;
 
+  // One CTA per 128-row block by default. The CTA-pair tiling is kept on request only: measured at
+  // config-5 size it gains 3 % on sorted (tiled) rows and loses 2x on gathered rows (eight remote
+  // barrier arrivals per K step from the peer's gather warps).
+  const bool pair = a->moe_tile_mode == 2;
   MoeParams p;
   memset(&p, 0, sizeof(p));
   const CUtensorMapDataType dt =
@@ -472,7 +556,7 @@ extern "C" int tb200_moe_gemm(const tb200_moe_gemm_args* a, void* stream_) {
   } else {
     const uint64_t dims[3] = {(uint64_t)a->k, (uint64_t)a->n, (uint64_t)a->n_experts};
     const uint64_t strides[2] = {(uint64_t)a->k * 2, (uint64_t)a->n * a->k * 2};
-    const uint32_t box[3] = {64, (uint32_t)MOE_BN, 1};
+    const uint32_t box[3] = {64, (uint32_t)(pair ? 128 : MOE_BN), 1};
     int rc = encode_tmap(&p.tmw, dt, 3, a->w, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != TB200_OK) return rc;
   }
@@ -506,11 +590,6 @@ extern "C" int tb200_moe_gemm(const tb200_moe_gemm_args* a, void* stream_) {
   p.limit = a->swiglu_limit;
   p.out_f16 = a->dtype == TB200_F16 ? 1 : 0;
   const uint32_t fmt = a->dtype == TB200_F16 ? 0u : 1u;
-  p.idesc = make_idesc(fmt, fmt, 0u, p.w_n_major ? 1u : 0u, MOE_BM, MOE_BN);
-  auto kfn = moe_gemm_kernel;
-  if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, MoeSmem::TOTAL) != cudaSuccess)
-    return TB200_ERR_CUDA;
-  const int grid = p.units < sms ? p.units : sms;
-  kfn<<<grid, MOE_THREADS, MoeSmem::TOTAL, stream>>>(p);
-  return cuda_err(cudaGetLastError());
+  p.idesc = make_idesc(fmt, fmt, 0u, p.w_n_major ? 1u : 0u, pair ? 256 : MOE_BM, MOE_BN);
+  return pair ? launch_moe<true>(p, sms, stream) : launch_moe<false>(p, sms, stream);
 }
