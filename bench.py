@@ -164,7 +164,7 @@ def build_workload(name: str, rank: int, dev):
             return reduce(y.view(T, k, D), dim=1)[0]
         R = T * k
         fl = 2.0 * R * D * 2 * F + 2.0 * R * F * D
-        active = min(E, R)
+        active = int((topk(logits, k).mask_metadata.col_sum > 0).sum().item())  # experts that get any row
         by = active * (D * 2 * F + F * D) * 2.0 + R * (D + F) * 2.0 + R * (F + D) * 2.0
         return (step, fl, by, f"MoE layer: {T} tokens, d_model {D}, E={E}, top-{k}, W1 [{D},{2*F}] SwiGLU W2 [{F},{D}], "
                 "gate-weighted combine, seed 4", "moe_gemm_kernel", "hbm" if name == "moe_decode" else "tensor")

@@ -83,7 +83,7 @@ def test_remap_ragged_metadata(cuda):
     assert np.array_equal(got.block_schedule_data.cpu().numpy(), ref.block_schedule_data)
 
 
-def _moe_layer(cuda, T, D, F, E, k, w_layout="n", gate=True, alpha=1.0, limit=None, bias=False, seed=4):
+def _moe_layer(cuda, T, D, F, E, k, w_layout="n", gate=True, alpha=1.0, limit=None, bias=False, seed=4, tile_mode=0):
     from triton_b200.triton_kernels.matmul import matmul, swiglu_activation
     from triton_b200.triton_kernels.reduce import reduce
     from triton_b200.triton_kernels.tensor import make_ragged_tensor_metadata
@@ -104,9 +104,9 @@ def _moe_layer(cuda, T, D, F, E, k, w_layout="n", gate=True, alpha=1.0, limit=No
     combine = mm.col_sorted_indx
     gather = torch.div(combine, k, rounding_mode="trunc")
     h = matmul(xd, w1d, None if b1 is None else b1.to(cuda), rg, gather_indx=gather,
-               fused_activation=swiglu_activation(alpha, limit))
+               fused_activation=swiglu_activation(alpha, limit), _tile_mode=tile_mode)
     gam = sm.vals.float().reshape(-1)[combine.long()] if gate else None
-    y = matmul(h, w2d, None, rg, scatter_indx=combine, gammas=gam)
+    y = matmul(h, w2d, None, rg, scatter_indx=combine, gammas=gam, _tile_mode=tile_mode)
     out, _ = reduce(y.view(T, k, D), dim=1)
     vals, indx, _ = o.topk_ref(logits, k)
     md = o.bitmatrix_metadata_ref(indx.numpy(), E)
@@ -121,6 +121,13 @@ def _moe_layer(cuda, T, D, F, E, k, w_layout="n", gate=True, alpha=1.0, limit=No
 @pytest.mark.parametrize("w_layout", ["n", "k"])
 def test_moe_layer_small(cuda, w_layout):
     _moe_layer(cuda, 64, 256, 128, 8, 2, w_layout=w_layout)
+
+
+@pytest.mark.parametrize("w_layout", ["n", "k"])
+def test_moe_layer_cta_pair_tiling(cuda, w_layout):
+    """The 2-CTA (256-row) tiling: experts with odd block counts, empty experts, both weight layouts."""
+    _moe_layer(cuda, 700, 512, 256, 8, 2, w_layout=w_layout, tile_mode=2)
+    _moe_layer(cuda, 96, 512, 256, 128, 4, w_layout=w_layout, tile_mode=2)
 
 
 def test_moe_layer_ragged_dims_bias_limit(cuda):
