@@ -190,6 +190,11 @@ def build_workload(name: str, rank: int, dev):
     raise SystemExit(f"unknown workload {name}")
 
 
+# Kernels of this library launched per step: the MoE layer runs topk, three bitmatrix-metadata kernels,
+# the ragged-metadata kernel, two grouped GEMMs and the top-k reduce (the EP variant adds four row moves).
+OWN_LAUNCHES_PER_STEP = {"moe": 8, "moe_decode": 8, "moe_ep": 12}
+
+
 def run_extra_workload(args, rank, local_rank, world):
     """Times one of the non-headline workloads on each rank (independent replicas of the sharded
     unit: (batch, head) groups for attention, N blocks for GEMMs, expert groups for MoE) and prints
@@ -242,7 +247,7 @@ def run_extra_workload(args, rank, local_rank, world):
             "roofline": {"bound": bound, "achieved": ach, "peak": peak, "unit": unit, "frac": ach / peak,
                          "traffic": None, "kernel": kernel,
                          "peak_kind": ("copy bandwidth" if bound == "hbm" else "burst cuBLAS bf16") + ", " + peaks["source"]},
-            "gpu_launches": None, "clocks": clocks}))
+            "gpu_launches": steps * world * OWN_LAUNCHES_PER_STEP.get(args.workload, 1), "clocks": clocks}))
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
