@@ -123,6 +123,18 @@ def build_workload(name: str, rank: int, dev):
         return (lambda: attention_with_lse(q, k, v, sc, causal), fl, 4.0 * B * H * S * D * 2,
                 f"flash-attention fwd bf16 [B={B},H={H},S={S},D={D}] causal={causal}, seed 2", "attention_fwd_kernel<128>",
                 "tensor")
+    if name in ("attn_bwd", "attn_bwd_causal", "attn_bwd_ref_shape", "attn_bwd_ref_shape_causal"):
+        from triton_b200.tutorials.blackwell_fa_ws_pipelined_persistent import attention_backward, attention_with_lse
+        causal = name.endswith("causal")
+        # "ref_shape": Z=4, H=16, N=2048, the first shape of the reference's published backward table
+        B, H, S, D = (4, 16, 2048, 128) if "ref_shape" in name else (4, 32, 8192, 128)
+        q, k, v, do = (torch.randn(B, H, S, D, generator=g).to(torch.bfloat16).to(dev) for _ in range(4))
+        sc = 1.0 / math.sqrt(D)
+        o, lse = attention_with_lse(q, k, v, sc, causal)
+        fl = 10.0 * B * H * D * (S * (S + 1) / 2 if causal else S * S)  # five S x S x D products
+        return (lambda: attention_backward(q, k, v, o, lse, do, sc, causal), fl, 8.0 * B * H * S * D * 2,
+                f"flash-attention bwd bf16 [B={B},H={H},S={S},D={D}] causal={causal} (delta + main + dq kernels), seed 2",
+                "attention_bwd_kernel", "tensor")
     if name in ("fp8", "mxfp8"):
         n = 8192
         a = (torch.randn(n, n, generator=g) * 0.1).to(torch.float8_e4m3fn).to(dev)
@@ -192,7 +204,8 @@ def build_workload(name: str, rank: int, dev):
 
 # Kernels of this library launched per step: the MoE layer runs topk, three bitmatrix-metadata kernels,
 # the ragged-metadata kernel, two grouped GEMMs and the top-k reduce (the EP variant adds four row moves).
-OWN_LAUNCHES_PER_STEP = {"moe": 8, "moe_decode": 8, "moe_ep": 12}
+OWN_LAUNCHES_PER_STEP = {"moe": 8, "moe_decode": 8, "moe_ep": 12, "attn_bwd": 3, "attn_bwd_causal": 3,
+                         "attn_bwd_ref_shape": 3, "attn_bwd_ref_shape_causal": 3}
 
 
 def run_extra_workload(args, rank, local_rank, world):
@@ -329,8 +342,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--workload", default="gemm",
-                    help="gemm (headline, default) | attn | attn_causal | attn_short | attn_short_causal | fp8 | mxfp8 | "
-                         "moe | moe_decode")
+                    help="gemm (headline, default) | attn | attn_causal | attn_short | attn_short_causal | attn_bwd | "
+                         "attn_bwd_causal | attn_bwd_ref_shape[_causal] | fp8 | mxfp8 | moe | moe_decode | moe_ep")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))

@@ -159,6 +159,42 @@ typedef struct {
 
 int tb200_attention_fwd(const tb200_attention_args* args, void* stream);
 
+/*
+ * Flash-attention backward: dq, dk, dv from q, k, v, the forward output o, its gradient d_o and
+ * the base-2 log-sum-exp `lse` written by tb200_attention_fwd.
+ * Stands behind: third_party/tlx/tutorials/blackwell_fa_ws_pipelined_persistent.py:3362
+ *   _attention.backward (kernels _attn_bwd_preprocess :1252, _attn_bwd_ws :2442,
+ *   _attn_bwd_dq_postprocess :1269).
+ * Layouts as in the forward call; d_o and dq are shaped like q, dk and dv like k; all gradients are
+ * written in `dtype` (the reference returns dq in fp32). head_dim 128 only. causal requires
+ * seq_q == seq_kv. `workspace` (device memory, 16-byte aligned, at least
+ * tb200_attention_bwd_workspace_bytes(args) bytes) holds the row sums of o * d_o and the fp32 dq
+ * accumulator. Partial dq tiles of different key blocks are summed with floating-point atomics:
+ * the last bits of dq can differ between two runs on the same inputs (as with the reference's
+ * reduce-add); dk and dv are reproducible.
+ */
+typedef struct {
+  const void* q;
+  const void* k;
+  const void* v;
+  const void* o;
+  const void* d_o;
+  const float* lse;
+  void* dq;
+  void* dk;
+  void* dv;
+  void* workspace;
+  size_t workspace_bytes;
+  int64_t batch, heads, seq_q, seq_kv;
+  int32_t head_dim;
+  int32_t dtype;
+  int32_t causal;
+  float sm_scale;
+} tb200_attention_bwd_args;
+
+size_t tb200_attention_bwd_workspace_bytes(const tb200_attention_bwd_args* args);
+int tb200_attention_bwd(const tb200_attention_bwd_args* args, void* stream);
+
 /* ---------------------------------------------------------------- MoE routing ------ */
 /* Paths below are inside python/triton_kernels/triton_kernels/ of the reference. */
 

@@ -1,4 +1,4 @@
-"""Oracle for flash-attention forward (test infrastructure only).
+"""Oracle for flash-attention forward and backward (test infrastructure only).
 
 The reference checks its kernel against ``F.scaled_dot_product_attention(q, k, v, scale=sm_scale,
 is_causal=causal)`` (``third_party/tlx/tutorials/testing/test_correctness.py:425-435``). Its
@@ -31,3 +31,33 @@ def attention_ref(q, k, v, sm_scale: float, causal: bool):
             o[b, h] = p @ v32[b, h]
             lse2[b, h] = lse * math.log2(math.e)
     return o.to(q.dtype), lse2
+
+
+def attention_bwd_ref(q, k, v, do, sm_scale: float, causal: bool):
+    """Gradients of ``sum(attention(q, k, v) * do)`` restated from the formulas the reference's
+    backward kernel implements (``blackwell_fa_ws_pipelined_persistent.py:1252-1266`` Delta,
+    ``:2272-2440`` P, dS; dV = P^T dO, dK = sm_scale dS^T Q, dQ = sm_scale dS K), in fp64.
+    The reference's own test compares with torch autograd (``testing/test_correctness.py:919-1068``);
+    ``tests/test_oracle.py`` pins this restatement against autograd the same way.
+    Returns (dq, dk, dv) in fp32 on the CPU."""
+    q64, k64, v64, do64 = (t.detach().cpu().double() for t in (q, k, v, do))
+    B, H, S, D = q64.shape
+    Sk = k64.shape[2]
+    dq = torch.empty(B, H, S, D, dtype=torch.float64)
+    dk = torch.empty(B, H, Sk, D, dtype=torch.float64)
+    dv = torch.empty(B, H, Sk, D, dtype=torch.float64)
+    mask = torch.ones(S, Sk, dtype=torch.bool).tril(diagonal=Sk - S) if causal else None
+    for b in range(B):
+        for h in range(H):
+            s = (q64[b, h] @ k64[b, h].t()) * sm_scale
+            if mask is not None:
+                s = s.masked_fill(~mask, float("-inf"))
+            p = torch.softmax(s, dim=-1)
+            o = p @ v64[b, h]
+            delta = (o * do64[b, h]).sum(dim=-1, keepdim=True)
+            dp = do64[b, h] @ v64[b, h].t()
+            ds = p * (dp - delta)
+            dv[b, h] = p.t() @ do64[b, h]
+            dk[b, h] = sm_scale * (ds.t() @ q64[b, h])
+            dq[b, h] = sm_scale * (ds @ k64[b, h])
+    return dq.float(), dk.float(), dv.float()

@@ -114,6 +114,21 @@ def test_attention_oracle_matches_sdpa():
         torch.testing.assert_close(lse2, torch.logsumexp(s, -1) * 1.4426950408889634, atol=1e-5, rtol=1e-5)
 
 
+def test_attention_bwd_oracle_matches_autograd():
+    """The backward restatement against torch autograd through SDPA (the check the reference's own
+    backward test uses, testing/test_correctness.py:919-1068)."""
+    torch.manual_seed(3)
+    for causal in (False, True):
+        q, k, v = (torch.randn(1, 2, 80, 32, dtype=torch.float64, requires_grad=True) for _ in range(3))
+        do = torch.randn(1, 2, 80, 32, dtype=torch.float64)
+        out = torch.nn.functional.scaled_dot_product_attention(q, k, v, scale=0.5, is_causal=causal)
+        out.backward(do)
+        dq, dk, dv = o_attn.attention_bwd_ref(q, k, v, do, 0.5, causal)
+        torch.testing.assert_close(dq, q.grad.float(), atol=1e-5, rtol=1e-5)
+        torch.testing.assert_close(dk, k.grad.float(), atol=1e-5, rtol=1e-5)
+        torch.testing.assert_close(dv, v.grad.float(), atol=1e-5, rtol=1e-5)
+
+
 def test_moe_layer_oracle_is_dense_mixture():
     """With k = E every expert sees every token: the layer equals the dense gate-weighted sum."""
     torch.manual_seed(1)

@@ -53,6 +53,16 @@ class AttentionArgs(Structure):
     ]
 
 
+class AttentionBwdArgs(Structure):
+    _fields_ = [
+        ("q", c_void_p), ("k", c_void_p), ("v", c_void_p), ("o", c_void_p), ("d_o", c_void_p), ("lse", c_void_p),
+        ("dq", c_void_p), ("dk", c_void_p), ("dv", c_void_p),
+        ("workspace", c_void_p), ("workspace_bytes", c_size_t),
+        ("batch", c_int64), ("heads", c_int64), ("seq_q", c_int64), ("seq_kv", c_int64),
+        ("head_dim", c_int32), ("dtype", c_int32), ("causal", c_int32), ("sm_scale", c_float),
+    ]
+
+
 class TopkArgs(Structure):
     _fields_ = [
         ("x", c_void_p), ("y_vals", c_void_p), ("y_indx", c_void_p), ("bitmatrix", c_void_p),
@@ -123,6 +133,10 @@ def _declare(l: ctypes.CDLL) -> None:
     l.tb200_gemm_workspace_bytes.argtypes = [POINTER(GemmArgs)]
     l.tb200_attention_fwd.restype = c_int
     l.tb200_attention_fwd.argtypes = [POINTER(AttentionArgs), c_void_p]
+    l.tb200_attention_bwd.restype = c_int
+    l.tb200_attention_bwd.argtypes = [POINTER(AttentionBwdArgs), c_void_p]
+    l.tb200_attention_bwd_workspace_bytes.restype = c_size_t
+    l.tb200_attention_bwd_workspace_bytes.argtypes = [POINTER(AttentionBwdArgs)]
     for name, typ in (("tb200_topk", TopkArgs), ("tb200_bitmatrix_metadata", BitmatrixMetadataArgs),
                       ("tb200_ragged_metadata", RaggedMetadataArgs), ("tb200_reduce_k", ReduceKArgs),
                       ("tb200_swiglu", SwigluArgs), ("tb200_moe_gemm", MoeGemmArgs)):

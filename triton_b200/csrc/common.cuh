@@ -32,6 +32,7 @@ enum WaitCode : int {
   WAIT_ATTN = 5,
   WAIT_SCALE = 6,
   WAIT_STORE = 7,
+  BAD_SMEM_ALIGNMENT = 8,  // not a wait: a kernel found its shared-memory window misaligned and did nothing
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

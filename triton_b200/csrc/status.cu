@@ -1,4 +1,5 @@
 // Status word, TMA descriptor encoder and device-property cache (host side).
+#include <stdio.h>
 #include <mutex>
 
 #include "host_common.h"
@@ -70,6 +71,13 @@ int encode_tmap(CUtensorMap* out, CUtensorMapDataType dtype, int rank, const voi
   for (int i = 0; i + 1 < rank; ++i) gstr[i] = strides_bytes[i];
   CUresult r = fn(out, dtype, (cuuint32_t)rank, const_cast<void*>(base), gdim, gstr, bx, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, promo, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r == CUDA_ERROR_INVALID_CONTEXT) {
+    // a host thread that has made no runtime call yet (e.g. an autograd worker) has no current
+    // context: bind the device's primary context and encode again
+    cudaFree(nullptr);
+    r = fn(out, dtype, (cuuint32_t)rank, const_cast<void*>(base), gdim, gstr, bx, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+           swizzle, promo, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  }
   return r == CUDA_SUCCESS ? TB200_OK : TB200_ERR_TMAP;
 }
 

@@ -2,9 +2,10 @@
 flash-attention forward, ``third_party/tlx/tutorials/blackwell_fa_ws_pipelined_persistent.py:3491``.
 
 q, k, v: ``[B, H, S, D]`` fp16 or bf16 CUDA tensors with equal head dims; returns ``o`` with the shape
-and dtype of ``q``. Forward only: the result carries no autograd graph (the reference wraps its
-kernel in an autograd Function whose backward is a separate kernel). The reference keeps the row
-statistic ``M = m*sm_scale*log2(e) + log2(l)`` (base-2 log-sum-exp, ``:886-894``) internal;
+and dtype of ``q``. Like the reference (``_attention``, ``:3285-3488``) the call is an autograd Function
+when an input requires grad: ``backward`` runs the backward kernel (head_dim 128) and returns
+``dq, dk, dv`` in the input dtype; ``attention_backward`` is the same step as a plain function.
+The reference keeps the row statistic ``M = m*sm_scale*log2(e) + log2(l)`` (base-2 log-sum-exp, ``:886-894``) internal;
 ``attention_with_lse`` returns it as a second fp32 ``[B, H, S]`` tensor without changing the
 signature of ``attention``. ``config`` is accepted for call compatibility (the tiling is fixed:
 256 query rows per CTA as two groups of 128, KV blocks of 128).
@@ -50,5 +51,60 @@ def attention_with_lse(q, k, v, sm_scale, causal, config=None):
     return o, M
 
 
+def attention_backward(q, k, v, o, lse, do, sm_scale, causal):
+    """dq, dk, dv for ``o, lse = attention_with_lse(q, k, v, sm_scale, causal)`` and the output gradient
+    ``do`` (the reference's ``_attention.backward``, ``:3362``; head_dim 128)."""
+    if not q.is_cuda:
+        raise RuntimeError("triton_b200 attention needs CUDA tensors (there is no CPU path)")
+    if q.shape[-1] != 128:
+        raise NotImplementedError(f"attention backward: head_dim {q.shape[-1]} (the kernel is built for 128)")
+    assert q.dtype in _DT and k.dtype == q.dtype and v.dtype == q.dtype and o.dtype == q.dtype
+    assert o.shape == q.shape and do.shape == q.shape and k.shape == v.shape
+    q, k, v, o = q.contiguous(), k.contiguous(), v.contiguous(), o.contiguous()
+    do = do.to(q.dtype).contiguous()
+    lse = lse.contiguous()
+    assert lse.dtype == torch.float32 and lse.shape == q.shape[:3]
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    if q.numel() == 0 or k.numel() == 0:
+        return dq.zero_(), dk.zero_(), dv.zero_()
+    B, H, S, D = q.shape
+    args = _lib.AttentionBwdArgs()
+    args.q, args.k, args.v, args.o, args.d_o = q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr()
+    args.lse = lse.data_ptr()
+    args.dq, args.dk, args.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
+    args.batch, args.heads, args.seq_q, args.seq_kv = B, H, S, k.shape[2]
+    args.head_dim = D
+    args.dtype = _DT[q.dtype]
+    args.causal = 1 if causal else 0
+    args.sm_scale = float(sm_scale)
+    need = _lib.lib().tb200_attention_bwd_workspace_bytes(ctypes.byref(args))
+    ws = torch.empty(max(need, 16), dtype=torch.uint8, device=q.device)
+    args.workspace, args.workspace_bytes = ws.data_ptr(), need
+    with torch.cuda.device(q.device):
+        rc = _lib.lib().tb200_attention_bwd(ctypes.byref(args), ctypes.c_void_p(_lib.current_stream_ptr(q.device)))
+    _lib.check(rc, "tb200_attention_bwd")
+    return dq, dk, dv
+
+
+class _attention(torch.autograd.Function):
+    """Forward + saved (q, k, v, o, M); backward through ``attention_backward``."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, sm_scale, causal):
+        o, M = attention_with_lse(q, k, v, sm_scale, causal)
+        ctx.save_for_backward(q, k, v, o, M)
+        ctx.sm_scale = sm_scale
+        ctx.causal = causal
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, M = ctx.saved_tensors
+        dq, dk, dv = attention_backward(q, k, v, o, M, do, ctx.sm_scale, ctx.causal)
+        return dq, dk, dv, None, None
+
+
 def attention(q, k, v, sm_scale, causal, config=None):
+    if torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad):
+        return _attention.apply(q, k, v, sm_scale, causal)
     return attention_with_lse(q, k, v, sm_scale, causal, config)[0]
