@@ -21,7 +21,10 @@
 //                O / l is unchanged. P (bf16) is written over the first half of S's columns.
 // Tensor memory (512 columns): S0 | S1 | O0 | O1 with P_g aliasing S_g.
 // In-order execution of one thread's tcgen05.mma stream gives the S/P write-after-read order
-// (QK_g(j+1) is issued after PV_g(j)) and makes PV_g(j-1) complete before S_g(j) is signalled.
+// (QK_g(j+1) is issued after PV_g(j)) and makes PV_g(j-1) complete before S_g(j) is signalled, so
+// only the last PV of a tile carries a completion barrier of its own. The issuing thread probes
+// the barrier it needs next (mbarrier.test_wait) before each batch of MMAs: a blocking wait costs
+// it ~70 cycles even when the phase is complete, a probe issued ahead of the MMAs costs nothing.
 //
 // Counterpart in the reference: _attn_fwd_ws / _attn_fwd_ws_kernel,
 // third_party/tlx/tutorials/blackwell_fa_ws_pipelined_persistent.py:600-1249 (softmax :223-322,
@@ -79,7 +82,7 @@ __device__ __forceinline__ AttnTile attn_tile(const AttnParams& p, int unit) {
   return t;
 }
 
-template <int D>
+template <int D, bool F16>
 __global__ void __launch_bounds__(ATT_THREADS, 1) attention_fwd_kernel(const __grid_constant__ AttnParams p) {
   using L = AttnSmem<D>;
   constexpr int DBOX = D / 64;                 // 64-column TMA boxes per tile
@@ -96,7 +99,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_fwd_kernel(const __g
   uint64_t* kv_empty = kv_full + ATT_KV_STAGES; // [KV]
   uint64_t* s_full = kv_empty + ATT_KV_STAGES;  // [2] MMA -> softmax: S_g ready
   uint64_t* p_full = s_full + 2;                // [2][4] softmax -> MMA: 32-column chunk c of P_g written (128 arrivals)
-  uint64_t* pv_done = p_full + 8;               // [2] MMA -> softmax: PV_g complete
+  uint64_t* pv_done = p_full + 8;               // [2] MMA -> softmax: last PV_g of the tile complete
   uint64_t* o_free = pv_done + 2;               // [2] softmax -> MMA: O_g read out (128 arrivals)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_free + 2);
 
@@ -180,7 +183,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_fwd_kernel(const __g
     if (lane == 0) {
       const uint32_t idesc_qk = make_idesc(1u, 1u, 0u, 0u, ATT_BM, ATT_BN);  // bf16 x bf16, both K-major
       const uint32_t idesc_pv = make_idesc(1u, 1u, 0u, 1u, ATT_BM, D);       // B (= V) MN-major
-      const uint32_t fmt_fix = p.out_f16 ? ((1u << 7) | (1u << 10)) : 0u;     // fp16: operand format 0
+      constexpr uint32_t fmt_fix = F16 ? ((1u << 7) | (1u << 10)) : 0u;     // fp16: operand format 0
       const uint32_t idq = idesc_qk & ~fmt_fix, idp = idesc_pv & ~fmt_fix;
       const uint64_t qdesc0 = make_smem_desc(smem_a + L::Q_OFFSET, 16, 1024, SWIZZLE_128B);
       const uint64_t kdesc0 = make_smem_desc(smem_a + L::KV_OFFSET, 16, 1024, SWIZZLE_128B);
@@ -203,19 +206,22 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_fwd_kernel(const __g
       };
       // PV_g in four slices: slice c (two MMAs, 32 kv rows) goes out as soon as the softmax has
       // published chunk c of P_g, so the MMA overlaps the tail of the softmax
-      auto issue_pv = [&](int g, uint32_t vstage, uint32_t accum, uint32_t iph) -> bool {
+      auto issue_pv = [&](int g, uint32_t vstage, uint32_t accum, uint32_t iph, bool ready, bool last) -> bool {
         const uint64_t vd = vdesc0 + (uint64_t)((vstage * L::TILE_BYTES) >> 4);
         const uint32_t d_o = tmem_base + O_COL0 + g * D;
         const uint32_t a_p = tmem_base + g * S_COLS;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-          if (!mbar_wait(&p_full[g * 4 + c], iph, status, WAIT_ATTN)) return false;
+          if (!ready && !mbar_wait(&p_full[g * 4 + c], iph, status, WAIT_ATTN)) return false;
           tc_fence_after_sync();
+          if (c < 3) ready = mbar_test(&p_full[g * 4 + c + 1], iph);  // probe ahead of this slice's MMAs
 #pragma unroll
           for (int k = 2 * c; k < 2 * c + 2; ++k)
             umma_f16_ts(d_o, a_p + k * 8, vd + (uint64_t)((k * 16 * 128) >> 4), idp, (k > 0) ? 1u : accum);
         }
-        umma_commit(&pv_done[g]);
+        // S_g(j+1) is committed after this in the same in-order stream, so only the last PV of a
+        // tile needs a completion signal of its own (the epilogue waits for it)
+        if (last) umma_commit(&pv_done[g]);
         return true;
       };
       auto advance = [&]() {
@@ -257,16 +263,19 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_fwd_kernel(const __g
           // PV0(j)
           if (!mbar_wait(&kv_full[vcur], vcur_ph, status, WAIT_SMEM_FULL)) { ok = false; break; }
           if (j == 0 && !mbar_wait(&o_free[0], tph ^ 1, status, WAIT_ATTN)) { ok = false; break; }
-          if (!issue_pv(0, vcur, j > 0 ? 1u : 0u, iph)) { ok = false; break; }
+          bool k_ready = more && mbar_test(&kv_full[knext], knext_ph);
+          if (!issue_pv(0, vcur, j > 0 ? 1u : 0u, iph, mbar_test(&p_full[0], iph), !more)) { ok = false; break; }
+          bool p1_ready = false;
           if (more) {
-            if (!mbar_wait(&kv_full[knext], knext_ph, status, WAIT_SMEM_FULL)) { ok = false; break; }
+            if (!k_ready && !mbar_wait(&kv_full[knext], knext_ph, status, WAIT_SMEM_FULL)) { ok = false; break; }
             tc_fence_after_sync();
+            p1_ready = mbar_test(&p_full[4], iph);
             issue_qk(0, knext);
             if (j + 2 == t.nkv) umma_commit(&q_empty[0]);
           }
           // PV1(j)
           if (j == 0 && !mbar_wait(&o_free[1], tph ^ 1, status, WAIT_ATTN)) { ok = false; break; }
-          if (!issue_pv(1, vcur, j > 0 ? 1u : 0u, iph)) { ok = false; break; }
+          if (!issue_pv(1, vcur, j > 0 ? 1u : 0u, iph, p1_ready, !more)) { ok = false; break; }
           umma_commit(&kv_empty[vcur]);
           if (more) {
             issue_qk(1, knext);
@@ -289,9 +298,9 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_fwd_kernel(const __g
     const uint32_t t_o = tmem_base + lane_off + O_COL0 + g * D;
     const float scale = p.scale_log2;
     const int s_kv = p.s_kv, s_q = p.s_q, causal = p.causal;
-    uint32_t it = 0;
+    uint32_t it = 0, tcount = 0;
     bool ok = true;
-    for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x) {
+    for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x, ++tcount) {
       const AttnTile t = attn_tile(p, unit);
       const int qrow = t.q0 + g * ATT_BM + row_in_group;  // position in the sequence
       float m = -INFINITY, l = 0.f;
@@ -333,8 +342,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_fwd_kernel(const __g
         }
         // ---- correction: rescale O_g when any row of this warp moved its reference max
         if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-          if (!mbar_wait(&pv_done[g], iph ^ 1, status, WAIT_ATTN)) { ok = false; break; }
-          tc_fence_after_sync();
+          // PV_g(j-1) is complete: it precedes S_g(j) in the MMA stream, and S_g(j) has arrived
           l *= alpha;
 #pragma unroll 1
           for (int c = 0; c < D; c += 32) {
@@ -361,7 +369,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_fwd_kernel(const __g
             unpack2(x, x0, x1);
             const float e0 = fast_exp2(x0), e1 = fast_exp2(x1);
             sum2 = add2(sum2, pack2(e0, e1));
-            pk[i >> 1] = p.out_f16 ? pack_f16x2(e0, e1) : pack_bf16x2(e0, e1);
+            pk[i >> 1] = F16 ? pack_f16x2(e0, e1) : pack_bf16x2(e0, e1);
           }
           if (c > 0) {
             // the previous chunk's store has had this chunk's arithmetic to land: publish it
@@ -381,7 +389,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_fwd_kernel(const __g
       }
       if (!ok) break;
       // ---- epilogue: wait for the last PV_g, normalise, store O and the base-2 LSE
-      if (!mbar_wait(&pv_done[g], (it - 1) & 1, status, WAIT_ATTN)) break;
+      if (!mbar_wait(&pv_done[g], tcount & 1, status, WAIT_ATTN)) break;
       tc_fence_after_sync();
       const float inv_l = 1.f / l;
       const bool valid = qrow < s_q;
@@ -399,7 +407,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_fwd_kernel(const __g
             for (int u = 0; u < 4; ++u) {
               const float lo = __uint_as_float(v[i * 8 + 2 * u]) * inv_l;
               const float hi = __uint_as_float(v[i * 8 + 2 * u + 1]) * inv_l;
-              w[u] = p.out_f16 ? pack_f16x2(lo, hi) : pack_bf16x2(lo, hi);
+              w[u] = F16 ? pack_f16x2(lo, hi) : pack_bf16x2(lo, hi);
             }
             reinterpret_cast<uint4*>(orow + c)[i] = make_uint4(w[0], w[1], w[2], w[3]);
           }
@@ -422,7 +430,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_fwd_kernel(const __g
 template <int D>
 static int launch_attn(const AttnParams& p, int grid, cudaStream_t stream) {
   using L = AttnSmem<D>;
-  auto kfn = attention_fwd_kernel<D>;
+  auto kfn = p.out_f16 ? attention_fwd_kernel<D, true> : attention_fwd_kernel<D, false>;
   if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL) != cudaSuccess)
     return TB200_ERR_CUDA;
   kfn<<<grid, ATT_THREADS, L::TOTAL, stream>>>(p);
