@@ -15,16 +15,17 @@
 //   S^T(j)  = K Q(j)^T        SS, 128 x 128 x D     -> TMEM S
 //   dP^T(j) = V dO(j)^T       SS, 128 x 128 x D     -> TMEM dP
 //   dV     += P^T(j) dO(j)    TS (P^T 16-bit, written over S), dO the MN-major B operand
-//   dK     += dS^T(j) Q(j)    TS (dS^T written over dP),        Q  the MN-major B operand
-//   dQ^T(j) = K^T dS^T(j)     SS, both operands MN-major (K tile; dS^T from shared memory),
+//   dK     += dS^T(j) Q(j)    SS (dS^T from shared memory, K-major), Q the MN-major B operand
+//   dQ^T(j) = K^T dS^T(j)     SS, both operands MN-major (K tile; the same dS^T tile),
 //                             128 (d) x 128 (q) x 128 (kv), written over dP
 // Tensor memory (512 columns): S (128) | dP (128) | dV (128) | dK (128).
 // Roles (512 threads):
-//   warp 0      TMA: K, V once; Q(j) and dO(j) through two-deep rings of 128-row tiles.
+//   warp 0      TMA: K, V once; Q(j) through a three-deep ring of 128-row tiles, dO(j) through a single
+//               buffer (dV(j) frees it early in the iteration; dP^T(j+1) needs it at the end).
 //   warp 1      one thread issues every MMA, in the order
-//                 dV(j) | S^T(j+1) | dK(j), dQ^T(j) | dP^T(j+1)
-//               so that the exponentials of tile j+1 run under dK, dQ^T and dP^T.
-//   warp 2      -LSE2 and -Delta of each query tile into shared memory (two-deep ring).
+//                 dV(j) | S^T(j+1) | dQ^T(j), dK(j) | dP^T(j+1)
+//               so that the exponentials of tile j+1 run under dQ^T, dK and dP^T, and dQ^T(j) is
+//               read out of tensor memory while dK(j) executes.
 //   warps 4-7   dQ reduction: read dQ^T(j) from TMEM (thread = head-dim column) and add it to the
 //               fp32 dQ accumulator in global memory with coalesced red.add (a warp covers 128
 //               contiguous bytes of one query row). Different KV blocks add to the same rows, so the
@@ -33,16 +34,17 @@
 //   warps 8-11 / 12-15   compute groups 0 / 1 own query columns 0-63 / 64-127 of every tile; thread t
 //               owns KV row t: P^T = exp2(S^T * scale - LSE2[q]) -> 16-bit -> TMEM (over the first
 //               32 columns of the group's half of S); dS^T = P^T o (dP^T - Delta[q]) -> 16-bit ->
-//               TMEM (for dK) and shared memory in the MN-major swizzled layout (for dQ^T). dS^T is
-//               formed from the 16-bit P^T that dV also uses (32 registers instead of 64, which is
+//               shared memory, rows = kv with the 64 query columns of the group as one swizzled
+//               128-byte row: read as the MN-major B operand by dQ^T and as the K-major A operand by
+//               dK. dS^T is formed from the 16-bit P^T that dV also uses (32 registers instead of 64, which is
 //               what lets the reduction group hold a whole dQ^T tile). The loops over a row are
 //               branch-free (mask applied beforehand, dtype a template parameter): with a branch
 //               per element pair they ran 1.6x slower, bound by MUFU latency instead of throughput.
 //               At the end group 0 stores dV, group 1 stores sm_scale * dK.
-// Registers per thread after setmaxnreg: 96 (load / MMA / statistics), 144 (dQ reduction, 128 of
+// Registers per thread after setmaxnreg: 96 (load / MMA), 144 (dQ reduction, 128 of
 // them one dQ^T row), 136 (compute groups).
 // One thread's tcgen05.mma stream executes in order: S^T(j+1) may overwrite P^T(j) right after
-// dV(j) was issued, and dQ^T(j) may overwrite dS^T(j) right after dK(j).
+// dV(j) was issued.
 // Non-causal CTAs start their walk at a query tile that depends on the KV block, so that the CTAs
 // of one head do not all add to the same dQ rows at the same time.
 //
@@ -61,7 +63,8 @@ static constexpr int BWD_THREADS = 512;
 static constexpr int BWD_BN = 128;  // kv rows per CTA
 static constexpr int BWD_BM = 128;  // query rows per inner tile
 static constexpr int BWD_D = 128;   // head dim
-static constexpr int BWD_STAGES = 2;  // ring depth of the Q, dO and row-statistics tiles
+static constexpr int BWD_Q_STAGES = 3;   // Q(j) is read by S^T(j) early and by dK(j) late: a deep ring
+// dO has a single buffer (freed by dV(j), refilled under S^T, dQ^T, dK)
 
 struct AttnBwdParams {
   CUtensorMap tmq, tmdo;  // 3-D (D, S_q, B*H), box (64, 128, 1), 128-byte swizzle
@@ -88,12 +91,10 @@ struct BwdSmem {
   static constexpr int K_OFFSET = 0;
   static constexpr int V_OFFSET = KV_TILE;
   static constexpr int Q_OFFSET = 2 * KV_TILE;
-  static constexpr int DO_OFFSET = Q_OFFSET + BWD_STAGES * Q_TILE;
-  static constexpr int DS_OFFSET = DO_OFFSET + BWD_STAGES * Q_TILE;
-  static constexpr int MD_OFFSET = DS_OFFSET + DS_TILE;
-  static constexpr int MD_STAGE_BYTES = 2 * BWD_BM * 4;  // 128 x -LSE2, 128 x -Delta
-  static constexpr int BAR_OFFSET = MD_OFFSET + BWD_STAGES * MD_STAGE_BYTES;
-  static constexpr int NUM_BARS = 2 + 6 * BWD_STAGES + 6 + 1;
+  static constexpr int DO_OFFSET = Q_OFFSET + BWD_Q_STAGES * Q_TILE;
+  static constexpr int DS_OFFSET = DO_OFFSET + Q_TILE;
+  static constexpr int BAR_OFFSET = DS_OFFSET + DS_TILE;
+  static constexpr int NUM_BARS = 2 + 2 * BWD_Q_STAGES + 2 + 6 + 1;
   // The tiles use all but a few hundred bytes of the 227 KB a CTA can have, so there is no room for
   // an alignment pad: the kernel checks that the dynamic window starts on a 1024-byte boundary.
   static constexpr int TOTAL = BAR_OFFSET + NUM_BARS * 8 + 16;
@@ -141,13 +142,11 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attention_bwd_kernel(const __g
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET);
   uint64_t* k_full = bars;                       // [1]
   uint64_t* v_full = bars + 1;                   // [1]
-  uint64_t* q_full = bars + 2;                   // [STAGES]
-  uint64_t* q_empty = q_full + BWD_STAGES;       // [STAGES]
-  uint64_t* do_full = q_empty + BWD_STAGES;      // [STAGES]
-  uint64_t* do_empty = do_full + BWD_STAGES;     // [STAGES]
-  uint64_t* md_full = do_empty + BWD_STAGES;     // [STAGES] 32 arrivals (stats warp)
-  uint64_t* md_empty = md_full + BWD_STAGES;     // [STAGES] 256 arrivals (both compute groups)
-  uint64_t* s_full = md_empty + BWD_STAGES;      // MMA -> compute: S^T ready
+  uint64_t* q_full = bars + 2;                   // [Q_STAGES]
+  uint64_t* q_empty = q_full + BWD_Q_STAGES;     // [Q_STAGES]
+  uint64_t* do_full = q_empty + BWD_Q_STAGES;    // [1]
+  uint64_t* do_empty = do_full + 1;              // [1]
+  uint64_t* s_full = do_empty + 1;               // MMA -> compute: S^T ready
   uint64_t* p_full = s_full + 1;                 // compute -> MMA: P^T in TMEM (256 arrivals)
   uint64_t* dp_full = p_full + 1;                // MMA -> compute: dP^T ready
   uint64_t* ds_full = dp_full + 1;               // compute -> MMA: dS^T in TMEM and smem (256)
@@ -172,14 +171,12 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attention_bwd_kernel(const __g
     tma_prefetch_desc(&p.tmv);
     mbar_init(k_full, 1);
     mbar_init(v_full, 1);
-    for (int i = 0; i < BWD_STAGES; ++i) {
+    for (int i = 0; i < BWD_Q_STAGES; ++i) {
       mbar_init(&q_full[i], 1);
       mbar_init(&q_empty[i], 1);
-      mbar_init(&do_full[i], 1);
-      mbar_init(&do_empty[i], 1);
-      mbar_init(&md_full[i], 32);
-      mbar_init(&md_empty[i], 256);
     }
+    mbar_init(do_full, 1);
+    mbar_init(do_empty, 1);
     mbar_init(s_full, 1);
     mbar_init(p_full, 256);
     mbar_init(dp_full, 1);
@@ -212,14 +209,15 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attention_bwd_kernel(const __g
         tma_load_3d(smem + off + L::KV_TILE / 2, tm, bar, 64, row, u.bh, pol);
       };
       load_tile(&p.tmk, L::K_OFFSET, k_full, u.kv0, pol_kv);
+      uint32_t qs = 0, qph = 0;
       for (int j = 0; j < n_tiles; ++j) {
         const int q0 = bwd_tile(p, u, j) * BWD_BM;
-        const uint32_t st = j & 1, ph = (j >> 1) & 1;
-        if (!mbar_wait(&q_empty[st], ph ^ 1, status, WAIT_SMEM_EMPTY)) break;
-        load_tile(&p.tmq, L::Q_OFFSET + st * L::Q_TILE, &q_full[st], q0, pol_q);
+        if (!mbar_wait(&q_empty[qs], qph ^ 1, status, WAIT_SMEM_EMPTY)) break;
+        load_tile(&p.tmq, L::Q_OFFSET + qs * L::Q_TILE, &q_full[qs], q0, pol_q);
         if (j == 0) load_tile(&p.tmv, L::V_OFFSET, v_full, u.kv0, pol_kv);
-        if (!mbar_wait(&do_empty[st], ph ^ 1, status, WAIT_SMEM_EMPTY)) break;
-        load_tile(&p.tmdo, L::DO_OFFSET + st * L::Q_TILE, &do_full[st], q0, pol_q);
+        if (!mbar_wait(do_empty, (j & 1) ^ 1, status, WAIT_SMEM_EMPTY)) break;
+        load_tile(&p.tmdo, L::DO_OFFSET, do_full, q0, pol_q);
+        if (++qs == BWD_Q_STAGES) { qs = 0; qph ^= 1; }
       }
     }
   } else if (warp == 1) {
@@ -239,6 +237,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attention_bwd_kernel(const __g
       const uint64_t do_kmaj0 = make_smem_desc(smem_a + L::DO_OFFSET, 16, 1024, SWIZZLE_128B);
       const uint64_t do_mnmaj0 = make_smem_desc(smem_a + L::DO_OFFSET, HALF, 1024, SWIZZLE_128B);
       const uint64_t ds_mnmaj = make_smem_desc(smem_a + L::DS_OFFSET, HALF, 1024, SWIZZLE_128B);
+      const uint64_t ds_kmaj = make_smem_desc(smem_a + L::DS_OFFSET, 16, 1024, SWIZZLE_128B);
+      const uint32_t id_dk = make_idesc(1u, 1u, 0u, 1u, BWD_BN, BWD_D) & ~fmt_fix;  // K-major A (smem), MN-major B
       bool ok = true;
 
       // S^T or dP^T: [128 kv] x [128 q] over D, both operands K-major
@@ -249,13 +249,20 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attention_bwd_kernel(const __g
           umma_f16_ss(tmem_base + d_col, a_desc + o, b_desc + o, id_st, k > 0 ? 1u : 0u);
         }
       };
-      // dV or dK: A = 16-bit [128 kv] x [128 q] in TMEM (32 columns at a_col and 32 at a_col + 64),
-      // B = the query-side tile as [128 q] x [128 d]
-      auto issue_acc = [&](uint32_t a_col, uint64_t b_desc, uint32_t d_col, uint32_t accum) {
+      // dV += P^T dO: A = 16-bit [128 kv] x [128 q] in TMEM (32 columns at 0 and 32 at 64),
+      // B = dO as [128 q] x [128 d]
+      auto issue_dv = [&](uint64_t b_desc, uint32_t accum) {
 #pragma unroll
         for (int k = 0; k < BWD_BM / 16; ++k)
-          umma_f16_ts(tmem_base + d_col, tmem_base + a_col + (k >> 2) * 64 + (k & 3) * 8,
+          umma_f16_ts(tmem_base + DV_COL0, tmem_base + (k >> 2) * 64 + (k & 3) * 8,
                       b_desc + (uint64_t)((k * 2048) >> 4), id_acc, k > 0 ? 1u : accum);
+      };
+      // dK += dS^T Q: A = dS^T from shared memory (K-major: rows kv, q contiguous), B = Q as [128 q] x [128 d]
+      auto issue_dk = [&](uint64_t b_desc, uint32_t accum) {
+#pragma unroll
+        for (int k = 0; k < BWD_BM / 16; ++k)
+          umma_f16_ss(tmem_base + DK_COL0, ds_kmaj + (uint64_t)(((k >> 2) * HALF + (k & 3) * 32) >> 4),
+                      b_desc + (uint64_t)((k * 2048) >> 4), id_dk, k > 0 ? 1u : accum);
       };
       // dQ^T = K^T dS^T: [128 d] x [128 q] over the 128 kv rows
       auto issue_dq = [&]() {
@@ -272,74 +279,65 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attention_bwd_kernel(const __g
         tc_fence_after_sync();
         issue_kq(k_kmaj, q_kmaj0, 0);
         umma_commit(s_full);
-        ok = mbar_wait(v_full, 0, status, WAIT_SMEM_FULL) && mbar_wait(&do_full[0], 0, status, WAIT_SMEM_FULL);
+        ok = mbar_wait(v_full, 0, status, WAIT_SMEM_FULL) && mbar_wait(do_full, 0, status, WAIT_SMEM_FULL);
       }
       if (ok) {
         tc_fence_after_sync();
         issue_kq(v_kmaj, do_kmaj0, DP_COL0);
         umma_commit(dp_full);
       }
+      bool p_ready = false;
+      uint32_t qs = 0, qph = 0;  // ring position of Q(j)
       for (int j = 0; j < n_tiles && ok; ++j) {
-        const uint32_t st = j & 1, ph = j & 1;
-        const uint64_t st_off = (uint64_t)((st * L::Q_TILE) >> 4);
-        const uint32_t st1 = st ^ 1, sph1 = ((j + 1) >> 1) & 1;
-        const uint64_t st1_off = (uint64_t)((st1 * L::Q_TILE) >> 4);
+        const uint32_t ph = j & 1;
+        const uint64_t st_off = (uint64_t)((qs * L::Q_TILE) >> 4);
+        uint32_t qs1 = qs + 1, qph1 = qph;
+        if (qs1 == BWD_Q_STAGES) { qs1 = 0; qph1 ^= 1; }
+        const uint64_t st1_off = (uint64_t)((qs1 * L::Q_TILE) >> 4);
         const bool more = j + 1 < n_tiles;
+        // Each barrier is probed (test_wait) ahead of the MMA batch that precedes its use: a blocking
+        // wait costs this thread ~70 cycles even when the phase is already complete.
         // dV += P^T(j) dO(j)
-        if (!mbar_wait(p_full, ph, status, WAIT_ATTN)) { ok = false; break; }
+        if (!p_ready && !mbar_wait(p_full, ph, status, WAIT_ATTN)) { ok = false; break; }
         tc_fence_after_sync();
-        issue_acc(0, do_mnmaj0 + st_off, DV_COL0, j > 0 ? 1u : 0u);
-        umma_commit(&do_empty[st]);
+        bool q_ready = more && mbar_test(&q_full[qs1], qph1);
+        issue_dv(do_mnmaj0, j > 0 ? 1u : 0u);
+        umma_commit(do_empty);
         // S^T(j+1) over P^T(j)
+        bool ds_ready = false;
         if (more) {
-          if (!mbar_wait(&q_full[st1], sph1, status, WAIT_SMEM_FULL)) { ok = false; break; }
+          if (!q_ready && !mbar_wait(&q_full[qs1], qph1, status, WAIT_SMEM_FULL)) { ok = false; break; }
           tc_fence_after_sync();
+          ds_ready = mbar_test(ds_full, ph);
           issue_kq(k_kmaj, q_kmaj0 + st1_off, 0);
           umma_commit(s_full);
         }
-        // dK += dS^T(j) Q(j);  dQ^T(j) = K^T dS^T(j) over dS^T(j)
-        if (!mbar_wait(ds_full, ph, status, WAIT_ATTN)) { ok = false; break; }
+        // dQ^T(j) = K^T dS^T(j) over dP^T(j); then dK += dS^T(j) Q(j) while the reduction group
+        // reads dQ^T(j) out
+        if (!ds_ready && !mbar_wait(ds_full, ph, status, WAIT_ATTN)) { ok = false; break; }
         tc_fence_after_sync();
-        issue_acc(DP_COL0, q_mnmaj0 + st_off, DK_COL0, j > 0 ? 1u : 0u);
-        umma_commit(&q_empty[st]);
+        bool do_ready = more && mbar_test(do_full, ph ^ 1);
         issue_dq();
         umma_commit(dq_full);
+        issue_dk(q_mnmaj0 + st_off, j > 0 ? 1u : 0u);
+        umma_commit(&q_empty[qs]);
         // dP^T(j+1), once dQ^T(j) has left those columns
+        p_ready = false;
         if (more) {
-          if (!mbar_wait(&do_full[st1], sph1, status, WAIT_SMEM_FULL)) { ok = false; break; }
+          if (!do_ready && !mbar_wait(do_full, ph ^ 1, status, WAIT_SMEM_FULL)) { ok = false; break; }
           if (!mbar_wait(dq_empty, ph, status, WAIT_TMEM_EMPTY)) { ok = false; break; }
           tc_fence_after_sync();
-          issue_kq(v_kmaj, do_kmaj0 + st1_off, DP_COL0);
+          p_ready = mbar_test(p_full, ph ^ 1);
+          issue_kq(v_kmaj, do_kmaj0, DP_COL0);
           umma_commit(dp_full);
         }
+        qs = qs1;
+        qph = qph1;
       }
       if (ok) umma_commit(dkv_done);
     }
-  } else if (warp == 2) {
-    // ------------------------------------------------------------------ row statistics
-    reg_dealloc<96>();
-    for (int j = 0; j < n_tiles; ++j) {
-      const int q0 = bwd_tile(p, u, j) * BWD_BM;
-      const uint32_t st = j & 1, ph = (j >> 1) & 1;
-      if (!mbar_wait(&md_empty[st], ph ^ 1, status, WAIT_SMEM_EMPTY)) break;
-      float* dst = reinterpret_cast<float*>(smem + L::MD_OFFSET + st * L::MD_STAGE_BYTES);
-#pragma unroll
-      for (int h = 0; h < BWD_BM / 32; ++h) {
-        const int c = lane + 32 * h;
-        const int q = q0 + c;
-        float nl = -INFINITY, nd = 0.f;  // a query row past the end gets P = 0
-        if (q < p.s_q) {
-          const size_t idx = (size_t)u.bh * p.s_q + q;
-          nl = -__ldg(p.lse + idx);
-          nd = -__ldg(p.delta + idx);
-        }
-        dst[c] = nl;
-        dst[BWD_BM + c] = nd;
-      }
-      mbar_arrive(&md_full[st]);
-    }
-  } else if (warp == 3) {
-    reg_dealloc<96>();  // takes part in the warpgroup-wide register release only
+  } else if (warp < 4) {
+    reg_dealloc<96>();  // warps 2 and 3 take part in the warpgroup-wide register release only
   } else if (warp < 8) {
     // ------------------------------------------------------------------ dQ reduction
     reg_alloc<144>();
@@ -374,18 +372,28 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attention_bwd_kernel(const __g
     const uint32_t t_s = tmem_base + lane_off + g * 64;
     const uint32_t t_dp = tmem_base + lane_off + DP_COL0 + g * 64;
     uint8_t* ds_row = smem + L::DS_OFFSET + g * (L::DS_TILE / 2) + r * 128;
-    const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2);
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
       const uint32_t ph = j & 1;
-      const uint32_t st = j & 1, sph = (j >> 1) & 1;
       const int q0 = bwd_tile(p, u, j) * BWD_BM + g * 64;
+      // -LSE2 and -Delta of the group's 64 query columns: lane L keeps columns L and L + 32 and the
+      // loops below broadcast them with shuffles. (Reading them from shared memory inside the loops
+      // took ~1200 cycles per tile: ordinary shared-memory loads crawl while SS MMAs stream their
+      // operands.) The global loads are in flight during the wait for S^T.
+      float nl0 = -INFINITY, nl1 = -INFINITY, nd0 = 0.f, nd1 = 0.f;  // a query row past the end gets P = 0
+      {
+        const size_t base = (size_t)u.bh * p.s_q;
+        if (q0 + lane < p.s_q) {
+          nl0 = -__ldg(p.lse + base + q0 + lane);
+          nd0 = -__ldg(p.delta + base + q0 + lane);
+        }
+        if (q0 + 32 + lane < p.s_q) {
+          nl1 = -__ldg(p.lse + base + q0 + 32 + lane);
+          nd1 = -__ldg(p.delta + base + q0 + 32 + lane);
+        }
+      }
       if (!mbar_wait(s_full, ph, status, WAIT_ATTN)) { ok = false; break; }
-      if (!mbar_wait(&md_full[st], sph, status, WAIT_ATTN)) { ok = false; break; }
       tc_fence_after_sync();
-      const uint64_t* nlse =
-          reinterpret_cast<const uint64_t*>(smem + L::MD_OFFSET + st * L::MD_STAGE_BYTES) + g * 32;
-      const uint64_t* ndel = nlse + BWD_BM / 2;
       uint32_t pp[32];  // P^T of this tile as stored (16-bit pairs); dS^T is formed from these values
       uint32_t pk[32];
       {
@@ -400,13 +408,13 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attention_bwd_kernel(const __g
           for (int c = 0; c < 64; ++c)
             if (c < lim) sv[c] = 0xff800000u;
         }
+        const float scale = p.scale_log2;
 #pragma unroll
         for (int c = 0; c < 32; ++c) {
-          const uint64_t x =
-              fma2(pack2(__uint_as_float(sv[2 * c]), __uint_as_float(sv[2 * c + 1])), scale2, nlse[c]);
-          float x0, x1;
-          unpack2(x, x0, x1);
-          const float e0 = fast_exp2(x0), e1 = fast_exp2(x1);
+          const float a0 = __shfl_sync(0xffffffffu, c < 16 ? nl0 : nl1, (2 * c) & 31);
+          const float a1 = __shfl_sync(0xffffffffu, c < 16 ? nl0 : nl1, (2 * c + 1) & 31);
+          const float e0 = fast_exp2(fmaf(__uint_as_float(sv[2 * c]), scale, a0));
+          const float e1 = fast_exp2(fmaf(__uint_as_float(sv[2 * c + 1]), scale, a1));
           pp[c] = F16 ? pack_f16x2(e0, e1) : pack_bf16x2(e0, e1);
         }
       }
@@ -414,33 +422,34 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attention_bwd_kernel(const __g
       tmem_st_wait();
       tc_fence_before_sync();
       mbar_arrive(p_full);
-      // dS^T = P^T o (dP^T - Delta)
+      // dS^T = P^T o (dP^T - Delta), 16-bit, into shared memory: rows = kv, 64 query columns of this
+      // group as one 128-byte swizzled row (the MN-major B operand of dQ^T and the K-major A operand of dK)
       if (!mbar_wait(dp_full, ph, status, WAIT_ATTN)) { ok = false; break; }
       tc_fence_after_sync();
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        uint32_t dv[32];
-        tmem_ld_32x32b_x32(t_dp + h * 32, dv);
+      {
+        uint32_t dv[64];
+        tmem_ld_row64(t_dp, dv);
         tmem_ld_wait();
 #pragma unroll
-        for (int c = 0; c < 16; ++c) {
-          const uint64_t t =
-              add2(pack2(__uint_as_float(dv[2 * c]), __uint_as_float(dv[2 * c + 1])), ndel[h * 16 + c]);
-          float d0, d1;
-          unpack2(mul2(unpack16x2<F16>(pp[h * 16 + c]), t), d0, d1);
-          pk[h * 16 + c] = F16 ? pack_f16x2(d0, d1) : pack_bf16x2(d0, d1);
+        for (int ch = 0; ch < 8; ++ch) {  // one 16-byte chunk of the dS^T row: 8 query columns
+#pragma unroll
+          for (int h = 0; h < 4; ++h) {
+            const int c = 4 * ch + h;
+            const float b0 = __shfl_sync(0xffffffffu, c < 16 ? nd0 : nd1, (2 * c) & 31);
+            const float b1 = __shfl_sync(0xffffffffu, c < 16 ? nd0 : nd1, (2 * c + 1) & 31);
+            float p0, p1;
+            unpack2(unpack16x2<F16>(pp[c]), p0, p1);
+            const float a0 = p0 * (__uint_as_float(dv[2 * c]) + b0);
+            const float a1 = p1 * (__uint_as_float(dv[2 * c + 1]) + b1);
+            pk[c] = F16 ? pack_f16x2(a0, a1) : pack_bf16x2(a0, a1);
+          }
+          *reinterpret_cast<uint4*>(ds_row + ((ch ^ (r & 7)) << 4)) =
+              make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
         }
       }
-      tmem_st_32x32b_x32(t_dp, pk);
-#pragma unroll
-      for (int ch = 0; ch < 8; ++ch)
-        *reinterpret_cast<uint4*>(ds_row + ((ch ^ (r & 7)) << 4)) =
-            make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
-      tmem_st_wait();
       fence_proxy_async_smem();
-      tc_fence_before_sync();
+      tc_fence_before_sync();  // orders this thread's reads of dP^T before the dQ^T MMA that overwrites them
       mbar_arrive(ds_full);
-      mbar_arrive(&md_empty[st]);
     }
     // ---- epilogue: group 0 stores dV, group 1 stores sm_scale * dK
     const int kv = u.kv0 + r;
