@@ -18,10 +18,17 @@
 //   dK     += dS^T(j) Q(j)    SS (dS^T from shared memory, K-major), Q the MN-major B operand
 //   dQ^T(j) = K^T dS^T(j)     SS, both operands MN-major (K tile; the same dS^T tile),
 //                             128 (d) x 128 (q) x 128 (kv), written over dP
+// The per-query statistics enter through the MMAs: S^T and dP^T get a ninth K step whose B operand
+// row q holds -LSE2[q] / scale (three 16-bit parts) and -Delta[q] (three parts) and whose A operand
+// is a 0/1 selector, so the accumulators arrive as K Q^T - LSE2 / scale and dP^T - Delta and the
+// compute groups need no per-column operand. (Reading the statistics inside their loops, from shared
+// memory or by shuffle, cost 1000-1500 cycles per tile: such accesses crawl while SS MMAs stream
+// their operands through the shared-memory pipe.)
 // Tensor memory (512 columns): S (128) | dP (128) | dV (128) | dK (128).
 // Roles (512 threads):
 //   warp 0      TMA: K, V once; Q(j) through a three-deep ring of 128-row tiles, dO(j) through a single
 //               buffer (dV(j) frees it early in the iteration; dP^T(j+1) needs it at the end).
+//   warp 2      writes the statistics tile of each query tile (128 rows x 16 bytes).
 //   warp 1      one thread issues every MMA, in the order
 //                 dV(j) | S^T(j+1) | dQ^T(j), dK(j) | dP^T(j+1)
 //               so that the exponentials of tile j+1 run under dQ^T, dK and dP^T, and dQ^T(j) is
@@ -32,8 +39,8 @@
 //               summation order - and the last bits of dQ - vary from run to run, as they do with
 //               the reference's TMA reduce-add.
 //   warps 8-11 / 12-15   compute groups 0 / 1 own query columns 0-63 / 64-127 of every tile; thread t
-//               owns KV row t: P^T = exp2(S^T * scale - LSE2[q]) -> 16-bit -> TMEM (over the first
-//               32 columns of the group's half of S); dS^T = P^T o (dP^T - Delta[q]) -> 16-bit ->
+//               owns KV row t: P^T = exp2(scale * S') -> 16-bit -> TMEM (over the first 32 columns
+//               of the group's half of S); dS^T = P^T o dP' -> 16-bit ->
 //               shared memory, rows = kv with the 64 query columns of the group as one swizzled
 //               128-byte row: read as the MN-major B operand by dQ^T and as the K-major A operand by
 //               dK. dS^T is formed from the 16-bit P^T that dV also uses (32 registers instead of 64, which is
@@ -93,8 +100,11 @@ struct BwdSmem {
   static constexpr int Q_OFFSET = 2 * KV_TILE;
   static constexpr int DO_OFFSET = Q_OFFSET + BWD_Q_STAGES * Q_TILE;
   static constexpr int DS_OFFSET = DO_OFFSET + Q_TILE;
-  static constexpr int BAR_OFFSET = DS_OFFSET + DS_TILE;
-  static constexpr int NUM_BARS = 2 + 2 * BWD_Q_STAGES + 2 + 6 + 1;
+  // Row statistics ride on the MMAs as a ninth K step (see the header comment):
+  static constexpr int AUG_B_OFFSET = DS_OFFSET + DS_TILE;      // [128 q] x 8 values, 16 bytes per row
+  static constexpr int AUG_A_OFFSET = AUG_B_OFFSET + BWD_BM * 16;  // two selectors of 256 bytes
+  static constexpr int BAR_OFFSET = AUG_A_OFFSET + 512;
+  static constexpr int NUM_BARS = 2 + 2 * BWD_Q_STAGES + 2 + 2 + 6 + 1;
   // The tiles use all but a few hundred bytes of the 227 KB a CTA can have, so there is no room for
   // an alignment pad: the kernel checks that the dynamic window starts on a 1024-byte boundary.
   static constexpr int TOTAL = BAR_OFFSET + NUM_BARS * 8 + 16;
@@ -146,7 +156,9 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attention_bwd_kernel(const __g
   uint64_t* q_empty = q_full + BWD_Q_STAGES;     // [Q_STAGES]
   uint64_t* do_full = q_empty + BWD_Q_STAGES;    // [1]
   uint64_t* do_empty = do_full + 1;              // [1]
-  uint64_t* s_full = do_empty + 1;               // MMA -> compute: S^T ready
+  uint64_t* aug_full = do_empty + 1;             // statistics warp -> MMA (32 arrivals)
+  uint64_t* aug_empty = aug_full + 1;            // MMA -> statistics warp: dP^T(j) has read the tile
+  uint64_t* s_full = aug_empty + 1;              // MMA -> compute: S^T ready
   uint64_t* p_full = s_full + 1;                 // compute -> MMA: P^T in TMEM (256 arrivals)
   uint64_t* dp_full = p_full + 1;                // MMA -> compute: dP^T ready
   uint64_t* ds_full = dp_full + 1;               // compute -> MMA: dS^T in TMEM and smem (256)
@@ -177,6 +189,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attention_bwd_kernel(const __g
     }
     mbar_init(do_full, 1);
     mbar_init(do_empty, 1);
+    mbar_init(aug_full, 32);
+    mbar_init(aug_empty, 1);
     mbar_init(s_full, 1);
     mbar_init(p_full, 256);
     mbar_init(dp_full, 1);
@@ -239,15 +253,22 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attention_bwd_kernel(const __g
       const uint64_t ds_mnmaj = make_smem_desc(smem_a + L::DS_OFFSET, HALF, 1024, SWIZZLE_128B);
       const uint64_t ds_kmaj = make_smem_desc(smem_a + L::DS_OFFSET, 16, 1024, SWIZZLE_128B);
       const uint32_t id_dk = make_idesc(1u, 1u, 0u, 1u, BWD_BN, BWD_D) & ~fmt_fix;  // K-major A (smem), MN-major B
+      // ninth K step (unswizzled K-major core matrices of 8 rows x 16 bytes): the B operand has one
+      // 16-byte row per query (both K halves alias it: leading byte offset 0), the A operand is one
+      // 8-row selector repeated down the 128 kv rows (stride byte offset 0)
+      const uint64_t aug_b = make_smem_desc(smem_a + L::AUG_B_OFFSET, 0, 128, SWIZZLE_NONE);
+      const uint64_t aug_a_s = make_smem_desc(smem_a + L::AUG_A_OFFSET, 128, 0, SWIZZLE_NONE);
+      const uint64_t aug_a_dp = make_smem_desc(smem_a + L::AUG_A_OFFSET + 256, 128, 0, SWIZZLE_NONE);
       bool ok = true;
 
-      // S^T or dP^T: [128 kv] x [128 q] over D, both operands K-major
-      auto issue_kq = [&](uint64_t a_desc, uint64_t b_desc, uint32_t d_col) {
+      // S^T or dP^T: [128 kv] x [128 q] over D, both operands K-major, plus the statistics step
+      auto issue_kq = [&](uint64_t a_desc, uint64_t b_desc, uint32_t d_col, uint64_t a_aug) {
 #pragma unroll
         for (int k = 0; k < BWD_D / 16; ++k) {
           const uint64_t o = (uint64_t)(((k >> 2) * HALF + (k & 3) * 32) >> 4);
           umma_f16_ss(tmem_base + d_col, a_desc + o, b_desc + o, id_st, k > 0 ? 1u : 0u);
         }
+        umma_f16_ss(tmem_base + d_col, a_aug, aug_b, id_st, 1u);
       };
       // dV += P^T dO: A = 16-bit [128 kv] x [128 q] in TMEM (32 columns at 0 and 32 at 64),
       // B = dO as [128 q] x [128 d]
@@ -274,17 +295,19 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attention_bwd_kernel(const __g
       };
 
       // prologue: S^T(0), dP^T(0)
-      ok = mbar_wait(k_full, 0, status, WAIT_SMEM_FULL) && mbar_wait(&q_full[0], 0, status, WAIT_SMEM_FULL);
+      ok = mbar_wait(k_full, 0, status, WAIT_SMEM_FULL) && mbar_wait(&q_full[0], 0, status, WAIT_SMEM_FULL) &&
+           mbar_wait(aug_full, 0, status, WAIT_SMEM_FULL);
       if (ok) {
         tc_fence_after_sync();
-        issue_kq(k_kmaj, q_kmaj0, 0);
+        issue_kq(k_kmaj, q_kmaj0, 0, aug_a_s);
         umma_commit(s_full);
         ok = mbar_wait(v_full, 0, status, WAIT_SMEM_FULL) && mbar_wait(do_full, 0, status, WAIT_SMEM_FULL);
       }
       if (ok) {
         tc_fence_after_sync();
-        issue_kq(v_kmaj, do_kmaj0, DP_COL0);
+        issue_kq(v_kmaj, do_kmaj0, DP_COL0, aug_a_dp);
         umma_commit(dp_full);
+        umma_commit(aug_empty);
       }
       bool p_ready = false;
       uint32_t qs = 0, qph = 0;  // ring position of Q(j)
@@ -300,16 +323,17 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attention_bwd_kernel(const __g
         // dV += P^T(j) dO(j)
         if (!p_ready && !mbar_wait(p_full, ph, status, WAIT_ATTN)) { ok = false; break; }
         tc_fence_after_sync();
-        bool q_ready = more && mbar_test(&q_full[qs1], qph1);
+        bool q_ready = more && mbar_test(&q_full[qs1], qph1) && mbar_test(aug_full, ph ^ 1);
         issue_dv(do_mnmaj0, j > 0 ? 1u : 0u);
         umma_commit(do_empty);
         // S^T(j+1) over P^T(j)
         bool ds_ready = false;
         if (more) {
-          if (!q_ready && !mbar_wait(&q_full[qs1], qph1, status, WAIT_SMEM_FULL)) { ok = false; break; }
+          if (!q_ready && !(mbar_wait(&q_full[qs1], qph1, status, WAIT_SMEM_FULL) &&
+                            mbar_wait(aug_full, ph ^ 1, status, WAIT_SMEM_FULL))) { ok = false; break; }
           tc_fence_after_sync();
           ds_ready = mbar_test(ds_full, ph);
-          issue_kq(k_kmaj, q_kmaj0 + st1_off, 0);
+          issue_kq(k_kmaj, q_kmaj0 + st1_off, 0, aug_a_s);
           umma_commit(s_full);
         }
         // dQ^T(j) = K^T dS^T(j) over dP^T(j); then dK += dS^T(j) Q(j) while the reduction group
@@ -328,16 +352,80 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attention_bwd_kernel(const __g
           if (!mbar_wait(dq_empty, ph, status, WAIT_TMEM_EMPTY)) { ok = false; break; }
           tc_fence_after_sync();
           p_ready = mbar_test(p_full, ph ^ 1);
-          issue_kq(v_kmaj, do_kmaj0, DP_COL0);
+          issue_kq(v_kmaj, do_kmaj0, DP_COL0, aug_a_dp);
           umma_commit(dp_full);
+          umma_commit(aug_empty);
         }
         qs = qs1;
         qph = qph1;
       }
       if (ok) umma_commit(dkv_done);
     }
-  } else if (warp < 4) {
-    reg_dealloc<96>();  // warps 2 and 3 take part in the warpgroup-wide register release only
+  } else if (warp == 2) {
+    // ------------------------------------------------------------------ row statistics
+    reg_dealloc<96>();
+    // selectors: ones in K columns 0-2 (S^T step) / 3-5 (dP^T step) of the first K half, zero elsewhere
+    {
+      const uint16_t one = F16 ? 0x3C00 : 0x3F80;
+      uint16_t* a = reinterpret_cast<uint16_t*>(smem + L::AUG_A_OFFSET);
+      for (int i = lane; i < 256; i += 32) {  // 2 selectors x 2 core matrices x 8 rows x 8 values
+        const int sel = i >> 7, half = (i >> 6) & 1, col = i & 7;
+        a[i] = (half == 0 && col >= 3 * sel && col < 3 * sel + 3) ? one : (uint16_t)0;
+      }
+    }
+    const float inv_scale = 1.f / p.scale_log2;
+    for (int j = 0; j < n_tiles; ++j) {
+      const int q0 = bwd_tile(p, u, j) * BWD_BM;
+      // a query row past the end gets zeros: S' = 0, P = 1, and its dO row and Delta are zero, so it
+      // contributes nothing. The loads are issued before the wait for the buffer.
+      float vals[BWD_BM / 32][2];
+#pragma unroll
+      for (int h = 0; h < BWD_BM / 32; ++h) {
+        const int q = q0 + lane + 32 * h;
+        vals[h][0] = 0.f;
+        vals[h][1] = 0.f;
+        if (q < p.s_q) {
+          const size_t idx = (size_t)u.bh * p.s_q + q;
+          vals[h][0] = -__ldg(p.lse + idx) * inv_scale;
+          vals[h][1] = -__ldg(p.delta + idx);
+        }
+      }
+      // the tile of step j-1 was last read by dP^T(j-1)
+      if (!mbar_wait(aug_empty, (j & 1) ^ 1, status, WAIT_SMEM_EMPTY)) break;
+#pragma unroll
+      for (int h = 0; h < BWD_BM / 32; ++h) {
+        // each value as three 16-bit parts (hi + mid + lo, ~24 bits together); the MMA multiplies
+        // them by 1 and adds them in fp32
+        uint16_t w[8];
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          float rem = vals[h][t];
+#pragma unroll
+          for (int part = 0; part < 3; ++part) {
+            float back;
+            if (F16) {
+              const __half hv = __float2half_rn(rem);
+              w[3 * t + part] = __half_as_ushort(hv);
+              back = __half2float(hv);
+            } else {
+              const __nv_bfloat16 bv = __float2bfloat16_rn(rem);
+              w[3 * t + part] = __bfloat16_as_ushort(bv);
+              back = __bfloat162float(bv);
+            }
+            rem -= back;
+          }
+        }
+        w[6] = 0;
+        w[7] = 0;
+        *reinterpret_cast<uint4*>(smem + L::AUG_B_OFFSET + (lane + 32 * h) * 16) =
+            make_uint4(w[0] | ((uint32_t)w[1] << 16), w[2] | ((uint32_t)w[3] << 16), w[4] | ((uint32_t)w[5] << 16),
+                       w[6] | ((uint32_t)w[7] << 16));
+      }
+      fence_proxy_async_smem();
+      mbar_arrive(aug_full);
+    }
+  } else if (warp == 3) {
+    reg_dealloc<96>();  // takes part in the warpgroup-wide register release only
   } else if (warp < 8) {
     // ------------------------------------------------------------------ dQ reduction
     reg_alloc<144>();
@@ -376,22 +464,6 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attention_bwd_kernel(const __g
     for (int j = 0; j < n_tiles; ++j) {
       const uint32_t ph = j & 1;
       const int q0 = bwd_tile(p, u, j) * BWD_BM + g * 64;
-      // -LSE2 and -Delta of the group's 64 query columns: lane L keeps columns L and L + 32 and the
-      // loops below broadcast them with shuffles. (Reading them from shared memory inside the loops
-      // took ~1200 cycles per tile: ordinary shared-memory loads crawl while SS MMAs stream their
-      // operands.) The global loads are in flight during the wait for S^T.
-      float nl0 = -INFINITY, nl1 = -INFINITY, nd0 = 0.f, nd1 = 0.f;  // a query row past the end gets P = 0
-      {
-        const size_t base = (size_t)u.bh * p.s_q;
-        if (q0 + lane < p.s_q) {
-          nl0 = -__ldg(p.lse + base + q0 + lane);
-          nd0 = -__ldg(p.delta + base + q0 + lane);
-        }
-        if (q0 + 32 + lane < p.s_q) {
-          nl1 = -__ldg(p.lse + base + q0 + 32 + lane);
-          nd1 = -__ldg(p.delta + base + q0 + 32 + lane);
-        }
-      }
       if (!mbar_wait(s_full, ph, status, WAIT_ATTN)) { ok = false; break; }
       tc_fence_after_sync();
       uint32_t pp[32];  // P^T of this tile as stored (16-bit pairs); dS^T is formed from these values
@@ -408,13 +480,13 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attention_bwd_kernel(const __g
           for (int c = 0; c < 64; ++c)
             if (c < lim) sv[c] = 0xff800000u;
         }
-        const float scale = p.scale_log2;
+        // S' already holds K Q^T - LSE2 / scale (ninth K step), so P^T = exp2(scale * S')
+        const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2);
 #pragma unroll
         for (int c = 0; c < 32; ++c) {
-          const float a0 = __shfl_sync(0xffffffffu, c < 16 ? nl0 : nl1, (2 * c) & 31);
-          const float a1 = __shfl_sync(0xffffffffu, c < 16 ? nl0 : nl1, (2 * c + 1) & 31);
-          const float e0 = fast_exp2(fmaf(__uint_as_float(sv[2 * c]), scale, a0));
-          const float e1 = fast_exp2(fmaf(__uint_as_float(sv[2 * c + 1]), scale, a1));
+          float x0, x1;
+          unpack2(mul2(pack2(__uint_as_float(sv[2 * c]), __uint_as_float(sv[2 * c + 1])), scale2), x0, x1);
+          const float e0 = fast_exp2(x0), e1 = fast_exp2(x1);
           pp[c] = F16 ? pack_f16x2(e0, e1) : pack_bf16x2(e0, e1);
         }
       }
@@ -435,12 +507,10 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attention_bwd_kernel(const __g
 #pragma unroll
           for (int h = 0; h < 4; ++h) {
             const int c = 4 * ch + h;
-            const float b0 = __shfl_sync(0xffffffffu, c < 16 ? nd0 : nd1, (2 * c) & 31);
-            const float b1 = __shfl_sync(0xffffffffu, c < 16 ? nd0 : nd1, (2 * c + 1) & 31);
-            float p0, p1;
+            float p0, p1;  // dP' already holds dP^T - Delta (ninth K step)
             unpack2(unpack16x2<F16>(pp[c]), p0, p1);
-            const float a0 = p0 * (__uint_as_float(dv[2 * c]) + b0);
-            const float a1 = p1 * (__uint_as_float(dv[2 * c + 1]) + b1);
+            const float a0 = p0 * __uint_as_float(dv[2 * c]);
+            const float a1 = p1 * __uint_as_float(dv[2 * c + 1]);
             pk[c] = F16 ? pack_f16x2(a0, a1) : pack_bf16x2(a0, a1);
           }
           *reinterpret_cast<uint4*>(ds_row + ((ch ^ (r & 7)) << 4)) =
