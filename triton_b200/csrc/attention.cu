@@ -42,6 +42,9 @@ static constexpr int ATT_BM = 128;   // query rows per group
 static constexpr int ATT_BN = 128;   // kv rows per block
 static constexpr int ATT_KV_STAGES = 4;
 static constexpr float ATT_RESCALE_THRESHOLD = 8.0f;
+#ifndef ATT_PV_SLICES
+#define ATT_PV_SLICES 4  // PV_g is issued in this many slices as P is published
+#endif
 
 struct AttnParams {
   CUtensorMap tmq, tmk, tmv;  // 3-D (D, S, B*H), box (64, 128, 1), 128-byte swizzle
@@ -211,12 +214,16 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_fwd_kernel(const __g
         const uint32_t d_o = tmem_base + O_COL0 + g * D;
         const uint32_t a_p = tmem_base + g * S_COLS;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          if (!ready && !mbar_wait(&p_full[g * 4 + c], iph, status, WAIT_ATTN)) return false;
+        for (int c = 0; c < ATT_PV_SLICES; ++c) {
+          // the softmax publishes P in four 32-column chunks; a slice waits for its last chunk (a
+          // thread arrives on the chunk barriers in order)
+          constexpr int CH = 4 / ATT_PV_SLICES;
+          if (!ready && !mbar_wait(&p_full[g * 4 + c * CH + CH - 1], iph, status, WAIT_ATTN)) return false;
           tc_fence_after_sync();
-          if (c < 3) ready = mbar_test(&p_full[g * 4 + c + 1], iph);  // probe ahead of this slice's MMAs
+          if (c + 1 < ATT_PV_SLICES)
+            ready = mbar_test(&p_full[g * 4 + (c + 1) * CH + CH - 1], iph);  // probe ahead of this slice's MMAs
 #pragma unroll
-          for (int k = 2 * c; k < 2 * c + 2; ++k)
+          for (int k = 2 * CH * c; k < 2 * CH * (c + 1); ++k)
             umma_f16_ts(d_o, a_p + k * 8, vd + (uint64_t)((k * 16 * 128) >> 4), idp, (k > 0) ? 1u : accum);
         }
         // S_g(j+1) is committed after this in the same in-order stream, so only the last PV of a
@@ -264,12 +271,12 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_fwd_kernel(const __g
           if (!mbar_wait(&kv_full[vcur], vcur_ph, status, WAIT_SMEM_FULL)) { ok = false; break; }
           if (j == 0 && !mbar_wait(&o_free[0], tph ^ 1, status, WAIT_ATTN)) { ok = false; break; }
           bool k_ready = more && mbar_test(&kv_full[knext], knext_ph);
-          if (!issue_pv(0, vcur, j > 0 ? 1u : 0u, iph, mbar_test(&p_full[0], iph), !more)) { ok = false; break; }
+          if (!issue_pv(0, vcur, j > 0 ? 1u : 0u, iph, mbar_test(&p_full[4 / ATT_PV_SLICES - 1], iph), !more)) { ok = false; break; }
           bool p1_ready = false;
           if (more) {
             if (!k_ready && !mbar_wait(&kv_full[knext], knext_ph, status, WAIT_SMEM_FULL)) { ok = false; break; }
             tc_fence_after_sync();
-            p1_ready = mbar_test(&p_full[4], iph);
+            p1_ready = mbar_test(&p_full[4 + 4 / ATT_PV_SLICES - 1], iph);
             issue_qk(0, knext);
             if (j + 2 == t.nkv) umma_commit(&q_empty[0]);
           }
