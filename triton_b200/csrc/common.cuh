@@ -135,6 +135,19 @@ __device__ __forceinline__ bool mbar_try_wait_a(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+__device__ __forceinline__ bool mbar_test_a(uint32_t bar, uint32_t parity) {  // non-blocking probe, see mbar_test
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 static __device__ __noinline__ bool mbar_wait_slow_a(uint32_t bar, uint32_t parity, int* status, int code) {
   uint64_t t0 = 0;
   uint32_t spins = 0;

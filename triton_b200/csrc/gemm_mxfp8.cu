@@ -148,7 +148,7 @@ __global__ void __launch_bounds__(MX_THREADS, 1) gemm_mxfp8_kernel(const __grid_
       const uint64_t sfdesc0 = make_smem_desc(smem_a + L::SF_OFFSET, 16, 128, SWIZZLE_NONE);
       const uint32_t tfull_a = smem_u32(tfull), tempty_a = smem_u32(tempty);
       uint32_t s = 0, ph = 0, tcount = 0, kpar = 0;
-      bool ok = true;
+      bool ok = true, ready = false;
       for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x, ++tcount) {
         const uint32_t acc = tcount % NACC;
         const uint32_t aph = (tcount / NACC) & 1;
@@ -163,11 +163,15 @@ __global__ void __launch_bounds__(MX_THREADS, 1) gemm_mxfp8_kernel(const __grid_
         // 5-10 % here, and scale copies placed between MMAs lost 13 %.)
         uint32_t accum = 0;
         for (int kb = 0; kb < k_blocks; ++kb) {
-          if (!mbar_wait_a(full_a + s * 8, ph, status, WAIT_SMEM_FULL)) {
+          if (!ready && !mbar_wait_a(full_a + s * 8, ph, status, WAIT_SMEM_FULL)) {
             ok = false;
             break;
           }
           tc_fence_after_sync();
+          {  // probe the next stage ahead of this stage's MMAs (a blocking wait costs ~70 cycles even when ready)
+            const uint32_t s1 = (s + 1 == STAGES) ? 0 : s + 1;
+            ready = mbar_test_a(full_a + s1 * 8, s1 == 0 ? ph ^ 1 : ph);
+          }
           const uint32_t t_sfa = tmem_base + SF_COL0 + kpar * 16;
           const uint32_t t_sfb = t_sfa + 4;
           const uint64_t sfd = sfdesc0 + (uint64_t)((s * L::SF_BYTES) >> 4);
@@ -366,18 +370,22 @@ __global__ void __launch_bounds__(MX_THREADS, 1) gemm_mxfp8_pair_kernel(const __
       const uint32_t tfull_a = smem_u32(tfull), tempty_a = smem_u32(tempty);
       const uint32_t peer_delta = mapa_shared(empty_a, 1) - empty_a;
       uint32_t s = 0, ph = 0, tcount = 0, kpar = 0;
-      bool ok = true;
+      bool ok = true, ready = false;
       for (int unit = worker; unit < units && ok; unit += num_workers, ++tcount) {
         if (!mbar_wait_a(tempty_a, (tcount & 1) ^ 1, status, WAIT_TMEM_EMPTY)) break;
         tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base;
         uint32_t accum = 0;
         for (int kb = 0; kb < k_blocks; ++kb) {
-          if (!mbar_wait_a(full_a + s * 8, ph, status, WAIT_SMEM_FULL)) {
+          if (!ready && !mbar_wait_a(full_a + s * 8, ph, status, WAIT_SMEM_FULL)) {
             ok = false;
             break;
           }
           tc_fence_after_sync();
+          {  // probe the next stage ahead of this stage's MMAs (a blocking wait costs ~70 cycles even when ready)
+            const uint32_t s1 = (s + 1 == STAGES) ? 0 : s + 1;
+            ready = mbar_test_a(full_a + s1 * 8, s1 == 0 ? ph ^ 1 : ph);
+          }
           const uint32_t t_sfa = tmem_base + SF_COL0 + kpar * 16;
           const uint32_t t_sfb = t_sfa + 4;
           const uint64_t sfd = sfdesc0 + (uint64_t)((s * L::SF_BYTES) >> 4);
