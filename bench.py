@@ -135,7 +135,7 @@ def build_workload(name: str, rank: int, dev):
         return (lambda: attention_backward(q, k, v, o, lse, do, sc, causal), fl, 8.0 * B * H * S * D * 2,
                 f"flash-attention bwd bf16 [B={B},H={H},S={S},D={D}] causal={causal} (delta + main + dq kernels), seed 2",
                 "attention_bwd_kernel", "tensor")
-    if name in ("fp8", "mxfp8"):
+    if name in ("fp8", "fp8_blockwise", "mxfp8"):
         n = 8192
         a = (torch.randn(n, n, generator=g) * 0.1).to(torch.float8_e4m3fn).to(dev)
         b = (torch.randn(n, n, generator=g) * 0.1).to(torch.float8_e4m3fn).to(dev)
@@ -144,6 +144,13 @@ def build_workload(name: str, rank: int, dev):
             sa, sb = torch.rand(1, generator=g).to(dev), torch.rand(1, generator=g).to(dev)
             return (lambda: blackwell_scaled_mm_ws(a, b, sa, sb, scale_mode="tensorwise"), 2.0 * n ** 3, 3.0 * n * n,
                     "per-tensor-scaled e4m3 GEMM 8192^3, bf16 out", "gemm_kernel<128,7,pair,f8>", "tensor")
+        if name == "fp8_blockwise":
+            from triton_b200.tutorials.blackwell_scaled_mm_ws import blackwell_scaled_mm_ws
+            sa = torch.rand(n, n // 128, generator=g).t().contiguous().t().to(dev)
+            sb = torch.rand(n // 128, n // 128, generator=g).to(dev)
+            return (lambda: blackwell_scaled_mm_ws(a, b, sa, sb, scale_mode="blockwise"), 2.0 * n ** 3, 3.0 * n * n,
+                    "blockwise-scaled (128-wide K groups) e4m3 GEMM 8192^3, bf16 out", "gemm_fp8_blockwise_kernel",
+                    "tensor")
         from triton_b200.tutorials.blackwell_gemm_ws_mxfp8 import matmul as mx_matmul
         u = torch.randint(-4, 5, (n * n // 32, ), generator=g)
         sc = (u + 127).to(torch.uint8).to(dev).view(torch.float8_e8m0fnu)
@@ -255,7 +262,7 @@ def run_extra_workload(args, rank, local_rank, world):
             "metric": f"{args.workload} throughput", "value": tf, "unit": "TFLOP/s", "n_gpus": world, "steps": steps,
             "warmup": warmup, "ms_per_step": ms, "higher_is_better": True,
             "scaling": "strong" if args.workload == "moe_ep" else "weak", "vs_baseline": None,
-            "dtype": "e4m3" if args.workload in ("fp8", "mxfp8") else "bf16", "data": "synthetic",
+            "dtype": "e4m3" if args.workload in ("fp8", "fp8_blockwise", "mxfp8") else "bf16", "data": "synthetic",
             "config": {"workload": desc},
             "roofline": {"bound": bound, "achieved": ach, "peak": peak, "unit": unit, "frac": ach / peak,
                          "traffic": None, "kernel": kernel,
@@ -343,7 +350,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--workload", default="gemm",
                     help="gemm (headline, default) | attn | attn_causal | attn_short | attn_short_causal | attn_bwd | "
-                         "attn_bwd_causal | attn_bwd_ref_shape[_causal] | fp8 | mxfp8 | moe | moe_decode | moe_ep")
+                         "attn_bwd_causal | attn_bwd_ref_shape[_causal] | fp8 | fp8_blockwise | mxfp8 | moe | moe_decode | moe_ep")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))

@@ -131,6 +131,29 @@ typedef struct {
 
 int tb200_gemm_mxfp8(const tb200_gemm_mxfp8_args* args, void* stream);
 
+/*
+ * Block-wise scaled FP8 GEMM: C[m,n] = sum over 128-wide K groups g of
+ *   (A[m, g] . B[n, g]) * scale_a[m, g] * scale_b[n / 128, g].
+ * Stands behind: third_party/tlx/tutorials/blackwell_scaled_mm_ws.py:392
+ *   blackwell_scaled_mm_ws(a, b, scale_a, scale_b, ..., scale_mode="blockwise")  (promotion :300-341).
+ * a [M, K], b [N, K] fp8 row-major (in_dtype TB200_E4M3 or TB200_E5M2); K % 128 == 0, N % 128 == 0;
+ * scale_a: float, M-major ([K/128][M] in memory: element (m, g) at g * M + m);
+ * scale_b: float [N/128][K/128] row-major; c [M, N] with row pitch ldc, out_dtype TB200_BF16, _F16 or _F32.
+ */
+typedef struct {
+  const void* a;
+  const void* b;
+  void* c;
+  const float* scale_a;
+  const float* scale_b;
+  int64_t m, n, k;
+  int64_t ldc;
+  int32_t in_dtype;
+  int32_t out_dtype;
+} tb200_gemm_fp8_blockwise_args;
+
+int tb200_gemm_fp8_blockwise(const tb200_gemm_fp8_blockwise_args* args, void* stream);
+
 /* ---------------------------------------------------------------- attention -------- */
 
 /*

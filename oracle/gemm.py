@@ -28,3 +28,18 @@ def scaled_mm_rowwise_ref(a, b, scale_a, scale_b, out_dtype=torch.bfloat16):
     (ScaledMM.get_reference, rowwise branch, test_correctness.py:548-551)."""
     prod = a.detach().cpu().float() @ b.detach().cpu().float().t()
     return (prod * scale_a.detach().cpu().float()[:, None] * scale_b.detach().cpu().float()[None, :]).to(out_dtype)
+
+
+def scaled_mm_blockwise_ref(a, b, scale_a, scale_b, out_dtype=torch.bfloat16):
+    """Blockwise (DeepSeek) scaled matmul: every 128-wide K group of A @ B^T is multiplied by
+    scale_a[:, g] (per row) and scale_b[n // 128, g] (per 128-column block) before it is summed —
+    ``ScaledMM.get_reference``, blockwise branch (``testing/test_correctness.py:535-547``)."""
+    af, bf = a.detach().cpu().float(), b.detach().cpu().float()
+    sa, sb = scale_a.detach().cpu().float(), scale_b.detach().cpu().float()
+    M, K = af.shape
+    N = bf.shape[0]
+    out = torch.zeros(M, N, dtype=torch.float32)
+    for g in range(K // 128):
+        partial = af[:, g * 128:(g + 1) * 128] @ bf[:, g * 128:(g + 1) * 128].t()
+        out += partial * sa[:, g][:, None] * sb[:, g].repeat_interleave(128)[None, :]
+    return out.to(out_dtype)

@@ -42,14 +42,50 @@ def test_scaled_mm_rowwise(cuda, shape):
     torch.testing.assert_close(out.cpu().float(), ref.float(), atol=1e-3, rtol=1e-2)
 
 
-def test_scaled_mm_other_modes_raise(cuda):
+@pytest.mark.parametrize("shape", [(1024, 1024, 1024), (384, 256, 640), (200, 128, 256), (4096, 2048, 4096)])
+def test_scaled_mm_blockwise(cuda, shape):
+    """DeepSeek blockwise: scale_a [M, K//128] M-major, scale_b [N//128, K//128]; inputs as in the
+    reference's ScaledMM.create_inputs (test_correctness.py:518-532), its tolerance atol 0.1 / rtol 0.05, and
+    a tighter bound near bf16 rounding of the fp32 result."""
+    from triton_b200.tutorials.blackwell_scaled_mm_ws import blackwell_scaled_mm_ws
+    M, N, K = shape
+    torch.manual_seed(0)
+    a = (torch.randn(M, K) * 0.1).to(torch.float8_e4m3fn)
+    b = (torch.randn(N, K) * 0.1).to(torch.float8_e4m3fn)
+    sa = torch.rand(M, K // 128).t().contiguous().t()  # M-major
+    sb = torch.rand(N // 128, K // 128)
+    out = blackwell_scaled_mm_ws(a.to(cuda), b.to(cuda), sa.to(cuda), sb.to(cuda))  # blockwise is the default mode
+    ref = o_gemm.scaled_mm_blockwise_ref(a, b, sa, sb)
+    torch.testing.assert_close(out.cpu().float(), ref.float(), atol=0.1, rtol=0.05)
+    torch.testing.assert_close(out.cpu().float(), ref.float(), atol=2e-3, rtol=1e-2)
+
+
+def test_scaled_mm_blockwise_exact_powers_of_two(cuda):
+    """Power-of-two data and scales: every product and partial sum is exact, so the fp32 output must equal
+    the oracle bit for bit (checks group/row/block indexing at a non-trivial size, fp32 out, row-major scale_a)."""
+    from triton_b200.tutorials.blackwell_scaled_mm_ws import blackwell_scaled_mm_ws
+    M, N, K = 512, 640, 1024
+    g = torch.Generator().manual_seed(5)
+    a = torch.pow(2.0, torch.randint(-3, 3, (M, K), generator=g).float()).to(torch.float8_e4m3fn)
+    b = torch.pow(2.0, torch.randint(-3, 3, (N, K), generator=g).float()).to(torch.float8_e4m3fn)
+    sa = torch.pow(2.0, torch.randint(-4, 4, (M, K // 128), generator=g).float())
+    sb = torch.pow(2.0, torch.randint(-4, 4, (N // 128, K // 128), generator=g).float())
+    out = blackwell_scaled_mm_ws(a.to(cuda), b.to(cuda), sa.to(cuda), sb.to(cuda), out_dtype=torch.float32,
+                                 scale_mode="blockwise")
+    ref = o_gemm.scaled_mm_blockwise_ref(a, b, sa, sb, out_dtype=torch.float32)
+    assert torch.equal(out.cpu(), ref)
+
+
+def test_scaled_mm_argument_checks(cuda):
     from triton_b200.tutorials.blackwell_scaled_mm_ws import blackwell_scaled_mm_ws
     a = torch.zeros(128, 128, device=cuda).to(torch.float8_e4m3fn)
     s = torch.ones(1, device=cuda)
-    with pytest.raises(NotImplementedError):
-        blackwell_scaled_mm_ws(a, a, s, s, scale_mode="blockwise")
+    with pytest.raises(AssertionError):
+        blackwell_scaled_mm_ws(a, a, s, s, scale_mode="blockwise")  # scalar scales are not blockwise scales
     with pytest.raises(AssertionError):
         blackwell_scaled_mm_ws(a[:, :64].contiguous(), a[:, :64].contiguous(), s, s, scale_mode="tensorwise")
+    with pytest.raises(KeyError):
+        blackwell_scaled_mm_ws(a, a, s, s, scale_mode="columnwise")
 
 
 def _mx_case(cuda, M, N, K, bn, seed=3):

@@ -101,6 +101,18 @@ def test_mxfp8_dequant_known_values():
     assert torch.all(d == 12.0)
 
 
+def test_scaled_mm_blockwise_oracle_equals_dequantised_matmul():
+    """Blockwise scaling is the same as multiplying each operand element by its own block's scale first
+    when scale_b is folded into B (the DeepSeek definition)."""
+    torch.manual_seed(2)
+    M, N, K = 64, 256, 384
+    a, b = torch.randn(M, K), torch.randn(N, K)
+    sa, sb = torch.rand(M, K // 128) + 0.5, torch.rand(N // 128, K // 128) + 0.5
+    want = (a * sa.repeat_interleave(128, dim=1)) @ (b * sb.repeat_interleave(128, 0).repeat_interleave(128, 1)).t()
+    got = o_gemm.scaled_mm_blockwise_ref(a, b, sa, sb, out_dtype=torch.float32)
+    torch.testing.assert_close(got, want, atol=1e-4, rtol=1e-5)
+
+
 def test_attention_oracle_matches_sdpa():
     torch.manual_seed(0)
     q, k, v = (torch.randn(1, 2, 96, 32) for _ in range(3))

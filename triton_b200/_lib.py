@@ -45,6 +45,14 @@ class GemmMxfp8Args(Structure):
     ]
 
 
+class GemmFp8BlockwiseArgs(Structure):
+    _fields_ = [
+        ("a", c_void_p), ("b", c_void_p), ("c", c_void_p), ("scale_a", c_void_p), ("scale_b", c_void_p),
+        ("m", c_int64), ("n", c_int64), ("k", c_int64), ("ldc", c_int64),
+        ("in_dtype", c_int32), ("out_dtype", c_int32),
+    ]
+
+
 class AttentionArgs(Structure):
     _fields_ = [
         ("q", c_void_p), ("k", c_void_p), ("v", c_void_p), ("o", c_void_p), ("lse", c_void_p),
@@ -149,6 +157,8 @@ def _declare(l: ctypes.CDLL) -> None:
     l.tb200_move_rows.argtypes = [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int32, c_void_p]
     l.tb200_bitmatrix_metadata_workspace_bytes.restype = c_size_t
     l.tb200_bitmatrix_metadata_workspace_bytes.argtypes = [c_int64, c_int32]
+    l.tb200_gemm_fp8_blockwise.restype = c_int
+    l.tb200_gemm_fp8_blockwise.argtypes = [POINTER(GemmFp8BlockwiseArgs), c_void_p]
     l.tb200_gemm_mxfp8.restype = c_int
     l.tb200_gemm_mxfp8.argtypes = [POINTER(GemmMxfp8Args), c_void_p]
 

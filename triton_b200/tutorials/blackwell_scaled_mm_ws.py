@@ -3,9 +3,10 @@ scaled matmul, ``third_party/tlx/tutorials/blackwell_scaled_mm_ws.py:392``.
 
 ``a`` [M, K] and ``b`` [N, K] are ``float8_e4m3fn`` (row-major; computes ``A @ B^T``), the result is
 ``out_dtype`` (bf16 by default). ``scale_mode="tensorwise"`` (one fp32 scalar per operand) and
-``"rowwise"`` (``scale_a`` [M] per row of A, ``scale_b`` [N] per row of B), both applied once after the
-K loop, are built here; ``"blockwise"`` (128-wide K groups promoted in registers) raises
-``NotImplementedError``. The tiling arguments (``BLOCK_M``, ``BLOCK_N``, ``NUM_CTAS``, ``USE_CLC``,
+``"rowwise"`` (``scale_a`` [M] per row of A, ``scale_b`` [N] per row of B) are applied once after the
+K loop; ``"blockwise"`` (the default, as in the reference: ``scale_a`` [M, K//128] M-major, ``scale_b``
+[N//128, K//128], every 128-wide K group scaled and promoted into an fp32 running sum) runs its own
+kernel. The tiling arguments (``BLOCK_M``, ``BLOCK_N``, ``NUM_CTAS``, ``USE_CLC``,
 ``EPI_SUB``, ``persistent``) are accepted for call compatibility; the kernel picks its own tiling
 (``NUM_CTAS=2`` forces the CTA-pair tiling). Same shape assertions as the reference (``:408``).
 """
@@ -25,8 +26,6 @@ def blackwell_scaled_mm_ws(a, b, scale_a, scale_b, out_dtype=torch.bfloat16, BLO
                            USE_CLC=False, EPI_SUB=2, persistent=True, scale_mode="blockwise"):
     if scale_mode not in ("blockwise", "rowwise", "tensorwise"):
         raise KeyError(scale_mode)
-    if scale_mode == "blockwise":
-        raise NotImplementedError("scale_mode='blockwise' is not implemented ('tensorwise' and 'rowwise' are)")
     if not a.is_cuda:
         raise RuntimeError("blackwell_scaled_mm_ws needs CUDA tensors (there is no CPU path)")
     M, K = a.shape
@@ -36,6 +35,27 @@ def blackwell_scaled_mm_ws(a, b, scale_a, scale_b, out_dtype=torch.bfloat16, BLO
     assert out_dtype in _OUT
     a = a.contiguous()
     b = b.contiguous()
+    if scale_mode == "blockwise":
+        assert 128 % BLOCK_N == 0, "blockwise requires BLOCK_N to divide 128"
+        G = K // 128
+        assert tuple(scale_a.shape) == (M, G) and tuple(scale_b.shape) == (N // 128, G), (
+            f"blockwise expects scale_a [M, K//128]=({M}, {G}) and scale_b [N//128, K//128]=({N // 128}, {G}); "
+            f"got {tuple(scale_a.shape)}, {tuple(scale_b.shape)}")
+        sa = scale_a.to(torch.float32).t().contiguous()  # [K//128, M]: no copy when scale_a is M-major already
+        sb = scale_b.to(torch.float32).contiguous()
+        c = torch.empty((M, N), dtype=out_dtype, device=a.device)
+        if M == 0:
+            return c
+        bargs = _lib.GemmFp8BlockwiseArgs()
+        bargs.a, bargs.b, bargs.c = a.data_ptr(), b.data_ptr(), c.data_ptr()
+        bargs.scale_a, bargs.scale_b = sa.data_ptr(), sb.data_ptr()
+        bargs.m, bargs.n, bargs.k, bargs.ldc = M, N, K, c.stride(0)
+        bargs.in_dtype, bargs.out_dtype = _IN[a.dtype], _OUT[out_dtype]
+        with torch.cuda.device(a.device):
+            rc = _lib.lib().tb200_gemm_fp8_blockwise(ctypes.byref(bargs),
+                                                     ctypes.c_void_p(_lib.current_stream_ptr(a.device)))
+        _lib.check(rc, "tb200_gemm_fp8_blockwise")
+        return c
     scale_a = scale_a.reshape(-1).contiguous().to(torch.float32)
     scale_b = scale_b.reshape(-1).contiguous().to(torch.float32)
     if scale_mode == "rowwise":
