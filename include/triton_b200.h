@@ -396,6 +396,45 @@ typedef struct {
 } tb200_moe_gemm_args;
 int tb200_moe_gemm(const tb200_moe_gemm_args* args, void* stream);
 
+/*
+ * The same grouped GEMM with FP8 activations and MXFP4 weights (the configuration the reference's MoE
+ * benchmark sweeps on Blackwell: x "fp8", w "mx4"):
+ *     acc = x_scale * x[r, :] @ dequant(w[e]) (+ bias[e]);  swiglu / gammas / scatter as above.
+ * Stands behind: python/triton_kernels/triton_kernels/matmul.py:243 called with an FP4 weight and
+ *   PrecisionConfig(weight_scale=...) (weights prepared as in bench/bench_mlp.py:36-57).
+ * x: [rows_x, k] TB200_E4M3 or TB200_E5M2, row-major (ldx bytes between rows, multiple of 16), rows sorted
+ *    by expert (no gather index); x_scale: one float or NULL (1).
+ * w: uint8 [E, N, K/2], two e2m1 values per byte along K (even index in the low nibble), 32-byte aligned.
+ * w_scale: uint8 e8m0, one per 32 values of K, per expert in 512-byte atoms
+ *    [E][N/128][K/128][n%32][n/32%4][k/32%4]   (the layout tb200_gemm_mxfp8 uses for its scales).
+ * k % 128 == 0, n % 128 == 0. Output TB200_BF16 or TB200_F16. Other fields as in tb200_moe_gemm_args.
+ */
+typedef struct {
+  const void* x;
+  const void* w;
+  const void* w_scale;
+  const float* x_scale;
+  const float* bias;
+  void* y;
+  const int32_t* slice_offs;
+  const int32_t* slice_sizes;
+  const int32_t* block_schedule;
+  const int32_t* scatter_indx;
+  const float* gammas;
+  int64_t n_experts, k, n;
+  int64_t rows_x, rows_y;
+  int64_t ldx, ldy;
+  int32_t n_sched;
+  int32_t x_dtype;
+  int32_t out_dtype;
+  int32_t swiglu;
+  float swiglu_alpha;
+  float swiglu_limit;
+  int32_t swiglu_has_limit;
+  int32_t reserved;
+} tb200_moe_gemm_mx4_args;
+int tb200_moe_gemm_mx4(const tb200_moe_gemm_mx4_args* args, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

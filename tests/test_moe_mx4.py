@@ -1,0 +1,98 @@
+"""FP8 activations x MXFP4 weights through ``triton_kernels.matmul.matmul`` (dense and grouped) against the
+CPU oracle applied to the dequantised weights. The products are exact in fp32 up to summation order (fp8 x
+fp4 values with power-of-two scales), so the tolerance is bf16 output rounding: rtol 1e-2 / atol 1e-2; the
+reference's own matmul tolerance is maxtol 2e-2 (triton_kernels testing.py:21-80)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import moe as o
+from triton_b200.triton_kernels.numerics_details.mxfp import downcast_to_mxfp, upcast_from_mxfp
+
+pytestmark = pytest.mark.gpu
+
+
+def _quantise(w):
+    v, s = downcast_to_mxfp(w.to(torch.bfloat16), torch.uint8, axis=1)
+    return v, s, upcast_from_mxfp(v, s, torch.float32, axis=1)
+
+
+def _prepared(v, s, cuda):
+    from triton_b200.triton_kernels.tensor import FP4, convert_layout, wrap_torch_tensor
+    from triton_b200.triton_kernels.tensor_details.layout import (make_default_matmul_mxfp4_w_layout,
+                                                                  make_default_matmul_mxfp4_w_scale_layout)
+    wv = convert_layout(wrap_torch_tensor(v.to(cuda), dtype=FP4), make_default_matmul_mxfp4_w_layout(mx_axis=1))
+    ws = convert_layout(wrap_torch_tensor(s.to(cuda)), make_default_matmul_mxfp4_w_scale_layout(mx_axis=1))
+    return wv, ws
+
+
+@pytest.mark.parametrize("shape", [(128, 256, 128), (300, 384, 512), (64, 128, 1024), (1024, 1024, 2048)])
+@pytest.mark.parametrize("prepared", [True, False])
+def test_dense_fp8_x_mx4(cuda, shape, prepared):
+    from triton_b200.triton_kernels.matmul import PrecisionConfig, matmul
+    M, N, K = shape
+    g = torch.Generator().manual_seed(1)
+    x = (torch.randn(M, K, generator=g) * 0.5).to(torch.float8_e4m3fn)
+    v, s, wdq = _quantise(torch.randn(1, K, N, generator=g))
+    if prepared:
+        wv, ws = _prepared(v, s, cuda)
+    else:
+        wv, ws = v.to(cuda), s.to(cuda)
+    out = matmul(x.to(cuda), wv, None, precision_config=PrecisionConfig(b_mx_scale=ws))
+    ref = x.float() @ wdq[0]
+    assert out.dtype == torch.bfloat16
+    torch.testing.assert_close(out.cpu().float(), ref, rtol=1e-2, atol=1e-2)
+
+
+def test_exact_on_random_codes(cuda):
+    """Random FP4 codes and scale exponents fed to the kernel as they are, small integer activations: every
+    product is a multiple of 2^-3 and every partial sum is exact in fp32, so the fp16 output must equal the
+    oracle's bit for bit (checks nibble order, scale-atom order and the 32-value block boundaries)."""
+    from triton_b200.triton_kernels.matmul import PrecisionConfig, matmul
+    M, N, K = 128, 256, 256
+    g = torch.Generator().manual_seed(2)
+    x = torch.randint(-2, 3, (M, K), generator=g).float().to(torch.float8_e4m3fn)
+    v = torch.randint(0, 256, (1, K // 2, N), generator=g).to(torch.uint8)
+    s = torch.randint(125, 130, (1, K // 32, N), generator=g).to(torch.uint8)
+    wdq = upcast_from_mxfp(v, s, torch.float32, axis=1)
+    out = matmul(x.to(cuda), v.to(cuda), None,
+                 precision_config=PrecisionConfig(b_mx_scale=s.to(cuda), out_dtype=torch.float16))
+    ref = (x.float() @ wdq[0]).to(torch.float16)
+    assert torch.equal(out.cpu(), ref)
+
+
+@pytest.mark.parametrize("T,E,k", [(64, 8, 2), (777, 16, 4), (4096, 32, 4)])
+@pytest.mark.parametrize("swiglu", [False, True])
+def test_grouped_fp8_x_mx4(cuda, T, E, k, swiglu):
+    """Expert-sorted rows, ragged metadata, bias, optional SwiGLU, gammas and scatter, with an activation scale."""
+    from triton_b200.triton_kernels.matmul import PrecisionConfig, matmul, swiglu_activation
+    from triton_b200.triton_kernels.tensor import make_ragged_tensor_metadata
+    from triton_b200.triton_kernels.topk import topk
+    K, N = 256, 512
+    g = torch.Generator().manual_seed(3)
+    logits = torch.randn(T, E, generator=g)
+    sm = topk(logits.to(cuda), k)
+    mm = sm.mask_metadata
+    rg = make_ragged_tensor_metadata(mm.col_sum, T * k)
+    combine = mm.col_sorted_indx  # sorted row r -> flat (token, slot) entry
+    x_tok = (torch.randn(T, K, generator=g) * 0.5)
+    x_sorted = x_tok[(combine.cpu().long() // k)].to(torch.float8_e4m3fn)  # rows already in expert order
+    v, s, wdq = _quantise(torch.randn(E, K, N, generator=g) * 0.5)
+    bias = torch.randn(E, N, generator=g)
+    gam = torch.rand(T * k, generator=g)
+    wv, ws = _prepared(v, s, cuda)
+    act = swiglu_activation(1.1, 7.0) if swiglu else None
+    out = matmul(x_sorted.to(cuda), wv, bias.to(cuda), rg, scatter_indx=combine, gammas=gam.to(cuda),
+                 precision_config=PrecisionConfig(b_mx_scale=ws, x_scale=0.25), fused_activation=act)
+    ref = o.grouped_matmul_ref(x_sorted.float() * 0.25, wdq, bias, mm.col_sum.cpu().numpy(), None,
+                               combine.cpu().numpy(), gam, (1.1, 7.0) if swiglu else None, out_dtype=torch.bfloat16)
+    torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=2e-2, atol=2e-2)
+
+
+def test_argument_checks(cuda):
+    from triton_b200.triton_kernels.matmul import PrecisionConfig, matmul
+    x = torch.zeros(128, 256, device=cuda, dtype=torch.bfloat16)
+    v = torch.zeros(1, 128, 128, device=cuda, dtype=torch.uint8)
+    s = torch.full((1, 8, 128), 127, device=cuda, dtype=torch.uint8)
+    with pytest.raises(NotImplementedError):
+        matmul(x, v, None, precision_config=PrecisionConfig(b_mx_scale=s))  # bf16 activations

@@ -123,6 +123,18 @@ class MoeGemmArgs(Structure):
     ]
 
 
+class MoeGemmMx4Args(Structure):
+    _fields_ = [
+        ("x", c_void_p), ("w", c_void_p), ("w_scale", c_void_p), ("x_scale", c_void_p), ("bias", c_void_p), ("y", c_void_p),
+        ("slice_offs", c_void_p), ("slice_sizes", c_void_p), ("block_schedule", c_void_p),
+        ("scatter_indx", c_void_p), ("gammas", c_void_p),
+        ("n_experts", c_int64), ("k", c_int64), ("n", c_int64), ("rows_x", c_int64), ("rows_y", c_int64),
+        ("ldx", c_int64), ("ldy", c_int64),
+        ("n_sched", c_int32), ("x_dtype", c_int32), ("out_dtype", c_int32), ("swiglu", c_int32),
+        ("swiglu_alpha", c_float), ("swiglu_limit", c_float), ("swiglu_has_limit", c_int32), ("reserved", c_int32),
+    ]
+
+
 _lib = None
 
 
@@ -159,6 +171,8 @@ def _declare(l: ctypes.CDLL) -> None:
     l.tb200_bitmatrix_metadata_workspace_bytes.argtypes = [c_int64, c_int32]
     l.tb200_gemm_fp8_blockwise.restype = c_int
     l.tb200_gemm_fp8_blockwise.argtypes = [POINTER(GemmFp8BlockwiseArgs), c_void_p]
+    l.tb200_moe_gemm_mx4.restype = c_int
+    l.tb200_moe_gemm_mx4.argtypes = [POINTER(MoeGemmMx4Args), c_void_p]
     l.tb200_gemm_mxfp8.restype = c_int
     l.tb200_gemm_mxfp8.argtypes = [POINTER(GemmMxfp8Args), c_void_p]
 

@@ -25,6 +25,7 @@
 #include "common.cuh"
 #include "gemm_common.cuh"
 #include "host_common.h"
+#include "moe_epilogue.cuh"
 
 namespace tb200 {
 
@@ -80,14 +81,6 @@ __device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap
       " [%0], [%1, {%3, %4, %5}], [%2], %6;"
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar_cluster_addr), "r"(x), "r"(y), "r"(z), "l"(policy)
       : "memory");
-}
-
-__device__ __forceinline__ float moe_swiglu(float g, float l, float alpha, float limit, int has_limit) {
-  if (has_limit) {
-    g = fminf(g, limit);
-    l = fminf(fmaxf(l, -limit), limit);
-  }
-  return g / (1.f + __expf(-alpha * g)) * (l + 1.f);
 }
 
 // BNC = W rows (N) staged per CTA. Single: 128 x 256 tile per CTA, 4 stages. Pair: a 2-CTA cluster
@@ -403,73 +396,7 @@ __global__ void __launch_bounds__(MOE_THREADS, 1) moe_gemm_kernel(const __grid_c
         tmem_ld_wait();
         const int col = n0 + cc;
         if (out_row < 0 || col >= n) continue;
-        float f[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          f[j] = __uint_as_float(v[j]);
-          if (brow && col + j < n) f[j] += __ldg(brow + col + j);
-        }
-        if (swiglu) {
-          // 32 accumulator columns -> 16 outputs at column (col / 2)
-          uint16_t* dst = y + (long long)out_row * ldy + (col >> 1);
-          const int cnt = min(16, (n - col) >> 1);
-          float o[16];
-#pragma unroll
-          for (int j = 0; j < 16; ++j) o[j] = moe_swiglu(f[2 * j], f[2 * j + 1], alpha, limit, has_limit) * gamma;
-          if (cnt == 16 && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
-#pragma unroll
-            for (int j = 0; j < 2; ++j) {
-              uint32_t w[4];
-#pragma unroll
-              for (int t = 0; t < 4; ++t)
-                w[t] = out_f16 ? pack_f16x2(o[j * 8 + 2 * t], o[j * 8 + 2 * t + 1])
-                               : pack_bf16x2(o[j * 8 + 2 * t], o[j * 8 + 2 * t + 1]);
-              reinterpret_cast<uint4*>(dst)[j] = make_uint4(w[0], w[1], w[2], w[3]);
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              if (j < cnt) {
-                if (out_f16) {
-                  __half h = __float2half_rn(o[j]);
-                  dst[j] = *reinterpret_cast<uint16_t*>(&h);
-                } else {
-                  __nv_bfloat16 h = __float2bfloat16_rn(o[j]);
-                  dst[j] = *reinterpret_cast<uint16_t*>(&h);
-                }
-              }
-            }
-          }
-        } else {
-          uint16_t* dst = y + (long long)out_row * ldy + col;
-          const int cnt = min(32, n - col);
-          if (cnt == 32 && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              uint32_t w[4];
-#pragma unroll
-              for (int t = 0; t < 4; ++t) {
-                const float lo = f[j * 8 + 2 * t] * gamma, hi = f[j * 8 + 2 * t + 1] * gamma;
-                w[t] = out_f16 ? pack_f16x2(lo, hi) : pack_bf16x2(lo, hi);
-              }
-              reinterpret_cast<uint4*>(dst)[j] = make_uint4(w[0], w[1], w[2], w[3]);
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              if (j < cnt) {
-                const float x = f[j] * gamma;
-                if (out_f16) {
-                  __half h = __float2half_rn(x);
-                  dst[j] = *reinterpret_cast<uint16_t*>(&h);
-                } else {
-                  __nv_bfloat16 h = __float2bfloat16_rn(x);
-                  dst[j] = *reinterpret_cast<uint16_t*>(&h);
-                }
-              }
-            }
-          }
-        }
+        moe_store_chunk(v, y, ldy, out_row, col, n, brow, swiglu, alpha, limit, has_limit, gamma, out_f16, 1.f);
       }
       tc_fence_before_sync();
       __syncwarp();

@@ -1,0 +1,342 @@
+// Grouped (per-expert) GEMM with FP8 activations and MXFP4 weights for sm_100a:
+//
+//   for each expert e and each sorted row r in [slice_offs[e], slice_offs[e+1]):
+//       acc      = x_scale * X[r, :] @ dequant(W[e])   (+ bias[e])       W[e][n, k] = e2m1 * 2^(scale[n, k/32] - 127)
+//       acc      = swiglu(acc)                          (optional)
+//       Y[scatter[r], :] = acc * gammas[r]
+//
+// X [rows, K] is e4m3 (or e5m2), rows sorted by expert; W is [E, N, K/2] bytes, two e2m1 values per byte
+// along K (low nibble first) with one e8m0 scale per 32 values of K, stored per expert in the 512-byte
+// atom order of the MXFP8 kernel ([n/128][K/128][n%32][n/32%4][k%4]). The weights stay packed in HBM
+// (4.25 bits per value: the decode regime streams 3.8x fewer bytes than bf16); the TMA unpacks them on
+// the way into shared memory (tensor-map type 16U4_ALIGN16B: 16 values in 8 bytes + 8 bytes of padding,
+// the operand format tcgen05.mma.kind::mxf8f6f4 wants for 4-bit types), so a K step of 128 values is a
+// 128-byte row like an fp8 one and the MMA loop is that of the MXFP8 kernel: scale atoms copied to
+// tensor memory with tcgen05.cp, four block-scaled MMAs of K = 32 per step. The activations carry no
+// block scales: their scale columns are written once with 1.0 (0x7f).
+// Work units are (block-schedule entry, N tile) as in the bf16 grouped kernel; one 128 x 256 accumulator
+// plus the scale columns fill tensor memory. Roles (192 threads): TMA warp, MMA warp, 4 epilogue warps.
+//
+// Counterpart in the reference: _p_matmul with an mxfp4 weight (python/triton_kernels/triton_kernels/
+// matmul_details/_p_matmul.py: scaled dot :466-530), host entry triton_kernels/matmul.py:243 with
+// PrecisionConfig(weight_scale=...); weight preparation bench/bench_mlp.py:36-57.
+#include <string.h>
+
+#include "common.cuh"
+#include "gemm_common.cuh"
+#include "host_common.h"
+#include "moe_epilogue.cuh"
+
+namespace tb200 {
+
+static constexpr int M4_THREADS = 192;
+static constexpr int M4_BM = 128;
+static constexpr int M4_BN = 256;
+static constexpr int M4_STAGES = 4;
+
+struct Mx4Params {
+  CUtensorMap tmx;  // X: (K bytes, rows), box (128, 128), fp8 as bytes
+  CUtensorMap tmw;  // W: (K values, N, E) 16U4_ALIGN16B, box (128, 256, 1)
+  const uint8_t* sfw;  // [E][N/128][K/128][512]
+  const int* slice_offs;
+  const int* slice_sizes;
+  const int* sched;
+  const int* scatter;
+  const float* gammas;
+  const float* bias;
+  const float* x_scale;  // optional: one float, multiplies every accumulator
+  void* y;
+  int* status;
+  long long ldy;
+  int n_sched, tiles_n, units;
+  int n, k_blocks, n_blocks, rows_y;
+  int swiglu, has_limit, out_f16;
+  float alpha, limit;
+  uint32_t idesc[4];
+};
+
+struct Mx4Smem {
+  static constexpr int A_BYTES = M4_BM * 128;
+  static constexpr int B_BYTES = M4_BN * 128;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int SF_BYTES = 2 * 512;  // two scale atoms of W per K step
+  static constexpr int SF_OFFSET = M4_STAGES * STAGE_BYTES;
+  static constexpr int BAR_OFFSET = SF_OFFSET + M4_STAGES * SF_BYTES;
+  static constexpr int TOTAL = BAR_OFFSET + (2 * M4_STAGES + 2) * 8 + 16 + 1024;
+};
+
+__device__ __forceinline__ void tma_load_3d_a4(uint32_t dst, const CUtensorMap* tmap, uint32_t bar, int x, int y, int z,
+                                               uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%3, %4, %5}], [%2], %6;"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(x), "r"(y), "r"(z), "l"(policy)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_32x32b_x4(uint32_t taddr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(a), "r"(b), "r"(c), "r"(d)
+               : "memory");
+}
+
+__global__ void __launch_bounds__(M4_THREADS, 1) moe_gemm_mx4_kernel(const __grid_constant__ Mx4Params p) {
+  using L = Mx4Smem;
+  constexpr int BN = M4_BN, STAGES = M4_STAGES;
+  constexpr uint32_t SFA_COL = 256;       // four columns of 1.0 for the activations
+  constexpr uint32_t SFW_COL0 = 256 + 16; // two sets of 8 columns for the weight scales
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET);
+  uint64_t* empty = full + STAGES;
+  uint64_t* tfull = empty + STAGES;
+  uint64_t* tempty = tfull + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 1);
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&p.tmx);
+    tma_prefetch_desc(&p.tmw);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(tfull, 1);
+    mbar_init(tempty, 4);
+    mbar_init_fence();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+  if (warp >= 2) {  // activation scale columns: 1.0 in every byte, on all 128 lanes
+    const uint32_t one = 0x7f7f7f7fu;
+    tmem_st_32x32b_x4(tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + SFA_COL, one, one, one, one);
+    tmem_st_wait();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+
+  const int units = p.units, tiles_n = p.tiles_n, k_blocks = p.k_blocks, n_blocks = p.n_blocks;
+  const int* const sched = p.sched;
+  const int* const slice_offs = p.slice_offs;
+  const int* const slice_sizes = p.slice_sizes;
+  int* const status = p.status;
+  const uint32_t smem_a = smem_u32(smem);
+  const uint32_t full_a = smem_u32(full), empty_a = smem_u32(empty);
+
+  if (warp == 0) {
+    // ------------------------------------------------------------- producer
+    if (lane == 0) {
+      const uint64_t pol_x = policy_evict_normal();
+      const uint64_t pol_w = policy_evict_first();  // a weight tile is read once per row block
+      uint32_t s = 0, ph = 0;
+      bool ok = true;
+      for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x) {
+        const int si = unit / tiles_n;
+        const int entry = __ldg(sched + si);
+        if (entry < 0) continue;
+        const int e = entry & 0xFFFF;
+        const int pid_n = unit - si * tiles_n;
+        const int n0 = pid_n * BN;
+        const int row0 = __ldg(slice_offs + e) + (entry >> 16) * M4_BM;
+        const int nb_valid = min(2, n_blocks - pid_n * 2);
+        const uint8_t* atoms = p.sfw + ((size_t)e * n_blocks + (size_t)pid_n * 2) * k_blocks * 512;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait_a(empty_a + s * 8, ph ^ 1, status, WAIT_SMEM_EMPTY)) {
+            ok = false;
+            break;
+          }
+          const uint32_t bar = full_a + s * 8;
+          // the unpacking load of W reports the bytes it read (64 per row), not the 128 it writes
+          mbar_expect_tx_a(bar, L::A_BYTES + L::B_BYTES / 2 + nb_valid * 512);
+          const uint32_t sa = smem_a + s * L::STAGE_BYTES;
+          tma_load_2d_a(sa, &p.tmx, bar, kb * 128, row0, pol_x);
+          tma_load_3d_a4(sa + L::A_BYTES, &p.tmw, bar, kb * 128, n0, e, pol_w);
+          uint8_t* sf = smem + L::SF_OFFSET + s * L::SF_BYTES;
+          for (int j = 0; j < nb_valid; ++j)
+            bulk_load(sf + j * 512, atoms + ((size_t)j * k_blocks + kb) * 512, 512, &full[s]);
+          if (++s == STAGES) {
+            s = 0;
+            ph ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      const uint64_t adesc0 = make_smem_desc(smem_a, 16, 1024, SWIZZLE_128B);
+      const uint64_t bdesc0 = make_smem_desc(smem_a + L::A_BYTES, 16, 1024, SWIZZLE_128B);
+      const uint64_t sfdesc0 = make_smem_desc(smem_a + L::SF_OFFSET, 16, 128, SWIZZLE_NONE);
+      const uint32_t tfull_a = smem_u32(tfull), tempty_a = smem_u32(tempty);
+      const uint32_t t_sfa = tmem_base + SFA_COL;
+      uint32_t s = 0, ph = 0, tcount = 0, kpar = 0;
+      bool ok = true, ready = false;
+      for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x) {
+        if (__ldg(sched + unit / tiles_n) < 0) continue;
+        if (!mbar_wait_a(tempty_a, (tcount & 1) ^ 1, status, WAIT_TMEM_EMPTY)) break;
+        ++tcount;
+        tc_fence_after_sync();
+        uint32_t accum = 0;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!ready && !mbar_wait_a(full_a + s * 8, ph, status, WAIT_SMEM_FULL)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t s1 = (s + 1 == STAGES) ? 0 : s + 1;
+          ready = mbar_test_a(full_a + s1 * 8, s1 == 0 ? ph ^ 1 : ph);
+          const uint32_t t_sfw = tmem_base + SFW_COL0 + kpar * 8;
+          const uint64_t sfd = sfdesc0 + (uint64_t)((s * L::SF_BYTES) >> 4);
+          tmem_cp_32x128b_warpx4(t_sfw, sfd);
+          tmem_cp_32x128b_warpx4(t_sfw + 4, sfd + (uint64_t)(512 >> 4));
+          const uint64_t ad = adesc0 + (uint64_t)(s * (L::STAGE_BYTES >> 4));
+          const uint64_t bd = bdesc0 + (uint64_t)(s * (L::STAGE_BYTES >> 4));
+          umma_mxf8_ss(tmem_base, ad, bd, p.idesc[0], t_sfa, t_sfw, accum);
+          umma_mxf8_ss(tmem_base, ad + 2, bd + 2, p.idesc[1], t_sfa, t_sfw, 1u);
+          umma_mxf8_ss(tmem_base, ad + 4, bd + 4, p.idesc[2], t_sfa, t_sfw, 1u);
+          umma_mxf8_ss(tmem_base, ad + 6, bd + 6, p.idesc[3], t_sfa, t_sfw, 1u);
+          accum = 1u;
+          umma_commit_a(empty_a + s * 8);
+          kpar ^= 1;
+          s = s1;
+          if (s == 0) ph ^= 1;
+        }
+        if (ok) umma_commit_a(tfull_a);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------- epilogue
+    const int q = warp & 3;
+    const int n = p.n, rows_y = p.rows_y;
+    uint16_t* const y = reinterpret_cast<uint16_t*>(p.y);
+    const float acc_scale = p.x_scale ? __ldg(p.x_scale) : 1.f;
+    const uint32_t tempty_a = smem_u32(tempty);
+    uint32_t tcount = 0;
+    for (int unit = blockIdx.x; unit < units; unit += gridDim.x) {
+      const int si = unit / tiles_n;
+      const int entry = __ldg(sched + si);
+      if (entry < 0) continue;
+      const int e = entry & 0xFFFF;
+      const int n0 = (unit - si * tiles_n) * BN;
+      const int row0 = __ldg(slice_offs + e) + (entry >> 16) * M4_BM;
+      const int row_end = slice_sizes ? __ldg(slice_offs + e) + __ldg(slice_sizes + e) : __ldg(slice_offs + e + 1);
+      if (!mbar_wait(tfull, tcount & 1, status, WAIT_TMEM_FULL)) break;
+      ++tcount;
+      tc_fence_after_sync();
+      const int sr = row0 + q * 32 + lane;
+      int out_row = -1;
+      float gamma = 1.f;
+      if (sr < row_end) {
+        out_row = p.scatter ? __ldg(p.scatter + sr) : sr;
+        if (out_row >= rows_y) out_row = -1;
+        if (p.gammas) gamma = __ldg(p.gammas + sr);
+      }
+      const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16);
+      const float* brow = p.bias ? p.bias + (long long)e * n : nullptr;
+#pragma unroll 1
+      for (int cc = 0; cc < BN; cc += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(taddr + cc, v);
+        tmem_ld_wait();
+        const int col = n0 + cc;
+        if (out_row < 0 || col >= n) continue;
+        moe_store_chunk(v, y, p.ldy, out_row, col, n, brow, p.swiglu, p.alpha, p.limit, p.has_limit, gamma, p.out_f16,
+                        acc_scale);
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_a(tempty_a);
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+}  // namespace tb200
+
+using namespace tb200;
+
+extern "C" int tb200_moe_gemm_mx4(const tb200_moe_gemm_mx4_args* a, void* stream_) {
+  if (!a || !a->x || !a->w || !a->w_scale || !a->y || !a->slice_offs || !a->block_schedule) return TB200_ERR_BAD_ARG;
+  if (a->n_experts <= 0 || a->n_experts > 65535 || a->k <= 0 || a->n <= 0 || a->n_sched < 0) return TB200_ERR_BAD_ARG;
+  if (a->rows_x < 0 || a->rows_y < 0) return TB200_ERR_BAD_ARG;
+  if (a->x_dtype != TB200_E4M3 && a->x_dtype != TB200_E5M2) return TB200_ERR_UNSUPPORTED;
+  if (a->out_dtype != TB200_BF16 && a->out_dtype != TB200_F16) return TB200_ERR_UNSUPPORTED;
+  if ((a->k % 128) || (a->n % 128)) return TB200_ERR_UNSUPPORTED;
+  if (a->swiglu && (a->n & 1)) return TB200_ERR_BAD_ARG;
+  if ((a->ldx % 16) || a->ldx < a->k) return TB200_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(a->x) & 15) || (reinterpret_cast<uintptr_t>(a->w) & 31) ||
+      (reinterpret_cast<uintptr_t>(a->w_scale) & 15))
+    return TB200_ERR_BAD_ARG;
+  if (a->rows_x > INT32_MAX - 1 || a->rows_y > INT32_MAX || a->k > INT32_MAX || a->n > INT32_MAX)
+    return TB200_ERR_UNSUPPORTED;
+  if (a->n_sched == 0 || a->rows_x == 0) return TB200_OK;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const int sms = sm_count();
+  if (sms <= 0) return TB200_ERR_CUDA;
+
+  Mx4Params p;
+  memset(&p, 0, sizeof(p));
+  {
+    const uint64_t dims[2] = {(uint64_t)a->k, (uint64_t)a->rows_x};
+    const uint64_t strides[1] = {(uint64_t)a->ldx};
+    const uint32_t box[2] = {128, M4_BM};
+    int rc = encode_tmap(&p.tmx, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a->x, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != TB200_OK) return rc;
+  }
+  {
+    // packed 4-bit values: dimensions in values, strides in bytes (K/2 per row of N, N*K/2 per expert)
+    const uint64_t dims[3] = {(uint64_t)a->k, (uint64_t)a->n, (uint64_t)a->n_experts};
+    const uint64_t strides[2] = {(uint64_t)a->k / 2, (uint64_t)a->n * (uint64_t)a->k / 2};
+    const uint32_t box[3] = {128, M4_BN, 1};
+    int rc = encode_tmap(&p.tmw, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 3, a->w, dims, strides, box,
+                         CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != TB200_OK) return rc;
+  }
+  p.sfw = static_cast<const uint8_t*>(a->w_scale);
+  p.slice_offs = a->slice_offs;
+  p.slice_sizes = a->slice_sizes;
+  p.sched = a->block_schedule;
+  p.scatter = a->scatter_indx;
+  p.gammas = a->gammas;
+  p.bias = a->bias;
+  p.x_scale = a->x_scale;
+  p.y = a->y;
+  p.ldy = a->ldy;
+  p.status = status_ptr();
+  if (!p.status) return TB200_ERR_CUDA;
+  p.n_sched = (int)a->n_sched;
+  p.tiles_n = (int)((a->n + M4_BN - 1) / M4_BN);
+  if ((long long)p.n_sched * p.tiles_n > INT32_MAX) return TB200_ERR_UNSUPPORTED;
+  p.units = p.n_sched * p.tiles_n;
+  p.n = (int)a->n;
+  p.k_blocks = (int)(a->k / 128);
+  p.n_blocks = (int)(a->n / 128);
+  p.rows_y = (int)a->rows_y;
+  p.swiglu = a->swiglu ? 1 : 0;
+  p.has_limit = a->swiglu_has_limit ? 1 : 0;
+  p.alpha = a->swiglu_alpha;
+  p.limit = a->swiglu_limit;
+  p.out_f16 = a->out_dtype == TB200_F16 ? 1 : 0;
+  const uint32_t afmt = a->x_dtype == TB200_E5M2 ? 1u : 0u;
+  const uint32_t bfmt = 5u;  // e2m1
+  for (uint32_t k = 0; k < 4; ++k) p.idesc[k] = make_idesc_mx(afmt, bfmt, M4_BM, M4_BN, k, k);
+
+  auto kfn = moe_gemm_mx4_kernel;
+  if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, Mx4Smem::TOTAL) != cudaSuccess)
+    return TB200_ERR_CUDA;
+  const int grid = p.units < sms ? p.units : sms;
+  kfn<<<grid, M4_THREADS, Mx4Smem::TOTAL, stream>>>(p);
+  return cuda_err(cudaGetLastError());
+}

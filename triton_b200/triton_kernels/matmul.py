@@ -53,8 +53,10 @@ class PrecisionConfig:
     acc_scale: float = 1.0
     out_dtype: torch.dtype | None = None
     a_mx_scale: object = None
-    b_mx_scale: object = None
+    b_mx_scale: object = None  # e8m0 scales of an MXFP4 weight: [E, K/32, N] uint8, or the Tensor convert_layout returns
+    b_microblock_size: int | None = None
     c_mx_scale: object = None
+    x_scale: object = None     # one fp32 value multiplying the fp8 activations (the reference's flexpoint scale)
 
 
 def swiglu_activation(alpha: float = 1.0, limit: float | None = None) -> FusedActivation:
@@ -74,11 +76,14 @@ def matmul(a, b, bias, a_ragged_metadata: RaggedTensorMetadata | None = None, b_
     if epilogue is not None and epilogue.specs.name != "dflt":
         raise NotImplementedError("matmul: custom epilogues are not implemented")
     if precision_config is not None and (precision_config.a_mx_scale is not None
-                                         or precision_config.b_mx_scale is not None
                                          or precision_config.c_mx_scale is not None):
-        raise NotImplementedError("matmul: MX precision configs are not implemented")
+        raise NotImplementedError("matmul: MX-scaled activations / outputs are not implemented")
+    if precision_config is not None and precision_config.b_mx_scale is not None:
+        if gather_indx is not None or c is not None:
+            raise NotImplementedError("matmul (MXFP4 weight): gather_indx / preallocated output are not implemented")
+        return _matmul_mx4(a, b, bias, a_ragged_metadata, scatter_indx, precision_config, gammas, fused_activation)
     if not isinstance(a, torch.Tensor) or not isinstance(b, torch.Tensor):
-        raise NotImplementedError("matmul: wrapped Tensor operands (MX / layouts) are not implemented")
+        raise NotImplementedError("matmul: wrapped Tensor operands need precision_config.b_mx_scale (MXFP4 weights)")
     if a.ndim != 2:
         raise NotImplementedError("matmul: batched input is not implemented")
     if not a.is_cuda:
@@ -157,4 +162,83 @@ def matmul(a, b, bias, a_ragged_metadata: RaggedTensorMetadata | None = None, b_
     with torch.cuda.device(dev):
         rc = _lib.lib().tb200_moe_gemm(ctypes.byref(args), ctypes.c_void_p(_lib.current_stream_ptr(dev)))
     _lib.check(rc, "tb200_moe_gemm")
+    return c
+
+
+_F8 = {torch.float8_e4m3fn: _lib.E4M3, torch.float8_e5m2: _lib.E5M2}
+
+
+def _matmul_mx4(a, b, bias, a_ragged_metadata, scatter_indx, pc: PrecisionConfig, gammas, fused_activation):
+    """FP8 activations x MXFP4 weights (the reference's Blackwell "fp8 x mx4" MoE configuration,
+    bench/bench_mlp.py:253-279). ``b`` / ``pc.b_mx_scale`` are either what ``downcast_to_mxfp(w, torch.uint8,
+    axis=1)`` returned ([E, K/2, N] and [E, K/32, N] uint8: re-laid here on every call) or the Tensors
+    ``convert_layout`` produced from them (no per-call work)."""
+    from .tensor import FP4, Tensor, convert_layout, wrap_torch_tensor
+    from .tensor_details.layout import (BlackwellMX4ValueLayout, BlackwellMXScaleLayout,
+                                        make_default_matmul_mxfp4_w_layout, make_default_matmul_mxfp4_w_scale_layout)
+    if not isinstance(a, torch.Tensor) or a.dtype not in _F8:
+        raise NotImplementedError("matmul (MXFP4 weight): activations must be float8_e4m3fn or float8_e5m2")
+    if not a.is_cuda:
+        raise RuntimeError("triton_b200 matmul needs CUDA tensors (there is no CPU path)")
+    if a.ndim != 2:
+        raise NotImplementedError("matmul: batched input is not implemented")
+    if pc.b_microblock_size not in (None, 32):
+        raise NotImplementedError("matmul (MXFP4 weight): microblock size 32 (e8m0 scales) only")
+    w = b if isinstance(b, Tensor) else wrap_torch_tensor(b, dtype=FP4)
+    ws = pc.b_mx_scale if isinstance(pc.b_mx_scale, Tensor) else wrap_torch_tensor(pc.b_mx_scale)
+    if not isinstance(w.layout, BlackwellMX4ValueLayout):
+        w = convert_layout(w, make_default_matmul_mxfp4_w_layout(mx_axis=1))
+    if not isinstance(ws.layout, BlackwellMXScaleLayout):
+        ws = convert_layout(ws, make_default_matmul_mxfp4_w_scale_layout(mx_axis=1))
+    E, K, N = w.shape
+    assert a.shape[1] == K, "inner dimensions differ"
+    assert ws.shape == (E, K // 32, N), "scale shape does not match the weight"
+    dev = a.device
+    if a.stride(1) != 1 or a.stride(0) % 16:
+        a = a.contiguous()
+    swiglu, alpha, limit = 0, 1.0, None
+    if fused_activation is not None and fused_activation.specs.name != "dflt":
+        if fused_activation.specs.name != "swiglu":
+            raise NotImplementedError(f"matmul: fused activation {fused_activation.specs.name!r}")
+        swiglu = 1
+        alpha = float(fused_activation.fn_args[0])
+        limit = fused_activation.fn_args[1] if len(fused_activation.fn_args) > 1 else None
+    n_out = N // 2 if swiglu else N
+    R = a.shape[0]
+    if a_ragged_metadata is None:
+        assert E == 1, "several weight matrices need a_ragged_metadata"
+        a_ragged_metadata = make_ragged_tensor_metadata(torch.tensor([R], dtype=torch.int32, device=dev), R)
+    md = a_ragged_metadata
+    sched = md.block_schedule(128)
+    rows_y = R if scatter_indx is None else scatter_indx.shape[0]
+    out_dtype = pc.out_dtype or torch.bfloat16
+    if out_dtype not in _DT:
+        raise NotImplementedError("matmul (MXFP4 weight): bf16 / fp16 output")
+    c = (torch.zeros if scatter_indx is not None else torch.empty)((rows_y, n_out), dtype=out_dtype, device=dev)
+    si = None if scatter_indx is None else scatter_indx.to(torch.int32).contiguous()
+    gm = None if gammas is None else gammas.float().contiguous()
+    bs = None if bias is None else bias.float().reshape(E, N).contiguous()
+    xs = None
+    if pc.x_scale is not None:
+        xs = torch.as_tensor(pc.x_scale, dtype=torch.float32, device=dev).reshape(1).contiguous()
+    args = _lib.MoeGemmMx4Args()
+    args.x, args.w, args.w_scale, args.y = a.data_ptr(), w.data.data_ptr(), ws.data.data_ptr(), c.data_ptr()
+    args.x_scale = xs.data_ptr() if xs is not None else None
+    args.bias = bs.data_ptr() if bs is not None else None
+    args.slice_offs, args.slice_sizes, args.block_schedule = (md.slice_offs.data_ptr(), md.slice_sizes.data_ptr(),
+                                                             sched.data_ptr())
+    args.scatter_indx = si.data_ptr() if si is not None else None
+    args.gammas = gm.data_ptr() if gm is not None else None
+    args.n_experts, args.k, args.n = E, K, N
+    args.rows_x, args.rows_y = R, rows_y
+    args.ldx, args.ldy = a.stride(0), c.stride(0)
+    args.n_sched = sched.shape[0]
+    args.x_dtype, args.out_dtype = _F8[a.dtype], _DT[out_dtype]
+    args.swiglu = swiglu
+    args.swiglu_alpha = alpha
+    args.swiglu_limit = float(limit) if limit is not None else 0.0
+    args.swiglu_has_limit = 1 if limit is not None else 0
+    with torch.cuda.device(dev):
+        rc = _lib.lib().tb200_moe_gemm_mx4(ctypes.byref(args), ctypes.c_void_p(_lib.current_stream_ptr(dev)))
+    _lib.check(rc, "tb200_moe_gemm_mx4")
     return c

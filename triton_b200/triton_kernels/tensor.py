@@ -170,3 +170,65 @@ class SparseMatrix:
 
     def __post_init__(self):
         self.mask_metadata = make_bitmatrix_metadata(self.indx, self.mask)
+
+
+# ----------------------------------------------------------------------------------------------
+# Wrapped tensors and layouts for MXFP4 weights (reference: triton_kernels/tensor.py ``Tensor``,
+# ``wrap_torch_tensor``, ``convert_layout``, ``FP4``; weight preparation bench/bench_mlp.py:36-57)
+# ----------------------------------------------------------------------------------------------
+class _FP4Type:
+    """Marker for packed e2m1 values (two per byte)."""
+    bitwidth = 4
+
+    def __repr__(self):
+        return "FP4"
+
+
+FP4 = _FP4Type()
+
+
+@dataclass
+class Tensor:
+    """A torch tensor plus what it means: element type (``FP4`` for packed 4-bit values, else the torch
+    dtype), logical shape and the layout its bytes are in."""
+    data: torch.Tensor
+    dtype: object
+    shape: tuple
+    layout: object = None
+
+
+def wrap_torch_tensor(t: torch.Tensor, dtype=None) -> Tensor:
+    from .tensor_details.layout import StridedLayout
+    if dtype is FP4:
+        # packed along the last-but-one axis (the mx axis of a [.., K, N] weight): K/2 bytes hold K values
+        shape = (*t.shape[:-2], t.shape[-2] * 2, t.shape[-1])
+    else:
+        dtype, shape = t.dtype, tuple(t.shape)
+    return Tensor(t, dtype, tuple(shape), StridedLayout())
+
+
+def convert_layout(t: Tensor, layout) -> Tensor:
+    """Re-lays an MXFP4 weight (values or scales, quantised along axis -2 of ``[E, K, N]``) into the order
+    the kernel reads: values ``[E, N, K/2]`` K-contiguous, scales in 512-byte atoms. Done once per weight."""
+    from .tensor_details.layout import BlackwellMX4ValueLayout, BlackwellMXScaleLayout, StridedLayout
+    if isinstance(layout, StridedLayout):
+        assert isinstance(t.layout, StridedLayout), "only strided -> kernel layout conversions are built"
+        return t
+    d = t.data
+    if d.ndim == 2:
+        d = d.unsqueeze(0)
+    assert d.ndim == 3, "expected a [E, K(/2 or /32), N] weight"
+    if isinstance(layout, BlackwellMX4ValueLayout):
+        assert t.dtype is FP4 and d.dtype == torch.uint8
+        E, K2, N = d.shape
+        assert (2 * K2) % 128 == 0 and N % 128 == 0, "K and N must be multiples of 128"
+        out = d.transpose(1, 2).contiguous()  # [E, N, K/2]; no copy if the quantiser already produced that order
+        return Tensor(out, FP4, (E, 2 * K2, N), layout)
+    if isinstance(layout, BlackwellMXScaleLayout):
+        assert d.dtype == torch.uint8
+        E, KB, N = d.shape  # KB = K / 32
+        assert KB % 4 == 0 and N % 128 == 0, "K and N must be multiples of 128"
+        s = d.transpose(1, 2).reshape(E, N // 128, 4, 32, KB // 4, 4)  # e, n/128, n/32%4, n%32, k/128, k/32%4
+        out = s.permute(0, 1, 4, 3, 2, 5).contiguous()                 # e, n/128, k/128, n%32, n/32%4, k/32%4
+        return Tensor(out, torch.uint8, (E, KB, N), layout)
+    raise NotImplementedError(f"convert_layout: {layout!r}")
