@@ -187,6 +187,47 @@ def build_workload(name: str, rank: int, dev):
         by = active * (D * 2 * F + F * D) * 2.0 + R * (D + F) * 2.0 + R * (F + D) * 2.0
         return (step, fl, by, f"MoE layer: {T} tokens, d_model {D}, E={E}, top-{k}, W1 [{D},{2*F}] SwiGLU W2 [{F},{D}], "
                 "gate-weighted combine, seed 4", "moe_gemm_kernel", "hbm" if name == "moe_decode" else "tensor")
+    if name in ("moe_mx4", "moe_mx4_decode"):
+        from triton_b200.triton_kernels.matmul import PrecisionConfig, matmul as moe_matmul, swiglu_activation
+        from triton_b200.triton_kernels.numerics_details.mxfp import downcast_to_mxfp
+        from triton_b200.triton_kernels.reduce import reduce
+        from triton_b200.triton_kernels.tensor import FP4, convert_layout, make_ragged_tensor_metadata, wrap_torch_tensor
+        from triton_b200.triton_kernels.tensor_details.layout import (make_default_matmul_mxfp4_w_layout,
+                                                                      make_default_matmul_mxfp4_w_scale_layout)
+        from triton_b200.triton_kernels.topk import topk
+        T = 64 if name == "moe_mx4_decode" else 16384
+        D, F, E, k = 4096, 1536, 128, 4
+        g4 = torch.Generator(device="cpu").manual_seed(4 + 1000 * rank)
+        x = torch.randn(T, D, generator=g4).to(torch.float8_e4m3fn).to(dev)
+        logits = torch.randn(T, E, generator=g4).to(dev)
+
+        def prep(w):  # quantise on the GPU, expert by expert chunks to bound memory
+            v, s = downcast_to_mxfp(w.to(dev).to(torch.bfloat16), torch.uint8, axis=1)
+            return (convert_layout(wrap_torch_tensor(v, dtype=FP4), make_default_matmul_mxfp4_w_layout(mx_axis=1)),
+                    convert_layout(wrap_torch_tensor(s), make_default_matmul_mxfp4_w_scale_layout(mx_axis=1)))
+        w1, s1 = prep(0.02 * torch.randn(E, D, 2 * F, generator=g4))
+        w2, s2 = prep(0.02 * torch.randn(E, F, D, generator=g4))
+        pc1, pc2 = PrecisionConfig(b_mx_scale=s1), PrecisionConfig(b_mx_scale=s2)
+        act = swiglu_activation(1.0, None)
+
+        def step():
+            sm = topk(logits, k)
+            mm = sm.mask_metadata
+            rg = make_ragged_tensor_metadata(mm.col_sum, T * k)
+            combine = mm.col_sorted_indx
+            gather = torch.div(combine, k, rounding_mode="trunc")
+            gam = sm.vals.float().reshape(-1)[combine.long()]
+            xs = x.view(torch.uint8)[gather.long()].view(torch.float8_e4m3fn)  # rows in expert order
+            h = moe_matmul(xs, w1, None, rg, precision_config=pc1, fused_activation=act)
+            y = moe_matmul(h.to(torch.float8_e4m3fn), w2, None, rg, scatter_indx=combine, gammas=gam, precision_config=pc2)
+            return reduce(y.view(T, k, D), dim=1)[0]
+        R = T * k
+        fl = 2.0 * R * D * 2 * F + 2.0 * R * F * D
+        active = int((topk(logits, k).mask_metadata.col_sum > 0).sum().item())
+        by = active * (D * 2 * F + F * D) * (0.5 + 1.0 / 32) + R * (D + F) * 1.0 + R * (F + D) * 2.0
+        return (step, fl, by, f"MoE layer, fp8 activations x MXFP4 weights: {T} tokens, d_model {D}, E={E}, top-{k}, "
+                f"W1 [{D},{2*F}] SwiGLU W2 [{F},{D}], gate-weighted combine, seed 4", "moe_gemm_mx4_kernel",
+                "hbm" if name == "moe_mx4_decode" else "tensor")
     if name == "moe_ep":
         import torch.distributed as dist
         from triton_b200.triton_kernels.distributed import (EpGroup, make_expt_assignment, make_expt_dict_uniform,
@@ -211,7 +252,7 @@ def build_workload(name: str, rank: int, dev):
 
 # Kernels of this library launched per step: the MoE layer runs topk, three bitmatrix-metadata kernels,
 # the ragged-metadata kernel, two grouped GEMMs and the top-k reduce (the EP variant adds four row moves).
-OWN_LAUNCHES_PER_STEP = {"moe": 8, "moe_decode": 8, "moe_ep": 12, "attn_bwd": 3, "attn_bwd_causal": 3,
+OWN_LAUNCHES_PER_STEP = {"moe": 8, "moe_decode": 8, "moe_ep": 12, "moe_mx4": 8, "moe_mx4_decode": 8, "attn_bwd": 3, "attn_bwd_causal": 3,
                          "attn_bwd_ref_shape": 3, "attn_bwd_ref_shape_causal": 3}
 
 
@@ -262,7 +303,7 @@ def run_extra_workload(args, rank, local_rank, world):
             "metric": f"{args.workload} throughput", "value": tf, "unit": "TFLOP/s", "n_gpus": world, "steps": steps,
             "warmup": warmup, "ms_per_step": ms, "higher_is_better": True,
             "scaling": "strong" if args.workload == "moe_ep" else "weak", "vs_baseline": None,
-            "dtype": "e4m3" if args.workload in ("fp8", "fp8_blockwise", "mxfp8") else "bf16", "data": "synthetic",
+            "dtype": "e4m3" if args.workload in ("fp8", "fp8_blockwise", "mxfp8", "moe_mx4", "moe_mx4_decode") else "bf16", "data": "synthetic",
             "config": {"workload": desc},
             "roofline": {"bound": bound, "achieved": ach, "peak": peak, "unit": unit, "frac": ach / peak,
                          "traffic": None, "kernel": kernel,
@@ -350,7 +391,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--workload", default="gemm",
                     help="gemm (headline, default) | attn | attn_causal | attn_short | attn_short_causal | attn_bwd | "
-                         "attn_bwd_causal | attn_bwd_ref_shape[_causal] | fp8 | fp8_blockwise | mxfp8 | moe | moe_decode | moe_ep")
+                         "attn_bwd_causal | attn_bwd_ref_shape[_causal] | fp8 | fp8_blockwise | mxfp8 | moe | moe_decode | moe_mx4 | moe_mx4_decode | moe_ep")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
