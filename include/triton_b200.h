@@ -404,7 +404,9 @@ int tb200_moe_gemm(const tb200_moe_gemm_args* args, void* stream);
  *   PrecisionConfig(weight_scale=...) (weights prepared as in bench/bench_mlp.py:36-57).
  * x: [rows_x, k] TB200_E4M3 or TB200_E5M2, row-major (ldx bytes between rows, multiple of 16), rows sorted
  *    by expert (no gather index); x_scale: one float or NULL (1).
- * w: uint8 [E, N, K/2], two e2m1 values per byte along K (even index in the low nibble), 32-byte aligned.
+ * w: uint8, two e2m1 values per byte along K (even index in the low nibble), blocked as
+ *    [E][ceil(N/256)][K/128][256][64]: block (e, t, s) holds rows 256 t .. 256 t + 255 of expert e (zero
+ *    rows past N) and values 128 s .. 128 s + 127 of each; 32-byte aligned.
  * w_scale: uint8 e8m0, one per 32 values of K, per expert in 512-byte atoms
  *    [E][N/128][K/128][n%32][n/32%4][k/32%4]   (the layout tb200_gemm_mxfp8 uses for its scales).
  * k % 128 == 0, n % 128 == 0. Output TB200_BF16 or TB200_F16. Other fields as in tb200_moe_gemm_args.
@@ -431,7 +433,7 @@ typedef struct {
   float swiglu_alpha;
   float swiglu_limit;
   int32_t swiglu_has_limit;
-  int32_t reserved;
+  int32_t reserved; /* 0 */
 } tb200_moe_gemm_mx4_args;
 int tb200_moe_gemm_mx4(const tb200_moe_gemm_mx4_args* args, void* stream);
 

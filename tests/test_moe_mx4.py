@@ -26,7 +26,8 @@ def _prepared(v, s, cuda):
     return wv, ws
 
 
-@pytest.mark.parametrize("shape", [(128, 256, 128), (300, 384, 512), (64, 128, 1024), (1024, 1024, 2048)])
+@pytest.mark.parametrize("shape", [(128, 256, 128), (300, 384, 512), (64, 128, 1024), (1024, 1024, 2048),
+                                   (16, 384, 512), (32, 256, 4096), (1, 128, 128)])
 @pytest.mark.parametrize("prepared", [True, False])
 def test_dense_fp8_x_mx4(cuda, shape, prepared):
     from triton_b200.triton_kernels.matmul import PrecisionConfig, matmul
@@ -61,7 +62,7 @@ def test_exact_on_random_codes(cuda):
     assert torch.equal(out.cpu(), ref)
 
 
-@pytest.mark.parametrize("T,E,k", [(64, 8, 2), (777, 16, 4), (4096, 32, 4)])
+@pytest.mark.parametrize("T,E,k", [(64, 8, 2), (777, 16, 4), (4096, 32, 4), (64, 128, 4), (300, 64, 4)])
 @pytest.mark.parametrize("swiglu", [False, True])
 def test_grouped_fp8_x_mx4(cuda, T, E, k, swiglu):
     """Expert-sorted rows, ragged metadata, bias, optional SwiGLU, gammas and scatter, with an activation scale."""

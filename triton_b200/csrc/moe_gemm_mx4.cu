@@ -5,8 +5,10 @@
 //       acc      = swiglu(acc)                          (optional)
 //       Y[scatter[r], :] = acc * gammas[r]
 //
-// X [rows, K] is e4m3 (or e5m2), rows sorted by expert; W is [E, N, K/2] bytes, two e2m1 values per byte
-// along K (low nibble first) with one e8m0 scale per 32 values of K, stored per expert in the 512-byte
+// X [rows, K] is e4m3 (or e5m2), rows sorted by expert; W holds two e2m1 values per byte along K (low nibble
+// first), blocked as [E][N/256][K/128][256 rows][64 bytes] so that what one tile needs per K step is one
+// contiguous 16 KB run (with 64-byte pieces of 256 different rows the same kernel reached 40 % of the HBM
+// rate), with one e8m0 scale per 32 values of K, stored per expert in the 512-byte
 // atom order of the MXFP8 kernel ([n/128][K/128][n%32][n/32%4][k%4]). The weights stay packed in HBM
 // (4.25 bits per value: the decode regime streams 3.8x fewer bytes than bf16); the TMA unpacks them on
 // the way into shared memory (tensor-map type 16U4_ALIGN16B: 16 values in 8 bytes + 8 bytes of padding,
@@ -16,6 +18,12 @@
 // block scales: their scale columns are written once with 1.0 (0x7f).
 // Work units are (block-schedule entry, N tile) as in the bf16 grouped kernel; one 128 x 256 accumulator
 // plus the scale columns fill tensor memory. Roles (192 threads): TMA warp, MMA warp, 4 epilogue warps.
+// With a few rows per expert (decode) the kernel streams the weights at 2.9 TB/s: per K step the four
+// 128 x 256 MMAs cost ~530 cycles however few rows are real, and the single accumulator serialises the
+// epilogue. A variant that moved the weights packed through an 8-deep ring and unpacked them with the
+// epilogue warps (twice the bytes in flight) measured slower (2.6 TB/s: its loads were never late, the
+// unpacking took ~700 cycles per step next to the MMAs' operand traffic); swapping the operand roles (weight
+// rows on the MMA's M, tokens on a small N) is the open step for that regime.
 //
 // Counterpart in the reference: _p_matmul with an mxfp4 weight (python/triton_kernels/triton_kernels/
 // matmul_details/_p_matmul.py: scaled dot :466-530), host entry triton_kernels/matmul.py:243 with
@@ -36,7 +44,7 @@ static constexpr int M4_STAGES = 4;
 
 struct Mx4Params {
   CUtensorMap tmx;  // X: (K bytes, rows), box (128, 128), fp8 as bytes
-  CUtensorMap tmw;  // W: (K values, N, E) 16U4_ALIGN16B, box (128, 256, 1)
+  CUtensorMap tmw;  // W blocks: (128 values, rows) 16U4_ALIGN16B, box (128, 256)
   const uint8_t* sfw;  // [E][N/128][K/128][512]
   const int* slice_offs;
   const int* slice_sizes;
@@ -65,14 +73,6 @@ struct Mx4Smem {
   static constexpr int TOTAL = BAR_OFFSET + (2 * M4_STAGES + 2) * 8 + 16 + 1024;
 };
 
-__device__ __forceinline__ void tma_load_3d_a4(uint32_t dst, const CUtensorMap* tmap, uint32_t bar, int x, int y, int z,
-                                               uint64_t policy) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
-      " [%0], [%1, {%3, %4, %5}], [%2], %6;"
-      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(x), "r"(y), "r"(z), "l"(policy)
-      : "memory");
-}
 __device__ __forceinline__ void tmem_st_32x32b_x4(uint32_t taddr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(a), "r"(b), "r"(c), "r"(d)
                : "memory");
@@ -156,7 +156,7 @@ __global__ void __launch_bounds__(M4_THREADS, 1) moe_gemm_mx4_kernel(const __gri
           mbar_expect_tx_a(bar, L::A_BYTES + L::B_BYTES / 2 + nb_valid * 512);
           const uint32_t sa = smem_a + s * L::STAGE_BYTES;
           tma_load_2d_a(sa, &p.tmx, bar, kb * 128, row0, pol_x);
-          tma_load_3d_a4(sa + L::A_BYTES, &p.tmw, bar, kb * 128, n0, e, pol_w);
+          tma_load_2d_a(sa + L::A_BYTES, &p.tmw, bar, 0, (((e * tiles_n + pid_n) * k_blocks) + kb) * BN, pol_w);
           uint8_t* sf = smem + L::SF_OFFSET + s * L::SF_BYTES;
           for (int j = 0; j < nb_valid; ++j)
             bulk_load(sf + j * 512, atoms + ((size_t)j * k_blocks + kb) * 512, 512, &full[s]);
@@ -286,6 +286,7 @@ extern "C" int tb200_moe_gemm_mx4(const tb200_moe_gemm_mx4_args* a, void* stream
   const int sms = sm_count();
   if (sms <= 0) return TB200_ERR_CUDA;
 
+  if (a->reserved != 0) return TB200_ERR_BAD_ARG;
   Mx4Params p;
   memset(&p, 0, sizeof(p));
   {
@@ -296,11 +297,15 @@ extern "C" int tb200_moe_gemm_mx4(const tb200_moe_gemm_mx4_args* a, void* stream
     if (rc != TB200_OK) return rc;
   }
   {
-    // packed 4-bit values: dimensions in values, strides in bytes (K/2 per row of N, N*K/2 per expert)
-    const uint64_t dims[3] = {(uint64_t)a->k, (uint64_t)a->n, (uint64_t)a->n_experts};
-    const uint64_t strides[2] = {(uint64_t)a->k / 2, (uint64_t)a->n * (uint64_t)a->k / 2};
-    const uint32_t box[3] = {128, M4_BN, 1};
-    int rc = encode_tmap(&p.tmw, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 3, a->w, dims, strides, box,
+    // blocked weights: one (expert, N tile, K step) block of 256 rows x 64 bytes after the other, so a tile
+    // step is one contiguous 16 KB run of HBM
+    const uint64_t tiles_n = (uint64_t)((a->n + M4_BN - 1) / M4_BN);
+    const uint64_t rows = (uint64_t)a->n_experts * tiles_n * (uint64_t)(a->k / 128) * M4_BN;
+    if (rows > (1ull << 31)) return TB200_ERR_UNSUPPORTED;
+    const uint64_t dims[2] = {128, rows};  // in 4-bit values
+    const uint64_t strides[1] = {64};
+    const uint32_t box[2] = {128, M4_BN};
+    int rc = encode_tmap(&p.tmw, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 2, a->w, dims, strides, box,
                          CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != TB200_OK) return rc;
   }

@@ -209,7 +209,7 @@ def wrap_torch_tensor(t: torch.Tensor, dtype=None) -> Tensor:
 
 def convert_layout(t: Tensor, layout) -> Tensor:
     """Re-lays an MXFP4 weight (values or scales, quantised along axis -2 of ``[E, K, N]``) into the order
-    the kernel reads: values ``[E, N, K/2]`` K-contiguous, scales in 512-byte atoms. Done once per weight."""
+    the kernel reads: values blocked as ``[E][N/256][K/128][256][64 bytes]``, scales in 512-byte atoms. Done once per weight."""
     from .tensor_details.layout import BlackwellMX4ValueLayout, BlackwellMXScaleLayout, StridedLayout
     if isinstance(layout, StridedLayout):
         assert isinstance(t.layout, StridedLayout), "only strided -> kernel layout conversions are built"
@@ -222,7 +222,12 @@ def convert_layout(t: Tensor, layout) -> Tensor:
         assert t.dtype is FP4 and d.dtype == torch.uint8
         E, K2, N = d.shape
         assert (2 * K2) % 128 == 0 and N % 128 == 0, "K and N must be multiples of 128"
-        out = d.transpose(1, 2).contiguous()  # [E, N, K/2]; no copy if the quantiser already produced that order
+        nk = d.transpose(1, 2)                                   # [E, N, K/2]
+        tiles = (N + 255) // 256
+        if tiles * 256 != N:
+            nk = torch.nn.functional.pad(nk, (0, 0, 0, tiles * 256 - N))
+        # blocked: [E][N/256][K/128][256 rows][64 bytes] - one tile step is one contiguous 16 KB run
+        out = nk.reshape(E, tiles, 256, K2 // 64, 64).permute(0, 1, 3, 2, 4).contiguous()
         return Tensor(out, FP4, (E, 2 * K2, N), layout)
     if isinstance(layout, BlackwellMXScaleLayout):
         assert d.dtype == torch.uint8

@@ -5,7 +5,8 @@
 The reference picks, per GPU generation, how packed FP4 values and their e8m0 scales are laid out for
 its kernel. Here there is one target and one kernel (``tb200_moe_gemm_mx4``):
 
-* values: ``[E, N, K/2]`` bytes, K contiguous (two e2m1 values per byte, even index in the low nibble);
+* values: two e2m1 values per byte along K (even index in the low nibble), blocked as
+  ``[E][N/256][K/128][256 rows][64 bytes]`` so that a tile's K step is one contiguous 16 KB run of HBM;
 * scales: per expert, 512-byte atoms ``[N/128][K/128][n % 32][n / 32 % 4][k / 32 % 4]`` — the order in
   which ``tcgen05.cp.32x128b.warpx4`` wants them (``layout_details/blackwell_scale.py:100-122``).
 """
