@@ -433,7 +433,7 @@ typedef struct {
   float swiglu_alpha;
   float swiglu_limit;
   int32_t swiglu_has_limit;
-  int32_t reserved; /* 0 */
+  int32_t block_rows; /* rows per entry of block_schedule: 0 or 128 = the 128-row schedule; 32 = the 32-row schedule (few rows per expert: operand roles swapped, weights on the MMA's M side) */
 } tb200_moe_gemm_mx4_args;
 int tb200_moe_gemm_mx4(const tb200_moe_gemm_mx4_args* args, void* stream);
 

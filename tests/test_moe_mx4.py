@@ -90,6 +90,20 @@ def test_grouped_fp8_x_mx4(cuda, T, E, k, swiglu):
     torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=2e-2, atol=2e-2)
 
 
+def test_exact_on_random_codes_few_rows_kernel(cuda):
+    """The same exactness check through the swapped-operand kernel (rows <= 32 per expert)."""
+    from triton_b200.triton_kernels.matmul import PrecisionConfig, matmul
+    M, N, K = 24, 384, 512
+    g = torch.Generator().manual_seed(6)
+    x = torch.randint(-2, 3, (M, K), generator=g).float().to(torch.float8_e4m3fn)
+    v = torch.randint(0, 256, (1, K // 2, N), generator=g).to(torch.uint8)
+    s = torch.randint(125, 130, (1, K // 32, N), generator=g).to(torch.uint8)
+    wdq = upcast_from_mxfp(v, s, torch.float32, axis=1)
+    out = matmul(x.to(cuda), v.to(cuda), None,
+                 precision_config=PrecisionConfig(b_mx_scale=s.to(cuda), out_dtype=torch.float16))
+    assert torch.equal(out.cpu(), (x.float() @ wdq[0]).to(torch.float16))
+
+
 def test_argument_checks(cuda):
     from triton_b200.triton_kernels.matmul import PrecisionConfig, matmul
     x = torch.zeros(128, 256, device=cuda, dtype=torch.bfloat16)

@@ -131,7 +131,7 @@ class MoeGemmMx4Args(Structure):
         ("n_experts", c_int64), ("k", c_int64), ("n", c_int64), ("rows_x", c_int64), ("rows_y", c_int64),
         ("ldx", c_int64), ("ldy", c_int64),
         ("n_sched", c_int32), ("x_dtype", c_int32), ("out_dtype", c_int32), ("swiglu", c_int32),
-        ("swiglu_alpha", c_float), ("swiglu_limit", c_float), ("swiglu_has_limit", c_int32), ("reserved", c_int32),
+        ("swiglu_alpha", c_float), ("swiglu_limit", c_float), ("swiglu_has_limit", c_int32), ("block_rows", c_int32),
     ]
 
 

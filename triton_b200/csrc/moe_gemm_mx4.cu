@@ -18,12 +18,14 @@
 // block scales: their scale columns are written once with 1.0 (0x7f).
 // Work units are (block-schedule entry, N tile) as in the bf16 grouped kernel; one 128 x 256 accumulator
 // plus the scale columns fill tensor memory. Roles (192 threads): TMA warp, MMA warp, 4 epilogue warps.
-// With a few rows per expert (decode) the kernel streams the weights at 2.9 TB/s: per K step the four
+// With a few rows per expert (decode) this kernel streams the weights at 2.9 TB/s: per K step the four
 // 128 x 256 MMAs cost ~530 cycles however few rows are real, and the single accumulator serialises the
 // epilogue. A variant that moved the weights packed through an 8-deep ring and unpacked them with the
 // epilogue warps (twice the bytes in flight) measured slower (2.6 TB/s: its loads were never late, the
 // unpacking took ~700 cycles per step next to the MMAs' operand traffic); swapping the operand roles (weight
-// rows on the MMA's M, tokens on a small N) is the open step for that regime.
+// rows on the MMA's M, tokens on a small N) is what the second kernel below does (3.1-3.4 TB/s; with 72 KB
+// of packed weights in flight per SM it is bound by load latency, and the padded operand format costs two
+// bytes of shared memory per byte in flight).
 //
 // Counterpart in the reference: _p_matmul with an mxfp4 weight (python/triton_kernels/triton_kernels/
 // matmul_details/_p_matmul.py: scaled dot :466-530), host entry triton_kernels/matmul.py:243 with
@@ -263,6 +265,227 @@ __global__ void __launch_bounds__(M4_THREADS, 1) moe_gemm_mx4_kernel(const __gri
   }
 }
 
+// --------------------------------------------------------------------------- few rows per expert
+// Operand roles swapped: the MMA's M = 128 weight rows (A: the unpacked weight tile, its e8m0 atom as the A
+// scales), N = 32 token rows (B: a 32-row activation tile of the 32-row block schedule, scales 1.0). A K
+// step then costs four N = 32 MMAs (~46 cycles each) per 128 weight rows instead of four 128 x 256 ones
+// (~530 cycles per 256 rows), a stage is 20.5 KB (9 of them), and a 128 x 32 accumulator is 32 columns, so
+// four of them rotate and the epilogue never blocks the MMAs. The accumulator is the output transposed:
+// thread = weight row n, columns = tokens; a warp writes 32 consecutive n of one token (64 bytes), SwiGLU
+// pairs are adjacent lanes.
+static constexpr int S4_XROWS = 32;
+static constexpr int S4_WROWS = 128;
+static constexpr int S4_STAGES = 9;
+static constexpr int S4_NACC = 4;
+
+struct Mx4SwapSmem {
+  static constexpr int W_BYTES = S4_WROWS * 128;  // unpacked
+  static constexpr int X_BYTES = S4_XROWS * 128;
+  static constexpr int STAGE_BYTES = W_BYTES + X_BYTES;  // 20 KB, a multiple of 1024
+  static constexpr int SF_OFFSET = S4_STAGES * STAGE_BYTES;
+  static constexpr int BAR_OFFSET = SF_OFFSET + S4_STAGES * 512;
+  static constexpr int TOTAL = BAR_OFFSET + (2 * S4_STAGES + 2 * S4_NACC) * 8 + 16 + 1024;
+};
+static_assert(Mx4SwapSmem::TOTAL <= 232448, "shared memory budget");
+
+__global__ void __launch_bounds__(M4_THREADS, 1) moe_gemm_mx4_swap_kernel(const __grid_constant__ Mx4Params p) {
+  using L = Mx4SwapSmem;
+  constexpr int STAGES = S4_STAGES;
+  constexpr uint32_t SFB_COL = S4_NACC * 32;      // token-side scale columns: 1.0
+  constexpr uint32_t SFA_COL0 = SFB_COL + 8;      // two sets of 4 columns for the weight scales
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET);
+  uint64_t* empty = full + STAGES;
+  uint64_t* tfull = empty + STAGES;   // [NACC]
+  uint64_t* tempty = tfull + S4_NACC; // [NACC] 4 arrivals
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + S4_NACC);
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&p.tmx);
+    tma_prefetch_desc(&p.tmw);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int i = 0; i < S4_NACC; ++i) {
+      mbar_init(&tfull[i], 1);
+      mbar_init(&tempty[i], 4);
+    }
+    mbar_init_fence();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 256);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+  if (warp >= 2) {
+    const uint32_t one = 0x7f7f7f7fu;
+    tmem_st_32x32b_x4(tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + SFB_COL, one, one, one, one);
+    tmem_st_wait();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+
+  // units: (entry of the 32-row schedule, tile of 128 weight rows)
+  const int units = p.units, tiles_w = p.tiles_n, k_blocks = p.k_blocks, n_blocks = p.n_blocks;
+  const int tiles_256 = (n_blocks + 1) / 2;  // 256-row blocks of the weight buffer per (expert, K step)
+  const int* const sched = p.sched;
+  const int* const slice_offs = p.slice_offs;
+  const int* const slice_sizes = p.slice_sizes;
+  int* const status = p.status;
+  const uint32_t smem_a = smem_u32(smem);
+  const uint32_t full_a = smem_u32(full), empty_a = smem_u32(empty);
+
+  if (warp == 0) {
+    // ------------------------------------------------------------- producer
+    if (lane == 0) {
+      const uint64_t pol_x = policy_evict_last();
+      const uint64_t pol_w = policy_evict_first();
+      uint32_t s = 0, ph = 0;
+      bool ok = true;
+      for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x) {
+        const int si = unit / tiles_w;
+        const int entry = __ldg(sched + si);
+        if (entry < 0) continue;
+        const int e = entry & 0xFFFF;
+        const int wt = unit - si * tiles_w;  // 128-row weight tile
+        const int row0 = __ldg(slice_offs + e) + (entry >> 16) * S4_XROWS;
+        const uint8_t* atoms = p.sfw + ((size_t)e * n_blocks + wt) * k_blocks * 512;
+        // weight rows 128 wt .. of expert e sit in 256-row block wt / 2, half wt % 2, of each K step
+        const int wrow0 = ((e * tiles_256 + (wt >> 1)) * k_blocks) * M4_BN + (wt & 1) * S4_WROWS;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait_a(empty_a + s * 8, ph ^ 1, status, WAIT_SMEM_EMPTY)) {
+            ok = false;
+            break;
+          }
+          const uint32_t bar = full_a + s * 8;
+          mbar_expect_tx_a(bar, L::W_BYTES / 2 + L::X_BYTES + 512);
+          const uint32_t sw = smem_a + s * L::STAGE_BYTES;
+          tma_load_2d_a(sw, &p.tmw, bar, 0, wrow0 + kb * M4_BN, pol_w);
+          tma_load_2d_a(sw + L::W_BYTES, &p.tmx, bar, kb * 128, row0, pol_x);
+          bulk_load(smem + L::SF_OFFSET + s * 512, atoms + (size_t)kb * 512, 512, &full[s]);
+          if (++s == STAGES) {
+            s = 0;
+            ph ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      const uint64_t adesc0 = make_smem_desc(smem_a, 16, 1024, SWIZZLE_128B);
+      const uint64_t bdesc0 = make_smem_desc(smem_a + L::W_BYTES, 16, 1024, SWIZZLE_128B);
+      const uint64_t sfdesc0 = make_smem_desc(smem_a + L::SF_OFFSET, 16, 128, SWIZZLE_NONE);
+      const uint32_t tfull_a = smem_u32(tfull), tempty_a = smem_u32(tempty);
+      const uint32_t t_sfb = tmem_base + SFB_COL;
+      uint32_t s = 0, ph = 0, tcount = 0, kpar = 0;
+      bool ok = true, ready = false;
+      for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x) {
+        if (__ldg(sched + unit / tiles_w) < 0) continue;
+        const uint32_t acc = tcount % S4_NACC, aph = (tcount / S4_NACC) & 1;
+        ++tcount;
+        if (!mbar_wait_a(tempty_a + acc * 8, aph ^ 1, status, WAIT_TMEM_EMPTY)) break;
+        tc_fence_after_sync();
+        const uint32_t tmem_d = tmem_base + acc * 32;
+        uint32_t accum = 0;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!ready && !mbar_wait_a(full_a + s * 8, ph, status, WAIT_SMEM_FULL)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t s1 = (s + 1 == STAGES) ? 0 : s + 1;
+          ready = mbar_test_a(full_a + s1 * 8, s1 == 0 ? ph ^ 1 : ph);
+          const uint32_t t_sfa = tmem_base + SFA_COL0 + kpar * 4;
+          tmem_cp_32x128b_warpx4(t_sfa, sfdesc0 + (uint64_t)((s * 512) >> 4));
+          const uint64_t ad = adesc0 + (uint64_t)(s * (L::STAGE_BYTES >> 4));
+          const uint64_t bd = bdesc0 + (uint64_t)(s * (L::STAGE_BYTES >> 4));
+          umma_mxf8_ss(tmem_d, ad, bd, p.idesc[0], t_sfa, t_sfb, accum);
+          umma_mxf8_ss(tmem_d, ad + 2, bd + 2, p.idesc[1], t_sfa, t_sfb, 1u);
+          umma_mxf8_ss(tmem_d, ad + 4, bd + 4, p.idesc[2], t_sfa, t_sfb, 1u);
+          umma_mxf8_ss(tmem_d, ad + 6, bd + 6, p.idesc[3], t_sfa, t_sfb, 1u);
+          accum = 1u;
+          umma_commit_a(empty_a + s * 8);
+          kpar ^= 1;
+          s = s1;
+          if (s == 0) ph ^= 1;
+        }
+        if (ok) umma_commit_a(tfull_a + acc * 8);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------- epilogue (transposed accumulator)
+    const int q = warp & 3;
+    const int n = p.n, rows_y = p.rows_y, swiglu = p.swiglu, has_limit = p.has_limit, out_f16 = p.out_f16;
+    const float alpha = p.alpha, limit = p.limit;
+    uint16_t* const y = reinterpret_cast<uint16_t*>(p.y);
+    const long long ldy = p.ldy;
+    const float acc_scale = p.x_scale ? __ldg(p.x_scale) : 1.f;
+    const uint32_t tempty_a = smem_u32(tempty);
+    uint32_t tcount = 0;
+    for (int unit = blockIdx.x; unit < units; unit += gridDim.x) {
+      const int si = unit / tiles_w;
+      const int entry = __ldg(sched + si);
+      if (entry < 0) continue;
+      const int e = entry & 0xFFFF;
+      const int wt = unit - si * tiles_w;
+      const int row0 = __ldg(slice_offs + e) + (entry >> 16) * S4_XROWS;
+      const int row_end = slice_sizes ? __ldg(slice_offs + e) + __ldg(slice_sizes + e) : __ldg(slice_offs + e + 1);
+      const int valid = min(S4_XROWS, row_end - row0);
+      const uint32_t acc = tcount % S4_NACC, aph = (tcount / S4_NACC) & 1;
+      ++tcount;
+      if (!mbar_wait(&tfull[acc], aph, status, WAIT_TMEM_FULL)) break;
+      tc_fence_after_sync();
+      uint32_t v[32];
+      tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * 32, v);
+      tmem_ld_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_a(tempty_a + acc * 8);  // the accumulator is in registers
+      const int col = wt * S4_WROWS + q * 32 + lane;  // weight row = output column of this thread
+      const float b = (p.bias && col < n) ? __ldg(p.bias + (long long)e * n + col) : 0.f;
+#pragma unroll
+      for (int c = 0; c < S4_XROWS; ++c) {
+        if (c >= valid) break;
+        const int sr = row0 + c;
+        int out_row = p.scatter ? __ldg(p.scatter + sr) : sr;
+        if (out_row >= rows_y) out_row = -1;
+        const float gamma = p.gammas ? __ldg(p.gammas + sr) : 1.f;
+        float f = __uint_as_float(v[c]) * acc_scale + b;
+        if (swiglu) {
+          const float other = __shfl_xor_sync(0xffffffffu, f, 1);  // (gate, linear) are adjacent columns
+          if ((lane & 1) == 0 && out_row >= 0 && col < n) {
+            const float o = moe_swiglu(f, other, alpha, limit, has_limit) * gamma;
+            uint16_t* dst = y + (long long)out_row * ldy + (col >> 1);
+            if (out_f16) { __half h = __float2half_rn(o); *dst = *reinterpret_cast<uint16_t*>(&h); }
+            else { __nv_bfloat16 h = __float2bfloat16_rn(o); *dst = *reinterpret_cast<uint16_t*>(&h); }
+          }
+        } else if (out_row >= 0 && col < n) {
+          const float o = f * gamma;
+          uint16_t* dst = y + (long long)out_row * ldy + col;
+          if (out_f16) { __half h = __float2half_rn(o); *dst = *reinterpret_cast<uint16_t*>(&h); }
+          else { __nv_bfloat16 h = __float2bfloat16_rn(o); *dst = *reinterpret_cast<uint16_t*>(&h); }
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 256);
+  }
+}
+
 }  // namespace tb200
 
 using namespace tb200;
@@ -286,13 +509,14 @@ extern "C" int tb200_moe_gemm_mx4(const tb200_moe_gemm_mx4_args* a, void* stream
   const int sms = sm_count();
   if (sms <= 0) return TB200_ERR_CUDA;
 
-  if (a->reserved != 0) return TB200_ERR_BAD_ARG;
+  const bool swap = a->block_rows == S4_XROWS;
+  if (!swap && a->block_rows != 0 && a->block_rows != M4_BM) return TB200_ERR_BAD_ARG;
   Mx4Params p;
   memset(&p, 0, sizeof(p));
   {
     const uint64_t dims[2] = {(uint64_t)a->k, (uint64_t)a->rows_x};
     const uint64_t strides[1] = {(uint64_t)a->ldx};
-    const uint32_t box[2] = {128, M4_BM};
+    const uint32_t box[2] = {128, (uint32_t)(swap ? S4_XROWS : M4_BM)};
     int rc = encode_tmap(&p.tmx, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a->x, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != TB200_OK) return rc;
   }
@@ -304,7 +528,7 @@ extern "C" int tb200_moe_gemm_mx4(const tb200_moe_gemm_mx4_args* a, void* stream
     if (rows > (1ull << 31)) return TB200_ERR_UNSUPPORTED;
     const uint64_t dims[2] = {128, rows};  // in 4-bit values
     const uint64_t strides[1] = {64};
-    const uint32_t box[2] = {128, M4_BN};
+    const uint32_t box[2] = {128, (uint32_t)(swap ? S4_WROWS : M4_BN)};
     int rc = encode_tmap(&p.tmw, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 2, a->w, dims, strides, box,
                          CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != TB200_OK) return rc;
@@ -322,7 +546,7 @@ extern "C" int tb200_moe_gemm_mx4(const tb200_moe_gemm_mx4_args* a, void* stream
   p.status = status_ptr();
   if (!p.status) return TB200_ERR_CUDA;
   p.n_sched = (int)a->n_sched;
-  p.tiles_n = (int)((a->n + M4_BN - 1) / M4_BN);
+  p.tiles_n = swap ? (int)(a->n / S4_WROWS) : (int)((a->n + M4_BN - 1) / M4_BN);
   if ((long long)p.n_sched * p.tiles_n > INT32_MAX) return TB200_ERR_UNSUPPORTED;
   p.units = p.n_sched * p.tiles_n;
   p.n = (int)a->n;
@@ -334,14 +558,22 @@ extern "C" int tb200_moe_gemm_mx4(const tb200_moe_gemm_mx4_args* a, void* stream
   p.alpha = a->swiglu_alpha;
   p.limit = a->swiglu_limit;
   p.out_f16 = a->out_dtype == TB200_F16 ? 1 : 0;
-  const uint32_t afmt = a->x_dtype == TB200_E5M2 ? 1u : 0u;
-  const uint32_t bfmt = 5u;  // e2m1
-  for (uint32_t k = 0; k < 4; ++k) p.idesc[k] = make_idesc_mx(afmt, bfmt, M4_BM, M4_BN, k, k);
+  const uint32_t xfmt = a->x_dtype == TB200_E5M2 ? 1u : 0u;
+  const uint32_t wfmt = 5u;  // e2m1
+  for (uint32_t k = 0; k < 4; ++k)
+    p.idesc[k] = swap ? make_idesc_mx(wfmt, xfmt, S4_WROWS, S4_XROWS, k, k) : make_idesc_mx(xfmt, wfmt, M4_BM, M4_BN, k, k);
 
-  auto kfn = moe_gemm_mx4_kernel;
-  if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, Mx4Smem::TOTAL) != cudaSuccess)
-    return TB200_ERR_CUDA;
   const int grid = p.units < sms ? p.units : sms;
-  kfn<<<grid, M4_THREADS, Mx4Smem::TOTAL, stream>>>(p);
+  if (swap) {
+    auto kfn = moe_gemm_mx4_swap_kernel;
+    if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, Mx4SwapSmem::TOTAL) != cudaSuccess)
+      return TB200_ERR_CUDA;
+    kfn<<<grid, M4_THREADS, Mx4SwapSmem::TOTAL, stream>>>(p);
+  } else {
+    auto kfn = moe_gemm_mx4_kernel;
+    if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, Mx4Smem::TOTAL) != cudaSuccess)
+      return TB200_ERR_CUDA;
+    kfn<<<grid, M4_THREADS, Mx4Smem::TOTAL, stream>>>(p);
+  }
   return cuda_err(cudaGetLastError());
 }

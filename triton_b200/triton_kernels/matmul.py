@@ -209,7 +209,9 @@ def _matmul_mx4(a, b, bias, a_ragged_metadata, scatter_indx, pc: PrecisionConfig
         assert E == 1, "several weight matrices need a_ragged_metadata"
         a_ragged_metadata = make_ragged_tensor_metadata(torch.tensor([R], dtype=torch.int32, device=dev), R)
     md = a_ragged_metadata
-    sched = md.block_schedule(128)
+    # few rows per expert (decode): the 32-row schedule and the kernel with swapped operand roles
+    block_rows = 32 if R <= 32 * E else 128
+    sched = md.block_schedule(block_rows)
     rows_y = R if scatter_indx is None else scatter_indx.shape[0]
     out_dtype = pc.out_dtype or torch.bfloat16
     if out_dtype not in _DT:
@@ -238,6 +240,7 @@ def _matmul_mx4(a, b, bias, a_ragged_metadata, scatter_indx, pc: PrecisionConfig
     args.swiglu_alpha = alpha
     args.swiglu_limit = float(limit) if limit is not None else 0.0
     args.swiglu_has_limit = 1 if limit is not None else 0
+    args.block_rows = block_rows
     with torch.cuda.device(dev):
         rc = _lib.lib().tb200_moe_gemm_mx4(ctypes.byref(args), ctypes.c_void_p(_lib.current_stream_ptr(dev)))
     _lib.check(rc, "tb200_moe_gemm_mx4")
