@@ -73,7 +73,10 @@ struct AttnTile {
   int bh, q0, nkv;
 };
 
-// Heaviest tiles first (largest query block = most KV blocks under a causal mask).
+// Heaviest tiles first (largest query block = most KV blocks under a causal mask), all heads of one query
+// block before the next block. This order re-reads each head's K / V from HBM for every query tile (15.8 GB
+// per launch at [4, 32, 8192, 128], 4 TB/s); head-major and L2-sized head-group orders cut that to ~1 GB but
+// measured equal (non-causal) or 5-30 % slower (causal: the long tiles no longer start first), so it stays.
 __device__ __forceinline__ AttnTile attn_tile(const AttnParams& p, int unit) {
   AttnTile t;
   const int qb = p.q_tiles - 1 - unit / p.bh;
