@@ -12,7 +12,7 @@ Each function restates the torch twin that the reference's own tests use as grou
   grouped_matmul_ref         <- matmul_torch                         matmul.py:823-914
   reduce_ref                 <- reduce_torch                         reduce.py:1173-1206
   moe_layer_ref              <- mixture_of_expt_nosharded            tests/test_distributed.py:201-218
-                                (plus the gate-weighted combine that BASELINE config 5 asks for)
+                                (plus the gate-weighted combine of the MoE benchmark configuration)
 """
 from dataclasses import dataclass
 

@@ -47,7 +47,7 @@ def mxfp8_gemm_ref(a, b, a_scale, b_scale, out_dtype=torch.bfloat16):
 
 
 def make_mxfp8_operand(rows: int, K: int, gen: torch.Generator):
-    """Synthetic operand as BASELINE config 4 describes it: per 1x32 block a scale 2**u with u an
+    """Synthetic operand of the MXFP8 benchmark configuration: per 1x32 block a scale 2**u with u an
     integer uniform in [-4, 4], elements N(0,1) clipped into the e4m3 range and rounded to e4m3.
     Returns (q float8_e4m3fn [rows, K], swizzled scale bytes uint8 [rows*K/32])."""
     x = torch.randn(rows, K, generator=gen)

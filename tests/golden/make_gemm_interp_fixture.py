@@ -46,7 +46,7 @@ def load_kernel(ref_root):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref_root = sys.argv[1]  # path of the reference checkout
     kernel = load_kernel(ref_root)
     M = N = K = 512
     torch.manual_seed(0)

@@ -1,7 +1,7 @@
 """Generates ``mxfp_cases.npz``: inputs and the outputs of the reference's own torch implementations
 ``downcast_to_mxfp_torch`` / ``upcast_from_mxfp_torch``
 (python/triton_kernels/triton_kernels/numerics_details/mxfp.py:212, :384), imported from the reference
-checkout given as argv[1] (default /root/reference). Run once where the reference is available; the
+checkout given as argv[1]. Run once where the reference is available; the
 committed fixture is what the tests read."""
 import sys
 
@@ -12,7 +12,7 @@ import ast
 import math
 import types
 
-ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+ref_root = sys.argv[1]  # path of the reference checkout
 ref_file = ref_root + "/python/triton_kernels/triton_kernels/numerics_details/mxfp.py"
 # The module's import line pulls in the fork's own triton build; only the pure-torch functions are needed,
 # so their definitions are taken from the reference file and executed as they stand.

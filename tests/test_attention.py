@@ -1,5 +1,5 @@
 """Parity of the flash-attention forward kernel against the CPU oracle (fp32 softmax(QK^T)V and
-base-2 LSE). Tolerances: bf16 rtol 1e-2 / atol 1e-2 (BASELINE); fp16 case uses the reference's own
+base-2 LSE). Tolerances: bf16 rtol 1e-2 / atol 1e-2 (the target tolerance); fp16 case uses the reference's own
 test setting (atol 1e-2, rtol 0, test_correctness.py:425-435)."""
 import math
 
@@ -64,7 +64,7 @@ def test_rescale_path_with_growing_logits(cuda):
 
 
 def test_config3_shapes_by_properties(cuda):
-    """BASELINE config 3 sizes ([4,32,8192,128] and [32,32,1024,128]) are too large for the CPU
+    """The benchmark sizes ([4,32,8192,128] and [32,32,1024,128]) are too large for the CPU
     oracle in full: check (i) the last 384 query rows of one (batch, head) against the oracle (its
     causal mask is aligned to the end of the sequence), (ii) the size-independent identity that
     with V = all-ones every output is 1 (softmax rows sum to 1), (iii) causal row 0 returns V[0]."""

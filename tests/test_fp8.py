@@ -1,6 +1,6 @@
 """Parity of the FP8 paths against the CPU oracle: tensorwise-scaled e4m3 GEMM (tolerance of the
 reference's own test, atol 0.1 / rtol 0.05, test_correctness.py:554-562) and the MXFP8 block-scaled
-GEMM (BASELINE: rtol 3e-2; the reference's test uses atol 0.1, rtol 0.01 on N(0, 0.5) inputs)."""
+GEMM (target: rtol 3e-2; the reference's test uses atol 0.1, rtol 0.01 on N(0, 0.5) inputs)."""
 import pytest
 import torch
 
@@ -96,7 +96,7 @@ def _mx_case(cuda, M, N, K, bn, seed=3):
     out = matmul(a.to(cuda), b.to(cuda), sa.to(cuda).view(torch.float8_e8m0fnu), sb.to(cuda).view(torch.float8_e8m0fnu),
                  {"BLOCK_SIZE_N": bn} if bn else None)
     ref = o_mx.dequantize(a, sa) @ o_mx.dequantize(b, sb).t()
-    # rtol 3e-2 (BASELINE) on entries, with an absolute floor of 3e-2 x the mean magnitude
+    # rtol 3e-2 (the target) on entries, with an absolute floor of 3e-2 x the mean magnitude
     torch.testing.assert_close(out.cpu().float(), ref, rtol=3e-2, atol=3e-2 * float(ref.abs().mean()))
 
 
@@ -124,7 +124,7 @@ def test_mxfp8_scale_layout_known_answer(cuda):
 
 def test_mxfp8_2048_and_linearity_at_full_size(cuda):
     _mx_case(cuda, 2048, 2048, 2048, 0)
-    # BASELINE config 4 size (8192^3): the CPU oracle is too slow; use exactness instead — with
+    # the benchmark size (8192^3): the CPU oracle is too slow; use exactness instead — with
     # all-ones data and power-of-two scales every product is exact, so C = K/32 * sum of 2^(ea+eb).
     from triton_b200.tutorials.blackwell_gemm_ws_mxfp8 import matmul
     n = 8192

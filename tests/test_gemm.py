@@ -1,5 +1,5 @@
 """Parity of the tcgen05 GEMM (through the C ABI, via the reference-named Python entry point)
-against the CPU oracle. Tolerances follow BASELINE: bf16 within rtol 1e-2 / atol 1e-2 of the
+against the CPU oracle. Target tolerances: bf16 within rtol 1e-2 / atol 1e-2 of the
 fp32 product; fp16 the same bounds."""
 import os
 
@@ -24,7 +24,7 @@ def _check(c, ref):
 
 
 def test_config1_512_cubed_row_major(cuda):
-    """BASELINE config 1: seed 0, N(0,1) entries, row-major A and B, bf16 out."""
+    """Benchmark config 1: seed 0, N(0,1) entries, row-major A and B, bf16 out."""
     torch.manual_seed(0)
     a = torch.randn(512, 512).to(torch.bfloat16)
     b = torch.randn(512, 512).to(torch.bfloat16)
@@ -92,7 +92,7 @@ def test_tile_widths_and_split_k(cuda, bn, split_k):
 
 
 def test_skinny_config2(cuda):
-    """BASELINE config 2's skinny case M=128, N=K=8192 (B K-major), seed 1."""
+    """The skinny case of benchmark config 2, M=128, N=K=8192 (B K-major), seed 1."""
     torch.manual_seed(1)
     M, N, K = 128, 8192, 8192
     a = (torch.randn(M, K) / K ** 0.5).to(torch.bfloat16)
@@ -102,7 +102,7 @@ def test_skinny_config2(cuda):
 
 
 def test_full_size_linearity_property(cuda):
-    """8192^3 (BASELINE config 2) is too slow for the CPU oracle; check size-independent
+    """8192^3 (benchmark config 2) is too slow for the CPU oracle; check size-independent
     properties instead: (i) a 256-row band against the oracle, (ii) linearity A(B1+B2) = AB1 + AB2
     on exactly-representable inputs (small integers: every partial sum is exact in fp32)."""
     torch.manual_seed(1)

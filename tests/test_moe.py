@@ -139,7 +139,7 @@ def test_moe_layer_many_experts_some_empty(cuda):
 
 
 def test_moe_layer_config5_down_scaled(cuda):
-    """BASELINE config 5 with 2048 tokens (d_model 4096, E=128, top-4, W1 [4096, 3072], W2 [1536, 4096])
+    """The MoE benchmark configuration with 2048 tokens (d_model 4096, E=128, top-4, W1 [4096, 3072], W2 [1536, 4096])
     and its decode-sized batch of 64 tokens; the full 16384-token case is covered by the property
     test below."""
     _moe_layer(cuda, 2048, 4096, 1536, 128, 4)

@@ -97,7 +97,7 @@ struct MoeCfg {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
   static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 4) * 8 + 16 + 1024;
-  static constexpr int LOOKAHEAD = PAIR ? 3 : 2;  // K steps a gather warp keeps in flight (< stages)
+  static constexpr int LOOKAHEAD = PAIR ? 3 : 3;  // K steps a gather warp keeps in flight (< stages)
 };
 
 template <bool PAIR>
