@@ -97,7 +97,10 @@ struct MoeCfg {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
   static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 4) * 8 + 16 + 1024;
-  static constexpr int LOOKAHEAD = PAIR ? 3 : 3;  // K steps a gather warp keeps in flight (< stages)
+  // K steps a gather warp keeps in flight. At most stages - 2: the MMA thread releases stage i only after the
+  // first MMA of step i + 1, which needs step i + 1 signalled - with stages - 1 steps held back the gather
+  // would wait for a stage whose release waits for the gather (measured: a 2 s bounded-wait timeout).
+  static constexpr int LOOKAHEAD = PAIR ? 3 : 2;
 };
 
 template <bool PAIR>
