@@ -13,7 +13,8 @@
 //                tcgen05.mma.cta_group::2 with M = 256, which reads A from each CTA's own shared
 //                memory and the two halves of B from both, and leaves rows 128r..128r+127 of the
 //                accumulator in CTA r's tensor memory. Per CTA a K step lands 32 KB instead of
-//                48 KB, which keeps the TMA engine (measured ~75 B/clk/SM) under the MMA rate.
+//                48 KB: a step's traffic through the 128 B/clk shared-memory port (TMA writes plus
+//                the MMAs' operand reads) drops from 96 KB (750 cycles per 512 of MMA) to 80 KB.
 //                Signalling: TMA bytes of both CTAs count on the leader's `full` barrier; the
 //                leader issues one tcgen05.commit per CTA onto that CTA's `empty` / `tfull` barrier
 //                (two plain commits, no multicast); epilogue warps of both CTAs arrive on the
