@@ -228,6 +228,22 @@ def build_workload(name: str, rank: int, dev):
         return (step, fl, by, f"MoE layer, fp8 activations x MXFP4 weights: {T} tokens, d_model {D}, E={E}, top-{k}, "
                 f"W1 [{D},{2*F}] SwiGLU W2 [{F},{D}], gate-weighted combine, seed 4", "moe_gemm_mx4_kernel",
                 "hbm" if name == "moe_mx4_decode" else "tensor")
+    if name == "mxfp4_upcast":
+        from triton_b200.triton_kernels.matmul import upcast_mxfp4_weight
+        from triton_b200.triton_kernels.tensor import FP4, convert_layout, wrap_torch_tensor
+        from triton_b200.triton_kernels.tensor_details.layout import (make_default_matmul_mxfp4_w_layout,
+                                                                      make_default_matmul_mxfp4_w_scale_layout)
+        E, Kd, Nd = 128, 4096, 3072
+        g4 = torch.Generator(device="cpu").manual_seed(4 + 1000 * rank)
+        v = torch.randint(0, 256, (E, Kd // 2, Nd), generator=g4, dtype=torch.uint8).to(dev)
+        s = torch.randint(118, 130, (E, Kd // 32, Nd), generator=g4, dtype=torch.uint8).to(dev)
+        wv = convert_layout(wrap_torch_tensor(v, dtype=FP4), make_default_matmul_mxfp4_w_layout(mx_axis=1))
+        ws = convert_layout(wrap_torch_tensor(s), make_default_matmul_mxfp4_w_scale_layout(mx_axis=1))
+        del v, s
+        by = E * Kd * Nd * (0.5 + 1.0 / 32 + 2.0)
+        return (lambda: upcast_mxfp4_weight(wv, ws, torch.bfloat16), 0.0, by,
+                f"MXFP4 -> bf16 weight upcast: E={E} matrices [{Kd},{Nd}] (W1 of the MoE layer), random codes, seed 4",
+                "mxfp4_upcast_kernel", "hbm")
     if name == "moe_ep":
         import torch.distributed as dist
         from triton_b200.triton_kernels.distributed import (EpGroup, make_expt_assignment, make_expt_dict_uniform,
@@ -391,7 +407,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--workload", default="gemm",
                     help="gemm (headline, default) | attn | attn_causal | attn_short | attn_short_causal | attn_bwd | "
-                         "attn_bwd_causal | attn_bwd_ref_shape[_causal] | fp8 | fp8_blockwise | mxfp8 | moe | moe_decode | moe_mx4 | moe_mx4_decode | moe_ep")
+                         "attn_bwd_causal | attn_bwd_ref_shape[_causal] | fp8 | fp8_blockwise | mxfp8 | moe | moe_decode | moe_mx4 | moe_mx4_decode | mxfp4_upcast | moe_ep")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))

@@ -437,6 +437,26 @@ typedef struct {
 } tb200_moe_gemm_mx4_args;
 int tb200_moe_gemm_mx4(const tb200_moe_gemm_mx4_args* args, void* stream);
 
+/*
+ * Upcast of an MXFP4 weight (the blocked layout above) to a 16-bit matrix out[E][N][K], K contiguous - the
+ * operand tb200_moe_gemm takes with w_n_major = 0. With 16-bit activations the reference multiplies by an
+ * MXFP4 weight through tl.dot_scaled(x, None, "bf16", w, w_scales, "e2m1")
+ * (python/triton_kernels/triton_kernels/matmul_details/_matmul.py:485-489), i.e. the weight upcast to bf16 and
+ * the ordinary 16-bit MMA; this pass followed by tb200_moe_gemm is that product. Element values follow
+ * numerics_details/mxfp.py upcast_from_mxfp_torch: e2m1 value * float(scale << 23), clamped to the finite range
+ * of the output type, NaN kept.
+ * w, w_scale: as in tb200_moe_gemm_mx4_args. out: n_experts * n * k elements of TB200_BF16 / TB200_F16,
+ * 16-byte aligned. k % 128 == 0, n % 128 == 0.
+ */
+typedef struct {
+  const void* w;
+  const void* w_scale;
+  void* out;
+  int64_t n_experts, k, n;
+  int32_t out_dtype;
+} tb200_mxfp4_upcast_args;
+int tb200_mxfp4_upcast(const tb200_mxfp4_upcast_args* args, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,4 +1,4 @@
-"""FP8 activations x MXFP4 weights through ``triton_kernels.matmul.matmul`` (dense and grouped) against the
+"""FP8 (and bf16 / fp16) activations x MXFP4 weights through ``triton_kernels.matmul.matmul`` (dense and grouped) against the
 CPU oracle applied to the dequantised weights. The products are exact in fp32 up to summation order (fp8 x
 fp4 values with power-of-two scales), so the tolerance is bf16 output rounding: rtol 1e-2 / atol 1e-2; the
 reference's own matmul tolerance is maxtol 2e-2 (triton_kernels testing.py:21-80)."""
@@ -104,10 +104,67 @@ def test_exact_on_random_codes_few_rows_kernel(cuda):
     assert torch.equal(out.cpu(), (x.float() @ wdq[0]).to(torch.float16))
 
 
+def test_upcast_bit_exact(cuda):
+    """tb200_mxfp4_upcast against upcast_from_mxfp (itself pinned on the reference's golden vectors): every code,
+    every scale byte - 0 (zero), 255 (infinity: NaN for a zero code) and the range where fp16 clamps included -
+    and an N that is a multiple of 128 but not of 256 (the blocked layout pads it)."""
+    from triton_b200.triton_kernels.matmul import upcast_mxfp4_weight
+    E, K, N = 3, 256, 384
+    g = torch.Generator().manual_seed(7)
+    v = torch.randint(0, 256, (E, K // 2, N), generator=g).to(torch.uint8)
+    s = torch.randint(0, 256, (E, K // 32, N), generator=g).to(torch.uint8)
+    for dtype in (torch.bfloat16, torch.float16):
+        got = upcast_mxfp4_weight(v.to(cuda), s.to(cuda), dtype)
+        assert got.shape == (E, K, N) and got.stride(1) == 1
+        want = upcast_from_mxfp(v, s, dtype, axis=1)
+        got = got.cpu()
+        nan = want.isnan()
+        assert torch.equal(got.isnan(), nan)
+        assert torch.equal(got.view(torch.int16)[~nan], want.view(torch.int16)[~nan])
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [(128, 256, 128), (300, 384, 512), (1, 128, 128)])
+def test_dense_16bit_x_mx4(cuda, shape, dtype):
+    from triton_b200.triton_kernels.matmul import PrecisionConfig, matmul
+    M, N, K = shape
+    g = torch.Generator().manual_seed(8)
+    x = (torch.randn(M, K, generator=g) * 0.5).to(dtype)
+    v, s, wdq = _quantise(torch.randn(1, K, N, generator=g))
+    out = matmul(x.to(cuda), v.to(cuda), None, precision_config=PrecisionConfig(b_mx_scale=s.to(cuda)))
+    assert out.dtype == dtype
+    torch.testing.assert_close(out.cpu().float(), x.float() @ wdq[0], rtol=1e-2, atol=1e-2)
+
+
+@pytest.mark.parametrize("T,E,k", [(64, 8, 2), (777, 16, 4)])
+def test_grouped_bf16_x_mx4(cuda, T, E, k):
+    """bf16 activations gathered by token, MXFP4 expert weights, SwiGLU, gammas and scatter."""
+    from triton_b200.triton_kernels.matmul import PrecisionConfig, matmul, swiglu_activation
+    from triton_b200.triton_kernels.tensor import make_ragged_tensor_metadata
+    from triton_b200.triton_kernels.topk import topk
+    K, N = 256, 512
+    g = torch.Generator().manual_seed(9)
+    sm = topk(torch.randn(T, E, generator=g).to(cuda), k)
+    mm = sm.mask_metadata
+    rg = make_ragged_tensor_metadata(mm.col_sum, T * k)
+    combine = mm.col_sorted_indx
+    gather = (combine // k).to(torch.int32)
+    x = (torch.randn(T, K, generator=g) * 0.5).to(torch.bfloat16)
+    v, s, wdq = _quantise(torch.randn(E, K, N, generator=g) * 0.5)
+    bias = torch.randn(E, N, generator=g)
+    gam = torch.rand(T * k, generator=g)
+    wv, ws = _prepared(v, s, cuda)
+    out = matmul(x.to(cuda), wv, bias.to(cuda), rg, gather_indx=gather, scatter_indx=combine, gammas=gam.to(cuda),
+                 precision_config=PrecisionConfig(b_mx_scale=ws), fused_activation=swiglu_activation(1.1, 7.0))
+    ref = o.grouped_matmul_ref(x.float(), wdq, bias, mm.col_sum.cpu().numpy(), gather.cpu().numpy(),
+                               combine.cpu().numpy(), gam, (1.1, 7.0), out_dtype=torch.bfloat16)
+    torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=2e-2, atol=2e-2)
+
+
 def test_argument_checks(cuda):
     from triton_b200.triton_kernels.matmul import PrecisionConfig, matmul
-    x = torch.zeros(128, 256, device=cuda, dtype=torch.bfloat16)
+    x = torch.zeros(128, 256, device=cuda, dtype=torch.float32)
     v = torch.zeros(1, 128, 128, device=cuda, dtype=torch.uint8)
     s = torch.full((1, 8, 128), 127, device=cuda, dtype=torch.uint8)
     with pytest.raises(NotImplementedError):
-        matmul(x, v, None, precision_config=PrecisionConfig(b_mx_scale=s))  # bf16 activations
+        matmul(x, v, None, precision_config=PrecisionConfig(b_mx_scale=s))  # fp32 activations

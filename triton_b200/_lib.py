@@ -135,6 +135,13 @@ class MoeGemmMx4Args(Structure):
     ]
 
 
+class Mxfp4UpcastArgs(Structure):
+    _fields_ = [
+        ("w", c_void_p), ("w_scale", c_void_p), ("out", c_void_p),
+        ("n_experts", c_int64), ("k", c_int64), ("n", c_int64), ("out_dtype", c_int32),
+    ]
+
+
 _lib = None
 
 
@@ -173,6 +180,8 @@ def _declare(l: ctypes.CDLL) -> None:
     l.tb200_gemm_fp8_blockwise.argtypes = [POINTER(GemmFp8BlockwiseArgs), c_void_p]
     l.tb200_moe_gemm_mx4.restype = c_int
     l.tb200_moe_gemm_mx4.argtypes = [POINTER(MoeGemmMx4Args), c_void_p]
+    l.tb200_mxfp4_upcast.restype = c_int
+    l.tb200_mxfp4_upcast.argtypes = [POINTER(Mxfp4UpcastArgs), c_void_p]
     l.tb200_gemm_mxfp8.restype = c_int
     l.tb200_gemm_mxfp8.argtypes = [POINTER(GemmMxfp8Args), c_void_p]
 

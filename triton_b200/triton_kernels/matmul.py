@@ -79,8 +79,16 @@ def matmul(a, b, bias, a_ragged_metadata: RaggedTensorMetadata | None = None, b_
                                          or precision_config.c_mx_scale is not None):
         raise NotImplementedError("matmul: MX-scaled activations / outputs are not implemented")
     if precision_config is not None and precision_config.b_mx_scale is not None:
+        if isinstance(a, torch.Tensor) and a.dtype in _DT:
+            # 16-bit activations: the weight is upcast to the activation dtype (what the reference's
+            # tl.dot_scaled(x, None, "bf16", w, w_scales, "e2m1") computes), then the 16-bit grouped GEMM runs
+            w16 = upcast_mxfp4_weight(b, precision_config.b_mx_scale, a.dtype,
+                                      precision_config.b_microblock_size)
+            pc16 = PrecisionConfig(out_dtype=precision_config.out_dtype)
+            return matmul(a, w16, bias, a_ragged_metadata, None, gather_indx, scatter_indx, pc16, None, gammas,
+                          None, c, None, fused_activation, epilogue, None, _tile_mode)
         if gather_indx is not None or c is not None:
-            raise NotImplementedError("matmul (MXFP4 weight): gather_indx / preallocated output are not implemented")
+            raise NotImplementedError("matmul (fp8 x MXFP4): gather_indx / preallocated output are not implemented")
         return _matmul_mx4(a, b, bias, a_ragged_metadata, scatter_indx, precision_config, gammas, fused_activation)
     if not isinstance(a, torch.Tensor) or not isinstance(b, torch.Tensor):
         raise NotImplementedError("matmul: wrapped Tensor operands need precision_config.b_mx_scale (MXFP4 weights)")
@@ -168,31 +176,60 @@ def matmul(a, b, bias, a_ragged_metadata: RaggedTensorMetadata | None = None, b_
 _F8 = {torch.float8_e4m3fn: _lib.E4M3, torch.float8_e5m2: _lib.E5M2}
 
 
-def _matmul_mx4(a, b, bias, a_ragged_metadata, scatter_indx, pc: PrecisionConfig, gammas, fused_activation):
-    """FP8 activations x MXFP4 weights (the reference's Blackwell "fp8 x mx4" MoE configuration,
-    bench/bench_mlp.py:253-279). ``b`` / ``pc.b_mx_scale`` are either what ``downcast_to_mxfp(w, torch.uint8,
-    axis=1)`` returned ([E, K/2, N] and [E, K/32, N] uint8: re-laid here on every call) or the Tensors
-    ``convert_layout`` produced from them (no per-call work)."""
+def _mx4_kernel_layout(b, b_mx_scale, microblock):
+    """The weight and its scales as the Tensors the kernels read (converted here when given as plain uint8)."""
     from .tensor import FP4, Tensor, convert_layout, wrap_torch_tensor
     from .tensor_details.layout import (BlackwellMX4ValueLayout, BlackwellMXScaleLayout,
                                         make_default_matmul_mxfp4_w_layout, make_default_matmul_mxfp4_w_scale_layout)
-    if not isinstance(a, torch.Tensor) or a.dtype not in _F8:
-        raise NotImplementedError("matmul (MXFP4 weight): activations must be float8_e4m3fn or float8_e5m2")
-    if not a.is_cuda:
-        raise RuntimeError("triton_b200 matmul needs CUDA tensors (there is no CPU path)")
-    if a.ndim != 2:
-        raise NotImplementedError("matmul: batched input is not implemented")
-    if pc.b_microblock_size not in (None, 32):
+    if microblock not in (None, 32):
         raise NotImplementedError("matmul (MXFP4 weight): microblock size 32 (e8m0 scales) only")
+    if not isinstance(b, Tensor) and b.dtype != torch.uint8:
+        raise NotImplementedError(f"matmul: b_mx_scale with a {b.dtype} weight (packed FP4 in uint8 is implemented)")
     w = b if isinstance(b, Tensor) else wrap_torch_tensor(b, dtype=FP4)
-    ws = pc.b_mx_scale if isinstance(pc.b_mx_scale, Tensor) else wrap_torch_tensor(pc.b_mx_scale)
+    ws = b_mx_scale if isinstance(b_mx_scale, Tensor) else wrap_torch_tensor(b_mx_scale)
     if not isinstance(w.layout, BlackwellMX4ValueLayout):
         w = convert_layout(w, make_default_matmul_mxfp4_w_layout(mx_axis=1))
     if not isinstance(ws.layout, BlackwellMXScaleLayout):
         ws = convert_layout(ws, make_default_matmul_mxfp4_w_scale_layout(mx_axis=1))
     E, K, N = w.shape
-    assert a.shape[1] == K, "inner dimensions differ"
     assert ws.shape == (E, K // 32, N), "scale shape does not match the weight"
+    return w, ws
+
+
+def upcast_mxfp4_weight(b, b_mx_scale, dtype, microblock=None):
+    """An MXFP4 weight ([E, K/2, N] uint8 + [E, K/32, N] e8m0, or the converted Tensors) as a ``[E, K, N]``
+    bf16 / fp16 view with K contiguous (``tb200_mxfp4_upcast``)."""
+    w, ws = _mx4_kernel_layout(b, b_mx_scale, microblock)
+    E, K, N = w.shape
+    dev = w.data.device
+    if not w.data.is_cuda:
+        raise RuntimeError("triton_b200 matmul needs CUDA tensors (there is no CPU path)")
+    out = torch.empty((E, N, K), dtype=dtype, device=dev)
+    if out.numel():
+        args = _lib.Mxfp4UpcastArgs()
+        args.w, args.w_scale, args.out = w.data.data_ptr(), ws.data.data_ptr(), out.data_ptr()
+        args.n_experts, args.k, args.n = E, K, N
+        args.out_dtype = _DT[dtype]
+        with torch.cuda.device(dev):
+            rc = _lib.lib().tb200_mxfp4_upcast(ctypes.byref(args), ctypes.c_void_p(_lib.current_stream_ptr(dev)))
+        _lib.check(rc, "tb200_mxfp4_upcast")
+    return out.transpose(1, 2)
+
+
+def _matmul_mx4(a, b, bias, a_ragged_metadata, scatter_indx, pc: PrecisionConfig, gammas, fused_activation):
+    """FP8 activations x MXFP4 weights (the reference's Blackwell "fp8 x mx4" MoE configuration,
+    bench/bench_mlp.py:253-279). ``b`` / ``pc.b_mx_scale`` are either what ``downcast_to_mxfp(w, torch.uint8,
+    axis=1)`` returned ([E, K/2, N] and [E, K/32, N] uint8: re-laid here on every call) or the Tensors
+    ``convert_layout`` produced from them (no per-call work)."""
+    if not isinstance(a, torch.Tensor) or a.dtype not in _F8:
+        raise NotImplementedError("matmul (MXFP4 weight): activations must be fp8 (e4m3fn / e5m2), bf16 or fp16")
+    if not a.is_cuda:
+        raise RuntimeError("triton_b200 matmul needs CUDA tensors (there is no CPU path)")
+    if a.ndim != 2:
+        raise NotImplementedError("matmul: batched input is not implemented")
+    w, ws = _mx4_kernel_layout(b, pc.b_mx_scale, pc.b_microblock_size)
+    E, K, N = w.shape
+    assert a.shape[1] == K, "inner dimensions differ"
     dev = a.device
     if a.stride(1) != 1 or a.stride(0) % 16:
         a = a.contiguous()
