@@ -207,7 +207,8 @@ def build_workload(name: str, rank: int, dev):
                     convert_layout(wrap_torch_tensor(s), make_default_matmul_mxfp4_w_scale_layout(mx_axis=1)))
         w1, s1 = prep(0.02 * torch.randn(E, D, 2 * F, generator=g4))
         w2, s2 = prep(0.02 * torch.randn(E, F, D, generator=g4))
-        pc1, pc2 = PrecisionConfig(b_mx_scale=s1), PrecisionConfig(b_mx_scale=s2)
+        # GEMM 1 writes fp8 (the default: the activations' dtype), GEMM 2 bf16 for the combine
+        pc1, pc2 = PrecisionConfig(b_mx_scale=s1), PrecisionConfig(b_mx_scale=s2, out_dtype=torch.bfloat16)
         act = swiglu_activation(1.0, None)
 
         def step():
@@ -219,12 +220,12 @@ def build_workload(name: str, rank: int, dev):
             gam = sm.vals.float().reshape(-1)[combine.long()]
             xs = x.view(torch.uint8)[gather.long()].view(torch.float8_e4m3fn)  # rows in expert order
             h = moe_matmul(xs, w1, None, rg, precision_config=pc1, fused_activation=act)
-            y = moe_matmul(h.to(torch.float8_e4m3fn), w2, None, rg, scatter_indx=combine, gammas=gam, precision_config=pc2)
+            y = moe_matmul(h, w2, None, rg, scatter_indx=combine, gammas=gam, precision_config=pc2)
             return reduce(y.view(T, k, D), dim=1)[0]
         R = T * k
         fl = 2.0 * R * D * 2 * F + 2.0 * R * F * D
         active = int((topk(logits, k).mask_metadata.col_sum > 0).sum().item())
-        by = active * (D * 2 * F + F * D) * (0.5 + 1.0 / 32) + R * (D + F) * 1.0 + R * (F + D) * 2.0
+        by = active * (D * 2 * F + F * D) * (0.5 + 1.0 / 32) + R * (D + F) * 1.0 + R * (F * 1.0 + D * 2.0)
         return (step, fl, by, f"MoE layer, fp8 activations x MXFP4 weights: {T} tokens, d_model {D}, E={E}, top-{k}, "
                 f"W1 [{D},{2*F}] SwiGLU W2 [{F},{D}], gate-weighted combine, seed 4", "moe_gemm_mx4_kernel",
                 "hbm" if name == "moe_mx4_decode" else "tensor")

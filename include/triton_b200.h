@@ -90,7 +90,7 @@ typedef struct {
   int32_t a_k_major;
   int32_t b_k_major;
   int32_t split_k;
-  int32_t block_n; /* 0 = choose; 64, 128 or 256 = one CTA per 128 x block_n tile; 512 = CTA pair per 256 x 256 tile */
+  int32_t block_n; /* 0 = choose; 64, 128 or 256 = one CTA per 128 x block_n tile; 512 = CTA pair per 256 x 256 tile; 1024 = CTA pair per 256 x 512 tile */
   void* workspace;
   size_t workspace_bytes;
   const float* scale_a;
@@ -409,7 +409,10 @@ int tb200_moe_gemm(const tb200_moe_gemm_args* args, void* stream);
  *    rows past N) and values 128 s .. 128 s + 127 of each; 32-byte aligned.
  * w_scale: uint8 e8m0, one per 32 values of K, per expert in 512-byte atoms
  *    [E][N/128][K/128][n%32][n/32%4][k/32%4]   (the layout tb200_gemm_mxfp8 uses for its scales).
- * k % 128 == 0, n % 128 == 0. Output TB200_BF16 or TB200_F16. Other fields as in tb200_moe_gemm_args.
+ * k % 128 == 0, n % 128 == 0. Output TB200_BF16, TB200_F16, or TB200_E4M3 / TB200_E5M2 (round to nearest even,
+ * saturating to the largest finite value: the conversion of the reference's kernels when the output tensor is
+ * fp8, which is what matmul.py:243 allocates for fp8 activations unless precision_config.out_dtype says otherwise).
+ * ldy in elements of the output type. Other fields as in tb200_moe_gemm_args.
  */
 typedef struct {
   const void* x;

@@ -40,6 +40,10 @@ def test_scaled_mm_rowwise(cuda, shape):
     out = blackwell_scaled_mm_ws(a.to(cuda), b.to(cuda), sa.to(cuda), sb.to(cuda), scale_mode="rowwise")
     ref = o_gemm.scaled_mm_rowwise_ref(a, b, sa, sb)
     torch.testing.assert_close(out.cpu().float(), ref.float(), atol=1e-3, rtol=1e-2)
+    # the 256 x 512 CTA-pair tile (permuted accumulator columns: the per-column scale must follow)
+    out = blackwell_scaled_mm_ws(a.to(cuda), b.to(cuda), sa.to(cuda), sb.to(cuda), scale_mode="rowwise", NUM_CTAS=2,
+                                 BLOCK_N=512)
+    torch.testing.assert_close(out.cpu().float(), ref.float(), atol=1e-3, rtol=1e-2)
 
 
 @pytest.mark.parametrize("shape", [(1024, 1024, 1024), (384, 256, 640), (200, 128, 256), (4096, 2048, 4096)])

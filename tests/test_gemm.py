@@ -91,6 +91,33 @@ def test_tile_widths_and_split_k(cuda, bn, split_k):
     _check(c, o_gemm.gemm_ref(a, w.T))
 
 
+@pytest.mark.parametrize("tile", [512, 1024])  # CTA pair: 256 x 256 and 256 x 512 tiles
+@pytest.mark.parametrize("layout", ["nn", "nt", "tn", "tt"])
+@pytest.mark.parametrize("shape", [(512, 1024, 512), (300, 700, 264), (1000, 1000, 1000)])
+def test_cta_pair_tiles(cuda, tile, layout, shape):
+    """Both CTA-pair tilings on all four operand layouts, with ragged M / N / K edges (the wide tile permutes
+    its accumulator columns: every 128-column group must land on the right output columns)."""
+    M, N, K = shape
+    torch.manual_seed(6)
+    a = (torch.randn(M, K) / K ** 0.5).to(torch.bfloat16)
+    b = torch.randn(K, N).to(torch.bfloat16)
+    ad = a.to(cuda) if layout[0] == "n" else a.t().contiguous().to(cuda).t()
+    bd = b.to(cuda) if layout[1] == "n" else b.t().contiguous().to(cuda).t()
+    if (ad.stride(0) if ad.stride(1) == 1 else ad.stride(1)) % 8 or (bd.stride(0) if bd.stride(1) == 1 else bd.stride(1)) % 8:
+        pytest.skip("leading dimension not 16-byte aligned in this layout")
+    c = _mm()(ad, bd, config={"BLOCK_SIZE_N": tile})
+    _check(c, o_gemm.gemm_ref(a, b))
+
+
+def test_wide_tile_split_k(cuda):
+    torch.manual_seed(7)
+    M, N, K = 256, 1024, 4096
+    a = (torch.randn(M, K) / K ** 0.5).to(torch.bfloat16)
+    w = torch.randn(N, K).to(torch.bfloat16)
+    c = _mm()(a.to(cuda), w.to(cuda).T, config={"BLOCK_SIZE_N": 1024, "SPLIT_K": 3})
+    _check(c, o_gemm.gemm_ref(a, w.T))
+
+
 def test_skinny_config2(cuda):
     """The skinny case of benchmark config 2, M=128, N=K=8192 (B K-major), seed 1."""
     torch.manual_seed(1)

@@ -39,7 +39,7 @@ def test_dense_fp8_x_mx4(cuda, shape, prepared):
         wv, ws = _prepared(v, s, cuda)
     else:
         wv, ws = v.to(cuda), s.to(cuda)
-    out = matmul(x.to(cuda), wv, None, precision_config=PrecisionConfig(b_mx_scale=ws))
+    out = matmul(x.to(cuda), wv, None, precision_config=PrecisionConfig(b_mx_scale=ws, out_dtype=torch.bfloat16))
     ref = x.float() @ wdq[0]
     assert out.dtype == torch.bfloat16
     torch.testing.assert_close(out.cpu().float(), ref, rtol=1e-2, atol=1e-2)
@@ -84,7 +84,8 @@ def test_grouped_fp8_x_mx4(cuda, T, E, k, swiglu):
     wv, ws = _prepared(v, s, cuda)
     act = swiglu_activation(1.1, 7.0) if swiglu else None
     out = matmul(x_sorted.to(cuda), wv, bias.to(cuda), rg, scatter_indx=combine, gammas=gam.to(cuda),
-                 precision_config=PrecisionConfig(b_mx_scale=ws, x_scale=0.25), fused_activation=act)
+                 precision_config=PrecisionConfig(b_mx_scale=ws, x_scale=0.25, out_dtype=torch.bfloat16),
+                 fused_activation=act)
     ref = o.grouped_matmul_ref(x_sorted.float() * 0.25, wdq, bias, mm.col_sum.cpu().numpy(), None,
                                combine.cpu().numpy(), gam, (1.1, 7.0) if swiglu else None, out_dtype=torch.bfloat16)
     torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=2e-2, atol=2e-2)
@@ -102,6 +103,57 @@ def test_exact_on_random_codes_few_rows_kernel(cuda):
     out = matmul(x.to(cuda), v.to(cuda), None,
                  precision_config=PrecisionConfig(b_mx_scale=s.to(cuda), out_dtype=torch.float16))
     assert torch.equal(out.cpu(), (x.float() @ wdq[0]).to(torch.float16))
+
+
+def _fp8_sat(x, dtype):
+    """fp32 -> fp8 the way the kernels convert: round to nearest even, saturate to the largest finite value."""
+    lim = torch.finfo(dtype).max
+    return x.clamp(-lim, lim).to(dtype)
+
+
+@pytest.mark.parametrize("M", [128, 24])  # the 128-row kernel and the swapped-operand one
+@pytest.mark.parametrize("out_dtype", [None, torch.float8_e5m2])
+def test_fp8_output_exact(cuda, M, out_dtype):
+    """Default output dtype = the activations' (fp8), as in the reference (matmul.py:175). Integer activations and
+    random codes make every accumulator exact, so the fp8 output must equal the saturating round-to-nearest cast
+    of the oracle's fp32 product bit for bit; the scale exponents are chosen so that some outputs saturate."""
+    from triton_b200.triton_kernels.matmul import PrecisionConfig, matmul
+    N, K = 384, 256
+    g = torch.Generator().manual_seed(11)
+    x = torch.randint(-2, 3, (M, K), generator=g).float().to(torch.float8_e4m3fn)
+    v = torch.randint(0, 256, (1, K // 2, N), generator=g).to(torch.uint8)
+    s = torch.randint(124, 132, (1, K // 32, N), generator=g).to(torch.uint8)
+    wdq = upcast_from_mxfp(v, s, torch.float32, axis=1)
+    out = matmul(x.to(cuda), v.to(cuda), None, precision_config=PrecisionConfig(b_mx_scale=s.to(cuda), out_dtype=out_dtype))
+    want_dtype = out_dtype or torch.float8_e4m3fn
+    assert out.dtype == want_dtype
+    ref = _fp8_sat(x.float() @ wdq[0], want_dtype)
+    if want_dtype == torch.float8_e4m3fn:
+        assert (ref.float().abs() == 448).any(), "the case is meant to saturate somewhere"
+    assert torch.equal(out.cpu().view(torch.uint8), ref.view(torch.uint8))
+
+
+def test_fp8_output_swiglu_scatter(cuda):
+    """fp8 output through SwiGLU, gammas and scatter (ragged N tail of 16 outputs per 32 columns included)."""
+    from triton_b200.triton_kernels.matmul import PrecisionConfig, matmul, swiglu_activation
+    from triton_b200.triton_kernels.tensor import make_ragged_tensor_metadata
+    from triton_b200.triton_kernels.topk import topk
+    T, E, k, K, N = 300, 16, 4, 256, 384
+    g = torch.Generator().manual_seed(12)
+    sm = topk(torch.randn(T, E, generator=g).to(cuda), k)
+    mm = sm.mask_metadata
+    rg = make_ragged_tensor_metadata(mm.col_sum, T * k)
+    combine = mm.col_sorted_indx
+    x_sorted = (torch.randn(T, K, generator=g) * 0.5)[(combine.cpu().long() // k)].to(torch.float8_e4m3fn)
+    v, s, wdq = _quantise(torch.randn(E, K, N, generator=g) * 0.5)
+    gam = torch.rand(T * k, generator=g)
+    out = matmul(x_sorted.to(cuda), v.to(cuda), None, rg, scatter_indx=combine, gammas=gam.to(cuda),
+                 precision_config=PrecisionConfig(b_mx_scale=s.to(cuda)), fused_activation=swiglu_activation(1.1, 7.0))
+    assert out.dtype == torch.float8_e4m3fn and out.shape == (T * k, N // 2)
+    ref = o.grouped_matmul_ref(x_sorted.float(), wdq, None, mm.col_sum.cpu().numpy(), None, combine.cpu().numpy(), gam,
+                               (1.1, 7.0), out_dtype=torch.float32)
+    # one fp8 rounding step (2^-3 relative) on top of the fp32 summation-order difference
+    torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=0.07, atol=2e-2)
 
 
 def test_upcast_bit_exact(cuda):

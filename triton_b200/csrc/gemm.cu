@@ -20,6 +20,14 @@
 //                (two plain commits, no multicast); epilogue warps of both CTAs arrive on the
 //                leader's `tempty`.
 //
+//   wide pair  : the same with a 256 x 512 tile: each CTA stages 128 A rows and 256 B rows per K step, the
+//                leader issues two N = 256 MMAs per K sub-step into the two halves of a single 512-column
+//                accumulator (all of tensor memory, so the epilogue is not overlapped with the next tile's
+//                MMAs: ~4 % of a K = 8192 tile). A is staged once for 512 columns: per 1024 MMA cycles a
+//                CTA's port carries 48 KB of TMA writes + 96 KB of operand reads at most, against
+//                2 x (32 + 48) KB for two 256 x 256 tiles - the port stops being the limit (tensor pipe
+//                active 85 % -> measured below), and L2 -> SM traffic per flop drops by a quarter.
+//
 // The issue loops are kept lean on purpose: measured on B200, tcgen05.mma issue blocks the issuing
 // thread until the tensor pipe accepts the instruction, so every other instruction in the MMA
 // thread's loop is exposed tensor-pipe idle time. All loop-invariant parameters are copied to
@@ -100,9 +108,13 @@ __device__ __forceinline__ void issue_mma(uint32_t tmem_d, uint64_t ad, uint64_t
 template <int BNC, int STAGES, bool PAIR, bool F8>
 __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const __grid_constant__ GemmParams p) {
   using L = GemmSmem<BNC, STAGES>;
-  constexpr int BN = PAIR ? 256 : BNC;        // accumulator columns per tile
+  constexpr int BN = PAIR ? 2 * BNC : BNC;    // accumulator columns per tile
   constexpr int TILE_M = PAIR ? 256 : BM;     // output rows per scheduling unit
-  constexpr uint32_t TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;
+  constexpr bool WIDE = PAIR && BNC == 256;   // 256 x 512 tile: two N = 256 MMAs per K step, one accumulator
+  constexpr uint32_t NACC = WIDE ? 1 : 2;     // accumulators in tensor memory
+  constexpr uint32_t TMEM_COLS = (NACC * BN < 32) ? 32 : NACC * BN;
+  // descriptor offset (16-byte units) of the second 128 B rows inside a CTA's staged B tile: 16 KB in both layouts
+  constexpr uint64_t B_HALF = (128 * STAGE_K_BYTES) >> 4;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET);
@@ -220,14 +232,20 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const __grid_cons
         const TileCoord t = unit_to_tile(unit, split_k, group_m, tiles_m, tiles_n);
         const int kb0 = t.ks * kb_per_split;
         const int nkb = min(k_blocks, kb0 + kb_per_split) - kb0;
-        const uint32_t acc = tcount & 1;
-        const uint32_t aph = (tcount >> 1) & 1;
+        const uint32_t acc = tcount % NACC;
+        const uint32_t aph = (tcount / NACC) & 1;
         if (!mbar_wait_a(tempty_a + acc * 8, aph ^ 1, status, WAIT_TMEM_EMPTY)) {
           ok = false;
           break;
         }
         tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + acc * BN;
+        // one K sub-step: N = 256 columns, or both 256-column halves of the wide tile (A is read twice from shared
+        // memory but staged once)
+        auto mma_step = [&](uint64_t a_desc, uint64_t b_desc, uint32_t accumulate) {
+          issue_mma<PAIR, F8>(tmem_d, a_desc, b_desc, idesc, accumulate);
+          if constexpr (WIDE) issue_mma<PAIR, F8>(tmem_d + 256, a_desc, b_desc + B_HALF, idesc, accumulate);
+        };
         // Loop shape: every non-MMA instruction sits between two MMAs of the same K step, where it
         // overlaps with tensor-pipe work already queued: the commit that frees the previous stage
         // comes after this step's first MMA, the wait for the next stage after the second.
@@ -241,7 +259,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const __grid_cons
         for (int i = 0; i < nkb; ++i) {
           const uint64_t ad = adesc0 + (uint64_t)(s * (L::STAGE_BYTES >> 4));
           const uint64_t bd = bdesc0 + (uint64_t)(s * (L::STAGE_BYTES >> 4));
-          issue_mma<PAIR, F8>(tmem_d, ad, bd, idesc, accum);
+          mma_step(ad, bd, accum);
           accum = 1u;
           if (prev_empty) {
             if constexpr (PAIR) {
@@ -252,7 +270,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const __grid_cons
             }
           }
           prev_empty = empty_a + s * 8;
-          issue_mma<PAIR, F8>(tmem_d, ad + ak, bd + bk, idesc, 1u);
+          mma_step(ad + ak, bd + bk, 1u);
           if (++s == STAGES) {
             s = 0;
             ph ^= 1;
@@ -264,8 +282,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const __grid_cons
             }
             tc_fence_after_sync();
           }
-          issue_mma<PAIR, F8>(tmem_d, ad + 2 * ak, bd + 2 * bk, idesc, 1u);
-          issue_mma<PAIR, F8>(tmem_d, ad + 3 * ak, bd + 3 * bk, idesc, 1u);
+          mma_step(ad + 2 * ak, bd + 2 * bk, 1u);
+          mma_step(ad + 3 * ak, bd + 3 * bk, 1u);
         }
         if (ok) {
           if constexpr (PAIR) {
@@ -301,8 +319,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const __grid_cons
     for (int unit = worker; unit < units && ok; unit += num_workers, ++tcount) {
       const TileCoord t = unit_to_tile(unit, split_k, group_m, tiles_m, tiles_n);
       const int m0 = t.pid_m * TILE_M + (int)rank * BM, n0 = t.pid_n * BN;
-      const uint32_t acc = tcount & 1;
-      const uint32_t aph = (tcount >> 1) & 1;
+      const uint32_t acc = tcount % NACC;
+      const uint32_t aph = (tcount / NACC) & 1;
       if (!mbar_wait(&tfull[acc], aph, status, WAIT_TMEM_FULL)) {
         ok = false;
         break;
@@ -311,12 +329,30 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const __grid_cons
       const int row = m0 + q * 32 + lane;
       const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + acc * BN;
       if (row_scale) alpha = row < m ? __ldg(row_scale + row) : 0.f;
+      // wide tile: accumulator columns [128 j, 128 j + 128) hold output columns of B rows staged by CTA (j & 1),
+      // MMA (j >> 1): CTA r stages B rows n0 + 256 r .. + 255 and MMA h takes rows 128 h .. 128 h + 127 of each
+      auto out_col = [&](int cc) { return WIDE ? n0 + ((cc >> 7) & 1) * 256 + (cc >> 8) * 128 + (cc & 127) : n0 + cc; };
+      if constexpr (BN >= 64) {
+        // two chunks in flight: the next tensor-memory load runs while this chunk is converted and stored
+        uint32_t v0[32], v1[32];
+        tmem_ld_32x32b_x32(taddr, v0);
 #pragma unroll 1
-      for (int cc = 0; cc < BN; cc += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(taddr + cc, v);
-        tmem_ld_wait();
-        store_chunk(c, ws, ldc, m, n, out_mode, v, row, n0 + cc, t.ks, alpha, col_scale);
+        for (int cc = 0; cc < BN; cc += 64) {
+          tmem_ld_wait();
+          tmem_ld_32x32b_x32(taddr + cc + 32, v1);
+          store_chunk(c, ws, ldc, m, n, out_mode, v0, row, out_col(cc), t.ks, alpha, col_scale);
+          tmem_ld_wait();
+          if (cc + 64 < BN) tmem_ld_32x32b_x32(taddr + cc + 64, v0);
+          store_chunk(c, ws, ldc, m, n, out_mode, v1, row, out_col(cc + 32), t.ks, alpha, col_scale);
+        }
+      } else {
+#pragma unroll 1
+        for (int cc = 0; cc < BN; cc += 32) {
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(taddr + cc, v);
+          tmem_ld_wait();
+          store_chunk(c, ws, ldc, m, n, out_mode, v, row, out_col(cc), t.ks, alpha, col_scale);
+        }
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -376,7 +412,7 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ ws, void* __restr
 // ------------------------------------------------------------------------------- host
 
 struct GemmPlan {
-  int pair;  // 1: CTA-pair kernel, 256 x 256 tile per cluster
+  int pair;  // 1: CTA-pair kernel, 256 x 256 tile per cluster; 2: 256 x 512 tile per cluster
   int bn;
   int split_k;
   int kb_per_split;
@@ -406,6 +442,9 @@ static bool plan_gemm(const tb200_gemm_args* a, int sms, GemmPlan* plan) {
   if (bn == 512) {
     pair = 1;
     bn = 256;
+  } else if (bn == 1024) {
+    pair = 2;
+    bn = 512;
   } else if (bn == 0) {
     // Estimated time = waves x per-tile cost; one SM handles a 128 x bn tile in ~(bn + 48) units.
     long long best = -1;
@@ -429,10 +468,20 @@ static bool plan_gemm(const tb200_gemm_args* a, int sms, GemmPlan* plan) {
       if (cost2 <= best) {
         pair = 1;
         bn = 256;
+        best = cost2;
+      }
+      // 256 x 512 per pair: twice the tile at ~88 % of twice the cost (measured at 8192^3); worth it when the
+      // coarser tiles still fill the waves
+      const long long tiles3 = ((a->m + 255) / 256) * ((a->n + 511) / 512);
+      const long long waves3 = (tiles3 + sms / 2 - 1) / (sms / 2);
+      const long long cost3 = waves3 * (512 + 24) * 3 * 88 / 100;
+      if (cost3 < best) {
+        pair = 2;
+        bn = 512;
       }
     }
   }
-  if (bn != 64 && bn != 128 && bn != 256) return false;
+  if (bn != 64 && bn != 128 && bn != 256 && !(pair == 2 && bn == 512)) return false;
   if (pair) tm_eff = (a->m + 255) / 256;
   const long long tn = (a->n + bn - 1) / bn;
   const long long tiles = tm_eff * tn * (pair ? 2 : 1);
@@ -536,6 +585,7 @@ template <bool F8>
 static int launch_gemm(const GemmParams& p, const GemmPlan& plan, int sms, cudaStream_t stream) {
   if (plan.pair) {
     const int clusters = p.units < sms / 2 ? p.units : sms / 2;
+    if (plan.pair == 2) return launch_one<256, 4, true, F8>(p, 2 * clusters, stream);
     return launch_one<128, 7, true, F8>(p, 2 * clusters, stream);
   }
   const int grid = p.units < sms ? p.units : sms;
@@ -583,7 +633,7 @@ extern "C" int tb200_gemm(const tb200_gemm_args* a, void* stream_) {
                                                            : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
   rc = set_operand(&p.ga, &p.tma, a->a, a->m, a->k, a->lda, a->a_k_major, eb, BM, dt);
   if (rc != TB200_OK) return rc;
-  rc = set_operand(&p.gb, &p.tmb, a->b, a->n, a->k, a->ldb, a->b_k_major, eb, plan.pair ? 128 : plan.bn, dt);
+  rc = set_operand(&p.gb, &p.tmb, a->b, a->n, a->k, a->ldb, a->b_k_major, eb, plan.pair == 2 ? 256 : plan.pair ? 128 : plan.bn, dt);
   if (rc != TB200_OK) return rc;
 
   uint32_t fmt;
@@ -591,7 +641,7 @@ extern "C" int tb200_gemm(const tb200_gemm_args* a, void* stream_) {
     fmt = a->in_dtype == TB200_E4M3 ? 0u : 1u;
   else
     fmt = a->in_dtype == TB200_F16 ? 0u : 1u;
-  p.idesc = make_idesc(fmt, fmt, p.ga.mn_major, p.gb.mn_major, plan.pair ? 256 : BM, plan.bn);
+  p.idesc = make_idesc(fmt, fmt, p.ga.mn_major, p.gb.mn_major, plan.pair ? 256 : BM, plan.pair ? 256 : plan.bn);
   p.c = a->c;
   p.ldc = a->ldc;
   p.m = (int)a->m;

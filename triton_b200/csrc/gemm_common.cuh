@@ -22,6 +22,14 @@ __device__ __forceinline__ TileCoord unit_to_tile(int unit, int split_k, int gro
   return t;
 }
 
+// One 32-byte global store (sm_100: 256-bit vector stores); dst 32-byte aligned.
+__device__ __forceinline__ void st_global_v8(void* dst, uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t e,
+                                             uint32_t f, uint32_t g, uint32_t h) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst), "r"(a), "r"(b), "r"(c), "r"(d),
+               "r"(e), "r"(f), "r"(g), "r"(h)
+               : "memory");
+}
+
 // Writes 32 consecutive columns of one output row (fp32 accumulators in v) in the output mode.
 __device__ __forceinline__ void store_chunk(void* c, float* ws, long long ldc, int m, int n, int out_mode,
                                             uint32_t (&v)[32], int row, int col, int ks, float alpha,
@@ -35,7 +43,19 @@ __device__ __forceinline__ void store_chunk(void* c, float* ws, long long ldc, i
   }
   if (out_mode <= 1) {
     uint16_t* dst = reinterpret_cast<uint16_t*>(c) + (long long)row * ldc + col;
-    if (full && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+    if (full && ((reinterpret_cast<uintptr_t>(dst) & 31) == 0)) {
+      // two 32-byte stores: each instruction writes whole sectors (a thread owns a row, so 16-byte stores
+      // leave every sector half written per instruction, which the write path handles at half the rate)
+      uint32_t w[16];
+#pragma unroll
+      for (int t = 0; t < 16; ++t) {
+        const float lo = __uint_as_float(v[2 * t]) * alpha;
+        const float hi = __uint_as_float(v[2 * t + 1]) * alpha;
+        w[t] = (out_mode == 0) ? pack_bf16x2(lo, hi) : pack_f16x2(lo, hi);
+      }
+      st_global_v8(dst, w[0], w[1], w[2], w[3], w[4], w[5], w[6], w[7]);
+      st_global_v8(dst + 16, w[8], w[9], w[10], w[11], w[12], w[13], w[14], w[15]);
+    } else if (full && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         uint32_t w[4];

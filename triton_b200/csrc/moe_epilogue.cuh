@@ -1,5 +1,7 @@
 // Epilogue pieces shared by the grouped (MoE) GEMM kernels.
 #pragma once
+#include <cuda_fp8.h>
+
 #include "common.cuh"
 
 namespace tb200 {
@@ -12,11 +14,69 @@ __device__ __forceinline__ float moe_swiglu(float g, float l, float alpha, float
   return g / (1.f + __expf(-alpha * g)) * (l + 1.f);
 }
 
+// Output element kinds of the grouped GEMMs' epilogue.
+enum MoeOutKind : int { MOE_OUT_BF16 = 0, MOE_OUT_F16 = 1, MOE_OUT_E4M3 = 2, MOE_OUT_E5M2 = 3 };
+
+__device__ __forceinline__ uint32_t moe_pack16(float lo, float hi, int kind) {
+  return kind == MOE_OUT_F16 ? pack_f16x2(lo, hi) : pack_bf16x2(lo, hi);
+}
+
+// Two floats -> two fp8 bytes (low byte = lo), round to nearest even, saturating to the largest finite value:
+// the conversion the reference's kernels perform when the output tensor is fp8 (cvt.rn.satfinite).
+__device__ __forceinline__ uint32_t moe_pack8(float lo, float hi, int kind) {
+  return (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(lo, hi), __NV_SATFINITE,
+                                            kind == MOE_OUT_E5M2 ? __NV_E5M2 : __NV_E4M3);
+}
+
+__device__ __forceinline__ void moe_store_one(void* y, long long elem, float x, int kind) {
+  if (kind >= MOE_OUT_E4M3) {
+    static_cast<uint8_t*>(y)[elem] = (uint8_t)(moe_pack8(x, 0.f, kind) & 0xffu);
+  } else {
+    static_cast<uint16_t*>(y)[elem] = (uint16_t)(moe_pack16(x, 0.f, kind) & 0xffffu);
+  }
+}
+
+// N (16 or 32) consecutive outputs of one row starting at element `elem`; the first `cnt` exist. 16-byte stores
+// when the run is whole and aligned, element stores otherwise.
+template <int N>
+__device__ __forceinline__ void moe_store_run(void* y, long long elem, const float (&o)[N], int cnt, int kind) {
+  if (kind >= MOE_OUT_E4M3) {
+    uint8_t* dst = static_cast<uint8_t*>(y) + elem;
+    if (cnt == N && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+      for (int j = 0; j < N / 16; ++j) {
+        uint32_t w[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t)
+          w[t] = moe_pack8(o[j * 16 + 4 * t], o[j * 16 + 4 * t + 1], kind) |
+                 (moe_pack8(o[j * 16 + 4 * t + 2], o[j * 16 + 4 * t + 3], kind) << 16);
+        reinterpret_cast<uint4*>(dst)[j] = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+      return;
+    }
+  } else {
+    uint16_t* dst = static_cast<uint16_t*>(y) + elem;
+    if (cnt == N && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+      for (int j = 0; j < N / 8; ++j) {
+        uint32_t w[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) w[t] = moe_pack16(o[j * 8 + 2 * t], o[j * 8 + 2 * t + 1], kind);
+        reinterpret_cast<uint4*>(dst)[j] = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+      return;
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < N; ++j)
+    if (j < cnt) moe_store_one(y, elem + j, o[j], kind);
+}
+
 // Epilogue of the grouped GEMMs for 32 accumulator columns of one output row: (x acc_scale) + bias ->
-// SwiGLU on adjacent (gate, linear) column pairs -> x gamma -> 16-bit store at row out_row.
-__device__ __forceinline__ void moe_store_chunk(const uint32_t (&v)[32], uint16_t* y, long long ldy, int out_row, int col,
+// SwiGLU on adjacent (gate, linear) column pairs -> x gamma -> store at row out_row (ldy in elements).
+__device__ __forceinline__ void moe_store_chunk(const uint32_t (&v)[32], void* y, long long ldy, int out_row, int col,
                                                 int n, const float* brow, int swiglu, float alpha, float limit,
-                                                int has_limit, float gamma, int out_f16, float acc_scale) {
+                                                int has_limit, float gamma, int out_kind, float acc_scale) {
   float f[32];
 #pragma unroll
   for (int j = 0; j < 32; ++j) {
@@ -25,64 +85,14 @@ __device__ __forceinline__ void moe_store_chunk(const uint32_t (&v)[32], uint16_
   }
   if (swiglu) {
     // 32 accumulator columns -> 16 outputs at column (col / 2)
-    uint16_t* dst = y + (long long)out_row * ldy + (col >> 1);
-    const int cnt = min(16, (n - col) >> 1);
     float o[16];
 #pragma unroll
     for (int j = 0; j < 16; ++j) o[j] = moe_swiglu(f[2 * j], f[2 * j + 1], alpha, limit, has_limit) * gamma;
-    if (cnt == 16 && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
-#pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        uint32_t w[4];
-#pragma unroll
-        for (int t = 0; t < 4; ++t)
-          w[t] = out_f16 ? pack_f16x2(o[j * 8 + 2 * t], o[j * 8 + 2 * t + 1])
-                         : pack_bf16x2(o[j * 8 + 2 * t], o[j * 8 + 2 * t + 1]);
-        reinterpret_cast<uint4*>(dst)[j] = make_uint4(w[0], w[1], w[2], w[3]);
-      }
-    } else {
-#pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        if (j < cnt) {
-          if (out_f16) {
-            __half h = __float2half_rn(o[j]);
-            dst[j] = *reinterpret_cast<uint16_t*>(&h);
-          } else {
-            __nv_bfloat16 h = __float2bfloat16_rn(o[j]);
-            dst[j] = *reinterpret_cast<uint16_t*>(&h);
-          }
-        }
-      }
-    }
+    moe_store_run<16>(y, (long long)out_row * ldy + (col >> 1), o, min(16, (n - col) >> 1), out_kind);
   } else {
-    uint16_t* dst = y + (long long)out_row * ldy + col;
-    const int cnt = min(32, n - col);
-    if (cnt == 32 && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        uint32_t w[4];
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          const float lo = f[j * 8 + 2 * t] * gamma, hi = f[j * 8 + 2 * t + 1] * gamma;
-          w[t] = out_f16 ? pack_f16x2(lo, hi) : pack_bf16x2(lo, hi);
-        }
-        reinterpret_cast<uint4*>(dst)[j] = make_uint4(w[0], w[1], w[2], w[3]);
-      }
-    } else {
-#pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        if (j < cnt) {
-          const float x = f[j] * gamma;
-          if (out_f16) {
-            __half h = __float2half_rn(x);
-            dst[j] = *reinterpret_cast<uint16_t*>(&h);
-          } else {
-            __nv_bfloat16 h = __float2bfloat16_rn(x);
-            dst[j] = *reinterpret_cast<uint16_t*>(&h);
-          }
-        }
-      }
-    }
+    for (int j = 0; j < 32; ++j) f[j] *= gamma;
+    moe_store_run<32>(y, (long long)out_row * ldy + col, f, min(32, n - col), out_kind);
   }
 }
 

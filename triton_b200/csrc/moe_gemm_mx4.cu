@@ -60,7 +60,7 @@ struct Mx4Params {
   long long ldy;
   int n_sched, tiles_n, units;
   int n, k_blocks, n_blocks, rows_y;
-  int swiglu, has_limit, out_f16;
+  int swiglu, has_limit, out_kind;
   float alpha, limit;
   uint32_t idesc[4];
 };
@@ -216,7 +216,7 @@ __global__ void __launch_bounds__(M4_THREADS, 1) moe_gemm_mx4_kernel(const __gri
     // ------------------------------------------------------------- epilogue
     const int q = warp & 3;
     const int n = p.n, rows_y = p.rows_y;
-    uint16_t* const y = reinterpret_cast<uint16_t*>(p.y);
+    void* const y = p.y;
     const float acc_scale = p.x_scale ? __ldg(p.x_scale) : 1.f;
     const uint32_t tempty_a = smem_u32(tempty);
     uint32_t tcount = 0;
@@ -248,7 +248,7 @@ __global__ void __launch_bounds__(M4_THREADS, 1) moe_gemm_mx4_kernel(const __gri
         tmem_ld_wait();
         const int col = n0 + cc;
         if (out_row < 0 || col >= n) continue;
-        moe_store_chunk(v, y, p.ldy, out_row, col, n, brow, p.swiglu, p.alpha, p.limit, p.has_limit, gamma, p.out_f16,
+        moe_store_chunk(v, y, p.ldy, out_row, col, n, brow, p.swiglu, p.alpha, p.limit, p.has_limit, gamma, p.out_kind,
                         acc_scale);
       }
       tc_fence_before_sync();
@@ -424,9 +424,9 @@ __global__ void __launch_bounds__(M4_THREADS, 1) moe_gemm_mx4_swap_kernel(const 
   } else {
     // ------------------------------------------------------------- epilogue (transposed accumulator)
     const int q = warp & 3;
-    const int n = p.n, rows_y = p.rows_y, swiglu = p.swiglu, has_limit = p.has_limit, out_f16 = p.out_f16;
+    const int n = p.n, rows_y = p.rows_y, swiglu = p.swiglu, has_limit = p.has_limit, out_kind = p.out_kind;
     const float alpha = p.alpha, limit = p.limit;
-    uint16_t* const y = reinterpret_cast<uint16_t*>(p.y);
+    void* const y = p.y;
     const long long ldy = p.ldy;
     const float acc_scale = p.x_scale ? __ldg(p.x_scale) : 1.f;
     const uint32_t tempty_a = smem_u32(tempty);
@@ -464,15 +464,11 @@ __global__ void __launch_bounds__(M4_THREADS, 1) moe_gemm_mx4_swap_kernel(const 
           const float other = __shfl_xor_sync(0xffffffffu, f, 1);  // (gate, linear) are adjacent columns
           if ((lane & 1) == 0 && out_row >= 0 && col < n) {
             const float o = moe_swiglu(f, other, alpha, limit, has_limit) * gamma;
-            uint16_t* dst = y + (long long)out_row * ldy + (col >> 1);
-            if (out_f16) { __half h = __float2half_rn(o); *dst = *reinterpret_cast<uint16_t*>(&h); }
-            else { __nv_bfloat16 h = __float2bfloat16_rn(o); *dst = *reinterpret_cast<uint16_t*>(&h); }
+            moe_store_one(y, (long long)out_row * ldy + (col >> 1), o, out_kind);
           }
         } else if (out_row >= 0 && col < n) {
           const float o = f * gamma;
-          uint16_t* dst = y + (long long)out_row * ldy + col;
-          if (out_f16) { __half h = __float2half_rn(o); *dst = *reinterpret_cast<uint16_t*>(&h); }
-          else { __nv_bfloat16 h = __float2bfloat16_rn(o); *dst = *reinterpret_cast<uint16_t*>(&h); }
+          moe_store_one(y, (long long)out_row * ldy + col, o, out_kind);
         }
       }
     }
@@ -495,7 +491,9 @@ extern "C" int tb200_moe_gemm_mx4(const tb200_moe_gemm_mx4_args* a, void* stream
   if (a->n_experts <= 0 || a->n_experts > 65535 || a->k <= 0 || a->n <= 0 || a->n_sched < 0) return TB200_ERR_BAD_ARG;
   if (a->rows_x < 0 || a->rows_y < 0) return TB200_ERR_BAD_ARG;
   if (a->x_dtype != TB200_E4M3 && a->x_dtype != TB200_E5M2) return TB200_ERR_UNSUPPORTED;
-  if (a->out_dtype != TB200_BF16 && a->out_dtype != TB200_F16) return TB200_ERR_UNSUPPORTED;
+  if (a->out_dtype != TB200_BF16 && a->out_dtype != TB200_F16 && a->out_dtype != TB200_E4M3 &&
+      a->out_dtype != TB200_E5M2)
+    return TB200_ERR_UNSUPPORTED;
   if ((a->k % 128) || (a->n % 128)) return TB200_ERR_UNSUPPORTED;
   if (a->swiglu && (a->n & 1)) return TB200_ERR_BAD_ARG;
   if ((a->ldx % 16) || a->ldx < a->k) return TB200_ERR_BAD_ARG;
@@ -557,7 +555,8 @@ extern "C" int tb200_moe_gemm_mx4(const tb200_moe_gemm_mx4_args* a, void* stream
   p.has_limit = a->swiglu_has_limit ? 1 : 0;
   p.alpha = a->swiglu_alpha;
   p.limit = a->swiglu_limit;
-  p.out_f16 = a->out_dtype == TB200_F16 ? 1 : 0;
+  p.out_kind = a->out_dtype == TB200_F16 ? MOE_OUT_F16 : a->out_dtype == TB200_E4M3 ? MOE_OUT_E4M3
+               : a->out_dtype == TB200_E5M2 ? MOE_OUT_E5M2 : MOE_OUT_BF16;
   const uint32_t xfmt = a->x_dtype == TB200_E5M2 ? 1u : 0u;
   const uint32_t wfmt = 5u;  // e2m1
   for (uint32_t k = 0; k < 4; ++k)

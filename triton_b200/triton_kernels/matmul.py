@@ -250,9 +250,10 @@ def _matmul_mx4(a, b, bias, a_ragged_metadata, scatter_indx, pc: PrecisionConfig
     block_rows = 32 if R <= 32 * E else 128
     sched = md.block_schedule(block_rows)
     rows_y = R if scatter_indx is None else scatter_indx.shape[0]
-    out_dtype = pc.out_dtype or torch.bfloat16
-    if out_dtype not in _DT:
-        raise NotImplementedError("matmul (MXFP4 weight): bf16 / fp16 output")
+    out_dtype = pc.out_dtype or a.dtype  # as the reference: the activation dtype (fp8) unless asked otherwise
+    out_codes = {**_DT, **_F8}
+    if out_dtype not in out_codes:
+        raise NotImplementedError("matmul (MXFP4 weight): bf16 / fp16 / fp8 output")
     c = (torch.zeros if scatter_indx is not None else torch.empty)((rows_y, n_out), dtype=out_dtype, device=dev)
     si = None if scatter_indx is None else scatter_indx.to(torch.int32).contiguous()
     gm = None if gammas is None else gammas.float().contiguous()
@@ -272,7 +273,7 @@ def _matmul_mx4(a, b, bias, a_ragged_metadata, scatter_indx, pc: PrecisionConfig
     args.rows_x, args.rows_y = R, rows_y
     args.ldx, args.ldy = a.stride(0), c.stride(0)
     args.n_sched = sched.shape[0]
-    args.x_dtype, args.out_dtype = _F8[a.dtype], _DT[out_dtype]
+    args.x_dtype, args.out_dtype = _F8[a.dtype], out_codes[out_dtype]
     args.swiglu = swiglu
     args.swiglu_alpha = alpha
     args.swiglu_limit = float(limit) if limit is not None else 0.0

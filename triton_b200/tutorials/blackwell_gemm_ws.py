@@ -75,7 +75,7 @@ def matmul(a: torch.Tensor, b: torch.Tensor, config=None) -> torch.Tensor:
     if config:
         args.split_k = int(config.get("SPLIT_K", 0) or 0)
         bn = int(config.get("BLOCK_SIZE_N", 0) or 0)
-        args.block_n = bn if bn in (64, 128, 256, 512) else 0
+        args.block_n = bn if bn in (64, 128, 256, 512, 1024) else 0  # 512 / 1024: CTA pair, 256 x 256 / 256 x 512 tile
         if int(config.get("NUM_CTAS", 1) or 1) == 2:
             args.block_n = 512  # CTA pair: 256 x 256 tile per 2-CTA cluster
     l = _lib.lib()

@@ -75,7 +75,8 @@ def blackwell_scaled_mm_ws(a, b, scale_a, scale_b, out_dtype=torch.bfloat16, BLO
     args.out_dtype = _OUT[out_dtype]
     args.a_k_major = args.b_k_major = 1
     args.split_k = 1
-    args.block_n = 512 if NUM_CTAS == 2 else 0
+    # NUM_CTAS=2 forces a CTA pair: 256 x 256 tile, or 256 x 512 when BLOCK_N asks for 512
+    args.block_n = (1024 if BLOCK_N == 512 else 512) if NUM_CTAS == 2 else 0
     args.scale_a, args.scale_b = scale_a.data_ptr(), scale_b.data_ptr()
     args.scale_mode = 1 if scale_mode == "rowwise" else 0
     with torch.cuda.device(a.device):
