@@ -22,8 +22,9 @@
 //
 //   wide pair  : the same with a 256 x 512 tile: each CTA stages 128 A rows and 256 B rows per K step, the
 //                leader issues two N = 256 MMAs per K sub-step into the two halves of a single 512-column
-//                accumulator (all of tensor memory, so the epilogue is not overlapped with the next tile's
-//                MMAs: ~4 % of a K = 8192 tile). A is staged once for 512 columns: per 1024 MMA cycles a
+//                accumulator (all of tensor memory: there is no second accumulator to overlap the epilogue
+//                with, so the halves are handed over separately and the first / last K steps of a tile work
+//                on one half while the other is drained). A is staged once for 512 columns: per 1024 MMA cycles a
 //                CTA's port carries 48 KB of TMA writes + 96 KB of operand reads at most, against
 //                2 x (32 + 48) KB for two 256 x 256 tiles - the port stops being the limit (tensor pipe
 //                active 85 % -> measured below), and L2 -> SM traffic per flop drops by a quarter.
@@ -63,6 +64,7 @@ struct OperandGeom {
 struct GemmParams {
   CUtensorMap tma;
   CUtensorMap tmb;
+  CUtensorMap tmc;  // output as 64-column x 32-row boxes (wide tile, 16-bit output); valid when c_tma != 0
   void* c;
   float* ws;
   const float* scale_a;
@@ -76,6 +78,7 @@ struct GemmParams {
   int group_m;
   int out_mode;  // 0 bf16, 1 fp16, 2 fp32 to c, 3 fp32 partial to ws
   int scale_mode;  // 0: scale_a / scale_b are scalars; 1: per-row (M) and per-column (N) vectors
+  int c_tma;       // 1: the wide kernel's epilogue stores through tmc
   uint32_t idesc;
   OperandGeom ga, gb;
 };
@@ -88,6 +91,10 @@ struct GemmSmem {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
   static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 4) * 8 + 16 + 1024;  // + alignment slack
+  // wide tile: per epilogue warp two 4 KB staging buffers (32 rows x 128 bytes) for TMA stores, 1 KB past the barriers
+  static constexpr int EPI_OFFSET = BAR_OFFSET + 1024;
+  static constexpr int EPI_BYTES = 4 * 2 * 4096;
+  static constexpr int TOTAL_WIDE = EPI_OFFSET + EPI_BYTES + 1024;
 };
 
 template <bool PAIR, bool F8>
@@ -132,6 +139,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const __grid_cons
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&p.tma);
     tma_prefetch_desc(&p.tmb);
+    if (WIDE && p.c_tma) tma_prefetch_desc(&p.tmc);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
@@ -232,6 +240,92 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const __grid_cons
         const TileCoord t = unit_to_tile(unit, split_k, group_m, tiles_m, tiles_n);
         const int kb0 = t.ks * kb_per_split;
         const int nkb = min(k_blocks, kb0 + kb_per_split) - kb0;
+        if constexpr (WIDE) {
+          // One 512-column accumulator, handed over in two 256-column halves (tfull / tempty index = half) so
+          // that the drain of one half overlaps MMAs on the other: the first HEAD K steps of a tile run on half
+          // 0 alone while the epilogue still drains half 1 of the previous tile, and the last TAIL steps finish
+          // half 0 first so that its drain starts while half 1 is completed. A stage is released when both halves
+          // have read it, so at most STAGES - 1 steps are held back.
+          const uint32_t tph = tcount & 1;
+          const int head = nkb < STAGES - 1 ? nkb : STAGES - 1;
+          const int tail = (nkb - head) < STAGES - 1 ? (nkb - head) : STAGES - 1;
+          auto half_step = [&](uint32_t st, uint32_t h, uint32_t accumulate) {
+            const uint64_t ad = adesc0 + (uint64_t)(st * (L::STAGE_BYTES >> 4));
+            const uint64_t bd = bdesc0 + (uint64_t)(st * (L::STAGE_BYTES >> 4)) + h * B_HALF;
+            const uint32_t d = tmem_base + h * 256;
+            issue_mma<PAIR, F8>(d, ad, bd, idesc, accumulate);
+            issue_mma<PAIR, F8>(d, ad + ak, bd + bk, idesc, 1u);
+            issue_mma<PAIR, F8>(d, ad + 2 * ak, bd + 2 * bk, idesc, 1u);
+            issue_mma<PAIR, F8>(d, ad + 3 * ak, bd + 3 * bk, idesc, 1u);
+          };
+          auto release = [&](uint32_t st) {
+            umma_commit_pair(empty_a + st * 8);
+            umma_commit_pair(empty_a + st * 8 + peer_delta);
+          };
+          auto wait_full = [&]() {
+            if (!mbar_wait_a(full_a + s * 8, ph, status, WAIT_SMEM_FULL)) return false;
+            tc_fence_after_sync();
+            return true;
+          };
+          auto advance = [&](uint32_t& st, uint32_t& phase) {
+            if (++st == STAGES) {
+              st = 0;
+              phase ^= 1;
+            }
+          };
+          if (!mbar_wait_a(tempty_a, tph ^ 1, status, WAIT_TMEM_EMPTY)) break;
+          tc_fence_after_sync();
+          uint32_t s_held = s, ph_unused = 0;
+          for (int i = 0; i < head && ok; ++i) {
+            ok = wait_full();
+            if (ok) {
+              half_step(s, 0, i == 0 ? 0u : 1u);
+              advance(s, ph);
+            }
+          }
+          if (!ok) break;
+          if (!mbar_wait_a(tempty_a + 8, tph ^ 1, status, WAIT_TMEM_EMPTY)) break;
+          tc_fence_after_sync();
+          for (int i = 0; i < head; ++i) {
+            half_step(s_held, 1, i == 0 ? 0u : 1u);
+            release(s_held);
+            advance(s_held, ph_unused);
+          }
+          for (int i = head; i < nkb - tail && ok; ++i) {
+            ok = wait_full();
+            if (ok) {
+              const uint64_t ad = adesc0 + (uint64_t)(s * (L::STAGE_BYTES >> 4));
+              const uint64_t bd = bdesc0 + (uint64_t)(s * (L::STAGE_BYTES >> 4));
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                issue_mma<PAIR, F8>(tmem_base, ad + j * ak, bd + j * bk, idesc, 1u);
+                issue_mma<PAIR, F8>(tmem_base + 256, ad + j * ak, bd + j * bk + B_HALF, idesc, 1u);
+              }
+              release(s);
+              advance(s, ph);
+            }
+          }
+          if (!ok) break;
+          s_held = s;
+          for (int i = 0; i < tail && ok; ++i) {
+            ok = wait_full();
+            if (ok) {
+              half_step(s, 0, 1u);
+              advance(s, ph);
+            }
+          }
+          if (!ok) break;
+          umma_commit_pair(tfull_a);
+          umma_commit_pair(tfull_peer);
+          for (int i = 0; i < tail; ++i) {
+            half_step(s_held, 1, 1u);
+            release(s_held);
+            advance(s_held, ph_unused);
+          }
+          umma_commit_pair(tfull_a + 8);
+          umma_commit_pair(tfull_peer + 8);
+          continue;
+        }
         const uint32_t acc = tcount % NACC;
         const uint32_t aph = (tcount / NACC) & 1;
         if (!mbar_wait_a(tempty_a + acc * 8, aph ^ 1, status, WAIT_TMEM_EMPTY)) {
@@ -240,11 +334,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const __grid_cons
         }
         tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + acc * BN;
-        // one K sub-step: N = 256 columns, or both 256-column halves of the wide tile (A is read twice from shared
-        // memory but staged once)
         auto mma_step = [&](uint64_t a_desc, uint64_t b_desc, uint32_t accumulate) {
           issue_mma<PAIR, F8>(tmem_d, a_desc, b_desc, idesc, accumulate);
-          if constexpr (WIDE) issue_mma<PAIR, F8>(tmem_d + 256, a_desc, b_desc + B_HALF, idesc, accumulate);
         };
         // Loop shape: every non-MMA instruction sits between two MMAs of the same K step, where it
         // overlaps with tensor-pipe work already queued: the commit that frees the previous stage
@@ -314,11 +405,75 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const __grid_cons
     const long long ldc = p.ldc;
     const int m = p.m, n = p.n, out_mode = p.out_mode;
     const uint32_t tempty_leader = PAIR ? mapa_shared(smem_u32(tempty), 0) : smem_u32(tempty);
+    [[maybe_unused]] const bool use_tma = WIDE && p.c_tma != 0;
+    [[maybe_unused]] const uint32_t stage_base = smem_a + L::EPI_OFFSET + (uint32_t)q * 8192;
+    [[maybe_unused]] uint32_t slab = 0;
+    [[maybe_unused]] const uint64_t store_pol = policy_evict_first();
     uint32_t tcount = 0;
     bool ok = true;
     for (int unit = worker; unit < units && ok; unit += num_workers, ++tcount) {
       const TileCoord t = unit_to_tile(unit, split_k, group_m, tiles_m, tiles_n);
       const int m0 = t.pid_m * TILE_M + (int)rank * BM, n0 = t.pid_n * BN;
+      const int row = m0 + q * 32 + lane;
+      if constexpr (WIDE) {
+        // the two 256-column halves arrive and are handed back separately (barrier index = half)
+        const uint32_t tph = tcount & 1;
+        if (row_scale) alpha = row < m ? __ldg(row_scale + row) : 0.f;
+        for (int h = 0; h < 2 && ok; ++h) {
+          if (!mbar_wait(&tfull[h], tph, status, WAIT_TMEM_FULL)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + h * 256;
+          // accumulator columns [128 j, 128 j + 128) of the tile hold output columns of the B rows staged by CTA
+          // (j & 1) and read by MMA (j >> 1) = half: CTA r stages rows n0 + 256 r .. + 255, half h takes rows
+          // 128 h .. 128 h + 127 of each
+          uint32_t v0[32], v1[32];
+          tmem_ld_32x32b_x32(taddr, v0);
+          if (use_tma) {
+            // 16-bit output through shared memory: 64 columns of the warp's 32 rows (128 bytes per row, 128-byte
+            // swizzle) per TMA store, two staging buffers per warp. The store engine writes whole lines and clips
+            // at the matrix edge; per-thread stores here wrote one 32-byte sector per thread and instruction, and
+            // all CTAs drain at the same time: that cost 3000 cycles per 256 columns.
+#pragma unroll 1
+            for (int cc = 0; cc < 256; cc += 64) {
+              const int gc = n0 + (cc >> 7) * 256 + h * 128 + (cc & 127);
+              const uint32_t buf = stage_base + (uint32_t)(slab & 1) * 4096;
+              ++slab;
+              if (lane == 0) bulk_wait_group_read<1>();  // the store that last read this buffer has finished
+              __syncwarp();
+              tmem_ld_wait();
+              tmem_ld_32x32b_x32(taddr + cc + 32, v1);
+              stage_chunk(buf, lane, 0, v0, gc, out_mode, alpha, col_scale, n);
+              tmem_ld_wait();
+              if (cc + 64 < 256) tmem_ld_32x32b_x32(taddr + cc + 64, v0);
+              stage_chunk(buf, lane, 4, v1, gc + 32, out_mode, alpha, col_scale, n);
+              fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0) {
+                if (gc < n && m0 + q * 32 < m) tma_store_2d_hint(&p.tmc, buf, gc, m0 + q * 32, store_pol);  // edges are clipped
+                bulk_commit_group();
+              }
+            }
+          } else {
+#pragma unroll 1
+            for (int cc = 0; cc < 256; cc += 64) {
+              const int gc = n0 + (cc >> 7) * 256 + h * 128 + (cc & 127);
+              tmem_ld_wait();
+              tmem_ld_32x32b_x32(taddr + cc + 32, v1);
+              store_chunk(c, ws, ldc, m, n, out_mode, v0, row, gc, t.ks, alpha, col_scale);
+              tmem_ld_wait();
+              if (cc + 64 < 256) tmem_ld_32x32b_x32(taddr + cc + 64, v0);
+              store_chunk(c, ws, ldc, m, n, out_mode, v1, row, gc + 32, t.ks, alpha, col_scale);
+            }
+          }
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(tempty_leader + h * 8);
+        }
+        continue;
+      }
       const uint32_t acc = tcount % NACC;
       const uint32_t aph = (tcount / NACC) & 1;
       if (!mbar_wait(&tfull[acc], aph, status, WAIT_TMEM_FULL)) {
@@ -326,12 +481,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const __grid_cons
         break;
       }
       tc_fence_after_sync();
-      const int row = m0 + q * 32 + lane;
       const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + acc * BN;
       if (row_scale) alpha = row < m ? __ldg(row_scale + row) : 0.f;
-      // wide tile: accumulator columns [128 j, 128 j + 128) hold output columns of B rows staged by CTA (j & 1),
-      // MMA (j >> 1): CTA r stages B rows n0 + 256 r .. + 255 and MMA h takes rows 128 h .. 128 h + 127 of each
-      auto out_col = [&](int cc) { return WIDE ? n0 + ((cc >> 7) & 1) * 256 + (cc >> 8) * 128 + (cc & 127) : n0 + cc; };
+      auto out_col = [&](int cc) { return n0 + cc; };
       if constexpr (BN >= 64) {
         // two chunks in flight: the next tensor-memory load runs while this chunk is converted and stored
         uint32_t v0[32], v1[32];
@@ -365,6 +517,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const __grid_cons
     }
   }
 
+  if constexpr (WIDE) {
+    if (warp >= 2 && lane == 0) bulk_wait_group<0>();  // this thread's TMA stores have completed
+  }
   tc_fence_before_sync();
   if constexpr (PAIR) cluster_sync_all(); else __syncthreads();
   if (warp == 1) {
@@ -470,12 +625,13 @@ static bool plan_gemm(const tb200_gemm_args* a, int sms, GemmPlan* plan) {
         bn = 256;
         best = cost2;
       }
-      // 256 x 512 per pair: twice the tile at ~88 % of twice the cost (measured at 8192^3); worth it when the
-      // coarser tiles still fill the waves
+      // 256 x 512 per pair: twice the tile at ~88 % of twice the cost (measured at 8192^3), plus an epilogue that
+      // is only partly overlapped (~9000 cycles a tile against 1024 per K step): worth it when the coarser tiles
+      // still fill the waves and K is long (measured: ahead from 48 K steps on, behind at 32)
       const long long tiles3 = ((a->m + 255) / 256) * ((a->n + 511) / 512);
       const long long waves3 = (tiles3 + sms / 2 - 1) / (sms / 2);
       const long long cost3 = waves3 * (512 + 24) * 3 * 88 / 100;
-      if (cost3 < best) {
+      if (cost3 < best && kb >= 48) {
         pair = 2;
         bn = 512;
       }
@@ -513,13 +669,14 @@ template <int BNC, int STAGES, bool PAIR, bool F8>
 static int launch_one(const GemmParams& p, int grid, cudaStream_t stream) {
   using L = GemmSmem<BNC, STAGES>;
   auto kfn = gemm_kernel<BNC, STAGES, PAIR, F8>;
-  cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+  constexpr int SMEM = (PAIR && BNC == 256) ? L::TOTAL_WIDE : L::TOTAL;
+  cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
   if (e != cudaSuccess) return TB200_ERR_CUDA;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(GEMM_THREADS);
-  cfg.dynamicSmemBytes = L::TOTAL;
+  cfg.dynamicSmemBytes = SMEM;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -671,6 +828,16 @@ extern "C" int tb200_gemm(const tb200_gemm_args* a, void* stream_) {
     p.out_mode = 3;
   } else {
     p.out_mode = final_mode;
+  }
+  if (plan.pair == 2 && p.out_mode <= 1 && (reinterpret_cast<uintptr_t>(a->c) & 15) == 0 && ((a->ldc * 2) & 15) == 0) {
+    // wide tile, 16-bit output: the epilogue stores 64-column x 32-row boxes by TMA
+    const uint64_t dims[2] = {(uint64_t)a->n, (uint64_t)a->m};
+    const uint64_t strides[1] = {(uint64_t)a->ldc * 2};
+    const uint32_t box[2] = {64, 32};
+    rc = encode_tmap(&p.tmc, a->out_dtype == TB200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                     2, a->c, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != TB200_OK) return rc;
+    p.c_tma = 1;
   }
   rc = f8 ? launch_gemm<true>(p, plan, sms, stream) : launch_gemm<false>(p, plan, sms, stream);
   if (rc != TB200_OK) return rc;

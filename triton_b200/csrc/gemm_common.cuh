@@ -30,6 +30,31 @@ __device__ __forceinline__ void st_global_v8(void* dst, uint32_t a, uint32_t b, 
                : "memory");
 }
 
+// Converts 32 consecutive columns of the thread's row (fp32 accumulators in v) to the 16-bit output type and puts
+// them into a 32-row x 128-byte staging buffer in the 128-byte-swizzle order a TMA store expects: row = lane, the
+// 16-byte chunk j of the row at ((j ^ (row & 7)) << 4). chunk0 = 0 for the first 32 columns of the 64, 4 for the rest.
+__device__ __forceinline__ void stage_chunk(uint32_t buf, int lane, int chunk0, const uint32_t (&v)[32], int col,
+                                            int out_mode, float alpha, const float* col_scale, int n) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint32_t w[4];
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      float lo = __uint_as_float(v[j * 8 + 2 * t]) * alpha;
+      float hi = __uint_as_float(v[j * 8 + 2 * t + 1]) * alpha;
+      if (col_scale) {  // columns past n are clipped by the store; their factors are not read
+        const int cidx = col + j * 8 + 2 * t;
+        lo *= cidx < n ? __ldg(col_scale + cidx) : 0.f;
+        hi *= cidx + 1 < n ? __ldg(col_scale + cidx + 1) : 0.f;
+      }
+      w[t] = (out_mode == 0) ? pack_bf16x2(lo, hi) : pack_f16x2(lo, hi);
+    }
+    const uint32_t addr = buf + (uint32_t)lane * 128 + ((uint32_t)((chunk0 + j) ^ (lane & 7)) << 4);
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])
+                 : "memory");
+  }
+}
+
 // Writes 32 consecutive columns of one output row (fp32 accumulators in v) in the output mode.
 __device__ __forceinline__ void store_chunk(void* c, float* ws, long long ldc, int m, int n, int out_mode,
                                             uint32_t (&v)[32], int row, int col, int ks, float alpha,
