@@ -216,16 +216,26 @@ __global__ void __launch_bounds__(MX_THREADS, 1) gemm_mxfp8_kernel(const __grid_
       tc_fence_after_sync();
       const int row = m0 + q * 32 + lane;
       const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + acc * BN;
+      // two tensor-memory loads in flight; the accumulator is handed back as soon as the last load has landed
+      // (before that chunk is converted and stored): the single accumulator's drain is exposed time
+      static_assert(BN % 64 == 0, "the drain works on pairs of 32-column chunks");
+      uint32_t v0[32], v1[32];
+      tmem_ld_32x32b_x32(taddr, v0);
 #pragma unroll 1
-      for (int cc = 0; cc < BN; cc += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(taddr + cc, v);
+      for (int cc = 0; cc < BN; cc += 64) {
         tmem_ld_wait();
-        store_chunk(c, nullptr, ldc, m, n, 0, v, row, n0 + cc, 0, 1.0f);
+        tmem_ld_32x32b_x32(taddr + cc + 32, v1);
+        store_chunk(c, nullptr, ldc, m, n, 0, v0, row, n0 + cc, 0, 1.0f);
+        tmem_ld_wait();
+        if (cc + 64 < BN) {
+          tmem_ld_32x32b_x32(taddr + cc + 64, v0);
+        } else {
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_a(tempty_a + acc * 8);
+        }
+        store_chunk(c, nullptr, ldc, m, n, 0, v1, row, n0 + cc + 32, 0, 1.0f);
       }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_a(tempty_a + acc * 8);
     }
   }
 
@@ -427,16 +437,23 @@ __global__ void __launch_bounds__(MX_THREADS, 1) gemm_mxfp8_pair_kernel(const __
       tc_fence_after_sync();
       const int row = m0 + q * 32 + lane;
       const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16);
+      uint32_t v0[32], v1[32];
+      tmem_ld_32x32b_x32(taddr, v0);
 #pragma unroll 1
-      for (int cc = 0; cc < BN; cc += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(taddr + cc, v);
+      for (int cc = 0; cc < BN; cc += 64) {
         tmem_ld_wait();
-        store_chunk(c, nullptr, ldc, m, n, 0, v, row, n0 + cc, 0, 1.0f);
+        tmem_ld_32x32b_x32(taddr + cc + 32, v1);
+        store_chunk(c, nullptr, ldc, m, n, 0, v0, row, n0 + cc, 0, 1.0f);
+        tmem_ld_wait();
+        if (cc + 64 < BN) {
+          tmem_ld_32x32b_x32(taddr + cc + 64, v0);
+        } else {  // the last load has landed: hand the accumulator back before the last chunk is stored
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(tempty_leader);
+        }
+        store_chunk(c, nullptr, ldc, m, n, 0, v1, row, n0 + cc + 32, 0, 1.0f);
       }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(tempty_leader);
     }
   }
 
