@@ -218,8 +218,7 @@ def build_workload(name: str, rank: int, dev):
             combine = mm.col_sorted_indx
             gather = torch.div(combine, k, rounding_mode="trunc")
             gam = sm.vals.float().reshape(-1)[combine.long()]
-            xs = x.view(torch.uint8)[gather.long()].view(torch.float8_e4m3fn)  # rows in expert order
-            h = moe_matmul(xs, w1, None, rg, precision_config=pc1, fused_activation=act)
+            h = moe_matmul(x, w1, None, rg, gather_indx=gather, precision_config=pc1, fused_activation=act)
             y = moe_matmul(h, w2, None, rg, scatter_indx=combine, gammas=gam, precision_config=pc2)
             return reduce(y.view(T, k, D), dim=1)[0]
         R = T * k
@@ -268,8 +267,9 @@ def build_workload(name: str, rank: int, dev):
 
 
 # Kernels of this library launched per step: the MoE layer runs topk, three bitmatrix-metadata kernels,
-# the ragged-metadata kernel, two grouped GEMMs and the top-k reduce (the EP variant adds four row moves).
-OWN_LAUNCHES_PER_STEP = {"moe": 8, "moe_decode": 8, "moe_ep": 12, "moe_mx4": 8, "moe_mx4_decode": 8, "attn_bwd": 3, "attn_bwd_causal": 3,
+# the ragged-metadata kernel, two grouped GEMMs and the top-k reduce (the EP variant adds four row moves), and
+# with 2048 or more sorted rows the row gather ahead of GEMM 1.
+OWN_LAUNCHES_PER_STEP = {"moe": 9, "moe_decode": 8, "moe_ep": 12, "moe_mx4": 9, "moe_mx4_decode": 9, "attn_bwd": 3, "attn_bwd_causal": 3,
                          "attn_bwd_ref_shape": 3, "attn_bwd_ref_shape_causal": 3}
 
 

@@ -209,3 +209,27 @@ def test_unsupported_combinations_raise(cuda):
         matmul(a, w, None, precision_config=PrecisionConfig(b_mx_scale=torch.ones(1)))
     with pytest.raises(NotImplementedError):
         matmul(a.float(), w.float(), None)
+
+
+def test_pregathered_rows_match_in_kernel_gather(cuda, monkeypatch):
+    """From 2048 sorted rows on, matmul gathers the rows in a pass of its own (tb200_gather_rows) and runs the GEMM on
+    tiled loads; the result must equal the in-kernel gather's bit for bit, also for indices outside the input
+    (zero rows)."""
+    from triton_b200.triton_kernels import matmul as mm_mod
+    from triton_b200.triton_kernels.tensor import make_ragged_tensor_metadata
+    R, T, K, N, E = 4096, 700, 256, 384, 8
+    g = torch.Generator().manual_seed(21)
+    x = torch.randn(T, K, generator=g).to(torch.bfloat16).to(cuda)
+    w = (0.1 * torch.randn(E, K, N, generator=g)).to(torch.bfloat16).to(cuda)
+    gather = torch.randint(0, T, (R,), generator=g).to(torch.int32)
+    gather[5], gather[77], gather[4095] = -1, T, T + 9   # outside the input: read as zero rows
+    sizes = torch.full((E,), R // E, dtype=torch.int32)
+    rg = make_ragged_tensor_metadata(sizes.to(cuda), R)
+    out_pre = mm_mod.matmul(x, w, None, rg, gather_indx=gather.to(cuda))
+    monkeypatch.setattr(mm_mod, "_PREGATHER_MIN_ROWS", 1 << 40)
+    out_in = mm_mod.matmul(x, w, None, rg, gather_indx=gather.to(cuda))
+    assert torch.equal(out_pre, out_in)
+    assert torch.count_nonzero(out_pre[5]) == 0 and torch.count_nonzero(out_pre[4095]) == 0
+    ref = x.cpu().float()[gather[:64].clamp(0, T - 1).long()] @ w[0].cpu().float()
+    ref[5] = 0
+    torch.testing.assert_close(out_pre[:64].cpu().float(), ref, rtol=2e-2, atol=2e-2)

@@ -156,6 +156,23 @@ def test_fp8_output_swiglu_scatter(cuda):
     torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=0.07, atol=2e-2)
 
 
+def test_fp8_x_mx4_gather_indx(cuda):
+    """gather_indx with fp8 activations: rows gathered by tb200_gather_rows, then the sorted-row kernel; equal to
+    gathering by hand."""
+    from triton_b200.triton_kernels.matmul import PrecisionConfig, matmul
+    from triton_b200.triton_kernels.tensor import make_ragged_tensor_metadata
+    T, R, K, N, E = 100, 384, 256, 256, 4
+    g = torch.Generator().manual_seed(13)
+    x = (torch.randn(T, K, generator=g) * 0.5).to(torch.float8_e4m3fn).to(cuda)
+    v, s, _ = _quantise(torch.randn(E, K, N, generator=g) * 0.5)
+    gather = torch.randint(0, T, (R,), generator=g).to(torch.int32).to(cuda)
+    rg = make_ragged_tensor_metadata(torch.full((E,), R // E, dtype=torch.int32, device=cuda), R)
+    pc = PrecisionConfig(b_mx_scale=s.to(cuda), out_dtype=torch.bfloat16)
+    got = matmul(x, v.to(cuda), None, rg, gather_indx=gather, precision_config=pc)
+    want = matmul(x.view(torch.uint8)[gather.long()].view(torch.float8_e4m3fn), v.to(cuda), None, rg, precision_config=pc)
+    assert torch.equal(got, want)
+
+
 def test_upcast_bit_exact(cuda):
     """tb200_mxfp4_upcast against upcast_from_mxfp (itself pinned on the reference's golden vectors): every code,
     every scale byte - 0 (zero), 255 (infinity: NaN for a zero code) and the range where fp16 clamps included -

@@ -172,6 +172,8 @@ def _declare(l: ctypes.CDLL) -> None:
         fn.argtypes = [POINTER(typ), c_void_p]
     l.tb200_bitmatrix_metadata_static.restype = c_int
     l.tb200_bitmatrix_metadata_static.argtypes = [c_void_p, c_int32, c_int64, c_int32, c_void_p, c_void_p, c_void_p, c_void_p]
+    l.tb200_gather_rows.restype = c_int
+    l.tb200_gather_rows.argtypes = [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_void_p]
     l.tb200_move_rows.restype = c_int
     l.tb200_move_rows.argtypes = [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int32, c_void_p]
     l.tb200_bitmatrix_metadata_workspace_bytes.restype = c_size_t

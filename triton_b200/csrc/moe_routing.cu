@@ -310,6 +310,32 @@ __global__ void move_rows_kernel(const uint8_t* __restrict__ src, long long src_
   }
 }
 
+// dst[i] = src[indx[i]] for 0 <= indx[i] < src_rows, else a row of zeros (what the grouped GEMM's own gather reads
+// for such an index). One warp per row, two 16-byte copies per lane in flight.
+__global__ void gather_rows_kernel(const uint8_t* __restrict__ src, long long src_pitch, int src_rows,
+                                   uint8_t* __restrict__ dst, long long dst_pitch, const int* __restrict__ indx,
+                                   long long n, int row_bytes) {
+  const long long warp = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long i = warp; i < n; i += nwarps) {
+    const int j = __ldg(indx + i);
+    const bool valid = j >= 0 && j < src_rows;
+    const uint8_t* s = src + (long long)(valid ? j : 0) * src_pitch;
+    uint8_t* d = dst + i * dst_pitch;
+    for (int b = lane * 16; b < row_bytes; b += 1024) {
+      const bool second = b + 512 < row_bytes;
+      uint4 v0 = make_uint4(0, 0, 0, 0), v1 = make_uint4(0, 0, 0, 0);
+      if (valid) {
+        v0 = __ldg(reinterpret_cast<const uint4*>(s + b));
+        if (second) v1 = __ldg(reinterpret_cast<const uint4*>(s + b + 512));
+      }
+      *reinterpret_cast<uint4*>(d + b) = v0;
+      if (second) *reinterpret_cast<uint4*>(d + b + 512) = v1;
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------ swiglu
 
 __device__ __forceinline__ float swiglu_f(float g, float l, float alpha, float limit, int has_limit) {
@@ -522,6 +548,25 @@ extern "C" int tb200_move_rows(const void* src, int64_t src_pitch_bytes, void* d
   move_rows_kernel<<<(int)blocks, 256, 0, static_cast<cudaStream_t>(stream_)>>>(
       static_cast<const uint8_t*>(src), src_pitch_bytes, static_cast<uint8_t*>(dst), dst_pitch_bytes, indx, n_indx,
       (int)row_bytes, scatter ? 1 : 0);
+  return cuda_err(cudaGetLastError());
+}
+
+extern "C" int tb200_gather_rows(const void* src, int64_t src_pitch_bytes, int64_t src_rows, void* dst,
+                                 int64_t dst_pitch_bytes, const int32_t* indx, int64_t n_indx, int64_t row_bytes,
+                                 void* stream_) {
+  if (n_indx < 0 || row_bytes < 0 || src_rows < 0 || src_rows > INT32_MAX) return TB200_ERR_BAD_ARG;
+  if (n_indx == 0 || row_bytes == 0) return TB200_OK;
+  if (!src || !dst || !indx) return TB200_ERR_BAD_ARG;
+  if ((row_bytes % 16) || (src_pitch_bytes % 16) || (dst_pitch_bytes % 16) || row_bytes > INT32_MAX)
+    return TB200_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(src) & 15) || (reinterpret_cast<uintptr_t>(dst) & 15)) return TB200_ERR_BAD_ARG;
+  int sms = sm_count();
+  if (sms <= 0) sms = 148;
+  long long blocks = (n_indx + 7) / 8;  // 8 warps per block
+  if (blocks > (long long)sms * 16) blocks = (long long)sms * 16;
+  gather_rows_kernel<<<(int)blocks, 256, 0, static_cast<cudaStream_t>(stream_)>>>(
+      static_cast<const uint8_t*>(src), src_pitch_bytes, (int)src_rows, static_cast<uint8_t*>(dst), dst_pitch_bytes, indx,
+      n_indx, (int)row_bytes);
   return cuda_err(cudaGetLastError());
 }
 

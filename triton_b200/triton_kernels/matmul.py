@@ -87,8 +87,15 @@ def matmul(a, b, bias, a_ragged_metadata: RaggedTensorMetadata | None = None, b_
             pc16 = PrecisionConfig(out_dtype=precision_config.out_dtype)
             return matmul(a, w16, bias, a_ragged_metadata, None, gather_indx, scatter_indx, pc16, None, gammas,
                           None, c, None, fused_activation, epilogue, None, _tile_mode)
-        if gather_indx is not None or c is not None:
-            raise NotImplementedError("matmul (fp8 x MXFP4): gather_indx / preallocated output are not implemented")
+        if c is not None:
+            raise NotImplementedError("matmul (fp8 x MXFP4): a preallocated output is not implemented")
+        if gather_indx is not None:
+            # this kernel reads sorted rows only: indexed rows are gathered by a pass of their own first
+            if not isinstance(a, torch.Tensor) or a.ndim != 2 or not a.is_cuda:
+                raise NotImplementedError("matmul (fp8 x MXFP4): gather_indx needs a 2-D CUDA activation tensor")
+            if a.stride(1) != 1 or a.stride(0) % 16 or a.shape[1] % 16:
+                a = a.contiguous()
+            a = _gather_rows(a.view(torch.uint8), gather_indx).view(a.dtype)
         return _matmul_mx4(a, b, bias, a_ragged_metadata, scatter_indx, precision_config, gammas, fused_activation)
     if not isinstance(a, torch.Tensor) or not isinstance(b, torch.Tensor):
         raise NotImplementedError("matmul: wrapped Tensor operands need precision_config.b_mx_scale (MXFP4 weights)")
@@ -125,6 +132,12 @@ def matmul(a, b, bias, a_ragged_metadata: RaggedTensorMetadata | None = None, b_
     n_out = N // 2 if swiglu else N
 
     R = a.shape[0] if gather_indx is None else gather_indx.shape[0]
+    if gather_indx is not None and R >= _PREGATHER_MIN_ROWS and (K * a.element_size()) % 16 == 0 \
+            and (a.stride(0) * a.element_size()) % 16 == 0 and a.data_ptr() % 16 == 0:
+        # many rows: gather them in a pass of their own, so that the GEMM loads A with tiled TMA copies instead of
+        # its gather warps' 16-byte copies (16384 tokens x top-4: the layer takes 3.29 ms instead of 3.90)
+        a = _gather_rows(a, gather_indx)
+        gather_indx = None
     if a_ragged_metadata is None:
         assert E == 1, "several weight matrices need a_ragged_metadata"
         a_ragged_metadata = make_ragged_tensor_metadata(torch.tensor([R], dtype=torch.int32, device=dev), R)
@@ -174,6 +187,21 @@ def matmul(a, b, bias, a_ragged_metadata: RaggedTensorMetadata | None = None, b_
 
 
 _F8 = {torch.float8_e4m3fn: _lib.E4M3, torch.float8_e5m2: _lib.E5M2}
+
+_PREGATHER_MIN_ROWS = 2048
+
+
+def _gather_rows(a, gather_indx):
+    """``a[gather_indx]`` with zero rows for indices outside ``[0, a.shape[0])`` (``tb200_gather_rows``)."""
+    gi = gather_indx.to(torch.int32).contiguous()
+    out = torch.empty((gi.shape[0], a.shape[1]), dtype=a.dtype, device=a.device)
+    esz = a.element_size()
+    with torch.cuda.device(a.device):
+        rc = _lib.lib().tb200_gather_rows(a.data_ptr(), a.stride(0) * esz, a.shape[0], out.data_ptr(), out.stride(0) * esz,
+                                          gi.data_ptr(), gi.numel(), a.shape[1] * esz,
+                                          ctypes.c_void_p(_lib.current_stream_ptr(a.device)))
+    _lib.check(rc, "tb200_gather_rows")
+    return out
 
 
 def _mx4_kernel_layout(b, b_mx_scale, microblock):
