@@ -143,7 +143,7 @@ def build_workload(name: str, rank: int, dev):
             from triton_b200.tutorials.blackwell_scaled_mm_ws import blackwell_scaled_mm_ws
             sa, sb = torch.rand(1, generator=g).to(dev), torch.rand(1, generator=g).to(dev)
             return (lambda: blackwell_scaled_mm_ws(a, b, sa, sb, scale_mode="tensorwise"), 2.0 * n ** 3, 3.0 * n * n,
-                    "per-tensor-scaled e4m3 GEMM 8192^3, bf16 out", "gemm_kernel<128,7,pair,f8>", "tensor")
+                    "per-tensor-scaled e4m3 GEMM 8192^3, bf16 out", "gemm_kernel<256,4,pair,f8>", "tensor")
         if name == "fp8_blockwise":
             from triton_b200.tutorials.blackwell_scaled_mm_ws import blackwell_scaled_mm_ws
             sa = torch.rand(n, n // 128, generator=g).t().contiguous().t().to(dev)
