@@ -109,6 +109,17 @@ def test_cta_pair_tiles(cuda, tile, layout, shape):
     _check(c, o_gemm.gemm_ref(a, b))
 
 
+def test_wide_tile_fp16(cuda):
+    """fp16 in and out through the 256 x 512 tile's TMA-store epilogue."""
+    torch.manual_seed(8)
+    M, N, K = 512, 1536, 320
+    a = (torch.randn(M, K) / K ** 0.5).to(torch.float16)
+    w = torch.randn(N, K).to(torch.float16)
+    c = _mm()(a.to(cuda), w.to(cuda).T, config={"BLOCK_SIZE_N": 1024})
+    assert c.dtype == torch.float16
+    _check(c, o_gemm.gemm_ref(a, w.T))
+
+
 def test_wide_tile_split_k(cuda):
     torch.manual_seed(7)
     M, N, K = 256, 1024, 4096
