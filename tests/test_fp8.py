@@ -105,7 +105,7 @@ def _mx_case(cuda, M, N, K, bn, seed=3):
 
 
 @pytest.mark.parametrize("shape", [(128, 128, 128), (256, 256, 256), (384, 256, 512), (384, 384, 1024)])
-@pytest.mark.parametrize("bn", [0, 128, 256])
+@pytest.mark.parametrize("bn", [0, 128, 256, 512])  # 512: CTA pair, 256 x 256 tile
 def test_mxfp8_reference_test_shapes(cuda, shape, bn):
     """Shapes of the reference's Mxfp8Gemm.SHAPES (test_correctness.py:446-450) plus a ragged-N tile."""
     _mx_case(cuda, *shape, bn)
