@@ -187,7 +187,7 @@ def build_workload(name: str, rank: int, dev):
         by = active * (D * 2 * F + F * D) * 2.0 + R * (D + F) * 2.0 + R * (F + D) * 2.0
         return (step, fl, by, f"MoE layer: {T} tokens, d_model {D}, E={E}, top-{k}, W1 [{D},{2*F}] SwiGLU W2 [{F},{D}], "
                 "gate-weighted combine, seed 4", "moe_gemm_kernel", "hbm" if name == "moe_decode" else "tensor")
-    if name in ("moe_mx4", "moe_mx4_decode"):
+    if name in ("moe_mx4", "moe_mx4_decode", "moe_bf16_mx4"):
         from triton_b200.triton_kernels.matmul import PrecisionConfig, matmul as moe_matmul, swiglu_activation
         from triton_b200.triton_kernels.numerics_details.mxfp import downcast_to_mxfp
         from triton_b200.triton_kernels.reduce import reduce
@@ -198,7 +198,8 @@ def build_workload(name: str, rank: int, dev):
         T = 64 if name == "moe_mx4_decode" else 16384
         D, F, E, k = 4096, 1536, 128, 4
         g4 = torch.Generator(device="cpu").manual_seed(4 + 1000 * rank)
-        x = torch.randn(T, D, generator=g4).to(torch.float8_e4m3fn).to(dev)
+        x = torch.randn(T, D, generator=g4)
+        x = (x.to(torch.bfloat16) if name == "moe_bf16_mx4" else x.to(torch.float8_e4m3fn)).to(dev)
         logits = torch.randn(T, E, generator=g4).to(dev)
 
         def prep(w):  # quantise on the GPU, expert by expert chunks to bound memory
@@ -223,6 +224,22 @@ def build_workload(name: str, rank: int, dev):
             return reduce(y.view(T, k, D), dim=1)[0]
         R = T * k
         fl = 2.0 * R * D * 2 * F + 2.0 * R * F * D
+        if name == "moe_bf16_mx4":
+            # bf16 activations: each GEMM upcasts its MXFP4 weight to bf16 first (per call, as a user of matmul gets it)
+            pcb1, pcb2 = PrecisionConfig(b_mx_scale=s1), PrecisionConfig(b_mx_scale=s2)
+
+            def step_bf16():
+                sm = topk(logits, k)
+                mm = sm.mask_metadata
+                rg = make_ragged_tensor_metadata(mm.col_sum, T * k)
+                combine = mm.col_sorted_indx
+                gather = torch.div(combine, k, rounding_mode="trunc")
+                gam = sm.vals.float().reshape(-1)[combine.long()]
+                h = moe_matmul(x, w1, None, rg, gather_indx=gather, precision_config=pcb1, fused_activation=act)
+                y = moe_matmul(h, w2, None, rg, scatter_indx=combine, gammas=gam, precision_config=pcb2)
+                return reduce(y.view(T, k, D), dim=1)[0]
+            return (step_bf16, fl, 0.0, f"MoE layer, bf16 activations x MXFP4 weights (upcast pass + 16-bit grouped GEMM per "
+                    f"call): {T} tokens, d_model {D}, E={E}, top-{k}, seed 4", "moe_gemm_kernel", "tensor")
         active = int((topk(logits, k).mask_metadata.col_sum > 0).sum().item())
         by = active * (D * 2 * F + F * D) * (0.5 + 1.0 / 32) + R * (D + F) * 1.0 + R * (F * 1.0 + D * 2.0)
         return (step, fl, by, f"MoE layer, fp8 activations x MXFP4 weights: {T} tokens, d_model {D}, E={E}, top-{k}, "
@@ -269,7 +286,7 @@ def build_workload(name: str, rank: int, dev):
 # Kernels of this library launched per step: the MoE layer runs topk, three bitmatrix-metadata kernels,
 # the ragged-metadata kernel, two grouped GEMMs and the top-k reduce (the EP variant adds four row moves), and
 # with 2048 or more sorted rows the row gather ahead of GEMM 1.
-OWN_LAUNCHES_PER_STEP = {"moe": 9, "moe_decode": 8, "moe_ep": 12, "moe_mx4": 9, "moe_mx4_decode": 9, "attn_bwd": 3, "attn_bwd_causal": 3,
+OWN_LAUNCHES_PER_STEP = {"moe": 9, "moe_decode": 8, "moe_ep": 12, "moe_mx4": 9, "moe_mx4_decode": 9, "moe_bf16_mx4": 11, "attn_bwd": 3, "attn_bwd_causal": 3,
                          "attn_bwd_ref_shape": 3, "attn_bwd_ref_shape_causal": 3}
 
 
@@ -408,7 +425,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--workload", default="gemm",
                     help="gemm (headline, default) | attn | attn_causal | attn_short | attn_short_causal | attn_bwd | "
-                         "attn_bwd_causal | attn_bwd_ref_shape[_causal] | fp8 | fp8_blockwise | mxfp8 | moe | moe_decode | moe_mx4 | moe_mx4_decode | mxfp4_upcast | moe_ep")
+                         "attn_bwd_causal | attn_bwd_ref_shape[_causal] | fp8 | fp8_blockwise | mxfp8 | moe | moe_decode | moe_mx4 | moe_mx4_decode | moe_bf16_mx4 | mxfp4_upcast | moe_ep")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
