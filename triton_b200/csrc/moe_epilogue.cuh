@@ -56,6 +56,19 @@ __device__ __forceinline__ void moe_store_run(void* y, long long elem, const flo
     }
   } else {
     uint16_t* dst = static_cast<uint16_t*>(y) + elem;
+    if (cnt == N && ((reinterpret_cast<uintptr_t>(dst) & 31) == 0)) {
+      // 32-byte stores: a thread owns a row, so each instruction then writes whole sectors
+#pragma unroll
+      for (int j = 0; j < N / 16; ++j) {
+        uint32_t w[8];
+#pragma unroll
+        for (int t = 0; t < 8; ++t) w[t] = moe_pack16(o[j * 16 + 2 * t], o[j * 16 + 2 * t + 1], kind);
+        asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst + j * 16), "r"(w[0]), "r"(w[1]),
+                     "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+                     : "memory");
+      }
+      return;
+    }
     if (cnt == N && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
 #pragma unroll
       for (int j = 0; j < N / 8; ++j) {
