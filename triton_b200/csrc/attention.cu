@@ -404,28 +404,50 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_fwd_kernel(const __g
       const float inv_l = 1.f / l;
       const bool valid = qrow < s_q;
       uint16_t* orow = reinterpret_cast<uint16_t*>(p.o) + ((size_t)t.bh * s_q + qrow) * D;
+      // two tensor-memory loads in flight; O_g is handed back as soon as the last load has landed (before that
+      // chunk is converted and stored); 32-byte stores when the row allows (each instruction writes whole sectors)
+      const bool wide_st = (reinterpret_cast<uintptr_t>(orow) & 31) == 0;
+      auto store32 = [&](const uint32_t (&v)[32], int c) {
+        if (!valid) return;
+        uint32_t w[16];
+#pragma unroll
+        for (int u = 0; u < 16; ++u) {
+          const float lo = __uint_as_float(v[2 * u]) * inv_l;
+          const float hi = __uint_as_float(v[2 * u + 1]) * inv_l;
+          w[u] = F16 ? pack_f16x2(lo, hi) : pack_bf16x2(lo, hi);
+        }
+        if (wide_st) {
+#pragma unroll
+          for (int i = 0; i < 2; ++i)
+            asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(orow + c + 16 * i), "r"(w[8 * i]),
+                         "r"(w[8 * i + 1]), "r"(w[8 * i + 2]), "r"(w[8 * i + 3]), "r"(w[8 * i + 4]), "r"(w[8 * i + 5]),
+                         "r"(w[8 * i + 6]), "r"(w[8 * i + 7])
+                         : "memory");
+        } else {
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            reinterpret_cast<uint4*>(orow + c)[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+        }
+      };
+      {
+        uint32_t v0[32], v1[32];
+        tmem_ld_32x32b_x32(t_o, v0);
 #pragma unroll 1
-      for (int c = 0; c < D; c += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(t_o + c, v);
-        tmem_ld_wait();
-        if (valid) {
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            uint32_t w[4];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              const float lo = __uint_as_float(v[i * 8 + 2 * u]) * inv_l;
-              const float hi = __uint_as_float(v[i * 8 + 2 * u + 1]) * inv_l;
-              w[u] = F16 ? pack_f16x2(lo, hi) : pack_bf16x2(lo, hi);
-            }
-            reinterpret_cast<uint4*>(orow + c)[i] = make_uint4(w[0], w[1], w[2], w[3]);
+        for (int c = 0; c < D; c += 64) {
+          tmem_ld_wait();
+          tmem_ld_32x32b_x32(t_o + c + 32, v1);
+          store32(v0, c);
+          tmem_ld_wait();
+          if (c + 64 < D) {
+            tmem_ld_32x32b_x32(t_o + c + 64, v0);
+          } else {
+            tc_fence_before_sync();
+            mbar_arrive(&o_free[g]);
           }
+          store32(v1, c + 32);
         }
       }
       if (valid && p.lse) p.lse[(size_t)t.bh * s_q + qrow] = m + log2f(l);
-      tc_fence_before_sync();
-      mbar_arrive(&o_free[g]);
     }
   }
 
