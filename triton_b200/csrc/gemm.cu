@@ -614,6 +614,13 @@ static bool plan_gemm(const tb200_gemm_args* a, int sms, GemmPlan* plan) {
         bn = cbn;
       }
     }
+    // One row of tiles and a long K: such a GEMM streams B at the rate (stages in flight) / (load latency), so a CTA
+    // per 128 x 64 tile walking all of K (one short wave) is slower than 128-wide tiles with K split in two or
+    // more, although that adds the partial-sum pass (M = 128, N = K = 8192: 46 us against 31 + 6).
+    if (tm == 1 && kb >= 32 && a->split_k <= 0) {
+      const long long t128 = (a->n + 127) / 128;
+      if (t128 * 2 <= sms) bn = 128;
+    }
     // CTA pair: two SMs share a 256 x 256 tile; each still computes 128 x 256 but stages a third
     // less data per K step, which is worth ~25% once the grid is full.
     if (a->m > BM && sms >= 2) {
