@@ -135,6 +135,19 @@ def build_workload(name: str, rank: int, dev):
         return (lambda: attention_backward(q, k, v, o, lse, do, sc, causal), fl, 8.0 * B * H * S * D * 2,
                 f"flash-attention bwd bf16 [B={B},H={H},S={S},D={D}] causal={causal} (delta + main + dq kernels), seed 2",
                 "attention_bwd_kernel", "tensor")
+    if name == "gemm_skinny":
+        from triton_b200.tutorials.blackwell_gemm_ws import matmul
+        m, n = 128, 8192
+        a = (torch.randn(m, n, generator=g) / n ** 0.5).to(torch.bfloat16).to(dev)
+        ws = [(torch.randn(n, n, generator=g) / n ** 0.5).to(torch.bfloat16).to(dev) for _ in range(4)]
+        turn = [0]
+
+        def step():  # four weight matrices in turn: 512 MiB, so none of them stays in the 126 MB L2
+            turn[0] = (turn[0] + 1) & 3
+            return matmul(a, ws[turn[0]].t())
+        return (step, 2.0 * m * n * n, 2.0 * (n * n + m * n + m * n),
+                "bf16 GEMM M=128, N=K=8192 (the skinny case), B K-major, four weight matrices in turn", "gemm_kernel<128,6> + splitk_reduce_kernel",
+                "hbm")
     if name in ("fp8", "fp8_blockwise", "mxfp8"):
         n = 8192
         a = (torch.randn(n, n, generator=g) * 0.1).to(torch.float8_e4m3fn).to(dev)
@@ -286,7 +299,7 @@ def build_workload(name: str, rank: int, dev):
 # Kernels of this library launched per step: the MoE layer runs topk, three bitmatrix-metadata kernels,
 # the ragged-metadata kernel, two grouped GEMMs and the top-k reduce (the EP variant adds four row moves), and
 # with 2048 or more sorted rows the row gather ahead of GEMM 1.
-OWN_LAUNCHES_PER_STEP = {"moe": 9, "moe_decode": 8, "moe_ep": 12, "moe_mx4": 9, "moe_mx4_decode": 9, "moe_bf16_mx4": 11, "attn_bwd": 3, "attn_bwd_causal": 3,
+OWN_LAUNCHES_PER_STEP = {"moe": 9, "moe_decode": 8, "moe_ep": 12, "moe_mx4": 9, "moe_mx4_decode": 9, "moe_bf16_mx4": 11, "gemm_skinny": 2, "attn_bwd": 3, "attn_bwd_causal": 3,
                          "attn_bwd_ref_shape": 3, "attn_bwd_ref_shape_causal": 3}
 
 
@@ -424,7 +437,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--workload", default="gemm",
-                    help="gemm (headline, default) | attn | attn_causal | attn_short | attn_short_causal | attn_bwd | "
+                    help="gemm (headline, default) | gemm_skinny | attn | attn_causal | attn_short | attn_short_causal | attn_bwd | "
                          "attn_bwd_causal | attn_bwd_ref_shape[_causal] | fp8 | fp8_blockwise | mxfp8 | moe | moe_decode | moe_mx4 | moe_mx4_decode | moe_bf16_mx4 | mxfp4_upcast | moe_ep")
     args = ap.parse_args()
 
