@@ -130,6 +130,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const __grid_cons
   uint64_t* tempty = tfull + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
 
+  // split-K: the reduction pass behind this grid may be launched now (it waits for this grid's completion itself)
+  if (p.out_mode == 3) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
@@ -534,6 +536,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const __grid_cons
 // C[m,n] = sum_s ws[s,m,n] (fp32) -> out dtype. One thread per 4 consecutive columns.
 __global__ void splitk_reduce_kernel(const float* __restrict__ ws, void* __restrict__ c, int m, int n, long long ldc,
                                      int split_k, int out_mode) {
+  // launched with programmatic stream serialization right behind the GEMM that writes ws: its blocks may be resident
+  // before that grid has finished, and wait here until it has (and its writes are visible)
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const long long n4 = (n + 3) / 4;
   const long long total = (long long)m * n4;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
@@ -853,8 +858,18 @@ extern "C" int tb200_gemm(const tb200_gemm_args* a, void* stream_) {
     const long long total = (long long)a->m * ((a->n + 3) / 4);
     int blocks = (int)((total + 255) / 256);
     if (blocks > sms * 8) blocks = sms * 8;
-    splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(p.ws, a->c, p.m, p.n, p.ldc, plan.split_k, final_mode);
-    rc = cuda_err(cudaGetLastError());
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(blocks);
+    cfg.blockDim = dim3(256);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    rc = cuda_err(cudaLaunchKernelEx(&cfg, splitk_reduce_kernel, (const float*)p.ws, a->c, p.m, p.n, p.ldc, plan.split_k,
+                                     final_mode));
   }
   return rc;
 }
