@@ -155,3 +155,102 @@ def test_moe_layer_oracle_is_dense_mixture():
     for e in range(E):
         want += gate[:, e:e + 1] * (o_moe.swiglu_ref(x @ w1[e], 1.0) @ w2[e])
     torch.testing.assert_close(got, want, atol=1e-5, rtol=1e-5)
+
+
+# --------------------------------------------------------------------------------------------------
+# MoE path: the oracle against outputs of the reference's own torch twins
+# (tests/golden/moe_cases.npz, written by tests/golden/make_moe_fixture.py from the reference checkout)
+# --------------------------------------------------------------------------------------------------
+
+def _moe_fx():
+    return np.load(os.path.join(GOLDEN, "moe_cases.npz"))
+
+
+def test_topk_oracle_matches_reference_twin():
+    """topk_torch (topk.py:144-185): indices and bitmatrix bit-exact, values to 1e-6; covers ties,
+    padded rows (n_rows), no softmax and bf16 logits."""
+    fx = _moe_fx()
+    for name in ("plain", "ties", "padded", "nosoftmax", "bf16"):
+        n_rows, softmax, is_bf16 = (int(v) for v in fx[f"topk_{name}_kw"])
+        x = torch.from_numpy(fx[f"topk_{name}_x"])
+        if is_bf16:
+            x = x.to(torch.bfloat16)
+        vals, indx, bits = o_moe.topk_ref(x, 4, apply_softmax=bool(softmax), n_rows=n_rows)
+        assert np.array_equal(indx.numpy(), fx[f"topk_{name}_indx"]), name
+        assert np.array_equal(bits.numpy(), fx[f"topk_{name}_bits"]), name
+        np.testing.assert_allclose(vals.float().numpy()[:n_rows], fx[f"topk_{name}_vals"][:n_rows], rtol=1e-6, atol=1e-7)
+
+
+def test_bitmatrix_metadata_oracle_matches_reference_twin():
+    """make_bitmatrix_metadata_torch (tensor_details/bitmatrix.py:157-168), bit-exact."""
+    fx = _moe_fx()
+    for name in ("plain", "ties", "padded"):
+        md = o_moe.bitmatrix_metadata_ref(fx[f"topk_{name}_indx"], 128)
+        assert np.array_equal(md.col_sum, fx[f"bm_{name}_col_sum"])
+        assert np.array_equal(md.col_sorted_indx, fx[f"bm_{name}_col_sorted"])
+        assert np.array_equal(md.row_sorted_indx, fx[f"bm_{name}_row_sorted"])
+
+
+def test_ragged_metadata_oracle_matches_reference_twin():
+    """make_ragged_tensor_metadata_torch and remap_ragged_tensor_metadata_torch
+    (tensor_details/ragged_tensor.py:217-253, 388-433), bit-exact."""
+    fx = _moe_fx()
+    for name in ("doc", "mixed", "routing", "empty"):
+        ss = fx[f"rg_{name}_slice_sizes"]
+        md = o_moe.ragged_metadata_ref(ss, int(ss.sum()))
+        assert np.array_equal(md.slice_offs, fx[f"rg_{name}_slice_offs"]), name
+        assert np.array_equal(md.block_offs_data, fx[f"rg_{name}_block_offs"]), name
+        assert np.array_equal(md.block_schedule_data, fx[f"rg_{name}_block_sched"]), name
+        if f"rg_{name}_map" in fx:
+            rm = o_moe.remap_ragged_metadata_ref(md, fx[f"rg_{name}_map"])
+            assert np.array_equal(rm.slice_sizes, fx[f"rg_{name}_re_slice_sizes"]), name
+            assert np.array_equal(rm.slice_offs, fx[f"rg_{name}_re_slice_offs"]), name
+            assert np.array_equal(rm.block_offs_data, fx[f"rg_{name}_re_block_offs"]), name
+            assert np.array_equal(rm.block_schedule_data, fx[f"rg_{name}_re_block_sched"]), name
+
+
+def test_grouped_matmul_oracle_matches_reference_twin():
+    """matmul_torch (matmul.py:823-914) with gather, scatter incl. -1, gammas and bias, and
+    swiglu_torch applied to its result; fp32 holders of bf16 values, so 1e-5 is rounding of the sums."""
+    fx = _moe_fx()
+    a, w = torch.from_numpy(fx["mm_a"]), torch.from_numpy(fx["mm_w"])
+    bias, gam = torch.from_numpy(fx["mm_bias"]), torch.from_numpy(fx["mm_gammas"])
+    sizes, gather, scatter = fx["mm_sizes"], fx["mm_gather"], fx["mm_scatter"]
+    a_sorted = a[torch.from_numpy(gather).long()]
+    tol = dict(rtol=1e-5, atol=1e-5)
+    f32 = torch.float32
+    got = o_moe.grouped_matmul_ref(a_sorted, w, None, sizes, out_dtype=f32)
+    np.testing.assert_allclose(got.numpy(), fx["mm_y_plain"], **tol)
+    got = o_moe.grouped_matmul_ref(a, w, None, sizes, gather_indx=gather, out_dtype=f32)
+    np.testing.assert_allclose(got.numpy(), fx["mm_y_gather"], **tol)
+    got = o_moe.grouped_matmul_ref(a_sorted, w, bias, sizes, gammas=gam, out_dtype=f32)
+    np.testing.assert_allclose(got.numpy(), fx["mm_y_bias_gamma"], **tol)
+    got = o_moe.grouped_matmul_ref(a_sorted, w, None, sizes, scatter_indx=scatter, gammas=gam, out_dtype=f32)
+    np.testing.assert_allclose(got.numpy(), fx["mm_y_scatter"], **tol)
+    got = o_moe.grouped_matmul_ref(a, w, bias, sizes, gather_indx=gather, scatter_indx=scatter, gammas=gam, out_dtype=f32)
+    np.testing.assert_allclose(got.numpy(), fx["mm_y_all"], **tol)
+    for limit in (None, 1.4):
+        got = o_moe.grouped_matmul_ref(a, w, bias, sizes, gather_indx=gather, swiglu=(1.1, limit), out_dtype=f32)
+        np.testing.assert_allclose(got.numpy(), fx[f"mm_y_swiglu_{limit}"], **tol)
+    # bf16 in, bf16 out: the twin rounds once per expert block, as the oracle does at the end
+    got = o_moe.grouped_matmul_ref(a.to(torch.bfloat16), w.to(torch.bfloat16), bias, sizes, gather_indx=gather,
+                                   scatter_indx=scatter, gammas=gam)
+    np.testing.assert_allclose(got.float().numpy(), fx["mm_y_all_bf16"], rtol=0, atol=0)
+
+
+def test_swiglu_and_reduce_oracles_match_reference_twins():
+    """swiglu_torch (swiglu.py:89-100) with and without limit; reduce_torch (reduce.py:1173-1206)
+    with mask and scale."""
+    fx = _moe_fx()
+    x = torch.from_numpy(fx["sw_x"])
+    np.testing.assert_allclose(o_moe.swiglu_ref(x, 1.702, None).numpy(), fx["sw_y_None"], rtol=1e-6, atol=1e-7)
+    np.testing.assert_allclose(o_moe.swiglu_ref(x, 1.702, 2.0).numpy(), fx["sw_y_limit"], rtol=1e-6, atol=1e-7)
+    xr = torch.from_numpy(fx["rd_x"])
+    mask, sc = torch.from_numpy(fx["rd_mask"]), torch.from_numpy(fx["rd_scale"])
+    tol = dict(rtol=1e-6, atol=1e-6)
+    np.testing.assert_allclose(o_moe.reduce_ref(xr, 1).numpy(), fx["rd_y_plain"], **tol)
+    np.testing.assert_allclose(o_moe.reduce_ref(xr, 1, mask=mask).numpy(), fx["rd_y_mask"], **tol)
+    np.testing.assert_allclose(o_moe.reduce_ref(xr, 1, scale=sc).numpy(), fx["rd_y_scale"], **tol)
+    np.testing.assert_allclose(o_moe.reduce_ref(xr, 1, mask=mask, scale=sc).numpy(), fx["rd_y_both"], **tol)
+    got = o_moe.reduce_ref(xr.to(torch.bfloat16), 1, mask=mask, scale=sc)
+    np.testing.assert_allclose(got.float().numpy(), fx["rd_y_both_bf16"], rtol=0, atol=0)
