@@ -54,6 +54,16 @@ const char* tb200_error_string(int code);
 int tb200_check(void* stream);
 /* Raw status word of the current device without clearing it: 0, or (wait_code<<16)|block. */
 int tb200_last_status_code(void);
+/*
+ * Self-test of the bounded-wait path (no counterpart in the reference, whose waits are unbounded
+ * mbarrier.try_wait loops): launches one block whose thread 0 waits, with the wait routine every
+ * kernel here uses, on an mbarrier that nothing completes, for at most limit_ns nanoseconds
+ * (1 .. 1e9). When the limit runs out the thread records wait code 9 in the status word and the
+ * block returns; no copy or MMA is in flight and nothing faults. After it, tb200_check() returns
+ * TB200_ERR_TIMEOUT once and TB200_OK from then on. completed: optional device int that receives
+ * 1 if the wait completed (it cannot) or 0 if it was abandoned.
+ */
+int tb200_selftest_wait(uint64_t limit_ns, int* completed, void* stream);
 
 /* ---------------------------------------------------------------- dense GEMM ------- */
 
@@ -232,7 +242,8 @@ int tb200_attention_bwd(const tb200_attention_bwd_args* args, void* stream);
  * y_vals: same dtype [rows_alloc, k]; y_indx: int16 [rows_alloc, k]; both with row stride stride_y.
  * bitmatrix: uint32 words; word w of row r lives at r*bits_stride_row + w*bits_stride_word
  *   (the reference stores it transposed: bits_stride_row = 1).
- * use_provided_indx: y_indx is an input (values are gathered, the mask is built from it).
+ * use_provided_indx: y_indx is an input (values are gathered, the mask is built from it); a provided
+ *   index outside [0, n_cols) is treated as "none": value 0, no mask bit.
  * n_cols <= 1024, k <= 32.
  */
 typedef struct {
@@ -279,11 +290,13 @@ size_t tb200_bitmatrix_metadata_workspace_bytes(int64_t n_entries, int32_t n_col
  * point has no counterpart in the reference; it exists for callers that cannot allocate device
  * memory at call time and have none to lend — processes that freeze their GPU memory plan at
  * start-up, or runtimes that forbid cudaMalloc (a device-wide stall) on the request path.
- * Limit: ceil(n_entries / 1024) * n_cols + n_cols <= 263168 (e.g. 262144 entries x 1024 columns,
- * or 65536 entries x 4096 columns); beyond that the call returns TB200_ERR_TOO_LARGE and launches
- * nothing. The first call on each device looks up the array's device address (make that call
- * outside stream capture). Calls on the same GPU share the array: run them on one stream or order
- * them yourself — kernels of two calls that overlap in time corrupt each other's scratch.
+ * Limit: ceil(n_entries / 1024) * n_cols + n_cols <= 263168 words (e.g. 262144 entries x 1024
+ * columns = 263168, exactly the limit; or 61440 entries x 4096 columns = 249856); beyond that the
+ * call returns TB200_ERR_TOO_LARGE and launches nothing. n_entries == 0 is accepted (col_sum is
+ * zeroed). The first call on each device looks up the array's device address (make that call
+ * outside stream capture); the address is cached per device ordinal and does not survive a
+ * cudaDeviceReset of that device. Calls on the same GPU share the array: run them on one stream or
+ * order them yourself — kernels of two calls that overlap in time corrupt each other's scratch.
  * No call here allocates or frees memory.
  */
 int tb200_bitmatrix_metadata_static(const void* indx, int32_t indx_is_int16, int64_t n_entries, int32_t n_cols,
@@ -309,6 +322,29 @@ typedef struct {
 int tb200_ragged_metadata(const tb200_ragged_metadata_args* args, void* stream);
 
 /*
+ * Metadata of the ragged tensor that keeps slice i iff slice_map[i] != -1, renumbered to slice_map[i]; dropped
+ * entries are compacted to the end as -1 and block_offs[s][number of kept slices] holds the number of kept
+ * schedule entries. The expert-parallel layer uses it to turn the global metadata into that of a rank's experts.
+ * Stands behind: tensor_details/ragged_tensor.py:348 remap_ragged_tensor_metadata(metadata, slice_map)
+ *   (torch twin remap_ragged_tensor_metadata_torch :388-433). All arrays int32, shaped as in
+ * tb200_ragged_metadata_args; the outputs must not alias the inputs.
+ */
+typedef struct {
+  const int32_t* slice_sizes;
+  const int32_t* slice_offs;
+  const int32_t* block_offs;
+  const int32_t* block_schedule;
+  const int32_t* slice_map;
+  int32_t* out_slice_sizes;
+  int32_t* out_slice_offs;
+  int32_t* out_block_offs;
+  int32_t* out_block_schedule;
+  int32_t n_slices;
+  int32_t max_n_blocks;
+} tb200_remap_ragged_metadata_args;
+int tb200_remap_ragged_metadata(const tb200_remap_ragged_metadata_args* args, void* stream);
+
+/*
  * y[t, :] = sum over the k slots of x[t, j, :] (optionally masked / scaled per (t, j)), fp32 sum.
  * Stands behind: reduce.py:1135 reduce(x, dim, mask=None, scale=None, ...) for the MoE combine
  *   `reduce(y.view(-1, k, d), dim=1)` (torch twin reduce_torch :1173).
@@ -324,18 +360,102 @@ typedef struct {
   int64_t d;
   int32_t k;
   int32_t dtype;
-  const int32_t* row_indx; /* optional int32 [n_tokens*k]: slot (t, j) reads row row_indx[t*k+j] of x (< 0 = skip) */
+  const int32_t* row_indx; /* optional int32 [n_tokens*k]: slot (t, j) reads row row_indx[t*k+j] of x (< 0 or >= x_rows = skip) */
+  int64_t x_rows;          /* rows of x when row_indx is given; 0 = n_tokens * k */
 } tb200_reduce_k_args;
 int tb200_reduce_k(const tb200_reduce_k_args* args, void* stream);
 
 /*
  * Row gather (scatter = 0: dst[i] = src[indx[i]]) or scatter (scatter = 1: dst[indx[i]] = src[i]) of
- * rows of row_bytes bytes (multiple of 16; pitches and bases 16-byte aligned); indx[i] < 0 skips.
+ * rows of row_bytes bytes (multiple of 16; pitches and bases 16-byte aligned). indexed_rows is the
+ * number of rows of the indexed side (src when gathering, dst when scattering): an index outside
+ * [0, indexed_rows) skips the row, so a corrupt index never becomes an out-of-bounds access.
  * Stands behind the local row moves around the expert-parallel exchange,
  * distributed.py:176-283 (convert_dp_to_ep / convert_ep_to_dp store rows at indexed positions).
  */
 int tb200_move_rows(const void* src, int64_t src_pitch_bytes, void* dst, int64_t dst_pitch_bytes,
-                    const int32_t* indx, int64_t n_indx, int64_t row_bytes, int32_t scatter, void* stream);
+                    const int32_t* indx, int64_t n_indx, int64_t row_bytes, int32_t scatter, int64_t indexed_rows,
+                    void* stream);
+
+/* ---------------------------------------------------------------- expert-parallel exchange -------- */
+
+/*
+ * Symmetric buffers: every rank (one process per GPU) allocates one buffer of the same size, exports a
+ * 64-byte CUDA IPC handle, exchanges the handles by any host-side means (the Python mirror uses
+ * torch.distributed.all_gather) and opens its peers' handles; it then holds a device pointer to every
+ * rank's buffer. Stands behind SymmetricMemoryPool._initialize, distributed_details/mesh.py:118-136
+ * (symm_mem.empty + rendezvous in the reference). These five calls are set-up / tear-down: they are the
+ * only calls of the library that allocate, free or synchronise the device.
+ */
+int tb200_symm_alloc(size_t bytes, void** ptr);              /* cudaMalloc + zero fill */
+int tb200_symm_free(void* ptr);
+int tb200_symm_export(const void* ptr, uint8_t* handle64);   /* handle of a tb200_symm_alloc buffer */
+int tb200_symm_open(const uint8_t* handle64, void** peer_ptr);   /* maps a peer's buffer, enables peer access */
+int tb200_symm_close(void* peer_ptr);
+
+/*
+ * Cross-GPU barrier on `stream` (hdl.barrier(channel) in the reference, mesh.py:130-136): one small kernel
+ * in which rank r stores its next epoch into flag r of every rank's signal block (st.release.sys) and waits
+ * until all `world` flags of its own block carry that epoch (ld.acquire.sys). signal_peers: HOST array of
+ * `world` device pointers, entry j = the signal block of this channel inside rank j's symmetric buffer
+ * (320 zero-initialised bytes, 16-byte aligned: uint32 flags[16] at byte 0, the owner's epoch at byte 256).
+ * All ranks must call it the same number of times. Writes a rank made before the barrier (peer stores
+ * included) are visible to kernels the others launch after it. The wait is bounded by limit_ns
+ * (<= 30 s): when a peer does not arrive the kernel records wait code 10 and returns; tb200_check()
+ * then reports TB200_ERR_TIMEOUT. Each rank must run on its own GPU.
+ */
+int tb200_symm_barrier(void* const* signal_peers, int32_t rank, int32_t world, uint64_t limit_ns, void* stream);
+
+/*
+ * DP -> EP dispatch: for every local token t and slot j with expert e = expt_indx[token_offset + t, j] >= 0,
+ * copies x[t, :] to row dispatch_indx[(token_offset + t) * k + j] of the buffer of rank expt_owner[e].
+ * Stands behind _convert_dp_to_ep, distributed.py:136-173 (host convert_dp_to_ep :176-211).
+ * expt_indx: GLOBAL [n_tokens_global, k] int16 or int32; dispatch_indx: global row_sorted_indx;
+ * expt_owner: int32 [n_experts]; dst_peers: HOST array of `world` device pointers, each a
+ * [dst_rows, row_bytes] buffer with pitch dst_pitch_bytes. Rows of 16-byte multiples, 16-byte aligned.
+ */
+typedef struct {
+  const void* x;
+  int64_t x_pitch_bytes;
+  const void* expt_indx;
+  const int32_t* dispatch_indx;
+  const int32_t* expt_owner;
+  void* const* dst_peers;
+  int64_t dst_pitch_bytes;
+  int64_t dst_rows;
+  int64_t row_bytes;
+  int64_t n_tokens_local;
+  int64_t token_offset;
+  int32_t k;
+  int32_t n_experts;
+  int32_t world;
+  int32_t indx_is_int16;
+} tb200_ep_dispatch_args;
+int tb200_ep_dispatch(const tb200_ep_dispatch_args* args, void* stream);
+
+/*
+ * EP -> DP combine: for every expert-sorted row r whose entry = combine_indx[r] belongs to an expert this
+ * rank owns, copies src[r, :] to row (entry % rows_per_rank) of the buffer of rank entry / rows_per_rank
+ * (rows_per_rank = n_tokens_local * k). Stands behind _convert_ep_to_dp, distributed.py:217-254 (host
+ * convert_ep_to_dp :257-283). tb200_moe_gemm does the same from its epilogue when given y_peers.
+ */
+typedef struct {
+  const void* src;
+  int64_t src_pitch_bytes;
+  const void* expt_indx;
+  const int32_t* combine_indx;
+  const int32_t* expt_owner;
+  void* const* dst_peers;
+  int64_t dst_pitch_bytes;
+  int64_t row_bytes;
+  int64_t n_rows;
+  int64_t rows_per_rank;
+  int32_t n_experts;
+  int32_t world;
+  int32_t rank;
+  int32_t indx_is_int16;
+} tb200_ep_combine_args;
+int tb200_ep_combine(const tb200_ep_combine_args* args, void* stream);
 
 /*
  * dst[i] = src[indx[i]] when 0 <= indx[i] < src_rows, else a row of zeros: the rows tb200_moe_gemm would read through
@@ -403,6 +523,15 @@ typedef struct {
   int32_t swiglu_has_limit;
   int32_t moe_tile_mode; /* 0 = choose; 1 = one CTA per 128-row block; 2 = CTA pair per two consecutive blocks */
   const int32_t* slice_sizes; /* optional int32 [E]: rows of expert e (needed for remapped metadata, whose slice_offs are not cumulative); NULL = slice_offs[e+1] - slice_offs[e] */
+  /* Fused expert-parallel combine (the reference's fused-comm epilogue, matmul_details/_p_matmul.py:755-782):
+   * with y_world > 0, y is ignored and the output row with index i (scatter_indx[r], or r) is stored to row
+   * i % rows_per_peer of y_peers[i / rows_per_peer]; y_peers is a HOST array of y_world device pointers
+   * (buffers of this and of other GPUs as tb200_symm_open maps them), each [rows_per_peer, N] with pitch ldy.
+   * Plain stores; follow the call with tb200_symm_barrier before any rank reads its buffer. */
+  void* const* y_peers;
+  int64_t rows_per_peer;
+  int32_t y_world;
+  int32_t reserved;
 } tb200_moe_gemm_args;
 int tb200_moe_gemm(const tb200_moe_gemm_args* args, void* stream);
 

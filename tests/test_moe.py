@@ -233,3 +233,45 @@ def test_pregathered_rows_match_in_kernel_gather(cuda, monkeypatch):
     ref = x.cpu().float()[gather[:64].clamp(0, T - 1).long()] @ w[0].cpu().float()
     ref[5] = 0
     torch.testing.assert_close(out_pre[:64].cpu().float(), ref, rtol=2e-2, atol=2e-2)
+
+
+def test_out_of_range_indices_are_skipped(cuda, lib):
+    """An index outside its table must never become an out-of-bounds access: the row mover skips it, top-k with
+    provided indices treats it as "none", and the k-way reduce skips the slot."""
+    import ctypes
+    from triton_b200 import _lib
+    from triton_b200.triton_kernels.reduce import reduce
+    from triton_b200.triton_kernels.topk import topk
+    with torch.cuda.device(cuda):
+        stream = ctypes.c_void_p(_lib.current_stream_ptr(cuda))
+        src = torch.arange(8 * 64, dtype=torch.float32, device=cuda).view(8, 64)
+        # scatter: indices 9 and -3 are outside the 6-row destination
+        dst = torch.full((6, 64), -1.0, device=cuda)
+        indx = torch.tensor([0, 9, 2, -3, 5, 1, 3, 4], dtype=torch.int32, device=cuda)
+        rc = lib.tb200_move_rows(src.data_ptr(), 256, dst.data_ptr(), 256, indx.data_ptr(), 8, 256, 1, 6, stream)
+        assert rc == 0
+        want = torch.full((6, 64), -1.0, device=cuda)
+        for i, j in enumerate(indx.tolist()):
+            if 0 <= j < 6:
+                want[j] = src[i]
+        assert torch.equal(dst, want)
+        # gather: index 8 is outside the 8-row source
+        dst = torch.full((3, 64), -1.0, device=cuda)
+        indx = torch.tensor([7, 8, 0], dtype=torch.int32, device=cuda)
+        rc = lib.tb200_move_rows(src.data_ptr(), 256, dst.data_ptr(), 256, indx.data_ptr(), 3, 256, 0, 8, stream)
+        assert rc == 0
+        assert torch.equal(dst[0], src[7]) and torch.equal(dst[2], src[0]) and bool((dst[1] == -1).all())
+        # provided top-k indices outside [0, n_cols): no mask bit, index reported as given
+        x = torch.randn(4, 64, device=cuda)
+        given = torch.tensor([[1, 64], [2, 3], [-5, 0], [63, 62]], dtype=torch.int16, device=cuda)
+        sm = topk(x, 2, apply_softmax=False, y_indx=given.clone())
+        bits = sm.mask.data.cpu().contiguous().numpy()
+        assert [sum(bin(int(w) & 0xffffffff).count("1") for w in row) for row in bits] == [1, 2, 1, 2]
+        assert float(sm.vals[0, 1]) == 0.0 and float(sm.vals[2, 0]) == 0.0
+        assert float(sm.vals[1, 0]) == float(x[1, 2])
+        # reduce with a row index past the end of x
+        xr = torch.ones(2, 2, 8, dtype=torch.bfloat16, device=cuda)
+        ri = torch.tensor([0, 4, 3, -1], dtype=torch.int32, device=cuda)
+        y, _ = reduce(xr, dim=1, row_indx=ri)
+        assert y[:, 0].tolist() == [1.0, 1.0]
+    _lib.sync_check(cuda)

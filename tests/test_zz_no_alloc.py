@@ -81,3 +81,28 @@ def test_static_scratch_rejects_oversized_problems(cuda, lib):
                                                  dummy.data_ptr(), None)
         assert rc == _lib.ERR_TOO_LARGE
         assert "capacity" in _lib.error_string(rc)
+
+
+def test_static_scratch_capacity_boundary_and_empty_input(cuda, lib):
+    """262144 entries x 1024 columns needs 256 * 1024 + 1024 = 263168 words, exactly the capacity: accepted and
+    equal to the workspace version. One entry more starts a 257th block of histograms: refused. An empty
+    routing table is accepted and yields an all-zero histogram."""
+    from triton_b200 import _lib
+    g = torch.Generator().manual_seed(12)
+    with torch.cuda.device(cuda):
+        indx = torch.randint(0, 1024, (262144, ), generator=g).to(torch.int32).to(cuda)
+        got = _static(lib, _lib, indx, 1024, cuda)
+        want = _regular(lib, _lib, indx, 1024, cuda)
+        for a, b in zip(got, want):
+            assert torch.equal(a, b)
+        one_more = torch.zeros(262145, dtype=torch.int32, device=cuda)
+        out = torch.empty(262145, dtype=torch.int32, device=cuda)
+        rc = lib.tb200_bitmatrix_metadata_static(one_more.data_ptr(), 0, 262145, 1024, out.data_ptr(), out.data_ptr(),
+                                                 out.data_ptr(), None)
+        assert rc == _lib.ERR_TOO_LARGE
+        col_sum = torch.full((128, ), 7, dtype=torch.int32, device=cuda)
+        rc = lib.tb200_bitmatrix_metadata_static(None, 0, 0, 128, col_sum.data_ptr(), None, None,
+                                                 ctypes.c_void_p(_lib.current_stream_ptr(cuda)))
+        assert rc == 0, _lib.error_string(rc)
+        assert int(col_sum.abs().sum()) == 0
+    _lib.sync_check(cuda)

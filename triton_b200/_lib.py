@@ -100,6 +100,7 @@ class ReduceKArgs(Structure):
     _fields_ = [
         ("x", c_void_p), ("mask", c_void_p), ("scale", c_void_p), ("y", c_void_p),
         ("n_tokens", c_int64), ("d", c_int64), ("k", c_int32), ("dtype", c_int32), ("row_indx", c_void_p),
+        ("x_rows", c_int64),
     ]
 
 
@@ -120,6 +121,35 @@ class MoeGemmArgs(Structure):
         ("n_sched", c_int32), ("w_n_major", c_int32), ("dtype", c_int32), ("swiglu", c_int32),
         ("swiglu_alpha", c_float), ("swiglu_limit", c_float), ("swiglu_has_limit", c_int32), ("moe_tile_mode", c_int32),
         ("slice_sizes", c_void_p),
+        ("y_peers", POINTER(c_void_p)), ("rows_per_peer", c_int64), ("y_world", c_int32), ("reserved", c_int32),
+    ]
+
+
+class RemapRaggedMetadataArgs(Structure):
+    _fields_ = [
+        ("slice_sizes", c_void_p), ("slice_offs", c_void_p), ("block_offs", c_void_p), ("block_schedule", c_void_p),
+        ("slice_map", c_void_p),
+        ("out_slice_sizes", c_void_p), ("out_slice_offs", c_void_p), ("out_block_offs", c_void_p),
+        ("out_block_schedule", c_void_p),
+        ("n_slices", c_int32), ("max_n_blocks", c_int32),
+    ]
+
+
+class EpDispatchArgs(Structure):
+    _fields_ = [
+        ("x", c_void_p), ("x_pitch_bytes", c_int64), ("expt_indx", c_void_p), ("dispatch_indx", c_void_p),
+        ("expt_owner", c_void_p), ("dst_peers", POINTER(c_void_p)), ("dst_pitch_bytes", c_int64), ("dst_rows", c_int64),
+        ("row_bytes", c_int64), ("n_tokens_local", c_int64), ("token_offset", c_int64),
+        ("k", c_int32), ("n_experts", c_int32), ("world", c_int32), ("indx_is_int16", c_int32),
+    ]
+
+
+class EpCombineArgs(Structure):
+    _fields_ = [
+        ("src", c_void_p), ("src_pitch_bytes", c_int64), ("expt_indx", c_void_p), ("combine_indx", c_void_p),
+        ("expt_owner", c_void_p), ("dst_peers", POINTER(c_void_p)), ("dst_pitch_bytes", c_int64), ("row_bytes", c_int64),
+        ("n_rows", c_int64), ("rows_per_rank", c_int64),
+        ("n_experts", c_int32), ("world", c_int32), ("rank", c_int32), ("indx_is_int16", c_int32),
     ]
 
 
@@ -154,6 +184,8 @@ def _declare(l: ctypes.CDLL) -> None:
     l.tb200_check.argtypes = [c_void_p]
     l.tb200_last_status_code.restype = c_int
     l.tb200_last_status_code.argtypes = []
+    l.tb200_selftest_wait.restype = c_int
+    l.tb200_selftest_wait.argtypes = [ctypes.c_uint64, c_void_p, c_void_p]
     l.tb200_gemm.restype = c_int
     l.tb200_gemm.argtypes = [POINTER(GemmArgs), c_void_p]
     l.tb200_gemm_workspace_bytes.restype = c_size_t
@@ -166,16 +198,31 @@ def _declare(l: ctypes.CDLL) -> None:
     l.tb200_attention_bwd_workspace_bytes.argtypes = [POINTER(AttentionBwdArgs)]
     for name, typ in (("tb200_topk", TopkArgs), ("tb200_bitmatrix_metadata", BitmatrixMetadataArgs),
                       ("tb200_ragged_metadata", RaggedMetadataArgs), ("tb200_reduce_k", ReduceKArgs),
-                      ("tb200_swiglu", SwigluArgs), ("tb200_moe_gemm", MoeGemmArgs)):
+                      ("tb200_swiglu", SwigluArgs), ("tb200_moe_gemm", MoeGemmArgs),
+                      ("tb200_remap_ragged_metadata", RemapRaggedMetadataArgs), ("tb200_ep_dispatch", EpDispatchArgs),
+                      ("tb200_ep_combine", EpCombineArgs)):
         fn = getattr(l, name)
         fn.restype = c_int
         fn.argtypes = [POINTER(typ), c_void_p]
+    l.tb200_symm_alloc.restype = c_int
+    l.tb200_symm_alloc.argtypes = [c_size_t, POINTER(c_void_p)]
+    l.tb200_symm_free.restype = c_int
+    l.tb200_symm_free.argtypes = [c_void_p]
+    l.tb200_symm_export.restype = c_int
+    l.tb200_symm_export.argtypes = [c_void_p, c_void_p]
+    l.tb200_symm_open.restype = c_int
+    l.tb200_symm_open.argtypes = [c_void_p, POINTER(c_void_p)]
+    l.tb200_symm_close.restype = c_int
+    l.tb200_symm_close.argtypes = [c_void_p]
+    l.tb200_symm_barrier.restype = c_int
+    l.tb200_symm_barrier.argtypes = [POINTER(c_void_p), c_int32, c_int32, ctypes.c_uint64, c_void_p]
     l.tb200_bitmatrix_metadata_static.restype = c_int
     l.tb200_bitmatrix_metadata_static.argtypes = [c_void_p, c_int32, c_int64, c_int32, c_void_p, c_void_p, c_void_p, c_void_p]
     l.tb200_gather_rows.restype = c_int
     l.tb200_gather_rows.argtypes = [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_void_p]
     l.tb200_move_rows.restype = c_int
-    l.tb200_move_rows.argtypes = [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int32, c_void_p]
+    l.tb200_move_rows.argtypes = [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int32, c_int64,
+                                  c_void_p]
     l.tb200_bitmatrix_metadata_workspace_bytes.restype = c_size_t
     l.tb200_bitmatrix_metadata_workspace_bytes.argtypes = [c_int64, c_int32]
     l.tb200_gemm_fp8_blockwise.restype = c_int
@@ -209,6 +256,11 @@ def error_string(code: int) -> str:
 def check(rc: int, what: str) -> None:
     if rc != OK:
         raise Tb200Error(rc, what)
+
+
+def pointer_array(ptrs):
+    """A ctypes array of device pointers (the HOST arrays of peer pointers some entry points take)."""
+    return (c_void_p * len(ptrs))(*[int(p) for p in ptrs])
 
 
 def current_stream_ptr(device=None) -> int:

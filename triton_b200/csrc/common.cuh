@@ -33,6 +33,8 @@ enum WaitCode : int {
   WAIT_SCALE = 6,
   WAIT_STORE = 7,
   BAD_SMEM_ALIGNMENT = 8,  // not a wait: a kernel found its shared-memory window misaligned and did nothing
+  WAIT_SELFTEST = 9,       // the wait of tb200_selftest_wait (status.cu), which nothing ever completes
+  WAIT_PEER = 10,          // cross-GPU barrier (ep_exchange.cu): a peer rank did not arrive; low bits = that rank
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -95,7 +97,10 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
 
 // Bounded wait. Returns false when the wait was abandoned (timeout here, or another
 // waiter already flagged a timeout); the caller must then leave its role loop.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
+// `limit_ns` is the wall-time bound; every kernel passes TB200_WAIT_TIMEOUT_NS, the self-test kernel
+// of status.cu passes a short run-time value so that a test can watch a wait run out.
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, int* status, int code,
+                                                uint64_t limit_ns) {
   if (mbar_try_wait(bar, parity)) return true;
   uint64_t t0 = 0;
   uint32_t spins = 0;
@@ -106,12 +111,15 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
       uint64_t now = globaltimer_ns();
       if (t0 == 0) {
         t0 = now;
-      } else if (now - t0 > TB200_WAIT_TIMEOUT_NS) {
+      } else if (now - t0 > limit_ns) {
         atomicCAS(status, 0, (code << 16) | (int)(blockIdx.x & 0xffff));
         return false;
       }
     }
   }
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
+  return mbar_wait_limit(bar, parity, status, code, TB200_WAIT_TIMEOUT_NS);
 }
 
 

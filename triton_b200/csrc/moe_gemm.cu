@@ -54,6 +54,11 @@ struct MoeParams {
   int swiglu, has_limit, out_f16;
   float alpha, limit;
   uint32_t idesc;
+  // fused combine: when y_world > 0 the row with output index i is stored to row i % rows_per_peer of
+  // y_peers[i / rows_per_peer] (buffers of other GPUs, mapped by CUDA IPC; plain st.global)
+  int y_world;
+  int rows_per_peer;
+  void* y_peers[16];
 };
 
 // 16-byte asynchronous copy global -> shared (LDGSTS); src_bytes = 0 writes zeros.
@@ -366,7 +371,8 @@ __global__ void __launch_bounds__(MOE_THREADS, 1) moe_gemm_kernel(const __grid_c
     const int n = p.n, swiglu = p.swiglu, has_limit = p.has_limit, out_f16 = p.out_f16, rows_y = p.rows_y;
     const float alpha = p.alpha, limit = p.limit;
     const long long ldy = p.ldy;
-    uint16_t* const y = reinterpret_cast<uint16_t*>(p.y);
+    uint16_t* const y_local = reinterpret_cast<uint16_t*>(p.y);
+    const int y_world = p.y_world, rows_per_peer = p.rows_per_peer;
     const uint32_t tempty_leader = PAIR ? mapa_shared(smem_u32(tempty), 0) : smem_u32(tempty);
     uint32_t tcount = 0;
     for (int unit = worker; unit < units; unit += num_workers) {
@@ -385,10 +391,16 @@ __global__ void __launch_bounds__(MOE_THREADS, 1) moe_gemm_kernel(const __grid_c
       const int sr = row0 + q * 32 + lane;  // sorted row handled by this thread
       int out_row = -1;
       float gamma = 1.f;
+      uint16_t* y = y_local;
       if (sr < row_end) {
         out_row = scatter ? __ldg(scatter + sr) : sr;
         if (out_row >= rows_y) out_row = -1;
         if (gammas) gamma = __ldg(gammas + sr);
+        if (y_world > 0 && out_row >= 0) {
+          const int to = out_row / rows_per_peer;
+          y = static_cast<uint16_t*>(p.y_peers[to]);
+          out_row -= to * rows_per_peer;
+        }
       }
       const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + acc * BN;
       const float* brow = bias ? bias + (long long)e * n : nullptr;
@@ -448,7 +460,15 @@ static int launch_moe(const MoeParams& p, int sms, cudaStream_t stream) {
 using namespace tb200;
 
 extern "C" int tb200_moe_gemm(const tb200_moe_gemm_args* a, void* stream_) {
-  if (!a || !a->x || !a->w || !a->y || !a->slice_offs || !a->block_schedule) return TB200_ERR_BAD_ARG;
+  if (!a || !a->x || !a->w || !a->slice_offs || !a->block_schedule) return TB200_ERR_BAD_ARG;
+  if (a->y_world < 0 || a->y_world > 16) return TB200_ERR_BAD_ARG;
+  if (a->y_world == 0 && !a->y) return TB200_ERR_BAD_ARG;
+  if (a->y_world > 0) {
+    if (!a->y_peers || a->rows_per_peer <= 0 || a->rows_per_peer > INT32_MAX) return TB200_ERR_BAD_ARG;
+    for (int i = 0; i < a->y_world; ++i)
+      if (!a->y_peers[i] || (reinterpret_cast<uintptr_t>(a->y_peers[i]) & 15)) return TB200_ERR_BAD_ARG;
+    if (a->rows_y > (int64_t)a->y_world * a->rows_per_peer) return TB200_ERR_BAD_ARG;
+  }
   if (a->n_experts <= 0 || a->n_experts > 65535 || a->k <= 0 || a->n <= 0 || a->n_sched < 0) return TB200_ERR_BAD_ARG;
   if (a->rows_x < 0 || a->rows_y < 0) return TB200_ERR_BAD_ARG;
   if (a->dtype != TB200_BF16 && a->dtype != TB200_F16) return TB200_ERR_UNSUPPORTED;
@@ -501,6 +521,9 @@ extern "C" int tb200_moe_gemm(const tb200_moe_gemm_args* a, void* stream_) {
   p.ldx = a->ldx;
   p.y = a->y;
   p.ldy = a->ldy;
+  p.y_world = a->y_world;
+  p.rows_per_peer = (int)a->rows_per_peer;
+  for (int i = 0; i < a->y_world; ++i) p.y_peers[i] = a->y_peers[i];
   p.status = status_ptr();
   if (!p.status) return TB200_ERR_CUDA;
   p.n_sched = a->n_sched;

@@ -75,7 +75,8 @@ __global__ void topk_kernel(const T* __restrict__ x, long long stride_x, int row
   if (use_provided_indx) {
     if (lane < k) {
       my_idx = y_indx[(long long)row * stride_y + lane];
-      my_val = to_f32<T>(xr[my_idx]);
+      if (my_idx < 0 || my_idx >= n_cols) my_idx = -1;  // outside the row: no value, no mask bit
+      my_val = my_idx >= 0 ? to_f32<T>(xr[my_idx]) : 0.f;
     }
   } else {
     for (int j = 0; j < k; ++j) {
@@ -255,6 +256,75 @@ __global__ void ragged_metadata_kernel(const int* __restrict__ slice_sizes, int 
   if (threadIdx.x == 0) offs[n_slices] = carry_s;
 }
 
+// ---------------------------------------------------------------------- ragged metadata remap
+
+// Stable compaction by a whole thread block: out[0..count) = val(i) for the i in [0, n) with keep(i), in order;
+// out[count..out_len) = -1. Returns count to every thread. `scratch` holds 33 ints of shared memory.
+template <typename KeepFn, typename ValFn>
+__device__ int block_compact(int n, KeepFn keep, ValFn val, int* __restrict__ out, int out_len, int* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  __syncthreads();
+  if (threadIdx.x == 0) scratch[32] = 0;
+  __syncthreads();
+  for (int base = 0; base < n; base += blockDim.x) {
+    const int i = base + threadIdx.x;
+    const bool k = i < n && keep(i);
+    const unsigned ballot = __ballot_sync(0xffffffffu, k);
+    if (lane == 0) scratch[warp] = __popc(ballot);
+    __syncthreads();
+    int before = scratch[32];
+    for (int w = 0; w < warp; ++w) before += scratch[w];
+    if (k) {
+      const int pos = before + __popc(ballot & ((1u << lane) - 1u));
+      if (pos < out_len) out[pos] = val(i);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int tot = scratch[32];
+      for (int w = 0; w < nwarps; ++w) tot += scratch[w];
+      scratch[32] = tot;
+    }
+    __syncthreads();
+  }
+  const int count = scratch[32];
+  for (int j = count + threadIdx.x; j < out_len; j += blockDim.x) out[j] = -1;
+  return count;
+}
+
+// Metadata of the ragged tensor that keeps slice i iff slice_map[i] != -1, renumbered to slice_map[i]
+// (remap_ragged_tensor_metadata, tensor_details/ragged_tensor.py:348-381; torch twin :388-433). Block 0 compacts
+// slice_sizes and slice_offs; block 1 + s compacts block_offs[s] and block_schedule[s], rewrites the slice id of
+// every kept schedule entry and stores the number of kept entries behind the kept block offsets.
+__global__ void remap_ragged_metadata_kernel(const int* __restrict__ slice_sizes, const int* __restrict__ slice_offs,
+                                             const int* __restrict__ block_offs, const int* __restrict__ sched,
+                                             const int* __restrict__ slice_map, int n_slices, int max_n_blocks,
+                                             int* __restrict__ o_sizes, int* __restrict__ o_offs,
+                                             int* __restrict__ o_block_offs, int* __restrict__ o_sched) {
+  __shared__ int scratch[33];
+  auto keep_slice = [&](int i) { return slice_map[i] != -1; };
+  if (blockIdx.x == 0) {
+    block_compact(n_slices, keep_slice, [&](int i) { return slice_sizes[i]; }, o_sizes, n_slices, scratch);
+    block_compact(n_slices, keep_slice, [&](int i) { return slice_offs[i]; }, o_offs, n_slices + 1, scratch);
+    return;
+  }
+  const int s = blockIdx.x - 1;
+  const int* bo = block_offs + (long long)s * (n_slices + 1);
+  const int* sc = sched + (long long)s * max_n_blocks;
+  int* obo = o_block_offs + (long long)s * (n_slices + 1);
+  int* osc = o_sched + (long long)s * max_n_blocks;
+  const int n_keep = block_compact(n_slices, keep_slice, [&](int i) { return bo[i]; }, obo, n_slices + 1, scratch);
+  const int n_sched = block_compact(
+      max_n_blocks,
+      [&](int i) {
+        const int id = sc[i] & 0xFFFF;
+        return id != 0xFFFF && id < n_slices && slice_map[id] != -1;
+      },
+      [&](int i) { return (int)((unsigned)sc[i] & 0xFFFF0000u) | slice_map[sc[i] & 0xFFFF]; }, osc, max_n_blocks,
+      scratch);
+  __syncthreads();
+  if (threadIdx.x == 0) obo[n_keep] = n_sched;
+}
+
 // ------------------------------------------------------------------------------- k-way reduce
 
 // y[t, d] = sum_j (mask[t, j] ? x[row(t, j), d] * scale[t, j] : 0), fp32 accumulation, 8 columns per
@@ -262,7 +332,7 @@ __global__ void ragged_metadata_kernel(const int* __restrict__ slice_sizes, int 
 template <typename T>
 __global__ void reduce_k_kernel(const T* __restrict__ x, const uint8_t* __restrict__ mask,
                                 const float* __restrict__ scale, const int* __restrict__ row_indx,
-                                T* __restrict__ y, long long n_tok, int k, int d) {
+                                T* __restrict__ y, long long n_tok, int k, int d, long long x_rows) {
   const int d8 = d >> 3;
   const long long total = n_tok * d8;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
@@ -276,7 +346,7 @@ __global__ void reduce_k_kernel(const T* __restrict__ x, const uint8_t* __restri
       long long row = t * k + j;
       if (row_indx) {
         row = row_indx[row];
-        if (row < 0) continue;
+        if (row < 0 || row >= x_rows) continue;
       }
       const uint4 raw = *reinterpret_cast<const uint4*>(x + (row * (long long)d + c));
       const T* e = reinterpret_cast<const T*>(&raw);
@@ -293,17 +363,17 @@ __global__ void reduce_k_kernel(const T* __restrict__ x, const uint8_t* __restri
 
 // ---------------------------------------------------------------------------------- row mover
 
-// gather: dst[i] = src[indx[i]];  scatter: dst[indx[i]] = src[i];  indx < 0 skips the row.
-// One warp per row, 16 bytes per lane per step.
+// gather: dst[i] = src[indx[i]];  scatter: dst[indx[i]] = src[i];  an index outside [0, indexed_rows)
+// skips the row. One warp per row, 16 bytes per lane per step.
 __global__ void move_rows_kernel(const uint8_t* __restrict__ src, long long src_pitch, uint8_t* __restrict__ dst,
                                  long long dst_pitch, const int* __restrict__ indx, long long n, int row_bytes,
-                                 int scatter) {
+                                 int scatter, long long indexed_rows) {
   const long long warp = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
   for (long long i = warp; i < n; i += nwarps) {
     const int j = indx[i];
-    if (j < 0) continue;
+    if (j < 0 || j >= indexed_rows) continue;
     const uint8_t* s = src + (scatter ? i : (long long)j) * src_pitch;
     uint8_t* d = dst + (scatter ? (long long)j : i) * dst_pitch;
     for (int b = lane * 16; b < row_bytes; b += 512) *reinterpret_cast<uint4*>(d + b) = *reinterpret_cast<const uint4*>(s + b);
@@ -413,10 +483,12 @@ int bitmatrix_metadata_launch(const void* indx, int is16, long long n, int n_col
   const int n_blocks = (int)((n + BM_BLOCK - 1) / BM_BLOCK);
   int* partial = scratch;
   int* col_offs = scratch + (long long)n_blocks * n_cols;
-  cudaError_t e = cudaMemsetAsync(col_sorted, 0xFF, (size_t)n * sizeof(int), stream);
-  if (e != cudaSuccess) return TB200_ERR_CUDA;
-  e = cudaMemsetAsync(row_sorted, 0xFF, (size_t)n * sizeof(int), stream);
-  if (e != cudaSuccess) return TB200_ERR_CUDA;
+  if (n > 0) {
+    cudaError_t e = cudaMemsetAsync(col_sorted, 0xFF, (size_t)n * sizeof(int), stream);
+    if (e != cudaSuccess) return TB200_ERR_CUDA;
+    e = cudaMemsetAsync(row_sorted, 0xFF, (size_t)n * sizeof(int), stream);
+    if (e != cudaSuccess) return TB200_ERR_CUDA;
+  }
   if (n_blocks > 0) bm_hist_kernel<<<n_blocks, BM_BLOCK, n_cols * sizeof(int), stream>>>(indx, is16, n, n_cols, partial);
   bm_scan_kernel<<<1, 1024, 0, stream>>>(partial, n_blocks, n_cols, col_sum, col_offs);
   if (n_blocks > 0)
@@ -454,9 +526,9 @@ extern "C" int tb200_bitmatrix_metadata(const tb200_bitmatrix_metadata_args* a, 
 //
 // `g_static_scratch` below is a device symbol. In host code that name is only a handle: taking
 // its address on the host does not give a pointer a kernel can use. The device address is fetched
-// once per device with cudaGetSymbolAddress (with that device current) and cached; this happens
-// inside the first call made on each device, so make that first call outside of any stream
-// capture. Nothing in the scratch has to start out as zero: every call overwrites the part it uses
+// once per device with cudaGetSymbolAddress (with that device current) and cached by device ordinal
+// (the cached address does not survive a cudaDeviceReset of that device); this happens inside the
+// first call made on each device, so make that first call outside of any stream capture. Nothing in the scratch has to start out as zero: every call overwrites the part it uses
 // (histograms, then prefix sums) before reading it. All calls on one GPU share the one array, so
 // two calls whose kernels may run at the same time (different streams) corrupt each other; issue
 // them on one stream or order them with events.
@@ -509,6 +581,18 @@ extern "C" int tb200_ragged_metadata(const tb200_ragged_metadata_args* a, void* 
   return cuda_err(cudaGetLastError());
 }
 
+extern "C" int tb200_remap_ragged_metadata(const tb200_remap_ragged_metadata_args* a, void* stream_) {
+  if (!a || !a->slice_sizes || !a->slice_offs || !a->block_offs || !a->slice_map || !a->out_slice_sizes ||
+      !a->out_slice_offs || !a->out_block_offs)
+    return TB200_ERR_BAD_ARG;
+  if (a->n_slices <= 0 || a->n_slices > 65535 || a->max_n_blocks < 0) return TB200_ERR_BAD_ARG;
+  if (a->max_n_blocks > 0 && (!a->block_schedule || !a->out_block_schedule)) return TB200_ERR_BAD_ARG;
+  remap_ragged_metadata_kernel<<<5, 1024, 0, static_cast<cudaStream_t>(stream_)>>>(
+      a->slice_sizes, a->slice_offs, a->block_offs, a->block_schedule, a->slice_map, a->n_slices, a->max_n_blocks,
+      a->out_slice_sizes, a->out_slice_offs, a->out_block_offs, a->out_block_schedule);
+  return cuda_err(cudaGetLastError());
+}
+
 extern "C" int tb200_reduce_k(const tb200_reduce_k_args* a, void* stream_) {
   if (!a || !a->x || !a->y) return TB200_ERR_BAD_ARG;
   if (a->n_tokens < 0 || a->k <= 0 || a->d <= 0 || (a->d % 8)) return TB200_ERR_UNSUPPORTED;
@@ -516,6 +600,8 @@ extern "C" int tb200_reduce_k(const tb200_reduce_k_args* a, void* stream_) {
   if (a->n_tokens == 0) return TB200_OK;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   const long long total = a->n_tokens * (a->d / 8);
+  if (a->x_rows < 0) return TB200_ERR_BAD_ARG;
+  const long long x_rows = a->x_rows > 0 ? a->x_rows : a->n_tokens * a->k;
   int sms = sm_count();
   if (sms <= 0) sms = 148;
   long long blocks = (total + 255) / 256;
@@ -523,19 +609,20 @@ extern "C" int tb200_reduce_k(const tb200_reduce_k_args* a, void* stream_) {
   if (a->dtype == TB200_BF16)
     reduce_k_kernel<__nv_bfloat16><<<(int)blocks, 256, 0, stream>>>(
         static_cast<const __nv_bfloat16*>(a->x), a->mask, a->scale, a->row_indx, static_cast<__nv_bfloat16*>(a->y),
-        a->n_tokens, a->k, (int)a->d);
+        a->n_tokens, a->k, (int)a->d, x_rows);
   else if (a->dtype == TB200_F16)
     reduce_k_kernel<__half><<<(int)blocks, 256, 0, stream>>>(static_cast<const __half*>(a->x), a->mask, a->scale,
                                                             a->row_indx, static_cast<__half*>(a->y), a->n_tokens, a->k,
-                                                            (int)a->d);
+                                                            (int)a->d, x_rows);
   else
     return TB200_ERR_UNSUPPORTED;
   return cuda_err(cudaGetLastError());
 }
 
 extern "C" int tb200_move_rows(const void* src, int64_t src_pitch_bytes, void* dst, int64_t dst_pitch_bytes,
-                               const int32_t* indx, int64_t n_indx, int64_t row_bytes, int32_t scatter, void* stream_) {
-  if (n_indx < 0 || row_bytes < 0) return TB200_ERR_BAD_ARG;
+                               const int32_t* indx, int64_t n_indx, int64_t row_bytes, int32_t scatter,
+                               int64_t indexed_rows, void* stream_) {
+  if (n_indx < 0 || row_bytes < 0 || indexed_rows < 0) return TB200_ERR_BAD_ARG;
   if (n_indx == 0 || row_bytes == 0) return TB200_OK;
   if (!src || !dst || !indx) return TB200_ERR_BAD_ARG;
   if ((row_bytes % 16) || (src_pitch_bytes % 16) || (dst_pitch_bytes % 16) || row_bytes > INT32_MAX)
@@ -547,7 +634,7 @@ extern "C" int tb200_move_rows(const void* src, int64_t src_pitch_bytes, void* d
   if (blocks > (long long)sms * 16) blocks = (long long)sms * 16;
   move_rows_kernel<<<(int)blocks, 256, 0, static_cast<cudaStream_t>(stream_)>>>(
       static_cast<const uint8_t*>(src), src_pitch_bytes, static_cast<uint8_t*>(dst), dst_pitch_bytes, indx, n_indx,
-      (int)row_bytes, scatter ? 1 : 0);
+      (int)row_bytes, scatter ? 1 : 0, indexed_rows);
   return cuda_err(cudaGetLastError());
 }
 

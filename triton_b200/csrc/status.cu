@@ -2,6 +2,7 @@
 #include <stdio.h>
 #include <mutex>
 
+#include "common.cuh"
 #include "host_common.h"
 
 namespace tb200 {
@@ -81,7 +82,28 @@ int encode_tmap(CUtensorMap* out, CUtensorMapDataType dtype, int rank, const voi
   return r == CUDA_SUCCESS ? TB200_OK : TB200_ERR_TMAP;
 }
 
+// One thread waits, through the same bounded wait every kernel of the library uses, on an mbarrier
+// that nobody arrives on. No copy and no MMA is in flight, so when the limit runs out the thread
+// records WAIT_SELFTEST in the status word and the block simply returns.
+__global__ void selftest_wait_kernel(int* status, unsigned long long limit_ns, int* waited_out) {
+  __shared__ __align__(8) uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    mbar_init_fence();
+    const bool done = mbar_wait_limit(&bar, 0, status, WAIT_SELFTEST, limit_ns);
+    if (waited_out) *waited_out = done ? 1 : 0;
+  }
+}
+
 }  // namespace tb200
+
+extern "C" int tb200_selftest_wait(uint64_t limit_ns, int* completed, void* stream) {
+  if (limit_ns == 0 || limit_ns > 1000000000ull) return TB200_ERR_BAD_ARG;  // at most one second
+  int* p = tb200::status_ptr();
+  if (!p) return TB200_ERR_CUDA;
+  tb200::selftest_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(p, limit_ns, completed);
+  return tb200::cuda_err(cudaGetLastError());
+}
 
 extern "C" int tb200_check(void* stream) {
   int* p = tb200::status_ptr();

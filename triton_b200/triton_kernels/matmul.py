@@ -2,9 +2,12 @@
 gammas=None, ..., fused_activation=None, ...)`` — counterpart of ``triton_kernels/matmul.py:243`` in
 the reference for the bf16/fp16 MoE subset: per-expert GEMM over expert-sorted rows with the row
 gather fused into the load and bias, SwiGLU, per-row gammas and row scatter fused into the epilogue.
-Unsupported combinations (MX / flexpoint precision, batched input, ragged K, fused communication,
-accumulator input, betas, out_alpha, custom epilogues) raise ``NotImplementedError``, as the
-reference does for combinations it cannot serve (``:288,437-447,467``)."""
+``fused_comm`` fuses the expert-parallel combine: the epilogue stores each output row straight into the
+buffer of the rank that owns the token (peer stores over NVLink; the reference's fused-comm epilogue,
+``matmul_details/_p_matmul.py:755-782``).
+Unsupported combinations (MX / flexpoint precision, batched input, ragged K, accumulator input, betas,
+out_alpha, custom epilogues) raise ``NotImplementedError``, as the reference does for combinations it
+cannot serve (``:288,437-447,467``)."""
 from __future__ import annotations
 
 import ctypes
@@ -59,6 +62,20 @@ class PrecisionConfig:
     x_scale: object = None     # one fp32 value multiplying the fp8 activations (the reference's flexpoint scale)
 
 
+@dataclass(frozen=True)
+class FusedComm:
+    """Destination of a matmul whose output rows leave this GPU (``triton_kernels/matmul.py:59-81`` in the
+    reference, where the row -> (shard, row) map is a jitted closure). Here the map is the one the
+    expert-parallel combine needs, stated declaratively: the row with output index ``i`` (``scatter_indx[r]``,
+    or ``r`` without a scatter) is stored to row ``i % rows_per_shard`` of ``out_handles[i // rows_per_shard]``.
+    ``out_handles``: one entry per shard, a CUDA tensor of this process or any object with ``data_ptr()``
+    (a peer's buffer mapped through ``SymmetricMemoryPool``); each ``[rows_per_shard, n_out]`` with row pitch
+    ``row_stride`` elements. The stores are plain: barrier (``hdl.barrier()``) before any rank reads."""
+    out_handles: tuple
+    rows_per_shard: int
+    row_stride: int | None = None
+
+
 def swiglu_activation(alpha: float = 1.0, limit: float | None = None) -> FusedActivation:
     """The fused SwiGLU spec the reference builds as
     ``FusedActivation(FnSpecs("swiglu", swiglu_fn, ("alpha", "limit"), reduction_n=2), (alpha, limit))``."""
@@ -71,8 +88,11 @@ def matmul(a, b, bias, a_ragged_metadata: RaggedTensorMetadata | None = None, b_
            epilogue: Epilogue | None = None, c_acc_in=None, _tile_mode: int = 0):
     if b_ragged_metadata is not None:
         raise NotImplementedError("matmul: ragged K (b_ragged_metadata) is not implemented")
-    if betas is not None or out_alpha is not None or fused_comm is not None or c_acc_in is not None:
-        raise NotImplementedError("matmul: betas / out_alpha / fused_comm / c_acc_in are not implemented")
+    if betas is not None or out_alpha is not None or c_acc_in is not None:
+        raise NotImplementedError("matmul: betas / out_alpha / c_acc_in are not implemented")
+    if fused_comm is not None and (c is not None or (precision_config is not None
+                                                     and precision_config.b_mx_scale is not None)):
+        raise NotImplementedError("matmul: fused_comm takes the 16-bit path and owns the output buffers")
     if epilogue is not None and epilogue.specs.name != "dflt":
         raise NotImplementedError("matmul: custom epilogues are not implemented")
     if precision_config is not None and (precision_config.a_mx_scale is not None
@@ -147,7 +167,11 @@ def matmul(a, b, bias, a_ragged_metadata: RaggedTensorMetadata | None = None, b_
     out_dtype = a.dtype
     if precision_config is not None and precision_config.out_dtype not in (None, a.dtype):
         raise NotImplementedError("matmul: out_dtype different from the input dtype")
-    if c is None:
+    peers = None
+    if fused_comm is not None:
+        peers = _lib.pointer_array([h.data_ptr() for h in fused_comm.out_handles])
+        assert rows_y <= len(fused_comm.out_handles) * fused_comm.rows_per_shard
+    elif c is None:
         # rows no sorted row maps to stay zero, as in the torch twin (matmul.py:902-906)
         c = (torch.zeros if scatter_indx is not None else torch.empty)((rows_y, n_out), dtype=out_dtype, device=dev)
     else:
@@ -162,7 +186,12 @@ def matmul(a, b, bias, a_ragged_metadata: RaggedTensorMetadata | None = None, b_
     if bias is not None:
         bs = bias.float().reshape(E, N).contiguous()
     args = _lib.MoeGemmArgs()
-    args.x, args.w, args.y = a.data_ptr(), b.data_ptr(), c.data_ptr()
+    args.x, args.w = a.data_ptr(), b.data_ptr()
+    if peers is not None:
+        args.y, args.y_peers, args.y_world = None, peers, len(fused_comm.out_handles)
+        args.rows_per_peer = fused_comm.rows_per_shard
+    else:
+        args.y = c.data_ptr()
     args.bias = bs.data_ptr() if bs is not None else None
     args.slice_offs, args.block_schedule = md.slice_offs.data_ptr(), sched.data_ptr()
     args.slice_sizes = md.slice_sizes.data_ptr()
@@ -171,7 +200,8 @@ def matmul(a, b, bias, a_ragged_metadata: RaggedTensorMetadata | None = None, b_
     args.gammas = gm.data_ptr() if gm is not None else None
     args.n_experts, args.k, args.n = E, K, N
     args.rows_x, args.rows_y = a.shape[0], rows_y
-    args.ldx, args.ldy = a.stride(0), c.stride(0)
+    args.ldx = a.stride(0)
+    args.ldy = c.stride(0) if peers is None else (fused_comm.row_stride or n_out)
     args.n_sched = sched.shape[0]
     args.w_n_major = w_n_major
     args.dtype = _DT[a.dtype]
@@ -183,7 +213,7 @@ def matmul(a, b, bias, a_ragged_metadata: RaggedTensorMetadata | None = None, b_
     with torch.cuda.device(dev):
         rc = _lib.lib().tb200_moe_gemm(ctypes.byref(args), ctypes.c_void_p(_lib.current_stream_ptr(dev)))
     _lib.check(rc, "tb200_moe_gemm")
-    return c
+    return c if peers is None else fused_comm.out_handles
 
 
 _F8 = {torch.float8_e4m3fn: _lib.E4M3, torch.float8_e5m2: _lib.E5M2}

@@ -128,38 +128,29 @@ def make_ragged_tensor_metadata(slice_sizes: torch.Tensor, n_total_rows: int) ->
 def remap_ragged_tensor_metadata(md: RaggedTensorMetadata, slice_map: torch.Tensor) -> RaggedTensorMetadata:
     """Metadata of the ragged tensor that keeps slice i iff ``slice_map[i] != -1`` (renumbered to
     ``slice_map[i]``); dropped entries are compacted to the end as -1
-    (``tensor_details/ragged_tensor.py:348-381``). Tiny index bookkeeping, done with device-side
-    tensor ops."""
+    (``tensor_details/ragged_tensor.py:348-381``). One kernel, no host synchronisation
+    (``tb200_remap_ragged_metadata``)."""
     assert slice_map.ndim == 1 and slice_map.shape[0] == md.slice_sizes.shape[0]
-    sm = slice_map.to(torch.int64)
-    dev = sm.device
-    keep = sm != -1
-    keep1 = torch.cat([keep, torch.zeros(1, dtype=torch.bool, device=dev)])
-
-    def compact(vals, cond):
-        pad = torch.full((int((~cond).sum().item()), ), -1, dtype=vals.dtype, device=dev)
-        return torch.cat([vals[cond], pad])
-
-    ss = compact(md.slice_sizes, keep)
-    so = compact(md.slice_offs, keep1)
-    bo, bs = [], []
-    for i in range(md.block_offs_data.shape[0]):
-        o = compact(md.block_offs_data[i], keep1)
-        sch = md.block_schedule_data[i]
-        sid = (sch & 0xFFFF).to(torch.int64)
-        valid = sid != 0xFFFF
-        cond = torch.zeros_like(valid)
-        cond[valid] = sm[sid[valid]] != -1
-        s2 = compact(sch, cond)
-        sid2 = (s2 & 0xFFFF).to(torch.int64)
-        v2 = sid2 != 0xFFFF
-        out = s2.clone()
-        out[v2] = ((s2[v2].to(torch.int64) & 0xFFFF0000) | sm[sid2[v2]]).to(torch.int32)
-        first = int((o == -1).nonzero()[0].item())
-        o[first] = int((out != -1).sum().item())
-        bo.append(o)
-        bs.append(out)
-    return RaggedTensorMetadata(ss, so, torch.stack(bo), torch.stack(bs))
+    dev = md.slice_sizes.device
+    if not md.slice_sizes.is_cuda:
+        raise RuntimeError("triton_b200 remap_ragged_tensor_metadata needs CUDA tensors (there is no CPU path)")
+    sm = slice_map.to(torch.int32).contiguous()
+    n_slices = md.slice_sizes.shape[0]
+    bo, bs = md.block_offs_data.contiguous(), md.block_schedule_data.contiguous()
+    ss, so = md.slice_sizes.contiguous(), md.slice_offs.contiguous()
+    o_ss, o_so = torch.empty_like(ss), torch.empty_like(so)
+    o_bo, o_bs = torch.empty_like(bo), torch.empty_like(bs)
+    args = _lib.RemapRaggedMetadataArgs()
+    args.slice_sizes, args.slice_offs, args.block_offs, args.block_schedule = (ss.data_ptr(), so.data_ptr(), bo.data_ptr(),
+                                                                               bs.data_ptr())
+    args.slice_map = sm.data_ptr()
+    args.out_slice_sizes, args.out_slice_offs = o_ss.data_ptr(), o_so.data_ptr()
+    args.out_block_offs, args.out_block_schedule = o_bo.data_ptr(), o_bs.data_ptr()
+    args.n_slices, args.max_n_blocks = n_slices, bs.shape[1]
+    with torch.cuda.device(dev):
+        rc = _lib.lib().tb200_remap_ragged_metadata(ctypes.byref(args), ctypes.c_void_p(_lib.current_stream_ptr(dev)))
+    _lib.check(rc, "tb200_remap_ragged_metadata")
+    return RaggedTensorMetadata(o_ss, o_so, o_bo, o_bs)
 
 
 @dataclass

@@ -2,8 +2,10 @@
 symm_mem_pool=None) -> SparseMatrix`` — counterpart of ``triton_kernels/topk.py:106`` in the
 reference: per-row top-k with ties to the smaller column, values in descending order, optional
 softmax over the k selected values, int16 indices and the transposed-in-memory bitmatrix.
-``all_gather`` (write the result into every rank's symmetric buffer) is the expert-parallel path; it
-is served by ``distributed.all_gather_topk`` and raises here."""
+``all_gather=True`` with a ``symm_mem_pool`` (a ``SymmetricMemoryPool`` or ``EpGroup`` of
+``triton_kernels.distributed``) is the expert-parallel path (``topk.py:41-69`` in the reference): every rank
+gets the values and indices of all ranks' rows, rank-major; the exchange is one NCCL all-gather and the
+bitmatrix words of the gathered result are not materialised (its metadata is built from the indices)."""
 from __future__ import annotations
 
 import ctypes
@@ -21,7 +23,7 @@ def topk_forward(x, k, apply_softmax=True, dim=1, y_indx=None, n_rows=None, all_
     assert x.ndim == 2 and dim == 1
     assert x.shape[-1] < 32768
     if all_gather:
-        raise NotImplementedError("all_gather=True: use triton_b200.triton_kernels.distributed.all_gather_topk")
+        raise NotImplementedError("topk_forward is the local kernel; call topk(..., all_gather=True, symm_mem_pool=...)")
     if not x.is_cuda:
         raise RuntimeError("triton_b200 topk needs CUDA tensors (there is no CPU path)")
     assert x.dtype in _DT and x.stride(1) == 1
@@ -55,5 +57,11 @@ def topk_forward(x, k, apply_softmax=True, dim=1, y_indx=None, n_rows=None, all_
 
 def topk(x: torch.Tensor, k: int, apply_softmax: bool = True, dim: int = 1, y_indx: Optional[torch.Tensor] = None,
          n_rows: Optional[int] = None, all_gather: bool = False, symm_mem_pool=None) -> SparseMatrix:
+    if all_gather:
+        if symm_mem_pool is None or y_indx is not None or n_rows is not None:
+            raise NotImplementedError("topk(all_gather=True) needs symm_mem_pool and takes neither y_indx nor n_rows")
+        from .distributed import all_gather_topk
+        assert dim == 1
+        return all_gather_topk(x, k, symm_mem_pool, apply_softmax)
     y_vals, y_indx, bitmatrix = topk_forward(x, k, apply_softmax, dim, y_indx, n_rows, all_gather, symm_mem_pool)
     return SparseMatrix(vals=y_vals, indx=y_indx, mask=bitmatrix)
