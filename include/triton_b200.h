@@ -112,6 +112,10 @@ typedef struct {
 int tb200_gemm(const tb200_gemm_args* args, void* stream);
 /* Bytes of workspace tb200_gemm needs for these args (0 when no split-K is used). */
 size_t tb200_gemm_workspace_bytes(const tb200_gemm_args* args);
+/* The tiling tb200_gemm takes for these args (no launch): out6 = {tile rows, tile columns, CTAs per tile (1 or 2),
+ * split_k, ring stages, K elements per stage}. Stands behind get_heuristic_config,
+ * third_party/tlx/tutorials/blackwell_gemm_ws.py:25-335 (which returns the reference kernel's config dict). */
+int tb200_gemm_plan(const tb200_gemm_args* args, int32_t* out6);
 
 /* ---------------------------------------------------------------- MXFP8 GEMM ------- */
 

@@ -55,3 +55,15 @@ def test_product_does_not_import_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".h")):
                 text = open(os.path.join(dirpath, f)).read()
                 assert not re.search(r"^\s*(from|import)\s+oracle\b", text, flags=re.M), f
+
+
+def test_heuristic_config_reports_the_plan_the_library_takes(lib):
+    """get_heuristic_config reads the tiling from the C side (no GPU needed): the headline shape takes the
+    256 x 512 CTA-pair tile, the skinny shape 128-wide tiles with K split, a tiny shape one CTA per tile."""
+    from triton_b200.tutorials.blackwell_gemm_ws import get_heuristic_config
+    big = get_heuristic_config(8192, 8192, 8192)
+    assert (big["BLOCK_SIZE_M"], big["BLOCK_SIZE_N"], big["NUM_CTAS"], big["SPLIT_K"]) == (256, 512, 2, 1)
+    skinny = get_heuristic_config(128, 8192, 8192)
+    assert skinny["BLOCK_SIZE_M"] == 128 and skinny["NUM_CTAS"] == 1 and skinny["SPLIT_K"] >= 2
+    small = get_heuristic_config(128, 128, 128)
+    assert small["NUM_CTAS"] == 1 and small["SPLIT_K"] == 1

@@ -188,6 +188,8 @@ def _declare(l: ctypes.CDLL) -> None:
     l.tb200_selftest_wait.argtypes = [ctypes.c_uint64, c_void_p, c_void_p]
     l.tb200_gemm.restype = c_int
     l.tb200_gemm.argtypes = [POINTER(GemmArgs), c_void_p]
+    l.tb200_gemm_plan.restype = c_int
+    l.tb200_gemm_plan.argtypes = [POINTER(GemmArgs), POINTER(c_int32)]
     l.tb200_gemm_workspace_bytes.restype = c_size_t
     l.tb200_gemm_workspace_bytes.argtypes = [POINTER(GemmArgs)]
     l.tb200_attention_fwd.restype = c_int

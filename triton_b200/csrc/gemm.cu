@@ -779,6 +779,23 @@ extern "C" size_t tb200_gemm_workspace_bytes(const tb200_gemm_args* a) {
   return (size_t)plan.split_k * (size_t)a->m * (size_t)a->n * sizeof(float);
 }
 
+extern "C" int tb200_gemm_plan(const tb200_gemm_args* a, int32_t* out6) {
+  if (!out6) return TB200_ERR_BAD_ARG;
+  int rc = validate(a);
+  if (rc != TB200_OK) return rc;
+  GemmPlan plan;
+  int sms = sm_count();
+  if (sms <= 0) sms = 148;
+  if (!plan_gemm(a, sms, &plan)) return TB200_ERR_UNSUPPORTED;
+  out6[0] = plan.pair ? 256 : BM;                       // rows of C per tile (per CTA pair when num_ctas = 2)
+  out6[1] = plan.bn;                                    // columns of C per tile
+  out6[2] = plan.pair ? 2 : 1;                          // CTAs that share a tile
+  out6[3] = plan.split_k;
+  out6[4] = plan.pair == 2 ? 4 : plan.pair == 1 ? 7 : plan.bn == 256 ? 4 : plan.bn == 128 ? 6 : 8;  // ring depth
+  out6[5] = STAGE_K_BYTES / elem_bytes(a->in_dtype);    // K elements per ring stage
+  return TB200_OK;
+}
+
 extern "C" int tb200_gemm(const tb200_gemm_args* a, void* stream_) {
   int rc = validate(a);
   if (rc != TB200_OK) return rc;

@@ -29,18 +29,20 @@ def _operand(t: torch.Tensor):
     return t, True, t.stride(0)
 
 
-def get_heuristic_config(M, N, K, num_sms=148):
-    """Tile / split-K choice for a shape, in the reference's vocabulary
-    (``blackwell_gemm_ws.py:25-335``). Informational: the C library makes the same choice."""
+def get_heuristic_config(M, N, K, num_sms=148, dtype=torch.bfloat16, b_k_major=True):
+    """The tiling the library takes for a shape, in the reference's vocabulary
+    (``blackwell_gemm_ws.py:25-335``), read from the C side (``tb200_gemm_plan``): ``BLOCK_SIZE_M`` x
+    ``BLOCK_SIZE_N`` is the tile one CTA (``NUM_CTAS`` = 1) or one CTA pair (2) computes."""
     args = _lib.GemmArgs()
     args.a = args.b = args.c = 16
     args.m, args.n, args.k = M, N, K
-    args.lda, args.ldb, args.ldc = K, K, N
-    args.in_dtype = args.out_dtype = _lib.BF16
-    args.a_k_major = args.b_k_major = 1
-    ws = _lib.lib().tb200_gemm_workspace_bytes(ctypes.byref(args))
-    split = ws // (4 * M * N) if ws else 1
-    return {"BLOCK_SIZE_M": 128, "BLOCK_SIZE_K": 64, "SPLIT_K": int(split), "NUM_CTAS": 1}
+    args.lda, args.ldb, args.ldc = K, (K if b_k_major else N), N
+    args.in_dtype = args.out_dtype = _DT[dtype]
+    args.a_k_major, args.b_k_major = 1, int(b_k_major)
+    out = (ctypes.c_int32 * 6)()
+    _lib.check(_lib.lib().tb200_gemm_plan(ctypes.byref(args), out), "tb200_gemm_plan")
+    return {"BLOCK_SIZE_M": out[0], "BLOCK_SIZE_N": out[1], "BLOCK_SIZE_K": out[5], "NUM_CTAS": out[2],
+            "SPLIT_K": out[3], "NUM_SMEM_BUFFERS": out[4]}
 
 
 def matmul(a: torch.Tensor, b: torch.Tensor, config=None) -> torch.Tensor:
