@@ -392,7 +392,7 @@ def build_workload(name: str, rank: int, world: int, dev):
         return Workload(lambda: upcast_mxfp4_weight(wv, ws, bf), 0.0, by,
                         f"MXFP4 -> bf16 weight upcast: E={E} matrices [{Kd},{Nd}] (W1 of the MoE layer), random codes, seed 4",
                         "mxfp4_upcast_kernel", "hbm", [wv.data])
-    if name in ("moe_ep", "moe_ep_nccl", "moe_ep_unfused"):
+    if name in ("moe_ep", "moe_ep_eager", "moe_ep_nccl", "moe_ep_unfused"):
         return build_moe_ep(name, rank, world, dev)
     raise SystemExit(f"unknown workload {name}")
 
@@ -400,17 +400,18 @@ def build_workload(name: str, rank: int, world: int, dev):
 def build_moe_ep(name, rank, world, dev):
     """The 16384-token MoE layer (config 5) with tokens and experts sharded over the ranks: strong scaling. The
     exchange (top-k all-gather, dispatch, combine) is inside every step. `moe_ep`: peer stores with the combine
-    fused into GEMM-2's epilogue; `moe_ep_unfused`: peer stores by separate kernels; `moe_ep_nccl`: NCCL
+    fused into GEMM-2's epilogue, the whole layer replayed as one CUDA graph; `moe_ep_eager`: the same, launched
+    call by call; `moe_ep_unfused`: peer stores by separate dispatch / combine kernels; `moe_ep_nccl`: NCCL
     all-to-all. Before anything is timed a small layer is run on the live ranks and each rank's slice is compared
     with the CPU oracle."""
     import torch
     import torch.distributed as dist
-    from triton_b200.triton_kernels.distributed import (EpGroup, Mesh, SymmetricMemoryPool, make_expt_assignment,
-                                                        make_expt_dict_uniform, moe_layer_ep)
+    from triton_b200.triton_kernels.distributed import (EpGroup, EpLayerGraph, Mesh, SymmetricMemoryPool,
+                                                        make_expt_assignment, make_expt_dict_uniform, moe_layer_ep)
     bf = torch.bfloat16
     T, D, F, E, k = 16384, 4096, 1536, 128, 4
     tl, per = T // world, E // world
-    fuse = name == "moe_ep"
+    fuse = name in ("moe_ep", "moe_ep_eager")
     ea = make_expt_assignment(world, E, make_expt_dict_uniform(world, E), dev)
     if name == "moe_ep_nccl":
         ep = EpGroup()
@@ -446,10 +447,17 @@ def build_moe_ep(name, rank, world, dev):
     w2 = _dev_randn((per, F, D), dev, 7 + 1000 * rank, 0.02, bf)
     R = T * k
     fl = (2.0 * R * D * 2 * F + 2.0 * R * F * D) / world  # per rank; the line reports world * this
-    how = {"moe_ep": "peer stores over NVLink, combine fused into GEMM-2's epilogue",
+    how = {"moe_ep": "peer stores over NVLink, combine fused into GEMM-2's epilogue, one CUDA graph per layer call",
+           "moe_ep_eager": "peer stores over NVLink, combine fused into GEMM-2's epilogue, launched call by call",
            "moe_ep_unfused": "peer stores over NVLink by dispatch / combine kernels",
            "moe_ep_nccl": "NCCL all_to_all_single dispatch / combine"}[name]
-    return Workload(lambda: moe_layer_ep(x, logits, w1, w2, k, ea, ep, fuse_combine=fuse), fl, 0.0,
+    step = lambda: moe_layer_ep(x, logits, w1, w2, k, ea, ep, fuse_combine=fuse)  # noqa: E731
+    if name == "moe_ep":
+        eager = step().clone()
+        graph = EpLayerGraph(x, logits, w1, w2, k, ea, ep, fuse_combine=True)
+        parity["graph_equals_eager"] = bool(torch.equal(graph.replay(), eager))
+        step = graph.replay
+    return Workload(step, fl, 0.0,
                     f"expert-parallel MoE layer: {T} tokens total ({tl}/GPU), E={E} ({per}/GPU), top-{k}, d_model {D}; "
                     f"{how}; exchange inside the timed region; strong scaling", "moe_gemm_kernel", "tensor",
                     [x, logits], launches=12, cpu=cpu_moe, sharded=True, footprint=(w1.numel() + w2.numel()) * 2,

@@ -411,6 +411,14 @@ int tb200_symm_close(void* peer_ptr);
 int tb200_symm_barrier(void* const* signal_peers, int32_t rank, int32_t world, uint64_t limit_ns, void* stream);
 
 /*
+ * Stores `bytes` (a multiple of 16, 16-byte aligned) of local memory to dst_peers[r] for every rank r: one rank's
+ * part of an all-gather through symmetric buffers (dst_peers[r] = this rank's slot inside rank r's buffer). The
+ * expert-parallel layer publishes its local top-k values and indices this way (topk(..., all_gather=True) in
+ * the reference, topk.py:41-69, writes them into symmetric memory too). Follow with tb200_symm_barrier.
+ */
+int tb200_symm_put(const void* src, size_t bytes, void* const* dst_peers, int32_t world, void* stream);
+
+/*
  * DP -> EP dispatch: for every local token t and slot j with expert e = expt_indx[token_offset + t, j] >= 0,
  * copies x[t, :] to row dispatch_indx[(token_offset + t) * k + j] of the buffer of rank expt_owner[e].
  * Stands behind _convert_dp_to_ep, distributed.py:136-173 (host convert_dp_to_ep :176-211).
@@ -535,7 +543,8 @@ typedef struct {
   void* const* y_peers;
   int64_t rows_per_peer;
   int32_t y_world;
-  int32_t reserved;
+  int32_t gammas_by_out_row; /* 1: the scale of sorted row r is gammas[i] with i its output index (scatter_indx[r], or r)
+                                instead of gammas[r]: lets the top-k values [tokens, k] serve as gate weights as they are */
 } tb200_moe_gemm_args;
 int tb200_moe_gemm(const tb200_moe_gemm_args* args, void* stream);
 

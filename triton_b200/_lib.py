@@ -121,7 +121,7 @@ class MoeGemmArgs(Structure):
         ("n_sched", c_int32), ("w_n_major", c_int32), ("dtype", c_int32), ("swiglu", c_int32),
         ("swiglu_alpha", c_float), ("swiglu_limit", c_float), ("swiglu_has_limit", c_int32), ("moe_tile_mode", c_int32),
         ("slice_sizes", c_void_p),
-        ("y_peers", POINTER(c_void_p)), ("rows_per_peer", c_int64), ("y_world", c_int32), ("reserved", c_int32),
+        ("y_peers", POINTER(c_void_p)), ("rows_per_peer", c_int64), ("y_world", c_int32), ("gammas_by_out_row", c_int32),
     ]
 
 
@@ -216,6 +216,8 @@ def _declare(l: ctypes.CDLL) -> None:
     l.tb200_symm_open.argtypes = [c_void_p, POINTER(c_void_p)]
     l.tb200_symm_close.restype = c_int
     l.tb200_symm_close.argtypes = [c_void_p]
+    l.tb200_symm_put.restype = c_int
+    l.tb200_symm_put.argtypes = [c_void_p, c_size_t, POINTER(c_void_p), c_int32, c_void_p]
     l.tb200_symm_barrier.restype = c_int
     l.tb200_symm_barrier.argtypes = [POINTER(c_void_p), c_int32, c_int32, ctypes.c_uint64, c_void_p]
     l.tb200_bitmatrix_metadata_static.restype = c_int

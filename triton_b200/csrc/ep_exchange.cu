@@ -135,6 +135,16 @@ __global__ void ep_combine_kernel(const uint8_t* __restrict__ src, long long src
   }
 }
 
+// ---------------------------------------------------------------------------------- put
+// The same `bytes` of local memory stored to one destination per rank (a rank's block of an all-gather:
+// destination r is this rank's slot inside rank r's buffer). 16 bytes per thread per step.
+__global__ void symm_put_kernel(const uint4* __restrict__ src, long long n16, PeerPtrs dst, int world) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n16; i += (long long)gridDim.x * blockDim.x) {
+    const uint4 v = __ldg(src + i);
+    for (int r = 0; r < world; ++r) static_cast<uint4*>(dst.p[r])[i] = v;
+  }
+}
+
 static bool fill_peers(PeerPtrs* out, void* const* peers, int world) {
   if (!peers || world < 1 || world > EP_MAX_RANKS) return false;
   memset(out, 0, sizeof(*out));
@@ -197,6 +207,21 @@ extern "C" int tb200_symm_barrier(void* const* signal_peers, int32_t rank, int32
   int* status = status_ptr();
   if (!status) return TB200_ERR_CUDA;
   symm_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(sig, rank, world, limit_ns, status);
+  return cuda_err(cudaGetLastError());
+}
+
+extern "C" int tb200_symm_put(const void* src, size_t bytes, void* const* dst_peers, int32_t world, void* stream) {
+  PeerPtrs dst;
+  if (!fill_peers(&dst, dst_peers, world) || !src || (bytes % 16) || (reinterpret_cast<uintptr_t>(src) & 15))
+    return TB200_ERR_BAD_ARG;
+  if (bytes == 0) return TB200_OK;
+  const long long n16 = (long long)(bytes / 16);
+  int sms = sm_count();
+  if (sms <= 0) sms = 148;
+  long long blocks = (n16 + 255) / 256;
+  if (blocks > sms * 4) blocks = sms * 4;
+  symm_put_kernel<<<(int)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint4*>(src), n16, dst,
+                                                                           world);
   return cuda_err(cudaGetLastError());
 }
 

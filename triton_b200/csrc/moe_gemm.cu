@@ -58,6 +58,7 @@ struct MoeParams {
   // y_peers[i / rows_per_peer] (buffers of other GPUs, mapped by CUDA IPC; plain st.global)
   int y_world;
   int rows_per_peer;
+  int gammas_by_out_row;
   void* y_peers[16];
 };
 
@@ -372,7 +373,7 @@ __global__ void __launch_bounds__(MOE_THREADS, 1) moe_gemm_kernel(const __grid_c
     const float alpha = p.alpha, limit = p.limit;
     const long long ldy = p.ldy;
     uint16_t* const y_local = reinterpret_cast<uint16_t*>(p.y);
-    const int y_world = p.y_world, rows_per_peer = p.rows_per_peer;
+    const int y_world = p.y_world, rows_per_peer = p.rows_per_peer, gammas_by_out_row = p.gammas_by_out_row;
     const uint32_t tempty_leader = PAIR ? mapa_shared(smem_u32(tempty), 0) : smem_u32(tempty);
     uint32_t tcount = 0;
     for (int unit = worker; unit < units; unit += num_workers) {
@@ -395,7 +396,7 @@ __global__ void __launch_bounds__(MOE_THREADS, 1) moe_gemm_kernel(const __grid_c
       if (sr < row_end) {
         out_row = scatter ? __ldg(scatter + sr) : sr;
         if (out_row >= rows_y) out_row = -1;
-        if (gammas) gamma = __ldg(gammas + sr);
+        if (gammas) gamma = gammas_by_out_row ? (out_row >= 0 ? __ldg(gammas + out_row) : 0.f) : __ldg(gammas + sr);
         if (y_world > 0 && out_row >= 0) {
           const int to = out_row / rows_per_peer;
           y = static_cast<uint16_t*>(p.y_peers[to]);
@@ -521,6 +522,7 @@ extern "C" int tb200_moe_gemm(const tb200_moe_gemm_args* a, void* stream_) {
   p.ldx = a->ldx;
   p.y = a->y;
   p.ldy = a->ldy;
+  p.gammas_by_out_row = a->gammas_by_out_row ? 1 : 0;
   p.y_world = a->y_world;
   p.rows_per_peer = (int)a->rows_per_peer;
   for (int i = 0; i < a->y_world; ++i) p.y_peers[i] = a->y_peers[i];

@@ -238,12 +238,15 @@ class SymmetricMemoryPool:
     def initialize_matmul(self, n_tokens_global: int, d_input: int, d_model: int, n_expts_act: int, n_expts_tot: int,
                           dtype: torch.dtype, device) -> None:
         """Reserves the regions one MoE layer needs (``mesh.py:138-166``): the dispatch buffer
-        ``[n_tokens_global * k, d_input]`` and the combine buffer ``[n_tokens_local * k, d_model]``."""
+        ``[n_tokens_global * k, d_input]``, the combine buffer ``[n_tokens_local * k, d_model]`` and the gathered
+        top-k values and indices."""
         if self._is_initialized:
             return
         esz = torch.empty((), dtype=dtype).element_size()
         n_local = n_tokens_global // self.mesh.world_size
         off = self._reserve_region("signal", self.SIGNAL_BYTES, 256, 0)
+        # gathered top-k: values (4 bytes at most) then int16 indices, [n_tokens_global, k] each
+        off = self._reserve_region("topk", n_tokens_global * n_expts_act * 6, 256, off)
         off = self._reserve_region("ep_to_dp", n_local * n_expts_act * d_model * esz, 256, off)
         off = self._reserve_region("dp_to_ep", n_tokens_global * n_expts_act * d_input * esz, 256, off)
         self._initialize(device)
@@ -366,12 +369,27 @@ def _transport(pool):
 def all_gather_topk(x_local: torch.Tensor, k: int, ep, apply_softmax: bool = True) -> SparseMatrix:
     """``topk(..., all_gather=True)`` of the reference (``topk.py:41-69``): local top-k, then every rank gets
     the values / indices of all ranks' tokens (rank-major), and the global routing metadata is built from them.
-    One NCCL all-gather of the packed (values | indices) bytes."""
+    With a ``SymmetricMemoryPool`` each rank stores its block into every rank's ``topk`` region (peer stores,
+    then a barrier), as the reference does; with an ``EpGroup`` it is one NCCL all-gather of the packed bytes."""
     from .topk import topk_forward
     vals, indx, _ = topk_forward(x_local, k, apply_softmax)
-    _, world, group = _transport(ep)
-    if world > 1:
-        n, vb = vals.shape[0], vals.element_size()
+    rank, world, group = _transport(ep)
+    n, vb = vals.shape[0], vals.element_size()
+    if world == 1:
+        g_vals, g_indx = vals, indx
+    elif isinstance(ep, SymmetricMemoryPool) and "topk" in ep.regions and (n * k * 2) % 16 == 0:
+        dev = vals.device
+        all_vals = ep.make_empty((world * n, k), vals.dtype, region="topk")
+        all_indx = ep.make_empty((world * n, k), torch.int16, region="topk", region_offset=world * n * k * 4)
+        l = _lib.lib()
+        with torch.cuda.device(dev):
+            stream = ctypes.c_void_p(_lib.current_stream_ptr(dev))
+            for src, bufs, esz in ((vals, all_vals, vb), (indx, all_indx, 2)):
+                slots = _lib.pointer_array([b.data_ptr() + rank * n * k * esz for b in bufs])
+                _lib.check(l.tb200_symm_put(src.data_ptr(), n * k * esz, slots, world, stream), "tb200_symm_put")
+        ep.hdl.barrier(channel=1)
+        g_vals, g_indx = all_vals[rank], all_indx[rank]
+    else:
         packed = torch.empty((n, k * (vb + 2)), dtype=torch.uint8, device=vals.device)
         packed[:, :k * vb] = vals.contiguous().view(torch.uint8).view(n, k * vb)
         packed[:, k * vb:] = indx.contiguous().view(torch.uint8).view(n, k * 2)
@@ -379,8 +397,6 @@ def all_gather_topk(x_local: torch.Tensor, k: int, ep, apply_softmax: bool = Tru
         dist.all_gather_into_tensor(gathered, packed, group=group)
         g_vals = gathered[:, :k * vb].contiguous().view(vals.dtype).view(world * n, k)
         g_indx = gathered[:, k * vb:].contiguous().view(torch.int16).view(world * n, k)
-    else:
-        g_vals, g_indx = vals, indx
     return SparseMatrix(vals=g_vals, indx=g_indx, mask=Bitmatrix(None, shape=[g_indx.shape[0], x_local.shape[1]]))
 
 
@@ -496,19 +512,50 @@ def moe_layer_ep(x_local, logits_local, w1_local, w2_local, k, expt_assignment: 
     rg_local = remap_ragged_tensor_metadata(rg, expt_assignment.expt_map[rank])
     y = convert_dp_to_ep(x_local, expt_assignment, sm.indx, mm.row_sorted_indx, ep)
     h = matmul(y, w1_local, None, rg_local, fused_activation=swiglu_activation(alpha, limit))
-    gam = None
-    if gate_weighted:
-        gam = sm.vals.float().reshape(-1)[mm.col_sorted_indx.long().clamp(min=0)]
     n_local = x_local.shape[0]
     if isinstance(ep, SymmetricMemoryPool) and fuse_combine:
         d_out = w2_local.shape[-1]
         peer_bufs = ep.make_empty((n_local * k, d_out), h.dtype, region="ep_to_dp")
-        matmul(h, w2_local, None, rg_local, gammas=gam, scatter_indx=mm.col_sorted_indx,
-               fused_comm=FusedComm(peer_bufs, n_local * k, d_out))
+        # the gate weight of an output row is the top-k value of its (token, slot): looked up by the epilogue
+        matmul(h, w2_local, None, rg_local, gammas=sm.vals if gate_weighted else None, scatter_indx=mm.col_sorted_indx,
+               fused_comm=FusedComm(peer_bufs, n_local * k, d_out), _gammas_by_out_row=True)
         ep.hdl.barrier(channel=0)
         y_dp = peer_bufs[rank]
     else:
+        gam = None
+        if gate_weighted:
+            gam = sm.vals.float().reshape(-1)[mm.col_sorted_indx.long().clamp(min=0)]
         o = matmul(h, w2_local, None, rg_local, gammas=gam)
         y_dp = convert_ep_to_dp(o, expt_assignment, sm.indx, mm.col_sorted_indx, ep)
     z, _ = reduce(y_dp.view(n_local, k, -1), dim=1)
     return z
+
+
+class EpLayerGraph:
+    """One expert-parallel layer call captured into a CUDA graph (the reference tests its EP layer under graph
+    replay too, ``tests/test_distributed.py:248-340``). At 8 GPUs a rank's share of the layer is a few hundred
+    microseconds of GPU work issued by some thirty launches; replaying a graph takes the host out of the
+    critical path. Needs the ``SymmetricMemoryPool`` transport (nothing in it touches the host; the barrier
+    keeps its epoch on the device, so a replay is a valid next barrier). Every rank must build and replay it the
+    same number of times. ``x_local`` / ``logits_local`` are the static inputs: copy new data into them, then
+    ``replay()``; the result tensor is reused from replay to replay."""
+
+    def __init__(self, x_local, logits_local, w1_local, w2_local, k, expt_assignment, pool: SymmetricMemoryPool, **kw):
+        assert isinstance(pool, SymmetricMemoryPool), "graph capture needs the peer-store transport"
+        self.x, self.logits = x_local, logits_local
+        args = (x_local, logits_local, w1_local, w2_local, k, expt_assignment, pool)
+        cur = torch.cuda.current_stream(x_local.device)
+        side = torch.cuda.Stream(x_local.device)
+        side.wait_stream(cur)
+        with torch.cuda.stream(side):
+            for _ in range(2):  # first calls load kernels and cache per-device state: keep them out of the capture
+                moe_layer_ep(*args, **kw)
+        cur.wait_stream(side)
+        torch.cuda.synchronize(x_local.device)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph, capture_error_mode="thread_local"):
+            self.out = moe_layer_ep(*args, **kw)
+
+    def replay(self):
+        self.graph.replay()
+        return self.out

@@ -85,7 +85,7 @@ def swiglu_activation(alpha: float = 1.0, limit: float | None = None) -> FusedAc
 def matmul(a, b, bias, a_ragged_metadata: RaggedTensorMetadata | None = None, b_ragged_metadata=None,
            gather_indx=None, scatter_indx=None, precision_config: PrecisionConfig | None = None, betas=None,
            gammas=None, out_alpha=None, c=None, fused_comm=None, fused_activation: FusedActivation | None = None,
-           epilogue: Epilogue | None = None, c_acc_in=None, _tile_mode: int = 0):
+           epilogue: Epilogue | None = None, c_acc_in=None, _tile_mode: int = 0, _gammas_by_out_row: bool = False):
     if b_ragged_metadata is not None:
         raise NotImplementedError("matmul: ragged K (b_ragged_metadata) is not implemented")
     if betas is not None or out_alpha is not None or c_acc_in is not None:
@@ -210,6 +210,8 @@ def matmul(a, b, bias, a_ragged_metadata: RaggedTensorMetadata | None = None, b_
     args.swiglu_limit = float(limit) if limit is not None else 0.0
     args.swiglu_has_limit = 1 if limit is not None else 0
     args.moe_tile_mode = int(_tile_mode)  # extension: 0 choose, 1 one CTA per block, 2 CTA pair per two blocks
+    # extension: gammas holds one value per OUTPUT row (e.g. the top-k values in (token, slot) order) instead of per sorted row
+    args.gammas_by_out_row = 1 if _gammas_by_out_row else 0
     with torch.cuda.device(dev):
         rc = _lib.lib().tb200_moe_gemm(ctypes.byref(args), ctypes.c_void_p(_lib.current_stream_ptr(dev)))
     _lib.check(rc, "tb200_moe_gemm")
