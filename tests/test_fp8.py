@@ -154,3 +154,17 @@ def test_mxfp8_asserts(cuda):
         matmul(a[:, :64].contiguous(), a[:, :64].contiguous(), s, s)
     with pytest.raises(AssertionError):
         matmul(a, a, s[:100], s)
+
+
+def test_rowwise_scaled_skinny_takes_the_in_cluster_split(cuda):
+    """M = 64 against N = 1024, K = 4096 (e4m3, row-wise scales): one row of tiles, so K is split inside a cluster
+    and the scales are applied by the reducing CTAs."""
+    from triton_b200.tutorials.blackwell_scaled_mm_ws import blackwell_scaled_mm_ws
+    g = torch.Generator().manual_seed(31)
+    M, N, K = 64, 1024, 4096
+    a = (torch.randn(M, K, generator=g) * 0.1).to(torch.float8_e4m3fn)
+    b = (torch.randn(N, K, generator=g) * 0.1).to(torch.float8_e4m3fn)
+    sa, sb = torch.rand(M, generator=g) + 0.5, torch.rand(N, generator=g) + 0.5
+    out = blackwell_scaled_mm_ws(a.to(cuda), b.to(cuda), sa.to(cuda), sb.to(cuda), scale_mode="rowwise")
+    ref = o_gemm.scaled_mm_rowwise_ref(a, b, sa, sb)
+    torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=1e-2, atol=2e-3)

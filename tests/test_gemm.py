@@ -170,3 +170,44 @@ def test_bad_inputs_raise(cuda):
         mm(a, torch.zeros(8, 16, dtype=torch.bfloat16, device=cuda))
     with pytest.raises(RuntimeError):
         mm(torch.zeros(8, 16, dtype=torch.bfloat16), torch.zeros(16, 8, dtype=torch.bfloat16))
+
+
+@pytest.mark.parametrize("bn,split_k", [(128, 2), (128, 4), (256, 4), (256, 8), (64, 2)])
+@pytest.mark.parametrize("shape", [(128, 1024, 4096), (16, 1000, 4104), (100, 512, 8192)])
+def test_in_cluster_split_k(cuda, lib, bn, split_k, shape):
+    """Few tiles and a long K: the split_k CTAs of a tile run as one thread-block cluster and sum their fp32
+    partials through distributed shared memory (one launch, no workspace). Ragged M / N / K, every tile width,
+    cluster sizes 2, 4 and 8; the rank-ordered sum makes two runs bit-identical."""
+    import ctypes
+    from triton_b200 import _lib
+    M, N, K = shape
+    torch.manual_seed(12)
+    a = (torch.randn(M, K) / K ** 0.5).to(torch.bfloat16)
+    w = torch.randn(N, K).to(torch.bfloat16)
+    ad, wd = a.to(cuda), w.to(cuda)
+    cfg = {"BLOCK_SIZE_N": bn, "SPLIT_K": split_k}
+    c = _mm()(ad, wd.T, config=cfg)
+    _check(c, o_gemm.gemm_ref(a, w.T))
+    assert torch.equal(c, _mm()(ad, wd.T, config=cfg))
+    # this plan needs no workspace: the partial sums never leave the SMs
+    args = _lib.GemmArgs()
+    args.a = args.b = args.c = 16
+    args.m, args.n, args.k = M, N, K
+    args.lda = args.ldb = K
+    args.ldc = N
+    args.in_dtype = args.out_dtype = _lib.BF16
+    args.a_k_major = args.b_k_major = 1
+    args.split_k, args.block_n = split_k, bn
+    with torch.cuda.device(cuda):
+        assert lib.tb200_gemm_workspace_bytes(ctypes.byref(args)) == 0
+
+
+def test_in_cluster_split_k_fp16_and_default_plan(cuda):
+    """The library's own choice for one row of tiles (the skinny shape scaled down) and fp16 output."""
+    torch.manual_seed(13)
+    M, N, K = 128, 2048, 8192
+    for dt in (torch.float16, torch.bfloat16):
+        a = (torch.randn(M, K) / K ** 0.5).to(dt)
+        w = torch.randn(N, K).to(dt)
+        c = _mm()(a.to(cuda), w.to(cuda).T)
+        _check(c, o_gemm.gemm_ref(a, w.T))

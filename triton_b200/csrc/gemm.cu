@@ -29,6 +29,17 @@
 //                2 x (32 + 48) KB for two 256 x 256 tiles - the port stops being the limit (tensor pipe
 //                active 85 % -> measured below), and L2 -> SM traffic per flop drops by a quarter.
 //
+// Split K, two forms. Few tiles and a long K (one row of tiles: M <= 128 against N = K = 8192) leave most SMs
+// idle and the B stream latency-bound, so K is cut into split_k ranges handled by different CTAs.
+//   in-cluster : when all of a tile's splits fit one wave (tiles x split_k <= SMs, split_k <= 8) they are launched as
+//                one thread-block cluster. Each CTA leaves its fp32 partial tile in its own shared memory (the
+//                operand ring is free by then), the cluster synchronises, and CTA r sums columns
+//                [r BN / split_k, (r + 1) BN / split_k) of all partials through distributed shared memory, in
+//                rank order (deterministic), converts and stores them. One launch, no workspace, no second pass
+//                over HBM (the reference reduces through a workspace: _reduce_k_kernel,
+//                third_party/tlx/tutorials/blackwell_gemm_ws.py:1098-1122).
+//   workspace  : otherwise fp32 partials go to a caller workspace and splitk_reduce_kernel sums them.
+//
 // The issue loops are kept lean on purpose: measured on B200, tcgen05.mma issue blocks the issuing
 // thread until the tensor pipe accepts the instruction, so every other instruction in the MMA
 // thread's loop is exposed tensor-pipe idle time. All loop-invariant parameters are copied to
@@ -79,6 +90,7 @@ struct GemmParams {
   int out_mode;  // 0 bf16, 1 fp16, 2 fp32 to c, 3 fp32 partial to ws
   int scale_mode;  // 0: scale_a / scale_b are scalars; 1: per-row (M) and per-column (N) vectors
   int c_tma;       // 1: the wide kernel's epilogue stores through tmc
+  int cluster_k;   // > 1: the split_k CTAs of a tile form a cluster and sum their partials through shared memory
   uint32_t idesc;
   OperandGeom ga, gb;
 };
@@ -484,6 +496,26 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const __grid_cons
       }
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + acc * BN;
+      if constexpr (!PAIR) {
+        if (p.cluster_k > 1) {
+          // in-cluster split K: leave this CTA's partial tile in shared memory, column-major ([column][row], fp32),
+          // so that lanes (= rows) touch consecutive words here and in the remote reads of the reduction below
+          const uint32_t red = smem_a + (uint32_t)(q * 32 + lane) * 4;
+#pragma unroll 1
+          for (int cc = 0; cc < BN; cc += 32) {
+            uint32_t v[32];
+            tmem_ld_32x32b_x32(taddr + cc, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              asm volatile("st.shared.b32 [%0], %1;" ::"r"(red + (uint32_t)(cc + j) * (BM * 4)), "r"(v[j]) : "memory");
+          }
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_a(tempty_leader + acc * 8);
+          continue;
+        }
+      }
       if (row_scale) alpha = row < m ? __ldg(row_scale + row) : 0.f;
       auto out_col = [&](int cc) { return n0 + cc; };
       if constexpr (BN >= 64) {
@@ -521,6 +553,53 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_kernel(const __grid_cons
 
   if constexpr (WIDE) {
     if (warp >= 2 && lane == 0) bulk_wait_group<0>();  // this thread's TMA stores have completed
+  }
+  if constexpr (!PAIR) {
+    if (p.cluster_k > 1) {
+      // ---- in-cluster split-K reduction: every CTA of the cluster holds the partial of the same tile
+      __syncwarp();
+      cluster_sync_all();  // all partials are in shared memory (the role loops above leave no thread behind)
+      if (warp >= 2 && worker < units) {
+        const int q = warp & 3;
+        const int S = p.cluster_k;
+        const TileCoord t = unit_to_tile(worker, split_k, group_m, tiles_m, tiles_n);
+        const int row = t.pid_m * BM + q * 32 + lane;
+        const int cols_per = BN / S;                      // a multiple of 32 (checked on the host)
+        const int c_first = (int)cluster_ctarank() * cols_per;
+        const bool rowwise = p.scale_mode == 1;
+        float alpha = 1.0f;
+        if (rowwise) {
+          alpha = row < p.m ? __ldg(p.scale_a + row) : 0.f;
+        } else {
+          if (p.scale_a) alpha *= __ldg(p.scale_a);
+          if (p.scale_b) alpha *= __ldg(p.scale_b);
+        }
+        const uint32_t own = smem_a + (uint32_t)(q * 32 + lane) * 4;
+        uint32_t remote[8];
+#pragma unroll
+        for (int r = 0; r < 8; ++r) remote[r] = r < S ? mapa_shared(own, (uint32_t)r) : 0u;
+#pragma unroll 1
+        for (int cc = c_first; cc < c_first + cols_per; cc += 32) {
+          uint32_t v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = 0u;
+#pragma unroll 1
+          for (int r = 0; r < S; ++r) {   // rank order: the sum does not depend on which CTA finished first
+            const uint32_t base = remote[r] + (uint32_t)cc * (BM * 4);
+            float x[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(x[j]) : "r"(base + (uint32_t)j * (BM * 4)) : "memory");
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + x[j]);
+          }
+          store_chunk(p.c, nullptr, p.ldc, p.m, p.n, p.out_mode, v, row, t.pid_n * BN + cc, 0, alpha,
+                      rowwise ? p.scale_b : nullptr);
+        }
+      }
+      __syncwarp();
+      cluster_sync_all();  // nobody leaves (and frees its shared memory) while a peer may still read it
+    }
   }
   tc_fence_before_sync();
   if constexpr (PAIR) cluster_sync_all(); else __syncthreads();
@@ -574,6 +653,7 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ ws, void* __restr
 struct GemmPlan {
   int pair;  // 1: CTA-pair kernel, 256 x 256 tile per cluster; 2: 256 x 512 tile per cluster
   int bn;
+  int cluster_reduce;  // 1: the split_k CTAs of a tile form a cluster and reduce through shared memory (no workspace)
   int split_k;
   int kb_per_split;
   int k_blocks;
@@ -667,6 +747,10 @@ static bool plan_gemm(const tb200_gemm_args* a, int sms, GemmPlan* plan) {
   if (split > kb) split = kb > 0 ? kb : 1;
   long long per = kb > 0 ? (kb + split - 1) / split : 0;
   if (per > 0) split = (kb + per - 1) / per;
+  // all splits of every tile resident at once, as clusters of split CTAs (power of two, at most 8, and at least 32
+  // output columns per CTA in the reduction): the partial sums never leave the SMs
+  plan->cluster_reduce = (!pair && split > 1 && split <= 8 && (split & (split - 1)) == 0 && tiles * split <= sms &&
+                          bn / split >= 32) ? 1 : 0;
   plan->pair = pair;
   plan->bn = bn;
   plan->split_k = (int)split;
@@ -679,6 +763,7 @@ static bool plan_gemm(const tb200_gemm_args* a, int sms, GemmPlan* plan) {
 
 template <int BNC, int STAGES, bool PAIR, bool F8>
 static int launch_one(const GemmParams& p, int grid, cudaStream_t stream) {
+  const int cluster = PAIR ? 2 : (p.cluster_k > 1 ? p.cluster_k : 1);
   using L = GemmSmem<BNC, STAGES>;
   auto kfn = gemm_kernel<BNC, STAGES, PAIR, F8>;
   constexpr int SMEM = (PAIR && BNC == 256) ? L::TOTAL_WIDE : L::TOTAL;
@@ -692,7 +777,7 @@ static int launch_one(const GemmParams& p, int grid, cudaStream_t stream) {
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = PAIR ? 2 : 1;
+  attr[0].val.clusterDim.x = cluster;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
@@ -775,7 +860,7 @@ extern "C" size_t tb200_gemm_workspace_bytes(const tb200_gemm_args* a) {
   int sms = sm_count();
   if (sms <= 0) sms = 148;
   if (!plan_gemm(a, sms, &plan)) return 0;
-  if (plan.split_k <= 1) return 0;
+  if (plan.split_k <= 1 || plan.cluster_reduce) return 0;
   return (size_t)plan.split_k * (size_t)a->m * (size_t)a->n * sizeof(float);
 }
 
@@ -849,7 +934,10 @@ extern "C" int tb200_gemm(const tb200_gemm_args* a, void* stream_) {
   p.status = status_ptr();
   if (!p.status) return TB200_ERR_CUDA;
   const int final_mode = a->out_dtype == TB200_BF16 ? 0 : (a->out_dtype == TB200_F16 ? 1 : 2);
-  if (plan.split_k > 1) {
+  if (plan.split_k > 1 && plan.cluster_reduce) {
+    p.out_mode = final_mode;
+    p.cluster_k = plan.split_k;
+  } else if (plan.split_k > 1) {
     const size_t need = (size_t)plan.split_k * (size_t)a->m * (size_t)a->n * sizeof(float);
     if (!a->workspace || a->workspace_bytes < need) return TB200_ERR_BAD_ARG;
     if (reinterpret_cast<uintptr_t>(a->workspace) & 15) return TB200_ERR_BAD_ARG;
@@ -870,7 +958,7 @@ extern "C" int tb200_gemm(const tb200_gemm_args* a, void* stream_) {
   }
   rc = f8 ? launch_gemm<true>(p, plan, sms, stream) : launch_gemm<false>(p, plan, sms, stream);
   if (rc != TB200_OK) return rc;
-  if (plan.split_k > 1) {
+  if (plan.split_k > 1 && !plan.cluster_reduce) {
     // scale factors were already applied to the partial sums
     const long long total = (long long)a->m * ((a->n + 3) / 4);
     int blocks = (int)((total + 255) / 256);

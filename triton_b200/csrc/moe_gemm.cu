@@ -483,9 +483,13 @@ extern "C" int tb200_moe_gemm(const tb200_moe_gemm_args* a, void* stream_) {
   const int sms = sm_count();
   if (sms <= 0) return TB200_ERR_CUDA;
 
-  // One CTA per 128-row block by default. The CTA-pair tiling is kept on request only: measured at
-  // config-5 size it gains 3 % on sorted (tiled) rows and loses 2x on gathered rows (eight remote
-  // barrier arrivals per K step from the peer's gather warps).
+  // One CTA per 128-row block (128 x 256 tile) by default. Two CTA-pair tilings were built and measured at the MoE
+  // benchmark size (65536 sorted rows, 128 experts): 256 rows x 256 columns per pair (kept on request, moe_tile_mode 2)
+  // gains 3 % on sorted rows with tiled loads in one run and loses in others, and loses 2x on gathered rows (eight
+  // remote barrier arrivals per K step from the peer's gather warps); 256 rows x 512 columns per pair with one
+  // 512-column accumulator (the dense kernel's wide tile) ran GEMM-1 at 590-800 TFLOP/s against 930 here, and at
+  // 1040 against 1225 even with 8192 rows per expert: its epilogue (SwiGLU, scattered per-thread stores) cannot hide
+  // behind a second accumulator, and units of 256 rows pad 26 % instead of 13 %.
   const bool pair = a->moe_tile_mode == 2;
   MoeParams p;
   memset(&p, 0, sizeof(p));
