@@ -545,6 +545,14 @@ typedef struct {
   int32_t y_world;
   int32_t gammas_by_out_row; /* 1: the scale of sorted row r is gammas[i] with i its output index (scatter_indx[r], or r)
                                 instead of gammas[r]: lets the top-k values [tokens, k] serve as gate weights as they are */
+  /* Remaining epilogue terms of matmul.py:245-256, applied in the reference's order (_p_matmul.py:606-622):
+   * acc = (acc + bias[e] * betas[r]) * out_alpha -> activation -> * gammas[r] -> + c_acc_in[row]. */
+  const float* betas;     /* optional float [R]: per sorted row factor on the bias */
+  const void* c_acc_in;   /* optional [rows_y, N or N/2] matrix of the output dtype added to the result (may be y itself);
+                             not with scatter_indx or y_peers */
+  int64_t ld_acc_in;      /* elements between rows of c_acc_in */
+  float out_alpha;
+  int32_t has_out_alpha;
 } tb200_moe_gemm_args;
 int tb200_moe_gemm(const tb200_moe_gemm_args* args, void* stream);
 

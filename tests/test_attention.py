@@ -84,6 +84,14 @@ def test_config3_shapes_by_properties(cuda):
             ro, rl = o_attn.attention_ref(q[-1:, -1:, -384:], k[-1:, -1:], v[-1:, -1:], sc, causal)
             torch.testing.assert_close(o[-1:, -1:, -384:].cpu().float(), ro.float(), rtol=1e-2, atol=1e-2)
             torch.testing.assert_close(lse[-1:, -1:, -384:].cpu(), rl, rtol=0, atol=1e-3)
+            # the first and a middle 256-row query tile of another (batch, head): a causal mask that ends inside the
+            # keys is the full-length mask restricted to the keys up to the tile's last row
+            for r0 in (0, (S // 2 // 256) * 256):
+                r1 = r0 + 256
+                kv_end = r1 if causal else S
+                ro, rl = o_attn.attention_ref(q[1:2, 3:4, r0:r1], k[1:2, 3:4, :kv_end], v[1:2, 3:4, :kv_end], sc, causal)
+                torch.testing.assert_close(o[1:2, 3:4, r0:r1].cpu().float(), ro.float(), rtol=1e-2, atol=1e-2)
+                torch.testing.assert_close(lse[1:2, 3:4, r0:r1].cpu(), rl, rtol=0, atol=1e-3)
             if causal:
                 torch.testing.assert_close(o[:, :, 0].cpu().float(), v[:, :, 0].float(), rtol=1e-2, atol=1e-2)
             o1, _ = attention_with_lse(qd, kd, ones, sc, causal)

@@ -144,6 +144,21 @@ def test_mxfp8_2048_and_linearity_at_full_size(cuda):
     assert torch.equal(out, want)
 
 
+def test_mxfp8_full_size_bands(cuda):
+    """MXFP8 benchmark configuration (8192^3, per-block scales 2^u, u in [-4, 4], seed 3): one band of full rows per
+    tile-row class (first, a middle and the last 256 rows; each crosses every column block) against the oracle."""
+    from triton_b200.tutorials.blackwell_gemm_ws_mxfp8 import matmul
+    n = 8192
+    g = torch.Generator().manual_seed(3)
+    qa, sa = o_mx.make_mxfp8_operand(n, n, g)
+    qb, sb = o_mx.make_mxfp8_operand(n, n, g)
+    out = matmul(qa.to(cuda), qb.to(cuda), sa.to(cuda).view(torch.float8_e8m0fnu), sb.to(cuda).view(torch.float8_e8m0fnu))
+    da, db = o_mx.dequantize(qa, sa), o_mx.dequantize(qb, sb)
+    for band in (slice(0, 256), slice(4096 - 128, 4096 + 128), slice(n - 256, n)):
+        ref = da[band] @ db.t()
+        torch.testing.assert_close(out[band].cpu().float(), ref, rtol=3e-2, atol=3e-2 * float(ref.abs().mean()))
+
+
 def test_mxfp8_asserts(cuda):
     from triton_b200.tutorials.blackwell_gemm_ws_mxfp8 import matmul
     a = torch.zeros(128, 128, device=cuda).to(torch.float8_e4m3fn)

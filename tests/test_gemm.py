@@ -149,8 +149,10 @@ def test_full_size_linearity_property(cuda):
     w = (torch.randn(n, n) / n ** 0.5).to(torch.bfloat16)
     mm = _mm()
     c = mm(a.to(cuda), w.to(cuda).T)
-    band = slice(4096 - 128, 4096 + 128)
-    _check(c[band], o_gemm.gemm_ref(a[band], w.T))
+    # one band of full rows per tile-row class of the 256 x 512 tiling: the first, a middle and the last 256-row
+    # block (each band crosses every 512-column block, the first and the last included)
+    for band in (slice(0, 256), slice(4096 - 128, 4096 + 128), slice(n - 256, n)):
+        _check(c[band], o_gemm.gemm_ref(a[band], w.T))
     g = torch.Generator().manual_seed(5)
     ai = torch.randint(-2, 3, (n, n), generator=g).to(torch.bfloat16).to(cuda)
     b1 = torch.randint(-1, 2, (n, n), generator=g).to(torch.bfloat16).to(cuda)

@@ -204,7 +204,8 @@ def test_unsupported_combinations_raise(cuda):
     a = torch.zeros(16, 64, dtype=torch.bfloat16, device=cuda)
     w = torch.zeros(64, 64, dtype=torch.bfloat16, device=cuda)
     with pytest.raises(NotImplementedError):
-        matmul(a, w, None, betas=torch.ones(16, device=cuda))
+        matmul(a, w, None, c_acc_in=torch.zeros(16, 64, dtype=torch.bfloat16, device=cuda),
+               scatter_indx=torch.arange(16, dtype=torch.int32, device=cuda))
     with pytest.raises(NotImplementedError):
         matmul(a, w, None, precision_config=PrecisionConfig(b_mx_scale=torch.ones(1)))
     with pytest.raises(NotImplementedError):
@@ -275,3 +276,37 @@ def test_out_of_range_indices_are_skipped(cuda, lib):
         y, _ = reduce(xr, dim=1, row_indx=ri)
         assert y[:, 0].tolist() == [1.0, 1.0]
     _lib.sync_check(cuda)
+
+
+def test_betas_out_alpha_and_accumulator_input(cuda):
+    """The remaining epilogue terms of the reference's matmul (matmul.py:245-256), in its order
+    (_p_matmul.py:606-622): out = act((acc + bias * beta) * out_alpha) * gamma + c_acc_in."""
+    from triton_b200.triton_kernels.matmul import matmul, swiglu_activation
+    from triton_b200.triton_kernels.tensor import make_ragged_tensor_metadata
+    g = torch.Generator().manual_seed(17)
+    R, K, N, E = 300, 128, 200, 3
+    a = torch.randn(R, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(E, K, N, generator=g) * 0.1).to(torch.bfloat16)
+    bias = torch.randn(E, N, generator=g)
+    betas, gam = torch.rand(R, generator=g), torch.rand(R, generator=g) + 0.5
+    sizes = torch.tensor([100, 60, 140], dtype=torch.int32)
+    rg = make_ragged_tensor_metadata(sizes.to(cuda), R)
+    offs = [0, 100, 160, 300]
+    acc = torch.zeros(R, N)
+    for e in range(E):
+        lo, hi = offs[e], offs[e + 1]
+        acc[lo:hi] = a[lo:hi].float() @ w[e].float() + bias[e] * betas[lo:hi, None]
+    acc *= 0.75
+    c_in = torch.randn(R, N, generator=g).to(torch.bfloat16)
+    got = matmul(a.to(cuda), w.to(cuda), bias.to(cuda), rg, betas=betas.to(cuda), gammas=gam.to(cuda), out_alpha=0.75,
+                 c_acc_in=c_in.to(cuda))
+    want = acc * gam[:, None] + c_in.float()
+    torch.testing.assert_close(got.cpu().float(), want, rtol=2e-2, atol=2e-2)
+    # accumulate in place (c is c_acc_in), with SwiGLU
+    c = torch.randn(R, N // 2, generator=g).to(torch.bfloat16)
+    want = o.swiglu_ref(acc, 1.1, None) * gam[:, None] + c.float()
+    cd = c.to(cuda)
+    got = matmul(a.to(cuda), w.to(cuda), bias.to(cuda), rg, betas=betas.to(cuda), gammas=gam.to(cuda), out_alpha=0.75,
+                 c=cd, c_acc_in=cd, fused_activation=swiglu_activation(1.1, None))
+    assert got.data_ptr() == cd.data_ptr()
+    torch.testing.assert_close(got.cpu().float(), want, rtol=2e-2, atol=2e-2)

@@ -122,6 +122,7 @@ class MoeGemmArgs(Structure):
         ("swiglu_alpha", c_float), ("swiglu_limit", c_float), ("swiglu_has_limit", c_int32), ("moe_tile_mode", c_int32),
         ("slice_sizes", c_void_p),
         ("y_peers", POINTER(c_void_p)), ("rows_per_peer", c_int64), ("y_world", c_int32), ("gammas_by_out_row", c_int32),
+        ("betas", c_void_p), ("c_acc_in", c_void_p), ("ld_acc_in", c_int64), ("out_alpha", c_float), ("has_out_alpha", c_int32),
     ]
 
 

@@ -85,27 +85,57 @@ __device__ __forceinline__ void moe_store_run(void* y, long long elem, const flo
     if (j < cnt) moe_store_one(y, elem + j, o[j], kind);
 }
 
-// Epilogue of the grouped GEMMs for 32 accumulator columns of one output row: (x acc_scale) + bias ->
-// SwiGLU on adjacent (gate, linear) column pairs -> x gamma -> store at row out_row (ldy in elements).
+// Optional terms of the epilogue beyond bias / activation / gamma (matmul.py:245-256 in the reference): a per-row
+// factor on the bias (betas), one factor on the biased accumulator (out_alpha), and a 16-bit matrix added to the
+// result (c_acc_in; may be the output itself).
+struct MoeEpilogueExtra {
+  float beta = 1.f;          // betas[sorted row]
+  float out_alpha = 1.f;
+  const void* acc_in = nullptr;  // row-major 16-bit matrix, same kind as the output
+  long long ld_acc = 0;
+};
+
+// o[j] += acc_in[elem + j] for the first cnt values (16-bit matrix of the output's kind)
+template <int N>
+__device__ __forceinline__ void moe_add_acc(float (&o)[N], int cnt, const void* acc_in, long long elem, int kind) {
+  const uint16_t* src = static_cast<const uint16_t*>(acc_in) + elem;
+#pragma unroll
+  for (int j = 0; j < N; ++j) {
+    if (j < cnt) {
+      const uint16_t raw = src[j];
+      o[j] += kind == MOE_OUT_F16 ? __half2float(*reinterpret_cast<const __half*>(&raw)) : __uint_as_float((uint32_t)raw << 16);
+    }
+  }
+}
+
+// Epilogue of the grouped GEMMs for 32 accumulator columns of one output row, in the reference's order
+// (_p_matmul.py:606-622): (x acc_scale) + bias * beta -> x out_alpha -> SwiGLU on adjacent (gate, linear) column
+// pairs -> x gamma -> + acc_in -> store at row out_row (ldy in elements).
 __device__ __forceinline__ void moe_store_chunk(const uint32_t (&v)[32], void* y, long long ldy, int out_row, int col,
                                                 int n, const float* brow, int swiglu, float alpha, float limit,
-                                                int has_limit, float gamma, int out_kind, float acc_scale) {
+                                                int has_limit, float gamma, int out_kind, float acc_scale,
+                                                const MoeEpilogueExtra ex = MoeEpilogueExtra()) {
   float f[32];
 #pragma unroll
   for (int j = 0; j < 32; ++j) {
     f[j] = __uint_as_float(v[j]) * acc_scale;
-    if (brow && col + j < n) f[j] += __ldg(brow + col + j);
+    if (brow && col + j < n) f[j] += __ldg(brow + col + j) * ex.beta;
+    f[j] *= ex.out_alpha;
   }
   if (swiglu) {
     // 32 accumulator columns -> 16 outputs at column (col / 2)
     float o[16];
 #pragma unroll
     for (int j = 0; j < 16; ++j) o[j] = moe_swiglu(f[2 * j], f[2 * j + 1], alpha, limit, has_limit) * gamma;
-    moe_store_run<16>(y, (long long)out_row * ldy + (col >> 1), o, min(16, (n - col) >> 1), out_kind);
+    const int cnt = min(16, (n - col) >> 1);
+    if (ex.acc_in) moe_add_acc<16>(o, cnt, ex.acc_in, (long long)out_row * ex.ld_acc + (col >> 1), out_kind);
+    moe_store_run<16>(y, (long long)out_row * ldy + (col >> 1), o, cnt, out_kind);
   } else {
 #pragma unroll
     for (int j = 0; j < 32; ++j) f[j] *= gamma;
-    moe_store_run<32>(y, (long long)out_row * ldy + col, f, min(32, n - col), out_kind);
+    const int cnt = min(32, n - col);
+    if (ex.acc_in) moe_add_acc<32>(f, cnt, ex.acc_in, (long long)out_row * ex.ld_acc + col, out_kind);
+    moe_store_run<32>(y, (long long)out_row * ldy + col, f, cnt, out_kind);
   }
 }
 

@@ -60,6 +60,10 @@ struct MoeParams {
   int rows_per_peer;
   int gammas_by_out_row;
   void* y_peers[16];
+  const float* betas;    // optional per sorted row factor on the bias
+  float out_alpha;       // factor on the biased accumulator (1 when unused)
+  const void* acc_in;    // optional 16-bit matrix added to the result (rows as in y, no scatter)
+  long long ld_acc;
 };
 
 // 16-byte asynchronous copy global -> shared (LDGSTS); src_bytes = 0 writes zeros.
@@ -393,6 +397,10 @@ __global__ void __launch_bounds__(MOE_THREADS, 1) moe_gemm_kernel(const __grid_c
       int out_row = -1;
       float gamma = 1.f;
       uint16_t* y = y_local;
+      MoeEpilogueExtra extra;
+      extra.out_alpha = p.out_alpha;
+      extra.acc_in = p.acc_in;
+      extra.ld_acc = p.ld_acc;
       if (sr < row_end) {
         out_row = scatter ? __ldg(scatter + sr) : sr;
         if (out_row >= rows_y) out_row = -1;
@@ -402,6 +410,7 @@ __global__ void __launch_bounds__(MOE_THREADS, 1) moe_gemm_kernel(const __grid_c
           y = static_cast<uint16_t*>(p.y_peers[to]);
           out_row -= to * rows_per_peer;
         }
+        if (p.betas) extra.beta = __ldg(p.betas + sr);
       }
       const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + acc * BN;
       const float* brow = bias ? bias + (long long)e * n : nullptr;
@@ -412,7 +421,7 @@ __global__ void __launch_bounds__(MOE_THREADS, 1) moe_gemm_kernel(const __grid_c
         tmem_ld_wait();
         const int col = n0 + cc;
         if (out_row < 0 || col >= n) continue;
-        moe_store_chunk(v, y, ldy, out_row, col, n, brow, swiglu, alpha, limit, has_limit, gamma, out_f16, 1.f);
+        moe_store_chunk(v, y, ldy, out_row, col, n, brow, swiglu, alpha, limit, has_limit, gamma, out_f16, 1.f, extra);
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -463,6 +472,7 @@ using namespace tb200;
 extern "C" int tb200_moe_gemm(const tb200_moe_gemm_args* a, void* stream_) {
   if (!a || !a->x || !a->w || !a->slice_offs || !a->block_schedule) return TB200_ERR_BAD_ARG;
   if (a->y_world < 0 || a->y_world > 16) return TB200_ERR_BAD_ARG;
+  if (a->c_acc_in && (a->scatter_indx || a->y_world > 0 || a->ld_acc_in <= 0)) return TB200_ERR_UNSUPPORTED;
   if (a->y_world == 0 && !a->y) return TB200_ERR_BAD_ARG;
   if (a->y_world > 0) {
     if (!a->y_peers || a->rows_per_peer <= 0 || a->rows_per_peer > INT32_MAX) return TB200_ERR_BAD_ARG;
@@ -527,6 +537,10 @@ extern "C" int tb200_moe_gemm(const tb200_moe_gemm_args* a, void* stream_) {
   p.y = a->y;
   p.ldy = a->ldy;
   p.gammas_by_out_row = a->gammas_by_out_row ? 1 : 0;
+  p.betas = a->betas;
+  p.out_alpha = a->has_out_alpha ? a->out_alpha : 1.f;
+  p.acc_in = a->c_acc_in;
+  p.ld_acc = a->ld_acc_in;
   p.y_world = a->y_world;
   p.rows_per_peer = (int)a->rows_per_peer;
   for (int i = 0; i < a->y_world; ++i) p.y_peers[i] = a->y_peers[i];

@@ -5,8 +5,10 @@ gather fused into the load and bias, SwiGLU, per-row gammas and row scatter fuse
 ``fused_comm`` fuses the expert-parallel combine: the epilogue stores each output row straight into the
 buffer of the rank that owns the token (peer stores over NVLink; the reference's fused-comm epilogue,
 ``matmul_details/_p_matmul.py:755-782``).
-Unsupported combinations (MX / flexpoint precision, batched input, ragged K, accumulator input, betas,
-out_alpha, custom epilogues) raise ``NotImplementedError``, as the reference does for combinations it
+``betas`` (per-row factor on the bias), ``out_alpha`` and ``c_acc_in`` (a matrix added to the result) follow the
+reference's epilogue order (``_p_matmul.py:606-622``).
+Unsupported combinations (MX / flexpoint precision, batched input, ragged K, custom epilogues) raise
+``NotImplementedError``, as the reference does for combinations it
 cannot serve (``:288,437-447,467``)."""
 from __future__ import annotations
 
@@ -88,8 +90,11 @@ def matmul(a, b, bias, a_ragged_metadata: RaggedTensorMetadata | None = None, b_
            epilogue: Epilogue | None = None, c_acc_in=None, _tile_mode: int = 0, _gammas_by_out_row: bool = False):
     if b_ragged_metadata is not None:
         raise NotImplementedError("matmul: ragged K (b_ragged_metadata) is not implemented")
-    if betas is not None or out_alpha is not None or c_acc_in is not None:
-        raise NotImplementedError("matmul: betas / out_alpha / c_acc_in are not implemented")
+    if (betas is not None or out_alpha is not None or c_acc_in is not None) and precision_config is not None \
+            and precision_config.b_mx_scale is not None:
+        raise NotImplementedError("matmul: betas / out_alpha / c_acc_in with an MXFP4 weight are not implemented")
+    if c_acc_in is not None and (scatter_indx is not None or fused_comm is not None):
+        raise NotImplementedError("matmul: c_acc_in with a scatter index or fused communication (as in the reference)")
     if fused_comm is not None and (c is not None or (precision_config is not None
                                                      and precision_config.b_mx_scale is not None)):
         raise NotImplementedError("matmul: fused_comm takes the 16-bit path and owns the output buffers")
@@ -209,6 +214,15 @@ def matmul(a, b, bias, a_ragged_metadata: RaggedTensorMetadata | None = None, b_
     args.swiglu_alpha = alpha
     args.swiglu_limit = float(limit) if limit is not None else 0.0
     args.swiglu_has_limit = 1 if limit is not None else 0
+    if betas is not None:
+        bt = betas.float().contiguous()
+        assert bt.numel() == R
+        args.betas = bt.data_ptr()
+    if out_alpha is not None:
+        args.out_alpha, args.has_out_alpha = float(out_alpha), 1
+    if c_acc_in is not None:
+        assert c_acc_in.shape == c.shape and c_acc_in.dtype == c.dtype and c_acc_in.stride(1) == 1
+        args.c_acc_in, args.ld_acc_in = c_acc_in.data_ptr(), c_acc_in.stride(0)
     args.moe_tile_mode = int(_tile_mode)  # extension: 0 choose, 1 one CTA per block, 2 CTA pair per two blocks
     # extension: gammas holds one value per OUTPUT row (e.g. the top-k values in (token, slot) order) instead of per sorted row
     args.gammas_by_out_row = 1 if _gammas_by_out_row else 0
