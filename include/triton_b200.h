@@ -9,8 +9,10 @@
  * Conventions
  *  - Plain pointers and sizes only. All data pointers are DEVICE pointers unless a name ends
  *    in `_host`. `stream` is a cudaStream_t passed as void* (NULL = default stream).
- *  - No entry point allocates device memory, creates streams or synchronises (except
- *    tb200_check and the *_host convenience calls). Outputs and workspaces are caller-owned.
+ *  - No entry point allocates device memory, creates streams or synchronises, except tb200_check
+ *    and the set-up calls of the expert-parallel path (tb200_symm_alloc / _free / _open / _close).
+ *    Outputs and workspaces are caller-owned. A few entry points take a HOST array of device
+ *    pointers (one per rank); their comments say so.
  *  - Return value: 0 (TB200_OK) or a negative TB200_ERR_* code. Nothing throws.
  *  - Launches are asynchronous on `stream`. Device-side waits are bounded; a wait that gives
  *    up records a code in a per-device status word that tb200_check() reads and clears.

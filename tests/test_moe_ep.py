@@ -127,3 +127,63 @@ def test_ep_layer_two_ranks_all_transports(cuda):
         p.join(timeout=60)
     assert results[0][0] == "ok" and results[1][0] == "ok", results
     assert len(results[0][1]) == 6
+
+
+def _late_rank_worker(rank, world, port, q):
+    """Rank 1 stays away from one barrier (it is alive and idle, its buffers stay mapped); rank 0's barrier kernel
+    waits its 0.3 s, gives up and returns: the host reads the timeout, the context stays usable, and after rank 1
+    makes up for the missed barrier both ranks meet again normally."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        import ctypes
+        from triton_b200 import _lib
+        from triton_b200.triton_kernels.distributed import Mesh, SymmetricMemoryPool
+        pool = SymmetricMemoryPool(Mesh())
+        pool._reserve_region("signal", pool.SIGNAL_BYTES, 256, 0)
+        pool._initialize(dev)
+        stream = ctypes.c_void_p(_lib.current_stream_ptr(dev))
+        l = _lib.lib()
+        pool.hdl.barrier(channel=2)                      # both arrive: fine
+        torch.cuda.synchronize()
+        assert l.tb200_check(stream) == _lib.OK
+        dist.barrier()
+        if rank == 0:
+            pool.hdl.barrier(channel=2, limit_ns=300_000_000)   # rank 1 never comes
+            torch.cuda.synchronize()
+            word = l.tb200_last_status_code()
+            assert (word >> 16) == 10 and (word & 0xffff) == 1, hex(word)   # wait code "peer", the missing rank
+            assert l.tb200_check(stream) == _lib.ERR_TIMEOUT
+            assert l.tb200_check(stream) == _lib.OK
+        dist.barrier()                                   # host-side: rank 0 has seen the timeout
+        if rank == 1:
+            pool.hdl.barrier(channel=2)                  # the missed one: rank 0's flag is there already
+            torch.cuda.synchronize()
+        dist.barrier()
+        pool.hdl.barrier(channel=2)                      # and the ranks are in step again
+        x = torch.full((4, ), float(rank + 1), device=dev)
+        torch.cuda.synchronize()
+        assert l.tb200_check(stream) == _lib.OK and float(x.sum()) == 4.0 * (rank + 1)
+        pool.close()
+        q.put((rank, "ok", []))
+    except Exception as e:
+        q.put((rank, f"error: {e!r}", []))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_barrier_wait_for_an_absent_rank_runs_out(cuda):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_late_rank_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = {r: s for r, s, _ in (q.get(timeout=300) for _ in range(2))}
+    for p in procs:
+        p.join(timeout=60)
+    assert results == {0: "ok", 1: "ok"}, results

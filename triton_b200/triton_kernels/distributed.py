@@ -154,7 +154,10 @@ class _Handle:
         self._pool = pool
         self._arrays = {}
 
-    def barrier(self, channel: int = 0):
+    def barrier(self, channel: int = 0, limit_ns: int | None = None):
+        """All ranks of the mesh meet on the current stream. ``limit_ns`` bounds the device-side wait (default
+        5 s): when a rank does not arrive the kernel gives up, and the next ``tb200_check`` / ``sync_check`` on
+        this device reports ``TB200_ERR_TIMEOUT``."""
         pool = self._pool
         if pool.mesh.world_size == 1:
             return
@@ -164,7 +167,7 @@ class _Handle:
             arr = _lib.pointer_array([b + channel * self.CHANNEL_BYTES for b in pool.base_ptrs])
             self._arrays[channel] = arr
         with torch.cuda.device(pool.device):
-            rc = _lib.lib().tb200_symm_barrier(arr, pool.mesh.local_rank, pool.mesh.world_size, self.LIMIT_NS,
+            rc = _lib.lib().tb200_symm_barrier(arr, pool.mesh.local_rank, pool.mesh.world_size, limit_ns or self.LIMIT_NS,
                                                ctypes.c_void_p(_lib.current_stream_ptr(pool.device)))
         _lib.check(rc, "tb200_symm_barrier")
 
