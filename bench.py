@@ -877,9 +877,14 @@ def main():
         if any(n in ("fp8", "mxfp8", "fp8_blockwise") for n in names):
             fp8_peak = measure_fp8_peak(dev)
         for name in names:
-            configs[name] = measure_config(name, rank, world, dev, 10, 3, peaks, fp8_peak, flush,
-                                           with_cpu=(world == 1 and rank == 0 and not args.no_cpu_baseline))
-        _lib.sync_check(dev)
+            # a config that cannot run must not take the headline down with it: its entry then says why
+            try:
+                configs[name] = measure_config(name, rank, world, dev, 10, 3, peaks, fp8_peak, flush,
+                                               with_cpu=(world == 1 and rank == 0 and not args.no_cpu_baseline))
+                _lib.sync_check(dev)
+            except Exception as e:  # noqa: BLE001
+                configs[name] = {"error": f"{type(e).__name__}: {e}"[:300]}
+                torch.cuda.empty_cache()
 
     if rank == 0:
         flops = 2.0 * M * N * K
