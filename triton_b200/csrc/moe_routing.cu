@@ -154,24 +154,43 @@ __global__ void bm_hist_kernel(const void* __restrict__ indx, int is16, long lon
   for (int c = threadIdx.x; c < n_cols; c += blockDim.x) partial[(long long)blockIdx.x * n_cols + c] = hist[c];
 }
 
-// partial -> exclusive prefix over blocks; col_sum; col_offs = exclusive scan of col_sum
+// partial -> exclusive prefix over blocks; col_sum; col_offs = exclusive scan of col_sum.
+// One block. A warp owns a column at a time: its lanes take 32 blocks per step and scan them with shuffles (a
+// thread per column walking all blocks one after the other took 22 us for 64 blocks x 128 columns: every step is a
+// dependent global load); warp 0 then scans the column sums the same way.
 __global__ void bm_scan_kernel(int* __restrict__ partial, int n_blocks, int n_cols, int* __restrict__ col_sum,
                                int* __restrict__ col_offs) {
-  for (int c = threadIdx.x; c < n_cols; c += blockDim.x) {
-    int run = 0;
-    for (int b = 0; b < n_blocks; ++b) {
-      const int v = partial[(long long)b * n_cols + c];
-      partial[(long long)b * n_cols + c] = run;
-      run += v;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  for (int c = warp; c < n_cols; c += nwarps) {
+    int carry = 0;
+    for (int b0 = 0; b0 < n_blocks; b0 += 32) {
+      const int b = b0 + lane;
+      const int v = b < n_blocks ? partial[(long long)b * n_cols + c] : 0;
+      int incl = v;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, incl, off);
+        if (lane >= off) incl += t;
+      }
+      if (b < n_blocks) partial[(long long)b * n_cols + c] = carry + incl - v;
+      carry += __shfl_sync(0xffffffffu, incl, 31);
     }
-    col_sum[c] = run;
+    if (lane == 0) col_sum[c] = carry;
   }
   __syncthreads();
-  if (threadIdx.x == 0) {
-    int run = 0;
-    for (int c = 0; c < n_cols; ++c) {
-      col_offs[c] = run;
-      run += col_sum[c];
+  if (warp == 0) {
+    int carry = 0;
+    for (int c0 = 0; c0 < n_cols; c0 += 32) {
+      const int c = c0 + lane;
+      const int v = c < n_cols ? col_sum[c] : 0;
+      int incl = v;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, incl, off);
+        if (lane >= off) incl += t;
+      }
+      if (c < n_cols) col_offs[c] = carry + incl - v;
+      carry += __shfl_sync(0xffffffffu, incl, 31);
     }
   }
 }
