@@ -438,6 +438,8 @@ def build_moe_ep(name, rank, world, dev):
         err = float(t.item())
     if not err <= 2e-2:
         raise SystemExit(f"{name}: parity check against the CPU oracle failed on the live ranks (max abs err {err})")
+    if world > 1:
+        dist.barrier()  # the CPU oracle above takes a different time on every rank: meet on the host before the next layer call
     parity = {"checked": True, "max_abs_err": err, "tolerance": 2e-2,
               "case": f"{pT} tokens, d_model {pD}, E={E}, top-{k} through the same transport, each rank's slice vs the CPU oracle"}
 

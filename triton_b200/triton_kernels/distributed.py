@@ -148,7 +148,7 @@ class _Handle:
 
     N_CHANNELS = 8
     CHANNEL_BYTES = 512
-    LIMIT_NS = 5_000_000_000
+    LIMIT_NS = 20_000_000_000  # ranks may reach a barrier seconds apart (first launches, host work between steps)
 
     def __init__(self, pool):
         self._pool = pool
@@ -156,8 +156,9 @@ class _Handle:
 
     def barrier(self, channel: int = 0, limit_ns: int | None = None):
         """All ranks of the mesh meet on the current stream. ``limit_ns`` bounds the device-side wait (default
-        5 s): when a rank does not arrive the kernel gives up, and the next ``tb200_check`` / ``sync_check`` on
-        this device reports ``TB200_ERR_TIMEOUT``."""
+        20 s): when a rank does not arrive the kernel gives up, and the next ``tb200_check`` / ``sync_check`` on
+        this device reports ``TB200_ERR_TIMEOUT``. The limit covers the time between the first and the last
+        rank's launch, host-side delays included."""
         pool = self._pool
         if pool.mesh.world_size == 1:
             return
