@@ -871,6 +871,63 @@ def main():
     peaks = read_peaks()
     configs = {}
     fp8_peak = {}
+    headline = {}  # filled below; the watchdog prints it if a multi-rank config never returns
+
+    def emit(extra_note=None):
+        if rank != 0 or not headline:
+            return
+        out = dict(headline)
+        if configs:
+            out["configs"] = dict(configs)
+        if fp8_peak:
+            out["peaks_measured_here"] = fp8_peak
+        if extra_note:
+            out["note"] = extra_note
+        print(json.dumps(out), flush=True)
+
+    # A config that involves other ranks (gemm_strong, moe_ep) can only hang if a peer is lost; the headline must
+    # not be lost with it: after this many seconds without finishing, rank 0 prints what it has and every rank exits.
+    watchdog = None
+    if world > 1 and not args.no_configs:
+        def give_up():
+            emit("a multi-rank config did not return within the watchdog limit; the line holds what was measured before")
+            os._exit(0)
+        watchdog = threading.Timer(420.0, give_up)
+        watchdog.daemon = True
+    if rank == 0:
+        flops = 2.0 * M * N * K
+        ms_per_step = total_ms / steps
+        value = world * flops / (ms_per_step * 1e-3) / 1e12
+        sustained = total_ms > 500.0
+        peak = peaks["bf16_sustained"] if sustained else peaks["bf16_burst"]
+        achieved = flops / (kernel_ms * 1e-3) / 1e12
+        headline.update({
+            "metric": "bf16 GEMM throughput", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": steps,
+            "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": CONFIG,
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                         "frac": achieved / peak, "traffic": NCU_TRAFFIC["gemm"],
+                         "peak_kind": ("sustained" if sustained else "burst") + " cuBLAS bf16, " + peaks["source"],
+                         "frac_of_nominal_2250": achieved / 2250.0, "kernel": "gemm_kernel<256,4,PAIR,bf16> (256x512 tile per CTA pair)"},
+            "e2e": {"value": world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                    "h2d_bytes_per_step": 2 * M * K * 2, "d2h_bytes_per_step": M * N * 2, "steps": e2e_steps,
+                    "pipeline": "3 streams (upload | product | read-back), 2 buffer sets", "matches_resident": e2e_check},
+            "gpu_launches": steps * world,
+            "clocks": clocks,
+        })
+        if sus is not None:
+            mhz, mx = sus["clocks"]["sm_mhz"], sus["clocks"]["sm_max_mhz"]
+            per_gpu = sus["tflops"]
+            headline["sustained"] = {
+                "tflops": world * per_gpu, "tflops_per_gpu": per_gpu, "seconds": sus["seconds"], "launches": sus["launches"],
+                "sm_mhz_median": mhz, "sm_max_mhz": mx, "reasons": sus["clocks"]["reasons"],
+                "tflops_per_gpu_at_max_clock": per_gpu * mx / mhz if mhz and mx else None,
+                "peak": peaks["bf16_sustained"], "frac": per_gpu / peaks["bf16_sustained"],
+                "peak_kind": "sustained cuBLAS bf16 (4 s back to back), " + peaks["source"]}
+        if world == 1 and not args.no_cpu_baseline:
+            headline["cpu_baseline"] = cpu_baseline()
+    if watchdog is not None:
+        watchdog.start()
     if not args.no_configs:
         names = [n for n in (args.configs.split(",") if args.configs else CONFIG_NAMES) if n]
         del a, w, b, c
@@ -888,43 +945,9 @@ def main():
                 configs[name] = {"error": f"{type(e).__name__}: {e}"[:300]}
                 torch.cuda.empty_cache()
 
-    if rank == 0:
-        flops = 2.0 * M * N * K
-        ms_per_step = total_ms / steps
-        value = world * flops / (ms_per_step * 1e-3) / 1e12
-        sustained = total_ms > 500.0
-        peak = peaks["bf16_sustained"] if sustained else peaks["bf16_burst"]
-        achieved = flops / (kernel_ms * 1e-3) / 1e12
-        out = {
-            "metric": "bf16 GEMM throughput", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": steps,
-            "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": CONFIG,
-            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                         "frac": achieved / peak, "traffic": NCU_TRAFFIC["gemm"],
-                         "peak_kind": ("sustained" if sustained else "burst") + " cuBLAS bf16, " + peaks["source"],
-                         "frac_of_nominal_2250": achieved / 2250.0, "kernel": "gemm_kernel<256,4,PAIR,bf16> (256x512 tile per CTA pair)"},
-            "e2e": {"value": world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
-                    "h2d_bytes_per_step": 2 * M * K * 2, "d2h_bytes_per_step": M * N * 2, "steps": e2e_steps,
-                    "pipeline": "3 streams (upload | product | read-back), 2 buffer sets", "matches_resident": e2e_check},
-            "gpu_launches": steps * world,
-            "clocks": clocks,
-        }
-        if sus is not None:
-            mhz, mx = sus["clocks"]["sm_mhz"], sus["clocks"]["sm_max_mhz"]
-            per_gpu = sus["tflops"]
-            out["sustained"] = {
-                "tflops": world * per_gpu, "tflops_per_gpu": per_gpu, "seconds": sus["seconds"], "launches": sus["launches"],
-                "sm_mhz_median": mhz, "sm_max_mhz": mx, "reasons": sus["clocks"]["reasons"],
-                "tflops_per_gpu_at_max_clock": per_gpu * mx / mhz if mhz and mx else None,
-                "peak": peaks["bf16_sustained"], "frac": per_gpu / peaks["bf16_sustained"],
-                "peak_kind": "sustained cuBLAS bf16 (4 s back to back), " + peaks["source"]}
-        if world == 1 and not args.no_cpu_baseline:
-            out["cpu_baseline"] = cpu_baseline()
-        if configs:
-            out["configs"] = configs
-        if fp8_peak:
-            out["peaks_measured_here"] = fp8_peak
-        print(json.dumps(out))
+    if watchdog is not None:
+        watchdog.cancel()
+    emit()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

@@ -106,7 +106,10 @@ struct MoeCfg {
   static constexpr int B_BYTES = BNC * 128;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
-  static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 4) * 8 + 16 + 1024;
+  // one 4 KB staging buffer (32 rows x 128 bytes) per epilogue warp, 256 bytes past the barriers: rows that leave the
+  // GPU are transposed through it so that a store instruction writes whole 128-byte lines of four rows
+  static constexpr int EPI_OFFSET = BAR_OFFSET + 256;
+  static constexpr int TOTAL = EPI_OFFSET + 4 * 4096 + 1024;
   // K steps a gather warp keeps in flight. At most stages - 2: the MMA thread releases stage i only after the
   // first MMA of step i + 1, which needs step i + 1 signalled - with stages - 1 steps held back the gather
   // would wait for a stage whose release waits for the gather (measured: a 2 s bounded-wait timeout).
@@ -414,6 +417,74 @@ __global__ void __launch_bounds__(MOE_THREADS, 1) moe_gemm_kernel(const __grid_c
       }
       const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + acc * BN;
       const float* brow = bias ? bias + (long long)e * n : nullptr;
+      if (y_world > 0 && !swiglu && !p.acc_in && (ldy & 7) == 0) {
+        // Fused combine: this warp's 32 rows go to other GPUs' buffers. A thread owns a row, so storing its 64 columns
+        // directly puts 32 rows x 32 bytes into every instruction - 32-byte packets over NVLink, measured at a quarter
+        // of the link rate (GEMM-2 of the expert-parallel layer: 0.56 ms at 4 GPUs against 0.24 for the same tiles
+        // stored locally). Instead the 64 columns (128 bytes) of all 32 rows are written to a swizzled staging buffer
+        // and read back transposed: eight lanes cover one row's 128-byte line, an instruction writes four whole lines.
+        const uint32_t stage = smem_a + L::EPI_OFFSET + (uint32_t)q * 4096;
+        uint8_t* const row_ptr = out_row >= 0 ? reinterpret_cast<uint8_t*>(y) + (long long)out_row * ldy * 2 : nullptr;
+#pragma unroll 1
+        for (int cc = 0; cc < BN; cc += 64) {
+          const int col = n0 + cc;
+          if (col >= n) break;
+          uint32_t v0[32], v1[32];
+          tmem_ld_32x32b_x32(taddr + cc, v0);
+          tmem_ld_32x32b_x32(taddr + cc + 32, v1);
+          tmem_ld_wait();
+          if (col + 64 > n) {  // ragged last columns: per-thread stores
+            if (out_row >= 0) {
+              moe_store_chunk(v0, y, ldy, out_row, col, n, brow, swiglu, alpha, limit, has_limit, gamma, out_f16, 1.f, extra);
+              if (col + 32 < n)
+                moe_store_chunk(v1, y, ldy, out_row, col + 32, n, brow, swiglu, alpha, limit, has_limit, gamma, out_f16, 1.f, extra);
+            }
+            continue;
+          }
+          uint32_t w[32];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            float a0 = __uint_as_float(v0[2 * j]), a1 = __uint_as_float(v0[2 * j + 1]);
+            float b0 = __uint_as_float(v1[2 * j]), b1 = __uint_as_float(v1[2 * j + 1]);
+            if (brow) {
+              a0 += __ldg(brow + col + 2 * j) * extra.beta;
+              a1 += __ldg(brow + col + 2 * j + 1) * extra.beta;
+              b0 += __ldg(brow + col + 32 + 2 * j) * extra.beta;
+              b1 += __ldg(brow + col + 33 + 2 * j) * extra.beta;
+            }
+            const float sc = extra.out_alpha * gamma;
+            w[j] = moe_pack16(a0 * sc, a1 * sc, out_f16);
+            w[16 + j] = moe_pack16(b0 * sc, b1 * sc, out_f16);
+          }
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            const uint32_t addr = stage + (uint32_t)lane * 128 + ((uint32_t)(c ^ (lane & 7)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[4 * c]), "r"(w[4 * c + 1]),
+                         "r"(w[4 * c + 2]), "r"(w[4 * c + 3])
+                         : "memory");
+          }
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int r = 4 * i + (lane >> 3), c = lane & 7;
+            uint4 val;
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(val.x), "=r"(val.y), "=r"(val.z), "=r"(val.w)
+                         : "r"(stage + (uint32_t)r * 128 + ((uint32_t)(c ^ (r & 7)) << 4))
+                         : "memory");
+            uint8_t* dst = reinterpret_cast<uint8_t*>(__shfl_sync(0xffffffffu, (unsigned long long)row_ptr, r));
+            if (dst) *reinterpret_cast<uint4*>(dst + (long long)col * 2 + c * 16) = val;
+          }
+          __syncwarp();
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) {
+          if constexpr (PAIR) mbar_arrive_cluster(tempty_leader + acc * 8);
+          else mbar_arrive_a(tempty_leader + acc * 8);
+        }
+        continue;
+      }
 #pragma unroll 1
       for (int cc = 0; cc < BN; cc += 32) {
         uint32_t v[32];

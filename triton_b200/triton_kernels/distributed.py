@@ -192,6 +192,7 @@ class SymmetricMemoryPool:
         self.device = None
         self.hdl = _Handle(self)
         self._own_ptr = None
+        self._side = None
 
     @staticmethod
     def align_up(value: int, alignment: int) -> int:
@@ -254,6 +255,12 @@ class SymmetricMemoryPool:
         off = self._reserve_region("ep_to_dp", n_local * n_expts_act * d_model * esz, 256, off)
         off = self._reserve_region("dp_to_ep", n_tokens_global * n_expts_act * d_input * esz, 256, off)
         self._initialize(device)
+
+    def side_stream(self):
+        """A second stream on the pool's device for work that may overlap the token exchange (created once)."""
+        if self._side is None:
+            self._side = torch.cuda.Stream(self.device)
+        return self._side
 
     def make_empty(self, shape, dtype, region: str, region_offset: int = 0, clear: bool = False):
         """One view per rank of ``region`` (this rank's as a torch tensor, the others as ``PeerBuffer``)."""
@@ -512,9 +519,21 @@ def moe_layer_ep(x_local, logits_local, w1_local, w2_local, k, expt_assignment: 
     sm = all_gather_topk(logits_local, k, ep)
     mm = sm.mask_metadata
     n_entries = sm.indx.numel()
-    rg = make_ragged_tensor_metadata(mm.col_sum, n_entries)
-    rg_local = remap_ragged_tensor_metadata(rg, expt_assignment.expt_map[rank])
-    y = convert_dp_to_ep(x_local, expt_assignment, sm.indx, mm.row_sorted_indx, ep)
+    if isinstance(ep, SymmetricMemoryPool) and world > 1:
+        # the ragged metadata is needed by the GEMMs only: derive it on a second stream while the token rows cross
+        # NVLink (under graph capture the two become parallel branches)
+        cur = torch.cuda.current_stream(x_local.device)
+        side = ep.side_stream()
+        side.wait_stream(cur)
+        with torch.cuda.stream(side):
+            rg = make_ragged_tensor_metadata(mm.col_sum, n_entries)
+            rg_local = remap_ragged_tensor_metadata(rg, expt_assignment.expt_map[rank])
+        y = convert_dp_to_ep(x_local, expt_assignment, sm.indx, mm.row_sorted_indx, ep)
+        cur.wait_stream(side)
+    else:
+        rg = make_ragged_tensor_metadata(mm.col_sum, n_entries)
+        rg_local = remap_ragged_tensor_metadata(rg, expt_assignment.expt_map[rank])
+        y = convert_dp_to_ep(x_local, expt_assignment, sm.indx, mm.row_sorted_indx, ep)
     h = matmul(y, w1_local, None, rg_local, fused_activation=swiglu_activation(alpha, limit))
     n_local = x_local.shape[0]
     if isinstance(ep, SymmetricMemoryPool) and fuse_combine:
