@@ -555,6 +555,15 @@ typedef struct {
   int64_t ld_acc_in;      /* elements between rows of c_acc_in */
   float out_alpha;
   int32_t has_out_alpha;
+  /* MX-quantised output (precision_config.c_mx_scale with the quantize_mxfp8 epilogue, matmul.py:362-366 and
+   * matmul_details/_p_matmul.py:650-704): with y_mx_scale set, y is a matrix of y_mx_dtype (TB200_E4M3 /
+   * TB200_E5M2; ldy in bytes), every 32 consecutive outputs of a row share the e8m0 scale
+   * 2^ceil(log2(amax / max_finite)) written to y_mx_scale[row][col / 32] (ld_y_mx_scale bytes between rows) and the
+   * values are output / scale rounded to nearest even. Not with c_acc_in or y_peers. */
+  void* y_mx_scale;
+  int64_t ld_y_mx_scale;
+  int32_t y_mx_dtype;
+  int32_t reserved0;
 } tb200_moe_gemm_args;
 int tb200_moe_gemm(const tb200_moe_gemm_args* args, void* stream);
 
@@ -599,6 +608,18 @@ typedef struct {
   float swiglu_limit;
   int32_t swiglu_has_limit;
   int32_t block_rows; /* rows per entry of block_schedule: 0 or 128 = the 128-row schedule; 32 = the 32-row schedule (few rows per expert: operand roles swapped, weights on the MMA's M side) */
+  /* MX-scaled activations (precision_config.a_mx_scale, matmul.py:309-334): uint8 e8m0, one per 32 values of K,
+   * [rows_x][k/32] row-major with ld_x_mx_scale bytes between rows (multiple of 4, pointer 4-byte aligned);
+   * NULL = the activations carry no block scales. */
+  const void* x_mx_scale;
+  int64_t ld_x_mx_scale;
+  /* MX-quantised output (precision_config.c_mx_scale with the quantize_mxfp8 epilogue, matmul.py:362-366 and
+   * matmul_details/_p_matmul.py:650-704): out_dtype TB200_E4M3 / TB200_E5M2, every 32 consecutive outputs of a
+   * row share the e8m0 scale 2^ceil(log2(amax / max_finite)) written to y_mx_scale[row][col / 32]
+   * (ld_y_mx_scale bytes between rows), values = round-to-nearest-even of output / scale. Not with swiglu on
+   * the 32-row schedule (TB200_ERR_UNSUPPORTED: use the 128-row schedule). NULL = plain output. */
+  void* y_mx_scale;
+  int64_t ld_y_mx_scale;
 } tb200_moe_gemm_mx4_args;
 int tb200_moe_gemm_mx4(const tb200_moe_gemm_mx4_args* args, void* stream);
 

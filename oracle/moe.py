@@ -13,6 +13,9 @@ Each function restates the torch twin that the reference's own tests use as grou
   reduce_ref                 <- reduce_torch                         reduce.py:1173-1206
   moe_layer_ref              <- mixture_of_expt_nosharded            tests/test_distributed.py:201-218
                                 (plus the gate-weighted combine of the MoE benchmark configuration)
+  quantize_mxfp8_ref         <- downcast_to_mxfp_torch (fp8, e8m0,   numerics_details/mxfp.py:212-318
+                                ROUND_UP), the twin of the quantize_mxfp8_fn matmul epilogue
+  dequantize_mxfp8_ref       <- upcast_from_mxfp_torch (fp8)         numerics_details/mxfp.py:384-449
 """
 from dataclasses import dataclass
 
@@ -229,3 +232,33 @@ def moe_layer_ref(x, logits, w1, w2, k: int, alpha: float = 1.0, limit=None, gat
         gammas = vals.float().reshape(-1)[torch.as_tensor(combine).long()]
     y = grouped_matmul_ref(h, w2, None, md.col_sum, scatter_indx=combine, gammas=gammas)
     return reduce_ref(y.view(-1, k, y.shape[-1]), dim=1)
+
+
+# ----------------------------------------------------------------------------- MX-quantised activations / outputs
+
+
+def quantize_mxfp8_ref(x: torch.Tensor, dtype=torch.float8_e4m3fn):
+    """MXFP8 quantisation along the last axis: every 32 consecutive values (the last block may be short) share
+    the e8m0 scale 2^ceil(log2(amax / max_finite)), computed on the bits as (bits(amax / max_finite) + 0x7FFFFF)
+    & 0x7F800000; values are multiplied by the reciprocal of the scale (by 0 when the scale is 0), clamped to the
+    finite range and converted with round to nearest even. Returns (values as ``dtype``, scales uint8)."""
+    x = x.detach().cpu().float()
+    max_q = 448.0 if dtype == torch.float8_e4m3fn else 57344.0
+    n = x.shape[-1]
+    pad = (-n) % 32
+    xp = torch.nn.functional.pad(x, (0, pad))
+    valid = torch.nn.functional.pad(torch.ones_like(x, dtype=torch.bool), (0, pad))
+    groups = xp.reshape(*xp.shape[:-1], -1, 32)
+    amax = torch.where(valid.reshape(groups.shape), groups.abs(), torch.full((), -1.0)).amax(dim=-1, keepdim=True)
+    bits = ((amax / max_q).view(torch.int32) + 0x007FFFFF) & 0x7F800000
+    scale = bits.view(torch.float32)
+    inv = torch.where(scale == 0, torch.zeros(()), 1.0 / scale)
+    q = (groups * inv).reshape(xp.shape)[..., :n].clamp(-max_q, max_q).to(dtype)
+    return q, (bits >> 23).to(torch.uint8).squeeze(-1)
+
+
+def dequantize_mxfp8_ref(q: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    """fp8 values x 2^(scale - 127) per block of 32 along the last axis, in fp32."""
+    q32 = q.detach().cpu().float()
+    s = torch.pow(2.0, scale.detach().cpu().float() - 127.0).repeat_interleave(32, dim=-1)[..., :q32.shape[-1]]
+    return q32 * s

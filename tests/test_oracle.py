@@ -254,3 +254,16 @@ def test_swiglu_and_reduce_oracles_match_reference_twins():
     np.testing.assert_allclose(o_moe.reduce_ref(xr, 1, mask=mask, scale=sc).numpy(), fx["rd_y_both"], **tol)
     got = o_moe.reduce_ref(xr.to(torch.bfloat16), 1, mask=mask, scale=sc)
     np.testing.assert_allclose(got.float().numpy(), fx["rd_y_both_bf16"], rtol=0, atol=0)
+
+
+def test_quantize_mxfp8_oracle_matches_reference_twin():
+    """oracle.moe.quantize_mxfp8_ref against the outputs of the reference's downcast_to_mxfp_torch (e4m3 values,
+    e8m0 scales, ROUND_UP) and upcast_from_mxfp_torch held in mxfp_cases.npz: bit-exact."""
+    d = np.load(os.path.join(os.path.dirname(__file__), "golden", "mxfp_cases.npz"))
+    for name in ("normal", "wide", "ties", "zeros"):
+        x = torch.from_numpy(d[f"{name}_x"])
+        q, s = o_moe.quantize_mxfp8_ref(x)
+        assert np.array_equal(q.view(torch.uint8).numpy(), d[f"{name}_e4m3_ROUND_UP_v"]), name
+        assert np.array_equal(s.numpy(), d[f"{name}_e4m3_ROUND_UP_s"]), name
+        up = o_moe.dequantize_mxfp8_ref(q, s)
+        assert np.array_equal(up.numpy(), d[f"{name}_e4m3_ROUND_UP_up"]), name

@@ -123,6 +123,7 @@ class MoeGemmArgs(Structure):
         ("slice_sizes", c_void_p),
         ("y_peers", POINTER(c_void_p)), ("rows_per_peer", c_int64), ("y_world", c_int32), ("gammas_by_out_row", c_int32),
         ("betas", c_void_p), ("c_acc_in", c_void_p), ("ld_acc_in", c_int64), ("out_alpha", c_float), ("has_out_alpha", c_int32),
+        ("y_mx_scale", c_void_p), ("ld_y_mx_scale", c_int64), ("y_mx_dtype", c_int32), ("reserved0", c_int32),
     ]
 
 
@@ -163,6 +164,7 @@ class MoeGemmMx4Args(Structure):
         ("ldx", c_int64), ("ldy", c_int64),
         ("n_sched", c_int32), ("x_dtype", c_int32), ("out_dtype", c_int32), ("swiglu", c_int32),
         ("swiglu_alpha", c_float), ("swiglu_limit", c_float), ("swiglu_has_limit", c_int32), ("block_rows", c_int32),
+        ("x_mx_scale", c_void_p), ("ld_x_mx_scale", c_int64), ("y_mx_scale", c_void_p), ("ld_y_mx_scale", c_int64),
     ]
 
 

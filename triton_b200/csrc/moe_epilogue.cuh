@@ -139,4 +139,48 @@ __device__ __forceinline__ void moe_store_chunk(const uint32_t (&v)[32], void* y
   }
 }
 
+// The same epilogue up to the store: the outputs of a 32-column accumulator chunk written to o[OFF ..] - 32 values
+// (OFF = 0), or 16 with SwiGLU (OFF = 0 or 16, so that two chunks fill one block of 32 outputs).
+template <int OFF>
+__device__ __forceinline__ void moe_chunk_values(const uint32_t (&v)[32], int col, int n, const float* brow, int swiglu,
+                                                 float alpha, float limit, int has_limit, float gamma, float acc_scale,
+                                                 const MoeEpilogueExtra ex, float (&o)[32]) {
+  float f[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    f[j] = __uint_as_float(v[j]) * acc_scale;
+    if (brow && col + j < n) f[j] += __ldg(brow + col + j) * ex.beta;
+    f[j] *= ex.out_alpha;
+  }
+  if (swiglu) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) o[OFF + j] = moe_swiglu(f[2 * j], f[2 * j + 1], alpha, limit, has_limit) * gamma;
+  } else if (OFF == 0) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) o[j] = f[j] * gamma;
+  }
+}
+
+// One MX block of the output: 32 consecutive values of a row (the first cnt exist) share an e8m0 scale
+// 2^ceil(log2(amax / max_finite)) - in bits (bits(amax / max_finite) + 0x7FFFFF) & 0x7F800000 -, each value is
+// multiplied by the reciprocal of that scale (by 0 when the scale is 0) and converted to fp8 with round to nearest
+// even. This is the reference's quantize_mxfp8_fn epilogue (numerics_details/mxfp_details/_downcast_to_mxfp.py:
+// 34-85, rounding mode ROUND_UP) and its torch twin downcast_to_mxfp_torch. dst: the block's first output byte;
+// scale_dst: its scale byte.
+__device__ __forceinline__ void moe_store_mx_block(const float (&o)[32], int cnt, void* y, long long elem,
+                                                   uint8_t* scale_dst, int kind) {
+  float amax = 0.f;
+#pragma unroll
+  for (int j = 0; j < 32; ++j)
+    if (j < cnt) amax = fmaxf(amax, fabsf(o[j]));
+  const float max_finite = kind == MOE_OUT_E5M2 ? 57344.f : 448.f;
+  const uint32_t bits = (__float_as_uint(__fdiv_rn(amax, max_finite)) + 0x007FFFFFu) & 0x7F800000u;
+  const float inv = bits == 0u ? 0.f : __frcp_rn(__uint_as_float(bits));
+  *scale_dst = (uint8_t)(bits >> 23);
+  float q[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) q[j] = j < cnt ? o[j] * inv : 0.f;
+  moe_store_run<32>(y, elem, q, cnt, kind);
+}
+
 }  // namespace tb200

@@ -55,11 +55,14 @@ struct Mx4Params {
   const float* gammas;
   const float* bias;
   const float* x_scale;  // optional: one float, multiplies every accumulator
+  const uint8_t* x_sf;   // optional e8m0 block scales of the activations: [rows_x][K/32], ld_xsf bytes between rows
+  uint8_t* y_sf;         // optional: the output is MX-quantised, its e8m0 scales go to [rows_y][N_out/32] (ld_ysf)
+  long long ld_xsf, ld_ysf;
   void* y;
   int* status;
   long long ldy;
   int n_sched, tiles_n, units;
-  int n, k_blocks, n_blocks, rows_y;
+  int n, k_blocks, n_blocks, rows_x, rows_y;
   int swiglu, has_limit, out_kind;
   float alpha, limit;
   uint32_t idesc[4];
@@ -69,7 +72,7 @@ struct Mx4Smem {
   static constexpr int A_BYTES = M4_BM * 128;
   static constexpr int B_BYTES = M4_BN * 128;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int SF_BYTES = 2 * 512;  // two scale atoms of W per K step
+  static constexpr int SF_BYTES = 3 * 512;  // two scale atoms of W per K step + one of the activations (MX-scaled x)
   static constexpr int SF_OFFSET = M4_STAGES * STAGE_BYTES;
   static constexpr int BAR_OFFSET = SF_OFFSET + M4_STAGES * SF_BYTES;
   static constexpr int TOTAL = BAR_OFFSET + (2 * M4_STAGES + 2) * 8 + 16 + 1024;
@@ -85,6 +88,7 @@ __global__ void __launch_bounds__(M4_THREADS, 1) moe_gemm_mx4_kernel(const __gri
   constexpr int BN = M4_BN, STAGES = M4_STAGES;
   constexpr uint32_t SFA_COL = 256;       // four columns of 1.0 for the activations
   constexpr uint32_t SFW_COL0 = 256 + 16; // two sets of 8 columns for the weight scales
+  constexpr uint32_t SFX_COL0 = 256 + 32; // two sets of 4 columns for the activations' own block scales
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET);
@@ -133,9 +137,16 @@ __global__ void __launch_bounds__(M4_THREADS, 1) moe_gemm_mx4_kernel(const __gri
 
   if (warp == 0) {
     // ------------------------------------------------------------- producer
-    if (lane == 0) {
+    // One lane issues the bulk copies. With MX-scaled activations the whole warp takes part: lane l fetches the four
+    // scale bytes of this K step for rows l, l + 32, l + 64, l + 96 (one step ahead, so the loads are in flight
+    // while the warp waits for a free stage) and writes them as the 16 bytes of row l of a 512-byte atom
+    // ([row % 32][row / 32][k]), the order tcgen05.cp.32x128b.warpx4 turns into the MMA's scale columns.
+    const uint8_t* const x_sf = p.x_sf;
+    if (lane == 0 || x_sf) {
       const uint64_t pol_x = policy_evict_normal();
       const uint64_t pol_w = policy_evict_first();  // a weight tile is read once per row block
+      const long long ld_xsf = p.ld_xsf;
+      const int rows_x = p.rows_x;
       uint32_t s = 0, ph = 0;
       bool ok = true;
       for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x) {
@@ -148,20 +159,40 @@ __global__ void __launch_bounds__(M4_THREADS, 1) moe_gemm_mx4_kernel(const __gri
         const int row0 = __ldg(slice_offs + e) + (entry >> 16) * M4_BM;
         const int nb_valid = min(2, n_blocks - pid_n * 2);
         const uint8_t* atoms = p.sfw + ((size_t)e * n_blocks + (size_t)pid_n * 2) * k_blocks * 512;
+        uint32_t sfx[4] = {0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu};
+        auto load_sfx = [&](int kb) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int r = row0 + lane + 32 * i;
+            sfx[i] = r < rows_x ? __ldg(reinterpret_cast<const uint32_t*>(x_sf + (long long)r * ld_xsf) + kb) : 0x7f7f7f7fu;
+          }
+        };
+        if (x_sf) load_sfx(0);
         for (int kb = 0; kb < k_blocks; ++kb) {
-          if (!mbar_wait_a(empty_a + s * 8, ph ^ 1, status, WAIT_SMEM_EMPTY)) {
+          bool free_stage = true;
+          if (lane == 0) free_stage = mbar_wait_a(empty_a + s * 8, ph ^ 1, status, WAIT_SMEM_EMPTY);
+          if (x_sf) free_stage = __shfl_sync(0xffffffffu, free_stage ? 1 : 0, 0) != 0;
+          if (!free_stage) {
             ok = false;
             break;
           }
-          const uint32_t bar = full_a + s * 8;
-          // the unpacking load of W reports the bytes it read (64 per row), not the 128 it writes
-          mbar_expect_tx_a(bar, L::A_BYTES + L::B_BYTES / 2 + nb_valid * 512);
-          const uint32_t sa = smem_a + s * L::STAGE_BYTES;
-          tma_load_2d_a(sa, &p.tmx, bar, kb * 128, row0, pol_x);
-          tma_load_2d_a(sa + L::A_BYTES, &p.tmw, bar, 0, (((e * tiles_n + pid_n) * k_blocks) + kb) * BN, pol_w);
           uint8_t* sf = smem + L::SF_OFFSET + s * L::SF_BYTES;
-          for (int j = 0; j < nb_valid; ++j)
-            bulk_load(sf + j * 512, atoms + ((size_t)j * k_blocks + kb) * 512, 512, &full[s]);
+          if (x_sf) {
+            *reinterpret_cast<uint4*>(sf + 1024 + lane * 16) = make_uint4(sfx[0], sfx[1], sfx[2], sfx[3]);
+            fence_proxy_async_smem();
+            __syncwarp();
+          }
+          if (lane == 0) {
+            const uint32_t bar = full_a + s * 8;
+            // the unpacking load of W reports the bytes it read (64 per row), not the 128 it writes
+            mbar_expect_tx_a(bar, L::A_BYTES + L::B_BYTES / 2 + nb_valid * 512);
+            const uint32_t sa = smem_a + s * L::STAGE_BYTES;
+            tma_load_2d_a(sa, &p.tmx, bar, kb * 128, row0, pol_x);
+            tma_load_2d_a(sa + L::A_BYTES, &p.tmw, bar, 0, (((e * tiles_n + pid_n) * k_blocks) + kb) * BN, pol_w);
+            for (int j = 0; j < nb_valid; ++j)
+              bulk_load(sf + j * 512, atoms + ((size_t)j * k_blocks + kb) * 512, 512, &full[s]);
+          }
+          if (x_sf && kb + 1 < k_blocks) load_sfx(kb + 1);
           if (++s == STAGES) {
             s = 0;
             ph ^= 1;
@@ -176,7 +207,8 @@ __global__ void __launch_bounds__(M4_THREADS, 1) moe_gemm_mx4_kernel(const __gri
       const uint64_t bdesc0 = make_smem_desc(smem_a + L::A_BYTES, 16, 1024, SWIZZLE_128B);
       const uint64_t sfdesc0 = make_smem_desc(smem_a + L::SF_OFFSET, 16, 128, SWIZZLE_NONE);
       const uint32_t tfull_a = smem_u32(tfull), tempty_a = smem_u32(tempty);
-      const uint32_t t_sfa = tmem_base + SFA_COL;
+      const uint32_t t_sfa_one = tmem_base + SFA_COL;
+      const bool mx_x = p.x_sf != nullptr;
       uint32_t s = 0, ph = 0, tcount = 0, kpar = 0;
       bool ok = true, ready = false;
       for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x) {
@@ -197,6 +229,11 @@ __global__ void __launch_bounds__(M4_THREADS, 1) moe_gemm_mx4_kernel(const __gri
           const uint64_t sfd = sfdesc0 + (uint64_t)((s * L::SF_BYTES) >> 4);
           tmem_cp_32x128b_warpx4(t_sfw, sfd);
           tmem_cp_32x128b_warpx4(t_sfw + 4, sfd + (uint64_t)(512 >> 4));
+          uint32_t t_sfa = t_sfa_one;
+          if (mx_x) {
+            t_sfa = tmem_base + SFX_COL0 + kpar * 4;
+            tmem_cp_32x128b_warpx4(t_sfa, sfd + (uint64_t)(1024 >> 4));
+          }
           const uint64_t ad = adesc0 + (uint64_t)(s * (L::STAGE_BYTES >> 4));
           const uint64_t bd = bdesc0 + (uint64_t)(s * (L::STAGE_BYTES >> 4));
           umma_mxf8_ss(tmem_base, ad, bd, p.idesc[0], t_sfa, t_sfw, accum);
@@ -241,15 +278,41 @@ __global__ void __launch_bounds__(M4_THREADS, 1) moe_gemm_mx4_kernel(const __gri
       }
       const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16);
       const float* brow = p.bias ? p.bias + (long long)e * n : nullptr;
+      if (p.y_sf) {
+        // MX-quantised output: a block of 32 outputs is one chunk of 32 accumulator columns, or two with SwiGLU
+        const int step = p.swiglu ? 64 : 32;
 #pragma unroll 1
-      for (int cc = 0; cc < BN; cc += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(taddr + cc, v);
-        tmem_ld_wait();
-        const int col = n0 + cc;
-        if (out_row < 0 || col >= n) continue;
-        moe_store_chunk(v, y, p.ldy, out_row, col, n, brow, p.swiglu, p.alpha, p.limit, p.has_limit, gamma, p.out_kind,
-                        acc_scale);
+        for (int cc = 0; cc < BN; cc += step) {
+          uint32_t v0[32], v1[32];
+          tmem_ld_32x32b_x32(taddr + cc, v0);
+          if (p.swiglu) tmem_ld_32x32b_x32(taddr + cc + 32, v1);
+          tmem_ld_wait();
+          const int col = n0 + cc;
+          if (out_row < 0 || col >= n) continue;
+          float o[32];
+          moe_chunk_values<0>(v0, col, n, brow, p.swiglu, p.alpha, p.limit, p.has_limit, gamma, acc_scale,
+                              MoeEpilogueExtra(), o);
+          int ocol = col, cnt = min(32, n - col);
+          if (p.swiglu) {
+            moe_chunk_values<16>(v1, col + 32, n, brow, 1, p.alpha, p.limit, p.has_limit, gamma, acc_scale,
+                                 MoeEpilogueExtra(), o);
+            ocol = col >> 1;
+            cnt = min(32, (n - col) >> 1);
+          }
+          moe_store_mx_block(o, cnt, y, (long long)out_row * p.ldy + ocol, p.y_sf + (long long)out_row * p.ld_ysf + (ocol >> 5),
+                             p.out_kind);
+        }
+      } else {
+#pragma unroll 1
+        for (int cc = 0; cc < BN; cc += 32) {
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(taddr + cc, v);
+          tmem_ld_wait();
+          const int col = n0 + cc;
+          if (out_row < 0 || col >= n) continue;
+          moe_store_chunk(v, y, p.ldy, out_row, col, n, brow, p.swiglu, p.alpha, p.limit, p.has_limit, gamma, p.out_kind,
+                          acc_scale);
+        }
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -283,7 +346,8 @@ struct Mx4SwapSmem {
   static constexpr int X_BYTES = S4_XROWS * 128;
   static constexpr int STAGE_BYTES = W_BYTES + X_BYTES;  // 20 KB, a multiple of 1024
   static constexpr int SF_OFFSET = S4_STAGES * STAGE_BYTES;
-  static constexpr int BAR_OFFSET = SF_OFFSET + S4_STAGES * 512;
+  static constexpr int SF_BYTES = 2 * 512;  // the weight tile's scale atom + one for MX-scaled activations
+  static constexpr int BAR_OFFSET = SF_OFFSET + S4_STAGES * SF_BYTES;
   static constexpr int TOTAL = BAR_OFFSET + (2 * S4_STAGES + 2 * S4_NACC) * 8 + 16 + 1024;
 };
 static_assert(Mx4SwapSmem::TOTAL <= 232448, "shared memory budget");
@@ -293,6 +357,7 @@ __global__ void __launch_bounds__(M4_THREADS, 1) moe_gemm_mx4_swap_kernel(const 
   constexpr int STAGES = S4_STAGES;
   constexpr uint32_t SFB_COL = S4_NACC * 32;      // token-side scale columns: 1.0
   constexpr uint32_t SFA_COL0 = SFB_COL + 8;      // two sets of 4 columns for the weight scales
+  constexpr uint32_t SFX_COL0 = SFB_COL + 16;     // two sets of 4 columns for the tokens' own block scales
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET);
@@ -345,9 +410,14 @@ __global__ void __launch_bounds__(M4_THREADS, 1) moe_gemm_mx4_swap_kernel(const 
 
   if (warp == 0) {
     // ------------------------------------------------------------- producer
-    if (lane == 0) {
+    // With MX-scaled activations lane l also stages the four scale bytes of token row0 + l for each K step (row l of
+    // a 512-byte atom, the other twelve bytes of the row are 1.0), fetched one step ahead.
+    const uint8_t* const x_sf = p.x_sf;
+    if (lane == 0 || x_sf) {
       const uint64_t pol_x = policy_evict_last();
       const uint64_t pol_w = policy_evict_first();
+      const long long ld_xsf = p.ld_xsf;
+      const int rows_x = p.rows_x;
       uint32_t s = 0, ph = 0;
       bool ok = true;
       for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x) {
@@ -360,17 +430,35 @@ __global__ void __launch_bounds__(M4_THREADS, 1) moe_gemm_mx4_swap_kernel(const 
         const uint8_t* atoms = p.sfw + ((size_t)e * n_blocks + wt) * k_blocks * 512;
         // weight rows 128 wt .. of expert e sit in 256-row block wt / 2, half wt % 2, of each K step
         const int wrow0 = ((e * tiles_256 + (wt >> 1)) * k_blocks) * M4_BN + (wt & 1) * S4_WROWS;
+        uint32_t sfx = 0x7f7f7f7fu;
+        auto load_sfx = [&](int kb) {
+          const int r = row0 + lane;
+          sfx = r < rows_x ? __ldg(reinterpret_cast<const uint32_t*>(x_sf + (long long)r * ld_xsf) + kb) : 0x7f7f7f7fu;
+        };
+        if (x_sf) load_sfx(0);
         for (int kb = 0; kb < k_blocks; ++kb) {
-          if (!mbar_wait_a(empty_a + s * 8, ph ^ 1, status, WAIT_SMEM_EMPTY)) {
+          bool free_stage = true;
+          if (lane == 0) free_stage = mbar_wait_a(empty_a + s * 8, ph ^ 1, status, WAIT_SMEM_EMPTY);
+          if (x_sf) free_stage = __shfl_sync(0xffffffffu, free_stage ? 1 : 0, 0) != 0;
+          if (!free_stage) {
             ok = false;
             break;
           }
-          const uint32_t bar = full_a + s * 8;
-          mbar_expect_tx_a(bar, L::W_BYTES / 2 + L::X_BYTES + 512);
-          const uint32_t sw = smem_a + s * L::STAGE_BYTES;
-          tma_load_2d_a(sw, &p.tmw, bar, 0, wrow0 + kb * M4_BN, pol_w);
-          tma_load_2d_a(sw + L::W_BYTES, &p.tmx, bar, kb * 128, row0, pol_x);
-          bulk_load(smem + L::SF_OFFSET + s * 512, atoms + (size_t)kb * 512, 512, &full[s]);
+          uint8_t* sf = smem + L::SF_OFFSET + s * L::SF_BYTES;
+          if (x_sf) {
+            *reinterpret_cast<uint4*>(sf + 512 + lane * 16) = make_uint4(sfx, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu);
+            fence_proxy_async_smem();
+            __syncwarp();
+          }
+          if (lane == 0) {
+            const uint32_t bar = full_a + s * 8;
+            mbar_expect_tx_a(bar, L::W_BYTES / 2 + L::X_BYTES + 512);
+            const uint32_t sw = smem_a + s * L::STAGE_BYTES;
+            tma_load_2d_a(sw, &p.tmw, bar, 0, wrow0 + kb * M4_BN, pol_w);
+            tma_load_2d_a(sw + L::W_BYTES, &p.tmx, bar, kb * 128, row0, pol_x);
+            bulk_load(sf, atoms + (size_t)kb * 512, 512, &full[s]);
+          }
+          if (x_sf && kb + 1 < k_blocks) load_sfx(kb + 1);
           if (++s == STAGES) {
             s = 0;
             ph ^= 1;
@@ -385,7 +473,8 @@ __global__ void __launch_bounds__(M4_THREADS, 1) moe_gemm_mx4_swap_kernel(const 
       const uint64_t bdesc0 = make_smem_desc(smem_a + L::W_BYTES, 16, 1024, SWIZZLE_128B);
       const uint64_t sfdesc0 = make_smem_desc(smem_a + L::SF_OFFSET, 16, 128, SWIZZLE_NONE);
       const uint32_t tfull_a = smem_u32(tfull), tempty_a = smem_u32(tempty);
-      const uint32_t t_sfb = tmem_base + SFB_COL;
+      const uint32_t t_sfb_one = tmem_base + SFB_COL;
+      const bool mx_x = p.x_sf != nullptr;
       uint32_t s = 0, ph = 0, tcount = 0, kpar = 0;
       bool ok = true, ready = false;
       for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x) {
@@ -405,7 +494,12 @@ __global__ void __launch_bounds__(M4_THREADS, 1) moe_gemm_mx4_swap_kernel(const 
           const uint32_t s1 = (s + 1 == STAGES) ? 0 : s + 1;
           ready = mbar_test_a(full_a + s1 * 8, s1 == 0 ? ph ^ 1 : ph);
           const uint32_t t_sfa = tmem_base + SFA_COL0 + kpar * 4;
-          tmem_cp_32x128b_warpx4(t_sfa, sfdesc0 + (uint64_t)((s * 512) >> 4));
+          tmem_cp_32x128b_warpx4(t_sfa, sfdesc0 + (uint64_t)((s * L::SF_BYTES) >> 4));
+          uint32_t t_sfb = t_sfb_one;
+          if (mx_x) {
+            t_sfb = tmem_base + SFX_COL0 + kpar * 4;
+            tmem_cp_32x128b_warpx4(t_sfb, sfdesc0 + (uint64_t)((s * L::SF_BYTES + 512) >> 4));
+          }
           const uint64_t ad = adesc0 + (uint64_t)(s * (L::STAGE_BYTES >> 4));
           const uint64_t bd = bdesc0 + (uint64_t)(s * (L::STAGE_BYTES >> 4));
           umma_mxf8_ss(tmem_d, ad, bd, p.idesc[0], t_sfa, t_sfb, accum);
@@ -429,6 +523,8 @@ __global__ void __launch_bounds__(M4_THREADS, 1) moe_gemm_mx4_swap_kernel(const 
     void* const y = p.y;
     const long long ldy = p.ldy;
     const float acc_scale = p.x_scale ? __ldg(p.x_scale) : 1.f;
+    uint8_t* const y_sf = p.y_sf;
+    const long long ld_ysf = p.ld_ysf;
     const uint32_t tempty_a = smem_u32(tempty);
     uint32_t tcount = 0;
     for (int unit = blockIdx.x; unit < units; unit += gridDim.x) {
@@ -460,6 +556,21 @@ __global__ void __launch_bounds__(M4_THREADS, 1) moe_gemm_mx4_swap_kernel(const 
         if (out_row >= rows_y) out_row = -1;
         const float gamma = p.gammas ? __ldg(p.gammas + sr) : 1.f;
         float f = __uint_as_float(v[c]) * acc_scale + b;
+        if (y_sf) {
+          // MX-quantised output (no SwiGLU here): the warp's 32 columns are one block of this token's row
+          const float o = f * gamma;
+          float amax = fabsf(o);
+#pragma unroll
+          for (int d = 16; d > 0; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, d));
+          const float max_finite = out_kind == MOE_OUT_E5M2 ? 57344.f : 448.f;
+          const uint32_t bits = (__float_as_uint(__fdiv_rn(amax, max_finite)) + 0x007FFFFFu) & 0x7F800000u;
+          const float inv = bits == 0u ? 0.f : __frcp_rn(__uint_as_float(bits));
+          if (out_row >= 0) {
+            moe_store_one(y, (long long)out_row * ldy + col, o * inv, out_kind);
+            if (lane == 0) y_sf[(long long)out_row * ld_ysf + (col >> 5)] = (uint8_t)(bits >> 23);
+          }
+          continue;
+        }
         if (swiglu) {
           const float other = __shfl_xor_sync(0xffffffffu, f, 1);  // (gate, linear) are adjacent columns
           if ((lane & 1) == 0 && out_row >= 0 && col < n) {
@@ -502,6 +613,14 @@ extern "C" int tb200_moe_gemm_mx4(const tb200_moe_gemm_mx4_args* a, void* stream
     return TB200_ERR_BAD_ARG;
   if (a->rows_x > INT32_MAX - 1 || a->rows_y > INT32_MAX || a->k > INT32_MAX || a->n > INT32_MAX)
     return TB200_ERR_UNSUPPORTED;
+  if (a->x_mx_scale && ((reinterpret_cast<uintptr_t>(a->x_mx_scale) & 3) || (a->ld_x_mx_scale % 4) ||
+                        a->ld_x_mx_scale < a->k / 32))
+    return TB200_ERR_BAD_ARG;
+  if (a->y_mx_scale) {
+    const int64_t n_out = a->swiglu ? a->n / 2 : a->n;
+    if (a->out_dtype != TB200_E4M3 && a->out_dtype != TB200_E5M2) return TB200_ERR_BAD_ARG;
+    if (a->ld_y_mx_scale < (n_out + 31) / 32) return TB200_ERR_BAD_ARG;
+  }
   if (a->n_sched == 0 || a->rows_x == 0) return TB200_OK;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   const int sms = sm_count();
@@ -509,6 +628,8 @@ extern "C" int tb200_moe_gemm_mx4(const tb200_moe_gemm_mx4_args* a, void* stream
 
   const bool swap = a->block_rows == S4_XROWS;
   if (!swap && a->block_rows != 0 && a->block_rows != M4_BM) return TB200_ERR_BAD_ARG;
+  // the swapped kernel quantises a warp's 32 columns as one block; with SwiGLU a block would span two warps
+  if (swap && a->y_mx_scale && a->swiglu) return TB200_ERR_UNSUPPORTED;
   Mx4Params p;
   memset(&p, 0, sizeof(p));
   {
@@ -539,6 +660,11 @@ extern "C" int tb200_moe_gemm_mx4(const tb200_moe_gemm_mx4_args* a, void* stream
   p.gammas = a->gammas;
   p.bias = a->bias;
   p.x_scale = a->x_scale;
+  p.x_sf = static_cast<const uint8_t*>(a->x_mx_scale);
+  p.ld_xsf = a->ld_x_mx_scale;
+  p.y_sf = static_cast<uint8_t*>(a->y_mx_scale);
+  p.ld_ysf = a->ld_y_mx_scale;
+  p.rows_x = (int)a->rows_x;
   p.y = a->y;
   p.ldy = a->ldy;
   p.status = status_ptr();

@@ -7,13 +7,18 @@ buffer of the rank that owns the token (peer stores over NVLink; the reference's
 ``matmul_details/_p_matmul.py:755-782``).
 ``betas`` (per-row factor on the bias), ``out_alpha`` and ``c_acc_in`` (a matrix added to the result) follow the
 reference's epilogue order (``_p_matmul.py:606-622``).
-Unsupported combinations (MX / flexpoint precision, batched input, ragged K, custom epilogues) raise
+``precision_config.c_mx_scale`` with ``epilogue=Epilogue(FnSpecs(FnName.QUANTIZE_MXFP8.name, quantize_mxfp8_fn, ...))``
+returns the output MX-quantised (fp8 values + one e8m0 scale per 32 outputs of a row written to ``c_mx_scale``,
+``matmul.py:362-366`` / ``_p_matmul.py:650-704``); ``precision_config.a_mx_scale`` makes the fp8 activations of the
+MXFP4-weight path MXFP8 (one e8m0 scale per 32 values of K, fed to the block-scaled MMA).
+Unsupported combinations (flexpoint / NVFP4 precision, batched input, ragged K, other epilogues) raise
 ``NotImplementedError``, as the reference does for combinations it
 cannot serve (``:288,437-447,467``)."""
 from __future__ import annotations
 
 import ctypes
 from dataclasses import dataclass
+from enum import Enum, auto
 
 import torch
 
@@ -37,6 +42,13 @@ class FnSpecs:
         return FnSpecs("dflt", None, tuple())
 
 
+class FnName(Enum):
+    """Names of the quantising epilogues (``triton_kernels/matmul.py:53-56`` in the reference)."""
+    QUANTIZE_MXFP8 = auto()
+    QUANTIZE_MXFP4 = auto()
+    QUANTIZE_NVFP4 = auto()
+
+
 @dataclass(frozen=True)
 class FusedActivation:
     specs: FnSpecs = FnSpecs.default()
@@ -57,10 +69,14 @@ class PrecisionConfig:
     allow_tf32: bool = True
     acc_scale: float = 1.0
     out_dtype: torch.dtype | None = None
-    a_mx_scale: object = None
+    a_mx_scale: object = None  # e8m0 block scales of MXFP8 activations: [rows, K/32] uint8 (with an MXFP4 weight)
+    a_microblock_size: int | None = None
     b_mx_scale: object = None  # e8m0 scales of an MXFP4 weight: [E, K/32, N] uint8, or the Tensor convert_layout returns
     b_microblock_size: int | None = None
+    # MX-quantised output (with epilogue = Epilogue(FnSpecs(FnName.QUANTIZE_MXFP8.name, quantize_mxfp8_fn, ...))): a
+    # [rows, ceil(N_out / 32)] uint8 tensor that receives the e8m0 scales; the values come back as fp8
     c_mx_scale: object = None
+    c_microblock_size: int | None = None
     x_scale: object = None     # one fp32 value multiplying the fp8 activations (the reference's flexpoint scale)
 
 
@@ -98,18 +114,36 @@ def matmul(a, b, bias, a_ragged_metadata: RaggedTensorMetadata | None = None, b_
     if fused_comm is not None and (c is not None or (precision_config is not None
                                                      and precision_config.b_mx_scale is not None)):
         raise NotImplementedError("matmul: fused_comm takes the 16-bit path and owns the output buffers")
+    quantize_out = False
     if epilogue is not None and epilogue.specs.name != "dflt":
-        raise NotImplementedError("matmul: custom epilogues are not implemented")
-    if precision_config is not None and (precision_config.a_mx_scale is not None
-                                         or precision_config.c_mx_scale is not None):
-        raise NotImplementedError("matmul: MX-scaled activations / outputs are not implemented")
+        if epilogue.specs.name != FnName.QUANTIZE_MXFP8.name:
+            raise NotImplementedError(f"matmul: epilogue {epilogue.specs.name!r} (the MXFP8 quantising epilogue is implemented)")
+        if precision_config is None or precision_config.c_mx_scale is None:
+            raise ValueError("matmul: the quantising epilogue needs precision_config.c_mx_scale")
+        quantize_out = True
+    if precision_config is not None and precision_config.c_mx_scale is not None:
+        if not quantize_out:
+            raise ValueError("matmul: precision_config.c_mx_scale needs epilogue = the MXFP8 quantising epilogue")
+        if fused_comm is not None:
+            raise NotImplementedError("fused comm with output MX scales is not supported")  # as the reference (:287)
+        if c_acc_in is not None or c is not None:
+            raise NotImplementedError("matmul: MX-quantised output with c / c_acc_in is not implemented")
+        if precision_config.c_microblock_size not in (None, 32):
+            raise NotImplementedError("matmul: microblock size 32 (e8m0 scales) only")
+    if precision_config is not None and precision_config.a_mx_scale is not None:
+        if precision_config.b_mx_scale is None or not isinstance(a, torch.Tensor) or a.dtype not in _F8:
+            raise NotImplementedError("matmul: MX-scaled activations are implemented as MXFP8 x MXFP4 "
+                                      "(fp8 values, precision_config.a_mx_scale and b_mx_scale)")
+        if precision_config.a_microblock_size not in (None, 32):
+            raise NotImplementedError("matmul: microblock size 32 (e8m0 scales) only")
     if precision_config is not None and precision_config.b_mx_scale is not None:
         if isinstance(a, torch.Tensor) and a.dtype in _DT:
             # 16-bit activations: the weight is upcast to the activation dtype (what the reference's
             # tl.dot_scaled(x, None, "bf16", w, w_scales, "e2m1") computes), then the 16-bit grouped GEMM runs
             w16 = upcast_mxfp4_weight(b, precision_config.b_mx_scale, a.dtype,
                                       precision_config.b_microblock_size)
-            pc16 = PrecisionConfig(out_dtype=precision_config.out_dtype)
+            pc16 = PrecisionConfig(out_dtype=precision_config.out_dtype, c_mx_scale=precision_config.c_mx_scale,
+                                   c_microblock_size=precision_config.c_microblock_size)
             return matmul(a, w16, bias, a_ragged_metadata, None, gather_indx, scatter_indx, pc16, None, gammas,
                           None, c, None, fused_activation, epilogue, None, _tile_mode)
         if c is not None:
@@ -121,6 +155,10 @@ def matmul(a, b, bias, a_ragged_metadata: RaggedTensorMetadata | None = None, b_
             if a.stride(1) != 1 or a.stride(0) % 16 or a.shape[1] % 16:
                 a = a.contiguous()
             a = _gather_rows(a.view(torch.uint8), gather_indx).view(a.dtype)
+            if precision_config.a_mx_scale is not None:  # the rows' block scales travel with them
+                import dataclasses
+                sc = _plain_scale(precision_config.a_mx_scale)
+                precision_config = dataclasses.replace(precision_config, a_mx_scale=_gather_scale_rows(sc, gather_indx))
         return _matmul_mx4(a, b, bias, a_ragged_metadata, scatter_indx, precision_config, gammas, fused_activation)
     if not isinstance(a, torch.Tensor) or not isinstance(b, torch.Tensor):
         raise NotImplementedError("matmul: wrapped Tensor operands need precision_config.b_mx_scale (MXFP4 weights)")
@@ -170,7 +208,16 @@ def matmul(a, b, bias, a_ragged_metadata: RaggedTensorMetadata | None = None, b_
     sched = md.block_schedule(128)
     rows_y = R if scatter_indx is None else scatter_indx.shape[0]
     out_dtype = a.dtype
-    if precision_config is not None and precision_config.out_dtype not in (None, a.dtype):
+    c_sf = None
+    if quantize_out:
+        # MX-quantised output: fp8 values (e4m3 unless out_dtype says e5m2) + the caller's scale tensor
+        out_dtype = precision_config.out_dtype or torch.float8_e4m3fn
+        if out_dtype not in _F8:
+            raise NotImplementedError("matmul: MX-quantised output is fp8 (e4m3fn / e5m2)")
+        c_sf = _plain_scale(precision_config.c_mx_scale)
+        assert c_sf.shape == (rows_y, (n_out + 31) // 32) and c_sf.stride(1) == 1, \
+            "c_mx_scale: [rows, ceil(N_out / 32)] uint8, row-major"
+    elif precision_config is not None and precision_config.out_dtype not in (None, a.dtype):
         raise NotImplementedError("matmul: out_dtype different from the input dtype")
     peers = None
     if fused_comm is not None:
@@ -223,6 +270,8 @@ def matmul(a, b, bias, a_ragged_metadata: RaggedTensorMetadata | None = None, b_
     if c_acc_in is not None:
         assert c_acc_in.shape == c.shape and c_acc_in.dtype == c.dtype and c_acc_in.stride(1) == 1
         args.c_acc_in, args.ld_acc_in = c_acc_in.data_ptr(), c_acc_in.stride(0)
+    if c_sf is not None:
+        args.y_mx_scale, args.ld_y_mx_scale, args.y_mx_dtype = c_sf.data_ptr(), c_sf.stride(0), _F8[out_dtype]
     args.moe_tile_mode = int(_tile_mode)  # extension: 0 choose, 1 one CTA per block, 2 CTA pair per two blocks
     # extension: gammas holds one value per OUTPUT row (e.g. the top-k values in (token, slot) order) instead of per sorted row
     args.gammas_by_out_row = 1 if _gammas_by_out_row else 0
@@ -247,6 +296,29 @@ def _gather_rows(a, gather_indx):
                                           gi.data_ptr(), gi.numel(), a.shape[1] * esz,
                                           ctypes.c_void_p(_lib.current_stream_ptr(a.device)))
     _lib.check(rc, "tb200_gather_rows")
+    return out
+
+
+def _plain_scale(t):
+    """A scale tensor given plain or wrapped (strided layout) as the plain uint8 tensor."""
+    from .tensor import Tensor
+    if isinstance(t, Tensor):
+        from .tensor_details.layout import StridedLayout
+        if t.layout is not None and not isinstance(t.layout, StridedLayout):
+            raise NotImplementedError("matmul: activation / output MX scales in a strided (row-major) layout only")
+        t = t.data
+    if t.dtype != torch.uint8:
+        raise NotImplementedError("matmul: MX scales are e8m0 bytes (torch.uint8)")
+    return t
+
+
+def _gather_scale_rows(sc, gather_indx):
+    if sc.stride(1) == 1 and sc.shape[1] % 16 == 0 and sc.stride(0) % 16 == 0:
+        return _gather_rows(sc, gather_indx)
+    gi = gather_indx.long()
+    ok = (gi >= 0) & (gi < sc.shape[0])
+    out = sc[gi.clamp(0, max(sc.shape[0] - 1, 0))]
+    out[~ok] = 127
     return out
 
 
@@ -320,8 +392,9 @@ def _matmul_mx4(a, b, bias, a_ragged_metadata, scatter_indx, pc: PrecisionConfig
         assert E == 1, "several weight matrices need a_ragged_metadata"
         a_ragged_metadata = make_ragged_tensor_metadata(torch.tensor([R], dtype=torch.int32, device=dev), R)
     md = a_ragged_metadata
-    # few rows per expert (decode): the 32-row schedule and the kernel with swapped operand roles
-    block_rows = 32 if R <= 32 * E else 128
+    # few rows per expert (decode): the 32-row schedule and the kernel with swapped operand roles (which cannot
+    # quantise a SwiGLU output: a block of 32 outputs would span two of its warps)
+    block_rows = 32 if R <= 32 * E and not (swiglu and pc.c_mx_scale is not None) else 128
     sched = md.block_schedule(block_rows)
     rows_y = R if scatter_indx is None else scatter_indx.shape[0]
     out_dtype = pc.out_dtype or a.dtype  # as the reference: the activation dtype (fp8) unless asked otherwise
@@ -329,6 +402,18 @@ def _matmul_mx4(a, b, bias, a_ragged_metadata, scatter_indx, pc: PrecisionConfig
     if out_dtype not in out_codes:
         raise NotImplementedError("matmul (MXFP4 weight): bf16 / fp16 / fp8 output")
     c = (torch.zeros if scatter_indx is not None else torch.empty)((rows_y, n_out), dtype=out_dtype, device=dev)
+    a_sf = c_sf = None
+    if pc.a_mx_scale is not None:
+        a_sf = _plain_scale(pc.a_mx_scale)
+        assert a_sf.shape == (R, K // 32), "a_mx_scale: one e8m0 byte per 32 values of K, [rows, K/32]"
+        if a_sf.stride(1) != 1 or a_sf.stride(0) % 4 or a_sf.data_ptr() % 4:
+            a_sf = a_sf.contiguous()
+    if pc.c_mx_scale is not None:
+        if out_dtype not in _F8:
+            raise NotImplementedError("matmul: MX-quantised output is fp8 (e4m3fn / e5m2)")
+        c_sf = _plain_scale(pc.c_mx_scale)
+        assert c_sf.shape == (rows_y, (n_out + 31) // 32) and c_sf.stride(1) == 1, \
+            "c_mx_scale: [rows, ceil(N_out / 32)] uint8, row-major"
     si = None if scatter_indx is None else scatter_indx.to(torch.int32).contiguous()
     gm = None if gammas is None else gammas.float().contiguous()
     bs = None if bias is None else bias.float().reshape(E, N).contiguous()
@@ -353,6 +438,10 @@ def _matmul_mx4(a, b, bias, a_ragged_metadata, scatter_indx, pc: PrecisionConfig
     args.swiglu_limit = float(limit) if limit is not None else 0.0
     args.swiglu_has_limit = 1 if limit is not None else 0
     args.block_rows = block_rows
+    if a_sf is not None:
+        args.x_mx_scale, args.ld_x_mx_scale = a_sf.data_ptr(), a_sf.stride(0)
+    if c_sf is not None:
+        args.y_mx_scale, args.ld_y_mx_scale = c_sf.data_ptr(), c_sf.stride(0)
     with torch.cuda.device(dev):
         rc = _lib.lib().tb200_moe_gemm_mx4(ctypes.byref(args), ctypes.c_void_p(_lib.current_stream_ptr(dev)))
     _lib.check(rc, "tb200_moe_gemm_mx4")

@@ -118,3 +118,18 @@ def upcast_from_mxfp(tensor: torch.Tensor, scale: torch.Tensor, target_dtype: to
 # the reference exposes the torch implementations under these names as well
 downcast_to_mxfp_torch = downcast_to_mxfp
 upcast_from_mxfp_torch = upcast_from_mxfp
+
+
+def _epilogue_marker(name):
+    def fn(*_args, **_kwargs):
+        raise RuntimeError(f"{name} names the quantising epilogue of triton_kernels.matmul.matmul (it runs inside the "
+                           "GEMM kernel's epilogue); it is not callable on its own")
+    fn.__name__ = name
+    return fn
+
+
+# What the reference passes as ``FnSpecs(FnName.QUANTIZE_MXFP8.name, quantize_mxfp8_fn, (), ())`` (jitted device
+# functions there, numerics_details/mxfp.py:452-454). Here the name selects the epilogue; the objects are markers.
+quantize_mxfp8_fn = _epilogue_marker("quantize_mxfp8_fn")
+quantize_mxfp4_fn = _epilogue_marker("quantize_mxfp4_fn")
+quantize_nvfp4_fn = _epilogue_marker("quantize_nvfp4_fn")
