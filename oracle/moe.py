@@ -13,6 +13,8 @@ Each function restates the torch twin that the reference's own tests use as grou
   reduce_ref                 <- reduce_torch                         reduce.py:1173-1206
   moe_layer_ref              <- mixture_of_expt_nosharded            tests/test_distributed.py:201-218
                                 (plus the gate-weighted combine of the MoE benchmark configuration)
+  batched_matmul_ref         <- matmul_torch, batched inputs          matmul.py:864-898
+  ragged_k_matmul_ref        <- matmul_torch, b_ragged_metadata       matmul.py:836-861
   quantize_mxfp8_ref         <- downcast_to_mxfp_torch (fp8, e8m0,   numerics_details/mxfp.py:212-318
                                 ROUND_UP), the twin of the quantize_mxfp8_fn matmul epilogue
   dequantize_mxfp8_ref       <- upcast_from_mxfp_torch (fp8)         numerics_details/mxfp.py:384-449
@@ -207,6 +209,32 @@ def grouped_matmul_ref(a, w, bias=None, slice_sizes=None, gather_indx=None, scat
     msk = si != -1
     out[si[msk]] = y[msk]
     return out
+
+
+def batched_matmul_ref(a, w, bias=None, swiglu=None, out_dtype=None) -> torch.Tensor:
+    """[B, M, K] x [B, K, N] (+ bias [B, N]) -> [B, M, N]: one independent product per batch entry."""
+    a32, w32 = a.detach().cpu().float(), w.detach().cpu().float()
+    y = torch.matmul(a32, w32)
+    if bias is not None:
+        y = y + bias.detach().cpu().float()[:, None, :]
+    if swiglu is not None:
+        y = swiglu_ref(y, swiglu[0], swiglu[1])
+    return y.to(out_dtype or a.dtype)
+
+
+def ragged_k_matmul_ref(a, w, slice_sizes, a_slice_offs=None, w_slice_offs=None, out_dtype=None) -> torch.Tensor:
+    """Ragged K: out[e] = a[:, xo_e : xo_e + k_e] @ w[wo_e : wo_e + k_e, :] for every slice e (zeros for an empty
+    slice). a: [M, K_total]; w: [K_total, N]; the offsets default to the cumulative slice sizes."""
+    a32, w32 = a.detach().cpu().float(), w.detach().cpu().float()
+    ss = np.asarray(slice_sizes).astype(np.int64)
+    cum = np.concatenate([[0], np.cumsum(ss)])
+    xo = cum if a_slice_offs is None else np.asarray(a_slice_offs).astype(np.int64)
+    wo = cum if w_slice_offs is None else np.asarray(w_slice_offs).astype(np.int64)
+    out = torch.zeros(len(ss), a32.shape[0], w32.shape[1], dtype=torch.float32)
+    for e, k in enumerate(ss):
+        if k:
+            out[e] = a32[:, int(xo[e]):int(xo[e] + k)] @ w32[int(wo[e]):int(wo[e] + k), :]
+    return out.to(out_dtype or a.dtype)
 
 
 def reduce_ref(x: torch.Tensor, dim: int, mask=None, scale=None) -> torch.Tensor:

@@ -237,5 +237,22 @@ put("rd_y_scale", reduce_torch(xr, 1, scale=sc, x_flex=None, y_flex=None)[0])
 put("rd_y_both", reduce_torch(xr, 1, mask=mask, scale=sc, x_flex=None, y_flex=None)[0])
 put("rd_y_both_bf16", reduce_torch(xr.to(torch.bfloat16), 1, mask=mask, scale=sc, x_flex=None, y_flex=None)[0])
 
+# -- batched matmul: [B, M, K] x [B, K, N] + bias [B, N] (matmul.py:864-868, 893-898)
+Bb, Mb, Kb, Nb = 3, 10, 32, 24
+ab = bf(torch.randn(Bb, Mb, Kb, generator=g))
+wb = bf(torch.randn(Bb, Kb, Nb, generator=g) * 0.2)
+biasb = torch.randn(Bb, Nb, generator=g)
+put("bt_a", ab), put("bt_w", wb), put("bt_bias", biasb)
+put("bt_y", matmul_torch(ab, wb, biasb, precision_config=PLAIN))
+
+# -- ragged K: out[e] = a[:, ks_e] @ b[ks_e, :] with one empty slice (matmul.py:836-861)
+ks = torch.tensor([16, 0, 40, 8], dtype=torch.int32)
+Ktot, Mr, Nr = int(ks.sum()), 12, 20
+ar = bf(torch.randn(Mr, Ktot, generator=g))
+wr = bf(torch.randn(Ktot, Nr, generator=g) * 0.2)
+rgk = make_ragged_tensor_metadata_torch(ks, Ktot)
+put("rk_a", ar), put("rk_w", wr), put("rk_sizes", ks)
+put("rk_y", matmul_torch(ar, wr, None, rgk, rgk, precision_config=PLAIN))
+
 np.savez_compressed(__file__.rsplit("/", 1)[0] + "/moe_cases.npz", **out)
 print("wrote", len(out), "arrays")

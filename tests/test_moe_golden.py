@@ -7,6 +7,8 @@ import numpy as np
 import pytest
 import torch
 
+from oracle import moe as o
+
 pytestmark = pytest.mark.gpu
 
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
@@ -113,3 +115,49 @@ def test_swiglu_and_reduce_match_reference_twins(cuda, fx):
     np.testing.assert_allclose(reduce(xr, 1, scale=sc)[0].cpu().float().numpy(), fx["rd_y_scale"], **tol)
     got = reduce(xr, 1, mask=mask, scale=sc)[0]
     np.testing.assert_allclose(got.cpu().float().numpy(), fx["rd_y_both_bf16"], rtol=2 ** -7, atol=2 ** -7)
+
+
+def test_batched_matmul_matches_reference_twin(cuda, fx):
+    """[B, M, K] x [B, K, N] + bias against matmul_torch's output (bf16 run of fp32 fixture values: the reference's
+    bf16 tolerance), and a larger case against the oracle."""
+    from triton_b200.triton_kernels.matmul import matmul, swiglu_activation
+    d = fx
+    a, w, bias = (torch.from_numpy(d[k]) for k in ("bt_a", "bt_w", "bt_bias"))
+    y = matmul(a.to(torch.bfloat16).to(cuda), w.to(torch.bfloat16).to(cuda), bias.to(cuda))
+    assert y.shape == (3, 10, 24)
+    torch.testing.assert_close(y.cpu().float(), torch.from_numpy(d["bt_y"]), rtol=2e-2, atol=2e-2)
+    g = torch.Generator().manual_seed(5)
+    a = torch.randn(4, 200, 192, generator=g).to(torch.bfloat16)
+    w = (0.1 * torch.randn(4, 192, 320, generator=g)).to(torch.bfloat16)
+    y = matmul(a.to(cuda), w.to(cuda), None, fused_activation=swiglu_activation(1.0, None))
+    ref = o.batched_matmul_ref(a, w, None, swiglu=(1.0, None))
+    torch.testing.assert_close(y.cpu().float(), ref.float(), rtol=2e-2, atol=2e-2)
+    with pytest.raises(ValueError):
+        matmul(a.to(cuda), w.to(cuda), None, gather_indx=torch.zeros(4, dtype=torch.int32, device=cuda))
+
+
+def test_ragged_k_matmul_matches_reference_twin(cuda, fx):
+    """b_ragged_metadata: out[e] = a[:, ks_e] @ b[ks_e, :] against matmul_torch's output (one empty slice), and a
+    larger case (K slices of 128 .. 512, one empty) against the oracle."""
+    from triton_b200.triton_kernels.matmul import matmul
+    from triton_b200.triton_kernels.tensor import make_ragged_tensor_metadata
+    d = fx
+    a, w = torch.from_numpy(d["rk_a"]), torch.from_numpy(d["rk_w"])
+    ks = torch.from_numpy(d["rk_sizes"]).to(cuda)
+    md = make_ragged_tensor_metadata(ks, int(ks.sum()))
+    y = matmul(a.to(torch.bfloat16).to(cuda), w.to(torch.bfloat16).to(cuda), None, md, md)
+    assert y.shape == (4, 12, 20)
+    torch.testing.assert_close(y.cpu().float(), torch.from_numpy(d["rk_y"]), rtol=2e-2, atol=2e-2)
+    assert float(y[1].abs().max()) == 0.0
+    g = torch.Generator().manual_seed(6)
+    sizes = torch.tensor([256, 0, 128, 512, 136], dtype=torch.int32)
+    K = int(sizes.sum())
+    a = torch.randn(300, K, generator=g).to(torch.float16)
+    w = (0.1 * torch.randn(K, 264, generator=g)).to(torch.float16)
+    md = make_ragged_tensor_metadata(sizes.to(cuda), K)
+    y = matmul(a.to(cuda), w.to(cuda), None, md, md)
+    ref = o.ragged_k_matmul_ref(a, w, sizes.numpy())
+    torch.testing.assert_close(y.cpu().float(), ref.float(), rtol=2e-2, atol=2e-2)
+    bad = make_ragged_tensor_metadata(torch.tensor([5, K - 5], dtype=torch.int32, device=cuda), K)
+    with pytest.raises(NotImplementedError):  # the second slice starts at element 5
+        matmul(a.to(cuda), w.to(cuda), None, bad, bad)

@@ -267,3 +267,15 @@ def test_quantize_mxfp8_oracle_matches_reference_twin():
         assert np.array_equal(s.numpy(), d[f"{name}_e4m3_ROUND_UP_s"]), name
         up = o_moe.dequantize_mxfp8_ref(q, s)
         assert np.array_equal(up.numpy(), d[f"{name}_e4m3_ROUND_UP_up"]), name
+
+
+def test_batched_and_ragged_k_oracles_match_reference_twin():
+    """oracle.moe.batched_matmul_ref / ragged_k_matmul_ref against matmul_torch outputs (batched inputs with bias;
+    K-ragged slices with an empty slice) in moe_cases.npz."""
+    d = np.load(os.path.join(GOLDEN, "moe_cases.npz"))
+    t = lambda k: torch.from_numpy(d[k])
+    y = o_moe.batched_matmul_ref(t("bt_a"), t("bt_w"), t("bt_bias"))
+    torch.testing.assert_close(y, t("bt_y"), rtol=1e-5, atol=1e-5)
+    y = o_moe.ragged_k_matmul_ref(t("rk_a"), t("rk_w"), d["rk_sizes"])
+    torch.testing.assert_close(y, t("rk_y"), rtol=1e-5, atol=1e-5)
+    assert float(y[1].abs().max()) == 0.0

@@ -285,7 +285,12 @@ struct MxPairSmem {
   // own SFA atom (512 B) + both SFB atoms as one 128-row x 32-byte matrix (4 KB): row L = the 16 bytes of row
   // L % 32 of each atom, in 8-row core groups [group][atom][8 rows x 16 B], so that ONE tcgen05.cp.128x256b fills the
   // eight SFB columns (a scale copy costs ~57 tensor-pipe cycles that do not overlap the MMAs: measured 773 cycles
-  // per K step with three copies, 716 with two)
+  // per K step with three copies, 716 with two). Taking the copies off the tensor pipe altogether was tried: four
+  // extra warps per CTA read the atoms from shared memory and wrote the scale columns with tcgen05.st (one 16-column
+  // store per K step and lane quarter, a barrier per stage towards the MMA thread, with the scale ring on the
+  // operand stages and then as a 16-deep ring of its own): 1360-1430 TFLOP/s against 2240-2300 in the same runs -
+  // a tcgen05.st issued while MMAs stream takes about a K step's time to complete, so the stores, not the copies,
+  // became the critical path.
   static constexpr int SF_BYTES = 512 + 4096;
   static constexpr int SF_OFFSET = STAGES * STAGE_BYTES;
   static constexpr int BAR_OFFSET = SF_OFFSET + STAGES * SF_BYTES;

@@ -78,11 +78,6 @@ struct Mx4Smem {
   static constexpr int TOTAL = BAR_OFFSET + (2 * M4_STAGES + 2) * 8 + 16 + 1024;
 };
 
-__device__ __forceinline__ void tmem_st_32x32b_x4(uint32_t taddr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-  asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(a), "r"(b), "r"(c), "r"(d)
-               : "memory");
-}
-
 __global__ void __launch_bounds__(M4_THREADS, 1) moe_gemm_mx4_kernel(const __grid_constant__ Mx4Params p) {
   using L = Mx4Smem;
   constexpr int BN = M4_BN, STAGES = M4_STAGES;

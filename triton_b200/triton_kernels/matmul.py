@@ -11,7 +11,9 @@ reference's epilogue order (``_p_matmul.py:606-622``).
 returns the output MX-quantised (fp8 values + one e8m0 scale per 32 outputs of a row written to ``c_mx_scale``,
 ``matmul.py:362-366`` / ``_p_matmul.py:650-704``); ``precision_config.a_mx_scale`` makes the fp8 activations of the
 MXFP4-weight path MXFP8 (one e8m0 scale per 32 values of K, fed to the block-scaled MMA).
-Unsupported combinations (flexpoint / NVFP4 precision, batched input, ragged K, other epilogues) raise
+Batched inputs (``[B, M, K] x [B, K, N]``) run as the grouped kernel with one slice per batch entry; ragged K
+(``b_ragged_metadata``) as one dense GEMM per slice.
+Unsupported combinations (flexpoint / NVFP4 precision, other epilogues) raise
 ``NotImplementedError``, as the reference does for combinations it
 cannot serve (``:288,437-447,467``)."""
 from __future__ import annotations
@@ -105,7 +107,18 @@ def matmul(a, b, bias, a_ragged_metadata: RaggedTensorMetadata | None = None, b_
            gammas=None, out_alpha=None, c=None, fused_comm=None, fused_activation: FusedActivation | None = None,
            epilogue: Epilogue | None = None, c_acc_in=None, _tile_mode: int = 0, _gammas_by_out_row: bool = False):
     if b_ragged_metadata is not None:
-        raise NotImplementedError("matmul: ragged K (b_ragged_metadata) is not implemented")
+        if (gather_indx is not None or scatter_indx is not None or fused_comm is not None or c_acc_in is not None
+                or (fused_activation is not None and fused_activation.specs.name != "dflt")
+                or (epilogue is not None and epilogue.specs.name != "dflt")
+                or (precision_config is not None and (precision_config.a_mx_scale is not None
+                                                      or precision_config.b_mx_scale is not None
+                                                      or precision_config.c_mx_scale is not None))):
+            raise NotImplementedError("matmul (ragged K): plain 16-bit products only")
+        return _matmul_ragged_k(a, b, a_ragged_metadata, b_ragged_metadata, c)
+    if isinstance(a, torch.Tensor) and a.ndim == 3 and isinstance(b, torch.Tensor) and b.ndim == 3 \
+            and a_ragged_metadata is None:
+        return _matmul_batched(a, b, bias, precision_config, betas, gammas, out_alpha, c, fused_comm, fused_activation,
+                               epilogue, c_acc_in, gather_indx, scatter_indx, _tile_mode)
     if (betas is not None or out_alpha is not None or c_acc_in is not None) and precision_config is not None \
             and precision_config.b_mx_scale is not None:
         raise NotImplementedError("matmul: betas / out_alpha / c_acc_in with an MXFP4 weight are not implemented")
@@ -297,6 +310,64 @@ def _gather_rows(a, gather_indx):
                                           ctypes.c_void_p(_lib.current_stream_ptr(a.device)))
     _lib.check(rc, "tb200_gather_rows")
     return out
+
+
+def _matmul_batched(a, b, bias, precision_config, betas, gammas, out_alpha, c, fused_comm, fused_activation, epilogue,
+                    c_acc_in, gather_indx, scatter_indx, _tile_mode):
+    """Batched inputs ([B, M, K] x [B, K, N] -> [B, M, N], matmul.py:864-868 in the reference): the batch entries are
+    the slices of the grouped kernel - entry i owns rows [i M, (i + 1) M) of the flattened activations and weight
+    matrix i."""
+    if gather_indx is not None or scatter_indx is not None:
+        raise ValueError("gather / scatter are not supported in batched mode")  # asserted in the reference too
+    if fused_comm is not None or c is not None or c_acc_in is not None or betas is not None or gammas is not None:
+        raise NotImplementedError("matmul (batched): bias, fused activation and the quantising epilogue are implemented")
+    B, M, K = a.shape
+    assert b.shape[0] == B and b.shape[1] == K, "batched operands differ in batch size or inner dimension"
+    md = make_ragged_tensor_metadata(torch.full((B, ), M, dtype=torch.int32, device=a.device), B * M)
+    y = matmul(a.reshape(B * M, K), b, bias, md, None, None, None, precision_config, None, None, out_alpha, None, None,
+               fused_activation, epilogue, None, _tile_mode)
+    return y.view(B, M, y.shape[-1])
+
+
+def _matmul_ragged_k(a, b, a_md, b_md, c):
+    """Ragged K (``b_ragged_metadata``; the weight-gradient shape of an MoE layer, matmul.py:836-861 in the
+    reference): ``out[e] = a[:, xo_e : xo_e + k_e] @ b[wo_e : wo_e + k_e, :]`` with the column slices of ``a``
+    described by ``a_ragged_metadata`` (default: the same slices as ``b``) and the row slices of ``b`` by
+    ``b_ragged_metadata``. One dense GEMM (``tb200_gemm``) per non-empty slice on operand views - the slice sizes
+    are read back to the host once; slices must start on multiples of 8 elements (TMA alignment), as the
+    reference asks of K-ragged operands (``slice_sizes_divisibility``)."""
+    from ..tutorials.blackwell_gemm_ws import matmul as dense_matmul
+    if not (isinstance(a, torch.Tensor) and isinstance(b, torch.Tensor) and a.ndim == 2 and b.ndim == 2):
+        raise NotImplementedError("matmul (ragged K): 2-D torch tensors")
+    if not a.is_cuda:
+        raise RuntimeError("triton_b200 matmul needs CUDA tensors (there is no CPU path)")
+    if a.dtype not in _DT or b.dtype != a.dtype:
+        raise NotImplementedError(f"matmul (ragged K): dtype {a.dtype}/{b.dtype} (bf16 and fp16 are implemented)")
+    a_md = a_md or b_md
+    sizes = b_md.slice_sizes.tolist()
+    xo, wo = a_md.slice_offs.tolist(), b_md.slice_offs.tolist()
+    E, M, N = len(sizes), a.shape[0], b.shape[1]
+    if c is None:
+        c = torch.empty((E, M, N), dtype=a.dtype, device=a.device)
+    assert c.shape == (E, M, N) and c.dtype == a.dtype and c.stride(2) == 1
+    # row pitches that are no multiple of 16 bytes (N or K_total not a multiple of 8): work on padded copies
+    n8 = (N + 7) // 8 * 8
+    if a.stride(1) != 1 or a.stride(0) % 8 or a.data_ptr() % 16:
+        a = torch.nn.functional.pad(a, (0, (-a.shape[1]) % 8))
+    if n8 != N or b.stride(1) != 1 or b.stride(0) % 8 or b.data_ptr() % 16:
+        b = torch.nn.functional.pad(b, (0, n8 - N))
+    work = c if (n8 == N and c.stride(1) % 8 == 0 and c.data_ptr() % 16 == 0) else \
+        torch.empty((E, M, n8), dtype=a.dtype, device=a.device)
+    for e, k in enumerate(sizes):
+        if k == 0:
+            work[e].zero_()
+            continue
+        if xo[e] % 8 or wo[e] % 8:
+            raise NotImplementedError("matmul (ragged K): slices must start on multiples of 8 elements")
+        dense_matmul(a[:, xo[e]:xo[e] + k], b[wo[e]:wo[e] + k, :], out=work[e])
+    if work is not c:
+        c.copy_(work[..., :N])
+    return c
 
 
 def _plain_scale(t):

@@ -45,7 +45,8 @@ def get_heuristic_config(M, N, K, num_sms=148, dtype=torch.bfloat16, b_k_major=T
             "SPLIT_K": out[3], "NUM_SMEM_BUFFERS": out[4]}
 
 
-def matmul(a: torch.Tensor, b: torch.Tensor, config=None) -> torch.Tensor:
+def matmul(a: torch.Tensor, b: torch.Tensor, config=None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``out`` (extension): an (M, N) tensor of ``a.dtype`` with unit column stride that receives the product."""
     assert a.dim() == 2 and b.dim() == 2, "matmul expects 2-D operands"
     assert a.shape[1] == b.shape[0], "Incompatible dimensions"
     if not a.is_cuda or not b.is_cuda:
@@ -54,7 +55,11 @@ def matmul(a: torch.Tensor, b: torch.Tensor, config=None) -> torch.Tensor:
     assert a.device == b.device
     M, K = a.shape
     _, N = b.shape
-    c = torch.empty((M, N), device=a.device, dtype=a.dtype)
+    if out is not None:
+        assert out.shape == (M, N) and out.dtype == a.dtype and out.device == a.device and out.stride(1) == 1
+        c = out
+    else:
+        c = torch.empty((M, N), device=a.device, dtype=a.dtype)
     if M == 0 or N == 0:
         return c
     if K == 0:
