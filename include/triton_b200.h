@@ -620,6 +620,17 @@ typedef struct {
    * the 32-row schedule (TB200_ERR_UNSUPPORTED: use the 128-row schedule). NULL = plain output. */
   void* y_mx_scale;
   int64_t ld_y_mx_scale;
+  /* Flexpoint (precision_config.flex_ctx, matmul.py:116-121; numerics_details/flexpoint.py:133-188): device
+   * scalars. w_flex_scale multiplies every accumulator like x_scale (rhs_data.scale; x_scale is lhs_data.scale).
+   * y_expected_scale: the finished output is divided by it before the conversion (out_data.expected_scale),
+   * clamped to the finite range of the output type first when flexpoint_saturate_inf is set.
+   * y_actual_scale: max |output| * (1 / max_finite(output type)) + 1e-30 is folded in with an atomic max
+   * (out_data.actual_scale; the caller zeroes it before the call). Ignored for an MX-quantised output. */
+  const float* w_flex_scale;
+  const float* y_expected_scale;
+  float* y_actual_scale;
+  int32_t flexpoint_saturate_inf;
+  int32_t reserved0;
 } tb200_moe_gemm_mx4_args;
 int tb200_moe_gemm_mx4(const tb200_moe_gemm_mx4_args* args, void* stream);
 

@@ -15,6 +15,7 @@ Each function restates the torch twin that the reference's own tests use as grou
                                 (plus the gate-weighted combine of the MoE benchmark configuration)
   batched_matmul_ref         <- matmul_torch, batched inputs          matmul.py:864-898
   ragged_k_matmul_ref        <- matmul_torch, b_ragged_metadata       matmul.py:836-861
+  flex_actual_scale_ref      <- compute_actual_scale                  matmul.py:810-820
   quantize_mxfp8_ref         <- downcast_to_mxfp_torch (fp8, e8m0,   numerics_details/mxfp.py:212-318
                                 ROUND_UP), the twin of the quantize_mxfp8_fn matmul epilogue
   dequantize_mxfp8_ref       <- upcast_from_mxfp_torch (fp8)         numerics_details/mxfp.py:384-449
@@ -290,3 +291,9 @@ def dequantize_mxfp8_ref(q: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
     q32 = q.detach().cpu().float()
     s = torch.pow(2.0, scale.detach().cpu().float() - 127.0).repeat_interleave(32, dim=-1)[..., :q32.shape[-1]]
     return q32 * s
+
+
+def flex_actual_scale_ref(y: torch.Tensor, dtype=torch.float8_e4m3fn) -> float:
+    """The flexpoint scale a kernel reports for its (unscaled) result: max |y| / max_finite(dtype)."""
+    max_finite = {torch.float8_e5m2: 57344.0, torch.float8_e4m3fn: 448.0, torch.float16: 65504.0}[dtype]
+    return float(y.detach().cpu().float().abs().max()) / max_finite

@@ -144,3 +144,42 @@ def test_argument_checks(cuda):
                epilogue=Epilogue(FnSpecs(FnName.QUANTIZE_MXFP4.name, None, (), ())))
     with pytest.raises(NotImplementedError):  # MX-scaled activations need the MXFP4-weight path
         matmul(x, w, None, precision_config=PrecisionConfig(a_mx_scale=sc, a_microblock_size=32))
+
+
+@pytest.mark.parametrize("T,E,k", [(300, 8, 2), (24, 16, 2)])  # the 128-row kernel and the swapped-operand one
+@pytest.mark.parametrize("swiglu", [False, True])
+def test_flexpoint_scales(cuda, T, E, k, swiglu):
+    """flex_ctx on the fp8 x MXFP4 path: lhs / rhs scales multiply the accumulator, the output is divided by
+    expected_scale and max |output| / 448 comes back in actual_scale (reference: matmul.py:116-121, 810-820,
+    flexpoint.py:133-188)."""
+    from triton_b200.triton_kernels.matmul import FlexCtx, PrecisionConfig, matmul, swiglu_activation
+    from triton_b200.triton_kernels.numerics import InFlexData, OutFlexData
+    from triton_b200.triton_kernels.tensor import make_ragged_tensor_metadata
+    from triton_b200.triton_kernels.topk import topk
+    K, N = 256, 256
+    g = torch.Generator().manual_seed(13)
+    sm = topk(torch.randn(T, E, generator=g).to(cuda), k)
+    mm = sm.mask_metadata
+    R = T * k
+    rg = make_ragged_tensor_metadata(mm.col_sum, R)
+    x = (torch.randn(R, K, generator=g) * 0.5).to(torch.float8_e4m3fn)
+    v, s = downcast_to_mxfp((0.3 * torch.randn(E, K, N, generator=g)).to(torch.bfloat16), torch.uint8, axis=1)
+    wdq = upcast_from_mxfp(v, s, torch.float32, axis=1)
+    xs, ws, expected = 0.75, 1.5, 0.05
+    actual = torch.zeros(1, dtype=torch.float32, device=cuda)
+    fc = FlexCtx(lhs_data=InFlexData(scale=torch.tensor([xs], device=cuda)),
+                 rhs_data=InFlexData(scale=torch.tensor([ws], device=cuda)),
+                 out_data=OutFlexData(expected_scale=torch.tensor([expected], device=cuda), actual_scale=actual))
+    out = matmul(x.to(cuda), v.to(cuda), None, rg, precision_config=PrecisionConfig(b_mx_scale=s.to(cuda), flex_ctx=fc,
+                                                                                      flexpoint_saturate_inf=True),
+                 fused_activation=swiglu_activation(1.0, None) if swiglu else None)
+    assert out.dtype == torch.float8_e4m3fn
+    real = o.grouped_matmul_ref(x.float() * xs, wdq * ws, None, mm.col_sum.cpu().numpy(),
+                                swiglu=(1.0, None) if swiglu else None, out_dtype=torch.float32)
+    want = (real / expected).clamp(-448, 448).to(torch.float8_e4m3fn).float()
+    got = out.cpu().float()
+    # fp8 rounding of nearly equal fp32 values may fall on either side of a tie: one e4m3 step (2^-3 relative)
+    assert float(((got - want).abs() / want.abs().clamp_min(2.0 ** -6)).max()) <= 0.13
+    assert float((got != want).float().mean()) < 0.02
+    ref_scale = o.flex_actual_scale_ref(real)
+    assert abs(float(actual) - ref_scale) <= 1e-5 * ref_scale + 1e-12

@@ -93,7 +93,28 @@ struct MoeEpilogueExtra {
   float out_alpha = 1.f;
   const void* acc_in = nullptr;  // row-major 16-bit matrix, same kind as the output
   long long ld_acc = 0;
+  // flexpoint output (numerics_details/flexpoint.py:155-188 float_to_flex): the largest |output| is reported
+  // (track_absmax; the caller folds it into actual_scale), then the output is multiplied by 1 / expected_scale
+  // and, on request, clamped to the finite range of the output type
+  float inv_expected = 1.f;
+  float clip = 0.f;  // > 0: clamp to [-clip, clip]
+  int track_absmax = 0;
 };
+
+// actual_scale of a flexpoint output from the largest |output|: absmax * (1 / max_finite) + 1e-30 with the
+// reference's rounded-up reciprocal constants (flexpoint.py:17-21,133-142); NaN counts as +inf.
+__device__ __forceinline__ float moe_flex_scale(float absmax, int kind) {
+  const uint32_t bits = min(__float_as_uint(absmax) & 0x7FFFFFFFu, 0x7F800000u);
+  const uint32_t rcp = kind == MOE_OUT_E5M2 ? 0x37924925u : kind == MOE_OUT_F16 ? 0x37802008u : 0x3B124925u;
+  return fmaf(__uint_as_float(bits), __uint_as_float(rcp), 1.0e-30f);
+}
+
+// one warp's contribution to actual_scale (positive floats order like their bit patterns)
+__device__ __forceinline__ void moe_flex_publish(float absmax, float* actual_scale, int kind) {
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) absmax = fmaxf(absmax, __shfl_xor_sync(0xffffffffu, absmax, d));
+  if ((threadIdx.x & 31) == 0) atomicMax(reinterpret_cast<int*>(actual_scale), __float_as_int(moe_flex_scale(absmax, kind)));
+}
 
 // o[j] += acc_in[elem + j] for the first cnt values (16-bit matrix of the output's kind)
 template <int N>
@@ -110,12 +131,14 @@ __device__ __forceinline__ void moe_add_acc(float (&o)[N], int cnt, const void* 
 
 // Epilogue of the grouped GEMMs for 32 accumulator columns of one output row, in the reference's order
 // (_p_matmul.py:606-622): (x acc_scale) + bias * beta -> x out_alpha -> SwiGLU on adjacent (gate, linear) column
-// pairs -> x gamma -> + acc_in -> store at row out_row (ldy in elements).
-__device__ __forceinline__ void moe_store_chunk(const uint32_t (&v)[32], void* y, long long ldy, int out_row, int col,
-                                                int n, const float* brow, int swiglu, float alpha, float limit,
-                                                int has_limit, float gamma, int out_kind, float acc_scale,
-                                                const MoeEpilogueExtra ex = MoeEpilogueExtra()) {
+// pairs -> x gamma -> + acc_in -> (flexpoint: absmax, x 1 / expected_scale, clamp) -> store at row out_row (ldy in
+// elements). Returns the largest |output| before the flexpoint scaling (0 unless asked for).
+__device__ __forceinline__ float moe_store_chunk(const uint32_t (&v)[32], void* y, long long ldy, int out_row, int col,
+                                                 int n, const float* brow, int swiglu, float alpha, float limit,
+                                                 int has_limit, float gamma, int out_kind, float acc_scale,
+                                                 const MoeEpilogueExtra ex = MoeEpilogueExtra()) {
   float f[32];
+  float absmax = 0.f;
 #pragma unroll
   for (int j = 0; j < 32; ++j) {
     f[j] = __uint_as_float(v[j]) * acc_scale;
@@ -129,14 +152,31 @@ __device__ __forceinline__ void moe_store_chunk(const uint32_t (&v)[32], void* y
     for (int j = 0; j < 16; ++j) o[j] = moe_swiglu(f[2 * j], f[2 * j + 1], alpha, limit, has_limit) * gamma;
     const int cnt = min(16, (n - col) >> 1);
     if (ex.acc_in) moe_add_acc<16>(o, cnt, ex.acc_in, (long long)out_row * ex.ld_acc + (col >> 1), out_kind);
+    if (ex.track_absmax || ex.inv_expected != 1.f || ex.clip > 0.f) {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        if (j < cnt) absmax = fmaxf(absmax, fabsf(o[j]));
+        o[j] *= ex.inv_expected;
+        if (ex.clip > 0.f) o[j] = fminf(fmaxf(o[j], -ex.clip), ex.clip);
+      }
+    }
     moe_store_run<16>(y, (long long)out_row * ldy + (col >> 1), o, cnt, out_kind);
   } else {
 #pragma unroll
     for (int j = 0; j < 32; ++j) f[j] *= gamma;
     const int cnt = min(32, n - col);
     if (ex.acc_in) moe_add_acc<32>(f, cnt, ex.acc_in, (long long)out_row * ex.ld_acc + col, out_kind);
+    if (ex.track_absmax || ex.inv_expected != 1.f || ex.clip > 0.f) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        if (j < cnt) absmax = fmaxf(absmax, fabsf(f[j]));
+        f[j] *= ex.inv_expected;
+        if (ex.clip > 0.f) f[j] = fminf(fmaxf(f[j], -ex.clip), ex.clip);
+      }
+    }
     moe_store_run<32>(y, (long long)out_row * ldy + col, f, cnt, out_kind);
   }
+  return absmax;
 }
 
 // The same epilogue up to the store: the outputs of a 32-column accumulator chunk written to o[OFF ..] - 32 values

@@ -55,6 +55,10 @@ struct Mx4Params {
   const float* gammas;
   const float* bias;
   const float* x_scale;  // optional: one float, multiplies every accumulator
+  const float* w_flex;   // optional: one float, the weight's flexpoint scale (multiplies every accumulator too)
+  const float* y_expected;  // optional flexpoint output: the result is divided by this value ...
+  float* y_actual;          // ... and max |result| / max_finite(out type) is folded into this one with an atomic max
+  int saturate;             // clamp the scaled output to the finite range of the output type
   const uint8_t* x_sf;   // optional e8m0 block scales of the activations: [rows_x][K/32], ld_xsf bytes between rows
   uint8_t* y_sf;         // optional: the output is MX-quantised, its e8m0 scales go to [rows_y][N_out/32] (ld_ysf)
   long long ld_xsf, ld_ysf;
@@ -249,7 +253,13 @@ __global__ void __launch_bounds__(M4_THREADS, 1) moe_gemm_mx4_kernel(const __gri
     const int q = warp & 3;
     const int n = p.n, rows_y = p.rows_y;
     void* const y = p.y;
-    const float acc_scale = p.x_scale ? __ldg(p.x_scale) : 1.f;
+    const float acc_scale = (p.x_scale ? __ldg(p.x_scale) : 1.f) * (p.w_flex ? __ldg(p.w_flex) : 1.f);
+    MoeEpilogueExtra flex;
+    if (p.y_expected) {
+      flex.inv_expected = 1.f / __ldg(p.y_expected);
+      if (p.saturate) flex.clip = p.out_kind == MOE_OUT_E5M2 ? 57344.f : p.out_kind == MOE_OUT_E4M3 ? 448.f : 65504.f;
+    }
+    flex.track_absmax = p.y_actual != nullptr;
     const uint32_t tempty_a = smem_u32(tempty);
     uint32_t tcount = 0;
     for (int unit = blockIdx.x; unit < units; unit += gridDim.x) {
@@ -298,6 +308,7 @@ __global__ void __launch_bounds__(M4_THREADS, 1) moe_gemm_mx4_kernel(const __gri
                              p.out_kind);
         }
       } else {
+        float absmax = 0.f;
 #pragma unroll 1
         for (int cc = 0; cc < BN; cc += 32) {
           uint32_t v[32];
@@ -305,9 +316,10 @@ __global__ void __launch_bounds__(M4_THREADS, 1) moe_gemm_mx4_kernel(const __gri
           tmem_ld_wait();
           const int col = n0 + cc;
           if (out_row < 0 || col >= n) continue;
-          moe_store_chunk(v, y, p.ldy, out_row, col, n, brow, p.swiglu, p.alpha, p.limit, p.has_limit, gamma, p.out_kind,
-                          acc_scale);
+          absmax = fmaxf(absmax, moe_store_chunk(v, y, p.ldy, out_row, col, n, brow, p.swiglu, p.alpha, p.limit,
+                                                 p.has_limit, gamma, p.out_kind, acc_scale, flex));
         }
+        if (p.y_actual) moe_flex_publish(absmax, p.y_actual, p.out_kind);
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -517,7 +529,11 @@ __global__ void __launch_bounds__(M4_THREADS, 1) moe_gemm_mx4_swap_kernel(const 
     const float alpha = p.alpha, limit = p.limit;
     void* const y = p.y;
     const long long ldy = p.ldy;
-    const float acc_scale = p.x_scale ? __ldg(p.x_scale) : 1.f;
+    const float acc_scale = (p.x_scale ? __ldg(p.x_scale) : 1.f) * (p.w_flex ? __ldg(p.w_flex) : 1.f);
+    const float inv_expected = p.y_expected ? 1.f / __ldg(p.y_expected) : 1.f;
+    const float clip = (p.y_expected && p.saturate)
+                           ? (out_kind == MOE_OUT_E5M2 ? 57344.f : out_kind == MOE_OUT_E4M3 ? 448.f : 65504.f) : 0.f;
+    float* const y_actual = p.y_actual;
     uint8_t* const y_sf = p.y_sf;
     const long long ld_ysf = p.ld_ysf;
     const uint32_t tempty_a = smem_u32(tempty);
@@ -543,6 +559,7 @@ __global__ void __launch_bounds__(M4_THREADS, 1) moe_gemm_mx4_swap_kernel(const 
       if (lane == 0) mbar_arrive_a(tempty_a + acc * 8);  // the accumulator is in registers
       const int col = wt * S4_WROWS + q * 32 + lane;  // weight row = output column of this thread
       const float b = (p.bias && col < n) ? __ldg(p.bias + (long long)e * n + col) : 0.f;
+      float absmax = 0.f;
 #pragma unroll
       for (int c = 0; c < S4_XROWS; ++c) {
         if (c >= valid) break;
@@ -569,14 +586,21 @@ __global__ void __launch_bounds__(M4_THREADS, 1) moe_gemm_mx4_swap_kernel(const 
         if (swiglu) {
           const float other = __shfl_xor_sync(0xffffffffu, f, 1);  // (gate, linear) are adjacent columns
           if ((lane & 1) == 0 && out_row >= 0 && col < n) {
-            const float o = moe_swiglu(f, other, alpha, limit, has_limit) * gamma;
+            float o = moe_swiglu(f, other, alpha, limit, has_limit) * gamma;
+            absmax = fmaxf(absmax, fabsf(o));
+            o *= inv_expected;
+            if (clip > 0.f) o = fminf(fmaxf(o, -clip), clip);
             moe_store_one(y, (long long)out_row * ldy + (col >> 1), o, out_kind);
           }
         } else if (out_row >= 0 && col < n) {
-          const float o = f * gamma;
+          float o = f * gamma;
+          absmax = fmaxf(absmax, fabsf(o));
+          o *= inv_expected;
+          if (clip > 0.f) o = fminf(fmaxf(o, -clip), clip);
           moe_store_one(y, (long long)out_row * ldy + col, o, out_kind);
         }
       }
+      if (y_actual && !y_sf) moe_flex_publish(absmax, y_actual, out_kind);
     }
   }
 
@@ -655,6 +679,10 @@ extern "C" int tb200_moe_gemm_mx4(const tb200_moe_gemm_mx4_args* a, void* stream
   p.gammas = a->gammas;
   p.bias = a->bias;
   p.x_scale = a->x_scale;
+  p.w_flex = a->w_flex_scale;
+  p.y_expected = a->y_expected_scale;
+  p.y_actual = a->y_actual_scale;
+  p.saturate = a->flexpoint_saturate_inf ? 1 : 0;
   p.x_sf = static_cast<const uint8_t*>(a->x_mx_scale);
   p.ld_xsf = a->ld_x_mx_scale;
   p.y_sf = static_cast<uint8_t*>(a->y_mx_scale);

@@ -25,6 +25,7 @@ from enum import Enum, auto
 import torch
 
 from .. import _lib
+from .numerics import InFlexData, OutFlexData
 from .swiglu import swiglu_fn
 from .tensor import RaggedTensorMetadata, make_ragged_tensor_metadata
 
@@ -65,11 +66,22 @@ class Epilogue:
     effective_itemsize: float | None = None
 
 
+@dataclass(frozen=True)
+class FlexCtx:
+    """Per-tensor scales of the operands and the output (``triton_kernels/matmul.py:116-121``)."""
+    lhs_data: InFlexData = InFlexData()
+    rhs_data: InFlexData = InFlexData()
+    out_data: OutFlexData = OutFlexData()
+    acc_data: InFlexData = InFlexData()
+
+
 @dataclass
 class PrecisionConfig:
     max_num_imprecise_acc: int | None = None
     allow_tf32: bool = True
+    flex_ctx: FlexCtx = FlexCtx()  # honoured on the fp8 x MXFP4 path (scalar scales); must be empty elsewhere
     acc_scale: float = 1.0
+    flexpoint_saturate_inf: bool = False
     out_dtype: torch.dtype | None = None
     a_mx_scale: object = None  # e8m0 block scales of MXFP8 activations: [rows, K/32] uint8 (with an MXFP4 weight)
     a_microblock_size: int | None = None
@@ -151,6 +163,8 @@ def matmul(a, b, bias, a_ragged_metadata: RaggedTensorMetadata | None = None, b_
             raise NotImplementedError("matmul: microblock size 32 (e8m0 scales) only")
     if precision_config is not None and precision_config.b_mx_scale is not None:
         if isinstance(a, torch.Tensor) and a.dtype in _DT:
+            if _flex_in_use(precision_config.flex_ctx):
+                raise NotImplementedError("matmul: flexpoint scales are implemented for fp8 activations x MXFP4 weights")
             # 16-bit activations: the weight is upcast to the activation dtype (what the reference's
             # tl.dot_scaled(x, None, "bf16", w, w_scales, "e2m1") computes), then the 16-bit grouped GEMM runs
             w16 = upcast_mxfp4_weight(b, precision_config.b_mx_scale, a.dtype,
@@ -173,6 +187,8 @@ def matmul(a, b, bias, a_ragged_metadata: RaggedTensorMetadata | None = None, b_
                 sc = _plain_scale(precision_config.a_mx_scale)
                 precision_config = dataclasses.replace(precision_config, a_mx_scale=_gather_scale_rows(sc, gather_indx))
         return _matmul_mx4(a, b, bias, a_ragged_metadata, scatter_indx, precision_config, gammas, fused_activation)
+    if precision_config is not None and _flex_in_use(precision_config.flex_ctx):
+        raise NotImplementedError("matmul: flexpoint scales are implemented for fp8 activations x MXFP4 weights")
     if not isinstance(a, torch.Tensor) or not isinstance(b, torch.Tensor):
         raise NotImplementedError("matmul: wrapped Tensor operands need precision_config.b_mx_scale (MXFP4 weights)")
     if a.ndim != 2:
@@ -370,6 +386,22 @@ def _matmul_ragged_k(a, b, a_md, b_md, c):
     return c
 
 
+def _flex_in_use(fc) -> bool:
+    return fc is not None and any(t is not None for t in (fc.lhs_data.scale, fc.rhs_data.scale, fc.acc_data.scale,
+                                                            fc.out_data.expected_scale, fc.out_data.actual_scale,
+                                                            fc.out_data.checksum_scale))
+
+
+def _flex_scalar(t, dev, what):
+    """A flexpoint scale as a one-element fp32 tensor on ``dev`` (per-batch scales are not implemented)."""
+    if t is None:
+        return None
+    t = torch.as_tensor(t, device=dev)
+    if t.numel() != 1:
+        raise NotImplementedError(f"matmul: per-batch {what} (one scale per tensor is implemented)")
+    return t.to(torch.float32).reshape(1).contiguous()
+
+
 def _plain_scale(t):
     """A scale tensor given plain or wrapped (strided layout) as the plain uint8 tensor."""
     from .tensor import Tensor
@@ -488,9 +520,21 @@ def _matmul_mx4(a, b, bias, a_ragged_metadata, scatter_indx, pc: PrecisionConfig
     si = None if scatter_indx is None else scatter_indx.to(torch.int32).contiguous()
     gm = None if gammas is None else gammas.float().contiguous()
     bs = None if bias is None else bias.float().reshape(E, N).contiguous()
-    xs = None
-    if pc.x_scale is not None:
-        xs = torch.as_tensor(pc.x_scale, dtype=torch.float32, device=dev).reshape(1).contiguous()
+    fc = pc.flex_ctx if pc.flex_ctx is not None else FlexCtx()
+    if fc.acc_data.scale is not None or fc.out_data.checksum_scale is not None:
+        raise NotImplementedError("matmul: flexpoint acc_data / checksum_scale are not implemented")
+    if pc.x_scale is not None and fc.lhs_data.scale is not None:
+        raise ValueError("matmul: x_scale and flex_ctx.lhs_data.scale name the same factor")
+    xs = _flex_scalar(pc.x_scale if pc.x_scale is not None else fc.lhs_data.scale, dev, "lhs scale")
+    wfs = _flex_scalar(fc.rhs_data.scale, dev, "rhs scale")
+    y_exp = _flex_scalar(fc.out_data.expected_scale, dev, "expected_scale")
+    y_act = fc.out_data.actual_scale
+    if y_act is not None:
+        if not (isinstance(y_act, torch.Tensor) and y_act.is_cuda and y_act.dtype == torch.float32
+                and y_act.numel() == 1):
+            raise ValueError("matmul: flex_ctx.out_data.actual_scale is a one-element fp32 CUDA tensor the kernel updates")
+        if out_dtype not in _F8 and out_dtype != torch.float16:
+            raise NotImplementedError("matmul: actual_scale needs an fp8 or fp16 output")
     args = _lib.MoeGemmMx4Args()
     args.x, args.w, args.w_scale, args.y = a.data_ptr(), w.data.data_ptr(), ws.data.data_ptr(), c.data_ptr()
     args.x_scale = xs.data_ptr() if xs is not None else None
@@ -509,6 +553,13 @@ def _matmul_mx4(a, b, bias, a_ragged_metadata, scatter_indx, pc: PrecisionConfig
     args.swiglu_limit = float(limit) if limit is not None else 0.0
     args.swiglu_has_limit = 1 if limit is not None else 0
     args.block_rows = block_rows
+    if wfs is not None:
+        args.w_flex_scale = wfs.data_ptr()
+    if y_exp is not None:
+        args.y_expected_scale = y_exp.data_ptr()
+        args.flexpoint_saturate_inf = 1 if pc.flexpoint_saturate_inf else 0
+    if y_act is not None:
+        args.y_actual_scale = y_act.data_ptr()
     if a_sf is not None:
         args.x_mx_scale, args.ld_x_mx_scale = a_sf.data_ptr(), a_sf.stride(0)
     if c_sf is not None:
