@@ -645,12 +645,14 @@ extern "C" int tb200_moe_gemm(const tb200_moe_gemm_args* a, void* stream_) {
   if (sms <= 0) return TB200_ERR_CUDA;
 
   // One CTA per 128-row block (128 x 256 tile) by default. Two CTA-pair tilings were built and measured at the MoE
-  // benchmark size (65536 sorted rows, 128 experts): 256 rows x 256 columns per pair (kept on request, moe_tile_mode 2)
-  // gains 3 % on sorted rows with tiled loads in one run and loses in others, and loses 2x on gathered rows (eight
-  // remote barrier arrivals per K step from the peer's gather warps); 256 rows x 512 columns per pair with one
-  // 512-column accumulator (the dense kernel's wide tile) ran GEMM-1 at 590-800 TFLOP/s against 930 here, and at
-  // 1040 against 1225 even with 8192 rows per expert: its epilogue (SwiGLU, scattered per-thread stores) cannot hide
-  // behind a second accumulator, and units of 256 rows pad 26 % instead of 13 %.
+  // benchmark size (65536 sorted rows, 128 experts). 256 rows x 256 columns per pair (kept on request, moe_tile_mode 2):
+  // ahead of the one-CTA tile up to about 63000 sorted rows (GEMM-1 with 512-row experts: 1100-1215 TFLOP/s against
+  // 920-1000; routed expert sizes: 945-1010 against 890-940), behind it from 64512 rows on (routed: 720-790 against
+  // 905-950; the L2 hit rate falls from 59 % to 49 % and the DRAM traffic grows by 40 % between 124 and 128 experts,
+  // cause not found), and 2x behind on gathered rows (eight remote barrier arrivals per K step from the peer's gather
+  // warps). 256 rows x 512 columns per pair with one 512-column accumulator (the dense kernel's wide tile) ran GEMM-1
+  // at 590-800 TFLOP/s against 930 here: its epilogue (SwiGLU, scattered per-thread stores) cannot hide behind a
+  // second accumulator, and units of 256 rows pad 26 % instead of 13 %.
   const bool pair = a->moe_tile_mode == 2;
   MoeParams p;
   memset(&p, 0, sizeof(p));
