@@ -24,12 +24,13 @@ def _inputs(T, D, F, E, seed=4):
     return x, logits, w1, w2
 
 
+@pytest.mark.parametrize("shape", [(192, 16), (1536, 8)])  # 48 and 768 rows per expert: one CTA per block, CTA pairs
 @pytest.mark.parametrize("transport", ["pool_fused", "pool", "nccl"])
-def test_ep_layer_world_size_one_matches_oracle(cuda, transport):
+def test_ep_layer_world_size_one_matches_oracle(cuda, transport, shape):
     from triton_b200 import _lib
     from triton_b200.triton_kernels.distributed import (EpGroup, Mesh, SymmetricMemoryPool, make_expt_assignment,
                                                         make_expt_dict_uniform, moe_layer_ep)
-    T, D, F, E, k = 192, 256, 128, 16, 4
+    (T, E), D, F, k = shape, 256, 128, 4
     x, logits, w1, w2 = _inputs(T, D, F, E)
     ea = make_expt_assignment(1, E, make_expt_dict_uniform(1, E), cuda)
     if transport == "nccl":

@@ -653,7 +653,13 @@ extern "C" int tb200_moe_gemm(const tb200_moe_gemm_args* a, void* stream_) {
   // warps). 256 rows x 512 columns per pair with one 512-column accumulator (the dense kernel's wide tile) ran GEMM-1
   // at 590-800 TFLOP/s against 930 here: its epilogue (SwiGLU, scattered per-thread stores) cannot hide behind a
   // second accumulator, and units of 256 rows pad 26 % instead of 13 %.
-  const bool pair = a->moe_tile_mode == 2;
+  // The choice: the pair tiling for sorted (not gathered) rows when the experts average at least 256 rows and there
+  // are fewer than 62000 rows in all - the per-GPU shapes of an expert-parallel layer (both GEMMs of 8192 / 16384 /
+  // 32768 / 49152 routed rows on 16 / 32 / 64 / 96 experts: 0.354 / 0.695 / 1.29 / 2.01 ms against 0.375 / 0.725 /
+  // 1.40 / 2.28 ms with one CTA per block).
+  const bool pair = a->moe_tile_mode == 2 ||
+                    (a->moe_tile_mode == 0 && !a->gather_indx && sms >= 2 && a->rows_x <= 62000 &&
+                     a->rows_x >= 256 * a->n_experts);
   MoeParams p;
   memset(&p, 0, sizeof(p));
   const CUtensorMapDataType dt =
