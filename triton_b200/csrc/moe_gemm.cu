@@ -115,7 +115,9 @@ struct MoeCfg {
   static constexpr int EPI_OFFSET = BAR_OFFSET + 256;
   // pair mode: the schedule entries a cluster works on (even blocks), compacted once per CTA so that the static
   // round-robin over units gives every cluster the same number of tiles (skipping the odd entries in place left
-  // the clusters with binomially spread loads: 53 +- 5 tiles each, the slowest one a quarter above the mean)
+  // the clusters with binomially spread loads: 53 +- 5 tiles each, the slowest one a quarter above the mean). The
+  // list holds what a cluster works on (at most ACT_CAP entries, else the kernel falls back to skipping in place);
+  // the schedule it is cut from may be ten times longer, being sized for the worst case and padded with -1.
   static constexpr int ACT_CAP = PAIR ? 4096 : 0;
   static constexpr int ACT_OFFSET = EPI_OFFSET + 4 * 4096;
   static constexpr int TOTAL = ACT_OFFSET + (PAIR ? ACT_CAP * 4 + 64 : 0) + 1024;
@@ -179,8 +181,9 @@ __global__ void __launch_bounds__(MOE_THREADS, 1) moe_gemm_kernel(const __grid_c
   const int* sched = p.sched;
   bool compact = false;
   if constexpr (PAIR) {
-    if (p.n_sched <= L::ACT_CAP) {
+    {
       // two passes over the schedule by all warps: count the active entries of a warp's chunk, then write them
+      // (the schedule may be much longer than the list: it is sized for the worst case and padded with -1)
       int* const act = reinterpret_cast<int*>(smem + L::ACT_OFFSET);
       int* const cnt = act + L::ACT_CAP;
       constexpr int NW = MOE_THREADS / 32;
@@ -200,18 +203,20 @@ __global__ void __launch_bounds__(MOE_THREADS, 1) moe_gemm_kernel(const __grid_c
         if (w < warp) pos += c;
         total += c;
       }
-      for (int base = lo; base < hi; base += 32) {
-        const int i = base + lane;
-        const int en = i < hi ? __ldg(p.sched + i) : -1;
-        const bool on = en >= 0 && ((en >> 16) & 1) == 0;
-        const uint32_t m = __ballot_sync(0xffffffffu, on);
-        if (on) act[pos + __popc(m & ((1u << lane) - 1u))] = en;
-        pos += __popc(m);
+      if (total <= L::ACT_CAP) {  // the same for every thread of the CTA
+        for (int base = lo; base < hi; base += 32) {
+          const int i = base + lane;
+          const int en = i < hi ? __ldg(p.sched + i) : -1;
+          const bool on = en >= 0 && ((en >> 16) & 1) == 0;
+          const uint32_t m = __ballot_sync(0xffffffffu, on);
+          if (on) act[pos + __popc(m & ((1u << lane) - 1u))] = en;
+          pos += __popc(m);
+        }
+        __syncthreads();
+        sched = act;
+        units = total * tiles_n;
+        compact = true;
       }
-      __syncthreads();
-      sched = act;
-      units = total * tiles_n;
-      compact = true;
     }
   }
   const int* const slice_offs = p.slice_offs;
@@ -644,19 +649,17 @@ extern "C" int tb200_moe_gemm(const tb200_moe_gemm_args* a, void* stream_) {
   const int sms = sm_count();
   if (sms <= 0) return TB200_ERR_CUDA;
 
-  // One CTA per 128-row block (128 x 256 tile) by default. Two CTA-pair tilings were built and measured at the MoE
-  // benchmark size (65536 sorted rows, 128 experts). 256 rows x 256 columns per pair (kept on request, moe_tile_mode 2):
-  // ahead of the one-CTA tile up to about 63000 sorted rows (GEMM-1 with 512-row experts: 1100-1215 TFLOP/s against
-  // 920-1000; routed expert sizes: 945-1010 against 890-940), behind it from 64512 rows on (routed: 720-790 against
-  // 905-950; the L2 hit rate falls from 59 % to 49 % and the DRAM traffic grows by 40 % between 124 and 128 experts,
-  // cause not found), and 2x behind on gathered rows (eight remote barrier arrivals per K step from the peer's gather
-  // warps). 256 rows x 512 columns per pair with one 512-column accumulator (the dense kernel's wide tile) ran GEMM-1
-  // at 590-800 TFLOP/s against 930 here: its epilogue (SwiGLU, scattered per-thread stores) cannot hide behind a
-  // second accumulator, and units of 256 rows pad 26 % instead of 13 %.
+  // Tilings. One CTA per 128-row block (128 x 256 tile), or a CTA pair per two consecutive blocks of an expert
+  // (256 x 256, moe_tile_mode 2): the pair stages a third less per K step (GEMM-1 with 512-row experts: 1100-1215
+  // TFLOP/s against 920-1000) but pads routed expert sizes to 256 rows (25 % instead of 12 %), and loses 2x on
+  // gathered rows (eight remote barrier arrivals per K step from the peer's gather warps). A third tiling, 256 rows x
+  // 512 columns per pair with one 512-column accumulator (the dense kernel's wide tile), ran GEMM-1 at 590-800
+  // TFLOP/s against 930: its epilogue (SwiGLU, scattered per-thread stores) cannot hide behind a second accumulator.
   // The choice: the pair tiling for sorted (not gathered) rows when the experts average at least 256 rows and there
   // are fewer than 62000 rows in all - the per-GPU shapes of an expert-parallel layer (both GEMMs of 8192 / 16384 /
   // 32768 / 49152 routed rows on 16 / 32 / 64 / 96 experts: 0.354 / 0.695 / 1.29 / 2.01 ms against 0.375 / 0.725 /
-  // 1.40 / 2.28 ms with one CTA per block).
+  // 1.40 / 2.28 ms with one CTA per block). At 65536 rows on 128 experts the two measure within the run-to-run
+  // spread of each other, so the one-CTA tile stays there.
   const bool pair = a->moe_tile_mode == 2 ||
                     (a->moe_tile_mode == 0 && !a->gather_indx && sms >= 2 && a->rows_x <= 62000 &&
                      a->rows_x >= 256 * a->n_experts);

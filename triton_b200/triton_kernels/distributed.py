@@ -534,13 +534,18 @@ def moe_layer_ep(x_local, logits_local, w1_local, w2_local, k, expt_assignment: 
         rg = make_ragged_tensor_metadata(mm.col_sum, n_entries)
         rg_local = remap_ragged_tensor_metadata(rg, expt_assignment.expt_map[rank])
         y = convert_dp_to_ep(x_local, expt_assignment, sm.indx, mm.row_sorted_indx, ep)
-    h = matmul(y, w1_local, None, rg_local, fused_activation=swiglu_activation(alpha, limit))
+    # The GEMMs see buffers sized for the worst case, so the tiling is chosen here from what balanced routing gives
+    # a rank: CTA pairs when the experts average 256 rows or more and a rank expects fewer than 62000 rows (the
+    # range where that tiling measured ahead), else the library's own choice.
+    n_expts_tot = expt_assignment.expt_map.shape[-1]
+    tile_mode = 2 if (world > 1 and n_entries >= 256 * n_expts_tot and n_entries // world <= 62000) else 0
+    h = matmul(y, w1_local, None, rg_local, fused_activation=swiglu_activation(alpha, limit), _tile_mode=tile_mode)
     n_local = x_local.shape[0]
     if isinstance(ep, SymmetricMemoryPool) and fuse_combine:
         d_out = w2_local.shape[-1]
         peer_bufs = ep.make_empty((n_local * k, d_out), h.dtype, region="ep_to_dp")
         # the gate weight of an output row is the top-k value of its (token, slot): looked up by the epilogue
-        matmul(h, w2_local, None, rg_local, gammas=sm.vals if gate_weighted else None, scatter_indx=mm.col_sorted_indx,
+        matmul(h, w2_local, None, rg_local, gammas=sm.vals if gate_weighted else None, scatter_indx=mm.col_sorted_indx, _tile_mode=tile_mode,
                fused_comm=FusedComm(peer_bufs, n_local * k, d_out), _gammas_by_out_row=True)
         ep.hdl.barrier(channel=0)
         y_dp = peer_bufs[rank]
@@ -548,7 +553,7 @@ def moe_layer_ep(x_local, logits_local, w1_local, w2_local, k, expt_assignment: 
         gam = None
         if gate_weighted:
             gam = sm.vals.float().reshape(-1)[mm.col_sorted_indx.long().clamp(min=0)]
-        o = matmul(h, w2_local, None, rg_local, gammas=gam)
+        o = matmul(h, w2_local, None, rg_local, gammas=gam, _tile_mode=tile_mode)
         y_dp = convert_ep_to_dp(o, expt_assignment, sm.indx, mm.col_sorted_indx, ep)
     z, _ = reduce(y_dp.view(n_local, k, -1), dim=1)
     return z
