@@ -310,3 +310,28 @@ def test_betas_out_alpha_and_accumulator_input(cuda):
                  c=cd, c_acc_in=cd, fused_activation=swiglu_activation(1.1, None))
     assert got.data_ptr() == cd.data_ptr()
     torch.testing.assert_close(got.cpu().float(), want, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("swiglu", [False, True])
+def test_tile_modes_agree_bit_for_bit(cuda, swiglu):
+    """One CTA per block and CTA pairs accumulate every output in the same order: identical results on sorted rows,
+    with experts of 0, 1, 2, 3 and more blocks, with and without a scatter."""
+    from triton_b200.triton_kernels.matmul import matmul, swiglu_activation
+    from triton_b200.triton_kernels.tensor import make_ragged_tensor_metadata
+    g = torch.Generator().manual_seed(17)
+    sizes = torch.tensor([0, 100, 128, 129, 256, 300, 384, 385, 1, 700, 0, 513], dtype=torch.int32)
+    R, K, N = int(sizes.sum()), 320, 384
+    E = sizes.numel()
+    x = torch.randn(R, K, generator=g).to(torch.bfloat16).to(cuda)
+    w = (0.1 * torch.randn(E, K, N, generator=g)).to(torch.bfloat16).to(cuda)
+    rg = make_ragged_tensor_metadata(sizes.to(cuda), R)
+    scat = torch.randperm(R, generator=g).to(torch.int32).to(cuda)
+    gam = torch.rand(R, generator=g).to(cuda)
+    act = swiglu_activation(1.0, None) if swiglu else None
+    outs = [matmul(x, w, None, rg, fused_activation=act, _tile_mode=m) for m in (1, 2)]
+    assert torch.equal(outs[0], outs[1])
+    outs = [matmul(x, w, None, rg, scatter_indx=scat, gammas=gam, fused_activation=act, _tile_mode=m) for m in (1, 2)]
+    assert torch.equal(outs[0], outs[1])
+    ref = o.grouped_matmul_ref(x.cpu(), w.cpu(), None, sizes.numpy(), scatter_indx=scat.cpu().numpy(), gammas=gam.cpu(),
+                               swiglu=(1.0, None) if swiglu else None)
+    torch.testing.assert_close(outs[1].cpu().float(), ref.float(), rtol=2e-2, atol=2e-2)

@@ -655,6 +655,9 @@ extern "C" int tb200_moe_gemm(const tb200_moe_gemm_args* a, void* stream_) {
   // gathered rows (eight remote barrier arrivals per K step from the peer's gather warps). A third tiling, 256 rows x
   // 512 columns per pair with one 512-column accumulator (the dense kernel's wide tile), ran GEMM-1 at 590-800
   // TFLOP/s against 930: its epilogue (SwiGLU, scattered per-thread stores) cannot hide behind a second accumulator.
+  // A mix (pairs for the blocks that have a partner, then a second launch with one CTA per leftover block, so that
+  // no pair carries a padded half) measured 3-8 % behind the pure pair tiling: the leftover blocks re-read their
+  // experts' weights from HBM (1.65 GB at 128 experts) instead of sharing them in L2 with the expert's other tiles.
   // The choice: the pair tiling for sorted (not gathered) rows when the experts average at least 256 rows and there
   // are fewer than 62000 rows in all - the per-GPU shapes of an expert-parallel layer (both GEMMs of 8192 / 16384 /
   // 32768 / 49152 routed rows on 16 / 32 / 64 / 96 experts: 0.354 / 0.695 / 1.29 / 2.01 ms against 0.375 / 0.725 /
