@@ -297,12 +297,14 @@ def build_workload(name: str, rank: int, world: int, dev):
         return Workload(lambda: mx_matmul(a, b, sc, sc), 2.0 * n ** 3, 4.0 * n * n + 2 * n * n / 32,
                         "MXFP8 block-scaled GEMM 8192^3 (e8m0 scales 2^u, u in [-4,4]), bf16 out", "gemm_mxfp8_kernel",
                         "tensor", [a, b], dtype="e4m3", cpu=cpu_mxfp8, peak="fp8")
-    if name in ("moe", "moe_decode"):
+    if name in ("moe", "moe_decode", "moe_small"):
         from triton_b200.triton_kernels.matmul import matmul as moe_matmul, swiglu_activation
         from triton_b200.triton_kernels.reduce import reduce
         from triton_b200.triton_kernels.tensor import make_ragged_tensor_metadata
         from triton_b200.triton_kernels.topk import topk
         T, D, F, E, k = (64 if name == "moe_decode" else 16384), 4096, 1536, 128, 4
+        if name == "moe_small":  # the layer down-scaled to 16 experts (the same rows per expert): the case profiled under ncu
+            T, E = 2048, 16
         x = _dev_randn((T, D), dev, 4 + 1000 * rank, dtype=bf)
         logits = _dev_randn((T, E), dev, 5 + 1000 * rank)
         w1 = _dev_randn((E, D, 2 * F), dev, 6 + 1000 * rank, 0.02, bf)
@@ -729,7 +731,7 @@ def main():
     ap.add_argument("--workload", default="gemm",
                     help="gemm (headline + configs, default) | " + " | ".join(CONFIG_NAMES) + " | attn_bwd | attn_bwd_causal | "
                          "attn_bwd_ref_shape[_causal] | fp8_blockwise | moe_mx4 | moe_mx4_decode | moe_bf16_mx4 | mxfp4_upcast | "
-                         "moe_ep_unfused | moe_ep_nccl")
+                         "moe_ep_unfused | moe_ep_nccl | moe_small")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
