@@ -55,8 +55,9 @@ CONFIG = {"workload": WORKLOAD, "sharding": "one 8192-column block of B per GPU,
 # ncu captures of `python bench.py --workload NAME`; None where no capture of the current kernel exists.
 NCU_TRAFFIC = {
     "gemm": 1.037e9,
-    "attn": None,
-    "attn_causal": None,
+    "gemm_skinny": 0.140e9,  # the kernel with the split-K partial sums reduced inside a cluster
+    "attn": 16.04e9,         # the tile order re-reads K / V for every query tile; kernel unchanged since the capture
+    "attn_causal": 8.16e9,
     "fp8": 0.509e9,
     "fp8_blockwise": 0.587e9,
     "mxfp8": 0.565e9,

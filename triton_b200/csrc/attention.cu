@@ -77,6 +77,9 @@ struct AttnTile {
 // block before the next block. This order re-reads each head's K / V from HBM for every query tile (15.8 GB
 // per launch at [4, 32, 8192, 128], 4 TB/s); head-major and L2-sized head-group orders cut that to ~1 GB but
 // measured equal (non-causal) or 5-30 % slower (causal: the long tiles no longer start first), so it stays.
+// Measured again with groups of heads sized to 16 / 32 MB of K + V, alternating with this order in one process
+// (five rounds): [4, 32, 8192, 128] 999 / 992 against 1044 TFLOP/s non-causal and 930 / 931 against 967 causal;
+// [32, 32, 1024, 128] 901 / 917 against 890 and 596 / 585 against 609.
 __device__ __forceinline__ AttnTile attn_tile(const AttnParams& p, int unit) {
   AttnTile t;
   const int qb = p.q_tiles - 1 - unit / p.bh;
