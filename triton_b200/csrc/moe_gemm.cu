@@ -658,14 +658,12 @@ extern "C" int tb200_moe_gemm(const tb200_moe_gemm_args* a, void* stream_) {
   // A mix (pairs for the blocks that have a partner, then a second launch with one CTA per leftover block, so that
   // no pair carries a padded half) measured 3-8 % behind the pure pair tiling: the leftover blocks re-read their
   // experts' weights from HBM (1.65 GB at 128 experts) instead of sharing them in L2 with the expert's other tiles.
-  // The choice: the pair tiling for sorted (not gathered) rows when the experts average at least 256 rows and there
-  // are fewer than 62000 rows in all - the per-GPU shapes of an expert-parallel layer (both GEMMs of 8192 / 16384 /
-  // 32768 / 49152 routed rows on 16 / 32 / 64 / 96 experts: 0.354 / 0.695 / 1.29 / 2.01 ms against 0.375 / 0.725 /
-  // 1.40 / 2.28 ms with one CTA per block). At 65536 rows on 128 experts the two measure within the run-to-run
-  // spread of each other, so the one-CTA tile stays there.
+  // The choice: the pair tiling for sorted (not gathered) rows when the experts average at least 256 rows. Both
+  // GEMMs of a layer, routed expert sizes, pair against one CTA per block: 8192 / 16384 / 32768 / 49152 rows on
+  // 16 / 32 / 64 / 96 experts 0.354 / 0.695 / 1.29 / 2.01 ms against 0.375 / 0.725 / 1.40 / 2.28 ms; 65536 rows on
+  // 128 experts 2.87 against 3.11 ms (alternating in one process, six rounds, the pair ahead in each).
   const bool pair = a->moe_tile_mode == 2 ||
-                    (a->moe_tile_mode == 0 && !a->gather_indx && sms >= 2 && a->rows_x <= 62000 &&
-                     a->rows_x >= 256 * a->n_experts);
+                    (a->moe_tile_mode == 0 && !a->gather_indx && sms >= 2 && a->rows_x >= 256 * a->n_experts);
   MoeParams p;
   memset(&p, 0, sizeof(p));
   const CUtensorMapDataType dt =

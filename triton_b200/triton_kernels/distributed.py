@@ -535,10 +535,10 @@ def moe_layer_ep(x_local, logits_local, w1_local, w2_local, k, expt_assignment: 
         rg_local = remap_ragged_tensor_metadata(rg, expt_assignment.expt_map[rank])
         y = convert_dp_to_ep(x_local, expt_assignment, sm.indx, mm.row_sorted_indx, ep)
     # The GEMMs see buffers sized for the worst case, so the tiling is chosen here from what balanced routing gives
-    # a rank: CTA pairs when the experts average 256 rows or more and a rank expects fewer than 62000 rows (the
-    # range where that tiling measured ahead), else the library's own choice.
+    # a rank: CTA pairs when the experts average 256 rows or more (the rule the library applies to the row count
+    # it is given), else the library's own choice.
     n_expts_tot = expt_assignment.expt_map.shape[-1]
-    tile_mode = 2 if (world > 1 and n_entries >= 256 * n_expts_tot and n_entries // world <= 62000) else 0
+    tile_mode = 2 if n_entries >= 256 * n_expts_tot else 0
     h = matmul(y, w1_local, None, rg_local, fused_activation=swiglu_activation(alpha, limit), _tile_mode=tile_mode)
     n_local = x_local.shape[0]
     if isinstance(ep, SymmetricMemoryPool) and fuse_combine:
