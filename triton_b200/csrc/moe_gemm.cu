@@ -235,7 +235,8 @@ __global__ void __launch_bounds__(MOE_THREADS, 1) moe_gemm_kernel(const __grid_c
     // ------------------------------------------------------------- TMA producer (one lane)
     if (lane == 0) {
       // measured at 65536 rows x 128 experts against the other combinations of evict_first / normal / last: this
-      // one is the fastest or within 1 % of it for both GEMMs of the layer
+      // one is the fastest or within 1 % of it for both GEMMs of the layer. (TMA prefetches into L2 of the boxes 8 to
+      // 24 K steps ahead of the loads, the next tile's first steps included, made the layer's GEMMs 30 % slower.)
       const uint64_t pol_x = policy_evict_normal();
       const uint64_t pol_w = policy_evict_last();
       const int w_n_major = p.w_n_major;
