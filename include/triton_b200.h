@@ -199,6 +199,39 @@ typedef struct {
 int tb200_attention_fwd(const tb200_attention_args* args, void* stream);
 
 /*
+ * MXFP8 flash-attention forward: o = softmax(dq(q) dq(k)^T * sm_scale [+ causal mask]) dq(v) as bf16, with q, k, v
+ * in e4m3 and one e8m0 scale per 32 values: q and k scaled along head_dim, v along the sequence (its transpose
+ * [head_dim, seq] was quantised along seq); the probabilities are quantised inside the kernel (e4m3, one e8m0
+ * scale per 32 keys of a row). lse as in tb200_attention_fwd (may be NULL).
+ * Stands behind: third_party/tlx/tutorials/blackwell_fa_ws_pipelined_persistent_mxfp8.py:3374
+ *   attention(q, k, v, q_scale, k_scale, v_scale, sm_scale, causal, config=None)   (kernel _attn_fwd_mxf8_ws :532).
+ * q: [batch, heads, seq_q, 128] e4m3 contiguous; k, v: [batch, heads, seq_kv, 128]; o: bf16 [batch, heads, seq_q, 128].
+ * Scales: uint8 e8m0 in 512-byte atoms [row % 32][row / 32 % 4][block % 4] (the "swizzled" / to_blocked order the
+ * reference feeds its kernel, viewed there as [batch*heads, blocks, 1, 2, 256]):
+ *   q_scale: [batch*heads][seq_q / 128] atoms, rows = the 128 query rows, blocks = the 4 groups of 32 along head_dim;
+ *   k_scale: [batch*heads][seq_kv / 128] atoms, the same for the key rows;
+ *   v_scale: [batch*heads][seq_kv / 128] atoms, rows = the 128 head-dim columns, blocks = the 4 groups of 32 keys.
+ * head_dim 128; seq_q and seq_kv multiples of 128; causal requires seq_q == seq_kv. Pointers 16-byte aligned.
+ */
+typedef struct {
+  const void* q;
+  const void* k;
+  const void* v;
+  const void* q_scale;
+  const void* k_scale;
+  const void* v_scale;
+  void* o;
+  float* lse;
+  int64_t batch, heads, seq_q, seq_kv;
+  int32_t head_dim;
+  int32_t causal;
+  float sm_scale;
+  int32_t reserved0;
+} tb200_attention_mxfp8_args;
+
+int tb200_attention_mxfp8_fwd(const tb200_attention_mxfp8_args* args, void* stream);
+
+/*
  * Flash-attention backward: dq, dk, dv from q, k, v, the forward output o, its gradient d_o and
  * the base-2 log-sum-exp `lse` written by tb200_attention_fwd.
  * Stands behind: third_party/tlx/tutorials/blackwell_fa_ws_pipelined_persistent.py:3362

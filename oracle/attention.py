@@ -61,3 +61,20 @@ def attention_bwd_ref(q, k, v, do, sm_scale: float, causal: bool):
             dk[b, h] = sm_scale * (ds.t() @ q64[b, h])
             dq[b, h] = sm_scale * (ds @ k64[b, h])
     return dq.float(), dk.float(), dv.float()
+
+
+def attention_mxfp8_ref(q, k, v, q_scale, k_scale, v_scale, sm_scale: float, causal: bool):
+    """MXFP8 attention as the product of the dequantised operands in fp32: q, k, v ``[Z, H, N, D]`` e4m3; the
+    scales as flat 512-byte atoms (``oracle.mxfp8.swizzle_scales`` order) - Q and K per 32 values of D, V per 32
+    keys of each head-dim column (its transpose ``[D, Z*H*N]`` was quantised). This is the check of the reference's own
+    test (``third_party/tlx/tutorials/testing/test_correctness.py:1071-1106``: SDPA on the unquantised tensors,
+    absolute tolerance 0.04-0.11), applied to the dequantised tensors so that only the kernel's own rounding (the
+    quantised probabilities, the bf16 output) is left. Returns ``(o fp32, lse2)``."""
+    from . import mxfp8 as mx
+    Z, H, N, D = q.shape
+    Nk = k.shape[2]
+    qd = mx.dequantize(q.reshape(Z * H * N, D).cpu(), q_scale.reshape(-1).cpu()).reshape(Z, H, N, D)
+    kd = mx.dequantize(k.reshape(Z * H * Nk, D).cpu(), k_scale.reshape(-1).cpu()).reshape(Z, H, Nk, D)
+    vt = v.reshape(Z * H * Nk, D).t().contiguous().cpu()            # [D, ZHN]: the matrix that was quantised
+    vd = mx.dequantize(vt, v_scale.reshape(-1).cpu()).t().reshape(Z, H, Nk, D)
+    return attention_ref(qd, kd, vd, sm_scale, causal)

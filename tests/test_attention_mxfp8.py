@@ -1,0 +1,70 @@
+"""MXFP8 flash-attention forward (``tutorials.blackwell_fa_ws_pipelined_persistent_mxfp8.attention``) against the CPU
+oracle: fp32 attention on the dequantised operands. What is left between the two is the kernel's own rounding - the
+probabilities quantised to e4m3 with one e8m0 scale per 32 keys, and the bf16 output - so the tolerance is absolute,
+as in the reference's test of this kernel (testing/test_correctness.py:1071-1106: 0.04-0.11 against SDPA on the
+unquantised tensors, N(0, 0.5) inputs, sm_scale 0.5); the same comparison with the reference's bounds is made too."""
+import pytest
+import torch
+
+from oracle import attention as o
+
+pytestmark = pytest.mark.gpu
+
+
+def _run(cuda, shape, causal, sm_scale=0.5, seed=20):
+    from triton_b200.tutorials.blackwell_fa_ws_pipelined_persistent_mxfp8 import attention, generate_attention_inputs
+    torch.manual_seed(seed)
+    (q, qs, q_ref), (k, ks, k_ref), (v, vs, v_ref) = generate_attention_inputs(shape, "cpu", torch.float8_e4m3fn)
+    out = attention(q.to(cuda), k.to(cuda), v.to(cuda), qs.to(cuda), ks.to(cuda), vs.to(cuda), sm_scale, causal)
+    assert out.dtype == torch.bfloat16 and out.shape == shape
+    ref_dq, _ = o.attention_mxfp8_ref(q, k, v, qs, ks, vs, sm_scale, causal)
+    ref_hp, _ = o.attention_ref(q_ref.float(), k_ref.float(), v_ref.float(), sm_scale, causal)
+    return out.cpu().float(), ref_dq, ref_hp
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("shape", [(1, 2, 128, 128), (2, 3, 384, 128), (1, 2, 1024, 128)])
+def test_matches_dequantised_attention(cuda, shape, causal):
+    from triton_b200 import _lib
+    out, ref_dq, ref_hp = _run(cuda, shape, causal)
+    # against the dequantised operands: the rounding of P (e4m3: up to 2^-4 relative per element, times |v| up to ~2,
+    # averaged over the keys a row sees - the first causal rows see one or two) and of the bf16 output
+    assert float((out - ref_dq).abs().max()) <= (0.08 if causal else 0.04)
+    assert float((out - ref_dq).abs().mean()) <= 0.004
+    # the reference's own check and bounds (head dim 128: 0.08 non-causal, 0.11 causal)
+    assert float((out - ref_hp).abs().max()) <= (0.11 if causal else 0.08)
+    _lib.sync_check(cuda)
+
+
+def test_growing_scores_rescale_path(cuda):
+    """Keys whose scores grow along the sequence force the running maximum (and the lazy rescale of O) to move in
+    almost every block."""
+    from triton_b200 import _lib
+    from triton_b200.triton_kernels.numerics_details.mxfp import downcast_to_mxfp
+    from triton_b200.tutorials.blackwell_fa_ws_pipelined_persistent_mxfp8 import attention, swizzle_block_scales
+    Z, H, N, D = 1, 2, 1024, 128
+    g = torch.Generator().manual_seed(3)
+    q_ref = torch.ones(Z, H, N, D) * 0.5 + 0.05 * torch.randn(Z, H, N, D, generator=g)
+    ramp = torch.linspace(0.1, 3.0, N).view(1, 1, N, 1)
+    k_ref = ramp * (1.0 + 0.05 * torch.randn(Z, H, N, D, generator=g))
+    v_ref = torch.randn(Z, H, N, D, generator=g)
+    q, qs = downcast_to_mxfp(q_ref.reshape(-1, D).to(torch.bfloat16), torch.float8_e4m3fn, axis=1)
+    k, ks = downcast_to_mxfp(k_ref.reshape(-1, D).to(torch.bfloat16), torch.float8_e4m3fn, axis=1)
+    vt, vs = downcast_to_mxfp(v_ref.reshape(-1, D).t().contiguous().to(torch.bfloat16), torch.float8_e4m3fn, axis=1)
+    q, k, v = q.reshape(Z, H, N, D), k.reshape(Z, H, N, D), vt.t().reshape(Z, H, N, D).contiguous()
+    qs, ks, vs = swizzle_block_scales(qs), swizzle_block_scales(ks), swizzle_block_scales(vs)
+    out = attention(q.to(cuda), k.to(cuda), v.to(cuda), qs.to(cuda), ks.to(cuda), vs.to(cuda), 0.25, False)
+    ref, _ = o.attention_mxfp8_ref(q, k, v, qs, ks, vs, 0.25, False)
+    assert float((out.cpu().float() - ref).abs().max()) <= 0.05
+    _lib.sync_check(cuda)
+
+
+def test_argument_checks(cuda):
+    from triton_b200.tutorials.blackwell_fa_ws_pipelined_persistent_mxfp8 import attention
+    q = torch.zeros(1, 1, 128, 64, device=cuda).to(torch.float8_e4m3fn)
+    s = torch.zeros(512, dtype=torch.uint8, device=cuda)
+    with pytest.raises(NotImplementedError):
+        attention(q, q, q, s, s, s, 0.5, False)
+    q = torch.zeros(1, 1, 96, 128, device=cuda).to(torch.float8_e4m3fn)
+    with pytest.raises(NotImplementedError):
+        attention(q, q, q, s, s, s, 0.5, False)

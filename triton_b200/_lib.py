@@ -61,6 +61,15 @@ class AttentionArgs(Structure):
     ]
 
 
+class AttentionMxfp8Args(Structure):
+    _fields_ = [
+        ("q", c_void_p), ("k", c_void_p), ("v", c_void_p), ("q_scale", c_void_p), ("k_scale", c_void_p),
+        ("v_scale", c_void_p), ("o", c_void_p), ("lse", c_void_p),
+        ("batch", c_int64), ("heads", c_int64), ("seq_q", c_int64), ("seq_kv", c_int64),
+        ("head_dim", c_int32), ("causal", c_int32), ("sm_scale", c_float), ("reserved0", c_int32),
+    ]
+
+
 class AttentionBwdArgs(Structure):
     _fields_ = [
         ("q", c_void_p), ("k", c_void_p), ("v", c_void_p), ("o", c_void_p), ("d_o", c_void_p), ("lse", c_void_p),
@@ -199,6 +208,8 @@ def _declare(l: ctypes.CDLL) -> None:
     l.tb200_gemm_workspace_bytes.argtypes = [POINTER(GemmArgs)]
     l.tb200_attention_fwd.restype = c_int
     l.tb200_attention_fwd.argtypes = [POINTER(AttentionArgs), c_void_p]
+    l.tb200_attention_mxfp8_fwd.restype = c_int
+    l.tb200_attention_mxfp8_fwd.argtypes = [POINTER(AttentionMxfp8Args), c_void_p]
     l.tb200_attention_bwd.restype = c_int
     l.tb200_attention_bwd.argtypes = [POINTER(AttentionBwdArgs), c_void_p]
     l.tb200_attention_bwd_workspace_bytes.restype = c_size_t
