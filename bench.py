@@ -223,6 +223,25 @@ def build_workload(name: str, rank: int, world: int, dev):
     distributions; seeds offset per rank) so that set-up costs seconds, not minutes."""
     import torch
     bf = torch.bfloat16
+    if name in ("attn_mxfp8", "attn_mxfp8_causal"):
+        from triton_b200.triton_kernels.numerics_details.mxfp import downcast_to_mxfp
+        from triton_b200.tutorials.blackwell_fa_ws_pipelined_persistent_mxfp8 import attention as mx_attention
+        from triton_b200.tutorials.blackwell_fa_ws_pipelined_persistent_mxfp8 import swizzle_block_scales
+        causal = name.endswith("causal")
+        B, H, S, D = 4, 32, 8192, 128
+        ops = []
+        for i in range(3):  # N(0,1) bf16 tensors quantised to MXFP8: Q, K along D; V (transposed) along the sequence
+            x = _dev_randn((B * H * S, D), dev, 2 + 1000 * rank + i, dtype=bf)
+            val, s8 = downcast_to_mxfp(x if i < 2 else x.t().contiguous(), torch.float8_e4m3fn, axis=1)
+            ops.append((val if i < 2 else val.t()).reshape(B, H, S, D).contiguous())
+            ops.append(swizzle_block_scales(s8))
+            del x, val, s8
+        q, qs, k, ks, v, vs = ops
+        sc = 1.0 / math.sqrt(D)
+        fl = 4.0 * B * H * D * (S * (S + 1) / 2 if causal else S * S)
+        return Workload(lambda: mx_attention(q, k, v, qs, ks, vs, sc, causal), fl, 3.0 * B * H * S * D + 2.0 * B * H * S * D,
+                        f"MXFP8 flash-attention fwd [B={B},H={H},S={S},D={D}] causal={causal}, N(0,1) quantised per 32, seed 2",
+                        "attention_mxfp8_fwd_kernel", "tensor", [q, k, v], dtype="e4m3", peak="fp8")
     if name.startswith("attn") and "bwd" not in name:
         from triton_b200.tutorials.blackwell_fa_ws_pipelined_persistent import attention_with_lse
         causal = name.endswith("causal")
@@ -732,7 +751,7 @@ def main():
     ap.add_argument("--workload", default="gemm",
                     help="gemm (headline + configs, default) | " + " | ".join(CONFIG_NAMES) + " | attn_bwd | attn_bwd_causal | "
                          "attn_bwd_ref_shape[_causal] | fp8_blockwise | moe_mx4 | moe_mx4_decode | moe_bf16_mx4 | mxfp4_upcast | "
-                         "moe_ep_unfused | moe_ep_nccl | moe_small")
+                         "moe_ep_unfused | moe_ep_nccl | moe_small | attn_mxfp8 | attn_mxfp8_causal")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
