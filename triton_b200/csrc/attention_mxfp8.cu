@@ -14,6 +14,7 @@
 //              p = exp2(s * scale - m) in fp32, its row sum in fp32; every 32 keys of a row share the e8m0 scale
 //              2^ceil(log2(amax / 448)), p / scale is rounded to e4m3 and written to shared memory in the 128-byte
 //              swizzled K-major layout the MMA descriptor expects, the four scale bytes of the row into an atom.
+//              P and its atom are double-buffered, so the softmax of block j+1 runs while P(j) V(j) executes;
 //              At the end: O / l as bf16 and the base-2 log-sum-exp.
 // Tensor memory (512 columns allocated): S0 | S1 | O | scale columns (Q 4; P, K, V two sets of 4 each).
 // This first version runs one query group per CTA (no second group to fill the tensor pipe while the softmax of
@@ -53,10 +54,10 @@ struct MxAttnSmem {
   static constexpr int TILE = 128 * 128;  // one 128-row tile of fp8
   static constexpr int Q_OFFSET = 0;
   static constexpr int KV_OFFSET = TILE;                              // ring: K tile, V tile per stage
-  static constexpr int P_OFFSET = KV_OFFSET + MXA_STAGES * 2 * TILE;  // P tile
-  static constexpr int SF_OFFSET = P_OFFSET + TILE;                   // atoms: Q | P | (K, V) per stage
-  static constexpr int BAR_OFFSET = SF_OFFSET + (2 + 2 * MXA_STAGES) * 512;
-  static constexpr int NUM_BARS = 2 + 2 * MXA_STAGES + 2 + 1 + 1 + 1;
+  static constexpr int P_OFFSET = KV_OFFSET + MXA_STAGES * 2 * TILE;  // two P tiles
+  static constexpr int SF_OFFSET = P_OFFSET + 2 * TILE;               // atoms: Q | P0 | P1 | (K, V) per stage
+  static constexpr int BAR_OFFSET = SF_OFFSET + (3 + 2 * MXA_STAGES) * 512;
+  static constexpr int NUM_BARS = 2 + 2 * MXA_STAGES + 2 + 2 + 2 + 1;
   static constexpr int TOTAL = BAR_OFFSET + NUM_BARS * 8 + 16 + 1024;
 };
 
@@ -66,14 +67,6 @@ __device__ __forceinline__ void mxa_tile(const MxAttnParams& p, int unit, int& b
   q0 = qb * MXA_BM;
   nkv = (p.s_kv + MXA_BN - 1) / MXA_BN;
   if (p.causal) nkv = min(nkv, (q0 + MXA_BM + MXA_BN - 1) / MXA_BN);
-}
-
-// four floats -> four e4m3 bytes (byte 0 = a), round to nearest even, saturating
-__device__ __forceinline__ uint32_t mxa_pack4(float a, float b, float c, float d) {
-  uint16_t lo, hi;
-  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(b), "f"(a));
-  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(d), "f"(c));
-  return (uint32_t)lo | ((uint32_t)hi << 16);
 }
 
 __global__ void __launch_bounds__(MXA_THREADS, 1) attention_mxfp8_fwd_kernel(const __grid_constant__ MxAttnParams p) {
@@ -89,9 +82,9 @@ __global__ void __launch_bounds__(MXA_THREADS, 1) attention_mxfp8_fwd_kernel(con
   uint64_t* kv_full = bars + 2;                    // [STAGES]
   uint64_t* kv_empty = kv_full + MXA_STAGES;       // [STAGES] commit after PV(j)
   uint64_t* s_full = kv_empty + MXA_STAGES;        // [2] MMA -> softmax
-  uint64_t* p_full = s_full + 2;                   // softmax -> MMA (128 arrivals): P(j) and its scales are in shared memory
-  uint64_t* pv_done = p_full + 1;                  // MMA -> softmax: PV(j) complete (O updated, P buffer free)
-  uint64_t* o_free = pv_done + 1;                  // softmax -> MMA (128 arrivals): O read out, the next tile may start
+  uint64_t* p_full = s_full + 2;                   // [2] softmax -> MMA (128 arrivals): P tile n (buffer n & 1) and its scales are in shared memory
+  uint64_t* pv_done = p_full + 2;                  // [2] MMA -> softmax: the product with P tile n is complete (O updated, buffer n & 1 free)
+  uint64_t* o_free = pv_done + 2;                  // softmax -> MMA (128 arrivals): O read out, the next tile may start
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_free + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -109,8 +102,10 @@ __global__ void __launch_bounds__(MXA_THREADS, 1) attention_mxfp8_fwd_kernel(con
     }
     mbar_init(&s_full[0], 1);
     mbar_init(&s_full[1], 1);
-    mbar_init(p_full, 128);
-    mbar_init(pv_done, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&p_full[i], 128);
+      mbar_init(&pv_done[i], 1);
+    }
     mbar_init(o_free, 128);
     mbar_init_fence();
   }
@@ -150,7 +145,7 @@ __global__ void __launch_bounds__(MXA_THREADS, 1) attention_mxfp8_fwd_kernel(con
           uint8_t* kt = smem + L::KV_OFFSET + kvs * 2 * L::TILE;
           tma_load_3d(kt, &p.tmk, &kv_full[kvs], 0, j * MXA_BN, bh, pol_kv);
           tma_load_3d(kt + L::TILE, &p.tmv, &kv_full[kvs], 0, j * MXA_BN, bh, pol_kv);
-          uint8_t* sf = smem + L::SF_OFFSET + (2 + 2 * kvs) * 512;
+          uint8_t* sf = smem + L::SF_OFFSET + (3 + 2 * kvs) * 512;
           const size_t atom = ((size_t)bh * kv_blocks_per_head + j) * 512;
           bulk_load(sf, p.sfk + atom, 512, &kv_full[kvs]);
           bulk_load(sf + 512, p.sfv + atom, 512, &kv_full[kvs]);
@@ -178,7 +173,7 @@ __global__ void __launch_bounds__(MXA_THREADS, 1) attention_mxfp8_fwd_kernel(con
       uint32_t kvs = 0, kvph = 0;  // ring position of the next K tile to multiply
       uint32_t vs = 0;             // ring position of the next V tile to multiply
       uint32_t sc = 0;             // S products issued so far (buffer = sc & 1)
-      uint32_t pc = 0;             // P tiles consumed so far
+      uint32_t pc = 0;             // P tiles consumed so far (tile n: buffer n & 1, barriers' phase n >> 1)
       uint32_t tcount = 0;
       bool ok = true;
 
@@ -186,7 +181,7 @@ __global__ void __launch_bounds__(MXA_THREADS, 1) attention_mxfp8_fwd_kernel(con
         if (!mbar_wait(&kv_full[kvs], kvph, status, WAIT_SMEM_FULL)) return false;
         tc_fence_after_sync();
         const uint32_t t_sfk = tmem_base + SFK_COL0 + (sc & 1) * 4;
-        tmem_cp_32x128b_warpx4(t_sfk, sfdesc0 + (uint64_t)(((2 + 2 * kvs) * 512) >> 4));
+        tmem_cp_32x128b_warpx4(t_sfk, sfdesc0 + (uint64_t)(((3 + 2 * kvs) * 512) >> 4));
         const uint64_t kd = kdesc0 + (uint64_t)((kvs * 2 * L::TILE) >> 4);
         const uint32_t d_s = tmem_base + S_COL0 + (sc & 1) * 128;
 #pragma unroll
@@ -219,23 +214,25 @@ __global__ void __launch_bounds__(MXA_THREADS, 1) attention_mxfp8_fwd_kernel(con
           } else {
             umma_commit(q_empty);  // every S of this tile has been issued: Q may be replaced when they complete
           }
-          // O += P(j) V(j)
-          if (!mbar_wait(p_full, pc & 1, status, WAIT_ATTN)) {
+          // O += P(j) V(j): P tile number pc sits in buffer pc & 1
+          const uint32_t pb = pc & 1;
+          if (!mbar_wait(&p_full[pb], (pc >> 1) & 1, status, WAIT_ATTN)) {
             ok = false;
             break;
           }
           tc_fence_after_sync();
-          const uint32_t t_sfv = tmem_base + SFV_COL0 + (pc & 1) * 4;
-          const uint32_t t_sfp = tmem_base + SFP_COL0 + (pc & 1) * 4;
-          tmem_cp_32x128b_warpx4(t_sfp, sfdesc0 + (uint64_t)(512 >> 4));
-          tmem_cp_32x128b_warpx4(t_sfv, sfdesc0 + (uint64_t)(((3 + 2 * vs) * 512) >> 4));
+          const uint32_t t_sfv = tmem_base + SFV_COL0 + pb * 4;
+          const uint32_t t_sfp = tmem_base + SFP_COL0 + pb * 4;
+          tmem_cp_32x128b_warpx4(t_sfp, sfdesc0 + (uint64_t)(((1 + pb) * 512) >> 4));
+          tmem_cp_32x128b_warpx4(t_sfv, sfdesc0 + (uint64_t)(((4 + 2 * vs) * 512) >> 4));
           const uint64_t vd = vdesc0 + (uint64_t)((vs * 2 * L::TILE) >> 4);
+          const uint64_t pd = pdesc + (uint64_t)((pb * L::TILE) >> 4);
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            umma_mxf8_ss(tmem_base + O_COL, pdesc + 2 * k, vd + (uint64_t)((k * 32 * 128) >> 4), id_pv[k],
+            umma_mxf8_ss(tmem_base + O_COL, pd + 2 * k, vd + (uint64_t)((k * 32 * 128) >> 4), id_pv[k],
                          t_sfp, t_sfv, (j > 0 || k > 0) ? 1u : 0u);
           umma_commit(&kv_empty[vs]);
-          umma_commit(pv_done);
+          umma_commit(&pv_done[pb]);
           ++pc;
           if (++vs == MXA_STAGES) vs = 0;
         }
@@ -249,9 +246,12 @@ __global__ void __launch_bounds__(MXA_THREADS, 1) attention_mxfp8_fwd_kernel(con
     const uint32_t t_o = tmem_base + lane_off + O_COL;
     const float scale = p.scale_log2;
     const int s_kv = p.s_kv, s_q = p.s_q, causal = p.causal;
-    uint8_t* const p_row = smem + L::P_OFFSET + row * 128;
-    uint32_t* const p_scale = reinterpret_cast<uint32_t*>(smem + L::SF_OFFSET + 512 + (row & 31) * 16 + (row >> 5) * 4);
-    uint32_t sc = 0, pvc = 0, tcount = 0;
+    uint8_t* const p_row0 = smem + L::P_OFFSET + row * 128;
+    uint8_t* const p_scale0 = smem + L::SF_OFFSET + 512 + (row & 31) * 16 + (row >> 5) * 4;
+    uint32_t sc = 0, tcount = 0;
+    uint32_t pc = 0;  // P tiles written so far (buffer = pc & 1; the MMA side counts the same way)
+    // the product with P tile n signals pv_done[n & 1], phase n >> 1
+    auto wait_pv = [&](uint32_t n) -> bool { return mbar_wait(&pv_done[n & 1], (n >> 1) & 1, status, WAIT_ATTN); };
     bool ok = true;
     for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x, ++tcount) {
       int bh, q0, nkv;
@@ -295,64 +295,81 @@ __global__ void __launch_bounds__(MXA_THREADS, 1) attention_mxfp8_fwd_kernel(con
           alpha = fast_exp2(m - m_blk);
           m = m_blk;
         }
-        // PV(j-1) must be complete before O is rescaled and before P's buffer is written again
-        if (j > 0) {
-          if (!mbar_wait(pv_done, pvc & 1, status, WAIT_ATTN)) {
+        // O may be rescaled only when the previous product is complete (rare: the lazy rescale), and this tile's P
+        // buffer is free once the product before that one is (usually long since)
+        if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+          if (!wait_pv(pc - 1)) {
             ok = false;
             break;
           }
-          ++pvc;
           tc_fence_after_sync();
-          if (__any_sync(0xffffffffu, alpha != 1.f)) {
-            l *= alpha;
+          l *= alpha;
 #pragma unroll 1
-            for (int c = 0; c < MXA_D; c += 32) {
-              uint32_t v[32];
-              tmem_ld_32x32b_x32(t_o + c, v);
-              tmem_ld_wait();
+          for (int c = 0; c < MXA_D; c += 32) {
+            uint32_t v[32];
+            tmem_ld_32x32b_x32(t_o + c, v);
+            tmem_ld_wait();
 #pragma unroll
-              for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-              tmem_st_32x32b_x32(t_o + c, v);
-            }
-            tmem_st_wait();
+            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+            tmem_st_32x32b_x32(t_o + c, v);
           }
+          tmem_st_wait();
+          tc_fence_before_sync();
         }
+        if (pc >= 2 && !wait_pv(pc - 2)) {
+          ok = false;
+          break;
+        }
+        uint8_t* const p_row = p_row0 + (pc & 1) * L::TILE;
+        uint32_t* const p_scale = reinterpret_cast<uint32_t*>(p_scale0 + (pc & 1) * 512);
         // p = exp2(s * scale - m); every 32 keys share the scale 2^ceil(log2(amax / 448)), where amax = exp2 of the
         // block's largest exponent (exp2 is monotonic: no second pass over p)
         uint32_t scale_word = 0;
-        float sum = 0.f;
+        const uint64_t scale2 = pack2(scale, scale), negm2 = pack2(-m, -m);
+        uint64_t sum2 = pack2(0.f, 0.f);
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
           const float amax = fast_exp2(fmaf(bmax[b], scale, -m));
           const uint32_t bits = (__float_as_uint(amax * (1.f / 448.f)) + 0x007FFFFFu) & 0x7F800000u;
           const float inv = bits == 0u ? 0.f : __uint_as_float(0x7F000000u - bits);  // 2^-(e - 127), exact
+          const uint64_t inv2 = pack2(inv, inv);
           scale_word |= (bits >> 23) << (8 * b);
 #pragma unroll
           for (int c = 0; c < 2; ++c) {  // two 16-byte chunks per block
             uint32_t w[4];
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
-              float e[4];
+              uint16_t h[2];
 #pragma unroll
-              for (int t = 0; t < 4; ++t) {
-                e[t] = fast_exp2(fmaf(__uint_as_float(sv[b * 32 + c * 16 + u * 4 + t]), scale, -m));
-                sum += e[t];
+              for (int t = 0; t < 2; ++t) {  // packed f32x2 arithmetic: one instruction per pair
+                const int i = b * 32 + c * 16 + u * 4 + t * 2;
+                const uint64_t x = fma2(pack2(__uint_as_float(sv[i]), __uint_as_float(sv[i + 1])), scale2, negm2);
+                float x0, x1;
+                unpack2(x, x0, x1);
+                const uint64_t e = pack2(fast_exp2(x0), fast_exp2(x1));
+                sum2 = add2(sum2, e);
+                float q0, q1;
+                unpack2(mul2(e, inv2), q0, q1);
+                asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(h[t]) : "f"(q1), "f"(q0));
               }
-              w[u] = mxa_pack4(e[0] * inv, e[1] * inv, e[2] * inv, e[3] * inv);
+              w[u] = (uint32_t)h[0] | ((uint32_t)h[1] << 16);
             }
             const int chunk = b * 2 + c;
             *reinterpret_cast<uint4*>(p_row + ((chunk ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
           }
         }
+        float sum_lo, sum_hi;
+        unpack2(sum2, sum_lo, sum_hi);
+        const float sum = sum_lo + sum_hi;
         *p_scale = scale_word;
         l += sum;
         fence_proxy_async_smem();
-        mbar_arrive(p_full);
+        mbar_arrive(&p_full[pc & 1]);
+        ++pc;
       }
       if (!ok) break;
       // ---- epilogue: the last PV, then O / l as bf16 and the base-2 log-sum-exp
-      if (!mbar_wait(pv_done, pvc & 1, status, WAIT_ATTN)) break;
-      ++pvc;
+      if (!wait_pv(pc - 1)) break;
       tc_fence_after_sync();
       const float inv_l = 1.f / l;
       const bool valid = qrow < s_q;
