@@ -49,7 +49,7 @@ struct MxAttnParams {
   void* o;                    // bf16 [B, H, S_q, D]
   float* lse;
   int* status;
-  int bh, s_q, s_kv, q_tiles, units, causal;
+  int bh, s_q, s_kv, q_tiles, units, causal, head_major;
   float scale_log2;
 };
 
@@ -65,8 +65,14 @@ struct MxAttnSmem {
 };
 
 __device__ __forceinline__ void mxa_tile(const MxAttnParams& p, int unit, int& bh, int& q0, int& nkv) {
-  const int qb = p.q_tiles - 1 - unit / p.bh;  // longest (causal) tiles first
-  bh = unit % p.bh;
+  int qb;
+  if (p.head_major) {  // all query tiles of a head side by side: its K / V stream is shared through L2
+    bh = unit / p.q_tiles;
+    qb = p.q_tiles - 1 - unit % p.q_tiles;
+  } else {             // longest (causal) tiles first, heads side by side
+    qb = p.q_tiles - 1 - unit / p.bh;
+    bh = unit % p.bh;
+  }
   q0 = qb * MXA_BM;
   nkv = (p.s_kv + MXA_BN - 1) / MXA_BN;
   if (p.causal) nkv = min(nkv, (q0 + MXA_BM + MXA_BN - 1) / MXA_BN);
@@ -458,6 +464,9 @@ extern "C" int tb200_attention_mxfp8_fwd(const tb200_attention_mxfp8_args* a, vo
   p.q_tiles = (int)(a->seq_q / MXA_BM);
   p.units = p.q_tiles * p.bh;
   p.causal = a->causal ? 1 : 0;
+  // non-causal: head-major order (the same speed - 1023 against 1017 TFLOP/s at [4, 32, 8192, 128] - with each head's
+  // K and V read from HBM once instead of once per query tile); causal: longest tiles first (976 against 909)
+  p.head_major = a->causal ? 0 : 1;
   p.scale_log2 = a->sm_scale * 1.4426950408889634f;
   auto kfn = attention_mxfp8_fwd_kernel;
   if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, MxAttnSmem::TOTAL) != cudaSuccess)
