@@ -9,7 +9,7 @@
 //              of two score buffers, so that S(j+1) is computed while the softmax works on S(j); then, when P(j) is
 //              published, O += P(j) V(j) (SS: P from shared memory, V the MN-major B operand, four steps over the
 //              128 keys). Scale atoms (512 bytes: [row % 32][row / 32][block]) go to tensor memory by tcgen05.cp.
-//   warps 4-7  softmax: thread t owns query row t. Online softmax in the exp2 domain with the lazy rescale of the
+//   warps 4-11 softmax: two threads per query row (64 score columns each). Online softmax in the exp2 domain with the lazy rescale of the
 //              16-bit kernel (the accumulator is rescaled only when a row's maximum grew by more than 2^8);
 //              p = exp2(s * scale - m) in fp32, its row sum in fp32; every 32 keys of a row share the e8m0 scale
 //              2^ceil(log2(amax / 448)), p / scale is rounded to e4m3 and written to shared memory in the 128-byte
@@ -21,7 +21,9 @@
 // handed back and forth, since tensor memory cannot hold two score buffers, two accumulators and the scale
 // columns) measured the same or slower (992 against 1030 TFLOP/s at [4, 32, 8192, 128]): with the scores and P
 // double-buffered the tensor pipe already runs under the softmax, and the softmax itself is bound by the
-// special-function unit, which serves the exponentials and the e4m3 conversions of both groups alike.
+// special-function unit, which serves the exponentials and the e4m3 conversions of both groups alike. Two threads
+// per query row (this version) gained 2-10 % over one; requesting the next block's scores from tensor memory
+// while the current block is worked on lost 25 % (the second row buffer spills).
 //
 // Counterpart in the reference: _attn_fwd_mxf8_ws and its host entry `attention(q, k, v, q_scale, k_scale, v_scale,
 // sm_scale, causal)`, third_party/tlx/tutorials/blackwell_fa_ws_pipelined_persistent_mxfp8.py:532-1130, :3374
@@ -34,7 +36,7 @@
 
 namespace tb200 {
 
-static constexpr int MXA_THREADS = 256;
+static constexpr int MXA_THREADS = 384;  // TMA warp, MMA warp, two idle, eight softmax warps (two threads per query row)
 static constexpr int MXA_BM = 128;
 static constexpr int MXA_BN = 128;
 static constexpr int MXA_D = 128;
@@ -59,7 +61,8 @@ struct MxAttnSmem {
   static constexpr int KV_OFFSET = TILE;                              // ring: K tile, V tile per stage
   static constexpr int P_OFFSET = KV_OFFSET + MXA_STAGES * 2 * TILE;  // two P tiles
   static constexpr int SF_OFFSET = P_OFFSET + 2 * TILE;               // atoms: Q | P0 | P1 | (K, V) per stage
-  static constexpr int BAR_OFFSET = SF_OFFSET + (3 + 2 * MXA_STAGES) * 512;
+  static constexpr int XCHG_OFFSET = SF_OFFSET + (3 + 2 * MXA_STAGES) * 512;  // [parity][half][row] floats
+  static constexpr int BAR_OFFSET = XCHG_OFFSET + 2 * 2 * 128 * 4;
   static constexpr int NUM_BARS = 2 + 2 * MXA_STAGES + 2 + 2 + 2 + 1;
   static constexpr int TOTAL = BAR_OFFSET + NUM_BARS * 8 + 16 + 1024;
 };
@@ -112,10 +115,10 @@ __global__ void __launch_bounds__(MXA_THREADS, 1) attention_mxfp8_fwd_kernel(con
     mbar_init(&s_full[0], 1);
     mbar_init(&s_full[1], 1);
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&p_full[i], 128);
+      mbar_init(&p_full[i], 256);
       mbar_init(&pv_done[i], 1);
     }
-    mbar_init(o_free, 128);
+    mbar_init(o_free, 256);
     mbar_init_fence();
   }
   if (warp == 1) {
@@ -249,18 +252,25 @@ __global__ void __launch_bounds__(MXA_THREADS, 1) attention_mxfp8_fwd_kernel(con
     }
   } else if (warp >= 4) {
     // ------------------------------------------------------------------ softmax / epilogue
+    // Two threads per query row: warps 4-7 take score columns 0-63 of their lane quarter's rows, warps 8-11 columns
+    // 64-127 (a pass of one warp per scheduler over whole rows is bound by the length of that warp's instruction
+    // stream; two warps per scheduler hide each other's latencies). The halves exchange their block maxima through
+    // shared memory (a 64-thread named barrier per lane quarter) and keep partial row sums, added at the end.
     const int q = warp & 3;
+    const int h = (warp - 4) >> 2;  // which half of the row
     const int row = q * 32 + lane;
     const uint32_t lane_off = (uint32_t)(q * 32) << 16;
-    const uint32_t t_o = tmem_base + lane_off + O_COL;
+    const uint32_t t_o = tmem_base + lane_off + O_COL + h * 64;
     const float scale = p.scale_log2;
     const int s_kv = p.s_kv, s_q = p.s_q, causal = p.causal;
     uint8_t* const p_row0 = smem + L::P_OFFSET + row * 128;
-    uint8_t* const p_scale0 = smem + L::SF_OFFSET + 512 + (row & 31) * 16 + (row >> 5) * 4;
+    uint8_t* const p_scale0 = smem + L::SF_OFFSET + 512 + (row & 31) * 16 + (row >> 5) * 4 + h * 2;
+    float* const xchg = reinterpret_cast<float*>(smem + L::XCHG_OFFSET);
     uint32_t sc = 0, tcount = 0;
     uint32_t pc = 0;  // P tiles written so far (buffer = pc & 1; the MMA side counts the same way)
     // the product with P tile n signals pv_done[n & 1], phase n >> 1
     auto wait_pv = [&](uint32_t n) -> bool { return mbar_wait(&pv_done[n & 1], (n >> 1) & 1, status, WAIT_ATTN); };
+    auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + q) : "memory"); };
     bool ok = true;
     for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x, ++tcount) {
       int bh, q0, nkv;
@@ -273,30 +283,35 @@ __global__ void __launch_bounds__(MXA_THREADS, 1) attention_mxfp8_fwd_kernel(con
           break;
         }
         tc_fence_after_sync();
-        const uint32_t t_s = tmem_base + lane_off + S_COL0 + (sc & 1) * 128;
-        uint32_t sv[128];
+        const uint32_t t_s = tmem_base + lane_off + S_COL0 + (sc & 1) * 128 + h * 64;
+        uint32_t sv[64];
         tmem_ld_row32<0>(t_s, sv);
         tmem_ld_row32<32>(t_s + 32, sv);
-        tmem_ld_row32<64>(t_s + 64, sv);
-        tmem_ld_row32<96>(t_s + 96, sv);
         tmem_ld_wait();
-        const int k0 = j * MXA_BN;
-        const bool need_mask = (k0 + MXA_BN > s_kv) || (causal && (k0 + MXA_BN - 1 > q0));
+        const int k0 = j * MXA_BN + h * 64;
+        const bool need_mask = (j * MXA_BN + MXA_BN > s_kv) || (causal && (j * MXA_BN + MXA_BN - 1 > q0));
         const int limit = causal ? min(s_kv - 1, qrow) : (s_kv - 1);
         if (need_mask) {
 #pragma unroll
-          for (int i = 0; i < 128; ++i)
+          for (int i = 0; i < 64; ++i)
             if (k0 + i > limit) sv[i] = 0xff800000u;
         }
-        float bmax[4];
+        float bmax[2];
 #pragma unroll
-        for (int b = 0; b < 4; ++b) {
-          float mx = -INFINITY;
+        for (int b = 0; b < 2; ++b) {
+          float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sv[b * 32 + i]));
-          bmax[b] = mx;
+          for (int i = 0; i < 32; i += 2) {
+            mx0 = fmaxf(mx0, __uint_as_float(sv[b * 32 + i]));
+            mx1 = fmaxf(mx1, __uint_as_float(sv[b * 32 + i + 1]));
+          }
+          bmax[b] = fmaxf(mx0, mx1);
         }
-        const float m_blk = fmaxf(fmaxf(bmax[0], bmax[1]), fmaxf(bmax[2], bmax[3])) * scale;
+        // the row's block maximum over both halves
+        float* const xs = xchg + (sc & 1) * 256;
+        xs[h * 128 + row] = fmaxf(bmax[0], bmax[1]);
+        pair_sync();
+        const float m_blk = fmaxf(fmaxf(bmax[0], bmax[1]), xs[(h ^ 1) * 128 + row]) * scale;
         float alpha = 1.f;
         if (j == 0) {
           m = m_blk;
@@ -305,7 +320,8 @@ __global__ void __launch_bounds__(MXA_THREADS, 1) attention_mxfp8_fwd_kernel(con
           m = m_blk;
         }
         // O may be rescaled only when the previous product is complete (rare: the lazy rescale), and this tile's P
-        // buffer is free once the product before that one is (usually long since)
+        // buffer is free once the product before that one is (usually long since). Both halves of a row take the same
+        // decisions (same maxima); each rescales its 64 columns of O.
         if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
           if (!wait_pv(pc - 1)) {
             ok = false;
@@ -314,7 +330,7 @@ __global__ void __launch_bounds__(MXA_THREADS, 1) attention_mxfp8_fwd_kernel(con
           tc_fence_after_sync();
           l *= alpha;
 #pragma unroll 1
-          for (int c = 0; c < MXA_D; c += 32) {
+          for (int c = 0; c < 64; c += 32) {
             uint32_t v[32];
             tmem_ld_32x32b_x32(t_o + c, v);
             tmem_ld_wait();
@@ -330,14 +346,14 @@ __global__ void __launch_bounds__(MXA_THREADS, 1) attention_mxfp8_fwd_kernel(con
           break;
         }
         uint8_t* const p_row = p_row0 + (pc & 1) * L::TILE;
-        uint32_t* const p_scale = reinterpret_cast<uint32_t*>(p_scale0 + (pc & 1) * 512);
+        uint16_t* const p_scale = reinterpret_cast<uint16_t*>(p_scale0 + (pc & 1) * 512);
         // p = exp2(s * scale - m); every 32 keys share the scale 2^ceil(log2(amax / 448)), where amax = exp2 of the
         // block's largest exponent (exp2 is monotonic: no second pass over p)
         uint32_t scale_word = 0;
         const uint64_t scale2 = pack2(scale, scale), negm2 = pack2(-m, -m);
         uint64_t sum2 = pack2(0.f, 0.f);
 #pragma unroll
-        for (int b = 0; b < 4; ++b) {
+        for (int b = 0; b < 2; ++b) {
           const float amax = fast_exp2(fmaf(bmax[b], scale, -m));
           const uint32_t bits = (__float_as_uint(amax * (1.f / 448.f)) + 0x007FFFFFu) & 0x7F800000u;
           const float inv = bits == 0u ? 0.f : __uint_as_float(0x7F000000u - bits);  // 2^-(e - 127), exact
@@ -348,7 +364,7 @@ __global__ void __launch_bounds__(MXA_THREADS, 1) attention_mxfp8_fwd_kernel(con
             uint32_t w[4];
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
-              uint16_t h[2];
+              uint16_t hh[2];
 #pragma unroll
               for (int t = 0; t < 2; ++t) {  // packed f32x2 arithmetic: one instruction per pair
                 const int i = b * 32 + c * 16 + u * 4 + t * 2;
@@ -357,34 +373,39 @@ __global__ void __launch_bounds__(MXA_THREADS, 1) attention_mxfp8_fwd_kernel(con
                 unpack2(x, x0, x1);
                 const uint64_t e = pack2(fast_exp2(x0), fast_exp2(x1));
                 sum2 = add2(sum2, e);
-                float q0, q1;
-                unpack2(mul2(e, inv2), q0, q1);
-                asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(h[t]) : "f"(q1), "f"(q0));
+                float q0f, q1f;
+                unpack2(mul2(e, inv2), q0f, q1f);
+                asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hh[t]) : "f"(q1f), "f"(q0f));
               }
-              w[u] = (uint32_t)h[0] | ((uint32_t)h[1] << 16);
+              w[u] = (uint32_t)hh[0] | ((uint32_t)hh[1] << 16);
             }
-            const int chunk = b * 2 + c;
+            const int chunk = h * 4 + b * 2 + c;
             *reinterpret_cast<uint4*>(p_row + ((chunk ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
           }
         }
         float sum_lo, sum_hi;
         unpack2(sum2, sum_lo, sum_hi);
-        const float sum = sum_lo + sum_hi;
-        *p_scale = scale_word;
-        l += sum;
+        *p_scale = (uint16_t)scale_word;
+        l += sum_lo + sum_hi;
         fence_proxy_async_smem();
         mbar_arrive(&p_full[pc & 1]);
         ++pc;
       }
       if (!ok) break;
-      // ---- epilogue: the last PV, then O / l as bf16 and the base-2 log-sum-exp
+      // ---- epilogue: the last PV, then O / l as bf16 and the base-2 log-sum-exp; the halves add their row sums
       if (!wait_pv(pc - 1)) break;
       tc_fence_after_sync();
+      float* const xs = xchg + (tcount & 1) * 256;
+      pair_sync();  // the pair has left the last block's exchange
+      xs[h * 128 + row] = l;
+      pair_sync();
+      l += xs[(h ^ 1) * 128 + row];
+      pair_sync();  // both have read: the exchange area may be written again
       const float inv_l = 1.f / l;
       const bool valid = qrow < s_q;
-      uint16_t* orow = reinterpret_cast<uint16_t*>(p.o) + ((size_t)bh * s_q + qrow) * MXA_D;
+      uint16_t* orow = reinterpret_cast<uint16_t*>(p.o) + ((size_t)bh * s_q + qrow) * MXA_D + h * 64;
 #pragma unroll 1
-      for (int c = 0; c < MXA_D; c += 32) {
+      for (int c = 0; c < 64; c += 32) {
         uint32_t v[32];
         tmem_ld_32x32b_x32(t_o + c, v);
         tmem_ld_wait();
@@ -400,7 +421,7 @@ __global__ void __launch_bounds__(MXA_THREADS, 1) attention_mxfp8_fwd_kernel(con
       }
       tc_fence_before_sync();
       mbar_arrive(o_free);
-      if (valid && p.lse) p.lse[(size_t)bh * s_q + qrow] = m + log2f(l);
+      if (valid && h == 0 && p.lse) p.lse[(size_t)bh * s_q + qrow] = m + log2f(l);
     }
   }
 
