@@ -10,7 +10,9 @@
 //                slices as the softmax publishes P in 32-column chunks, overlapping its tail.
 //                (Measured alternatives that lost: one issuing thread per group, 715 vs 900
 //                TFLOP/s - MMAs of two streams interleave one by one; a Cody-Waite + cubic exp2
-//                on the FMA pipe for 25-50 % of the elements, 5-20 % slower - issue-bound.)
+//                on the FMA pipe for 25-50 % of the elements, 5-20 % slower - issue-bound; and one
+//                ex2.approx.ftz.bf16x2 per pair of scores - half the special-function instructions, P
+//                produced directly in its stored precision - 983 vs 1106 TFLOP/s.)
 //                S_g = Q_g K^T : SS MMA, 128 x 128 x D.    O_g += P_g V : TS MMA, P read from TMEM,
 //                V is the MN-major B operand straight from its row-major tile.
 //   warps 4-7    softmax + correction + epilogue for group 0;  warps 8-11 the same for group 1.
