@@ -312,15 +312,16 @@ def test_betas_out_alpha_and_accumulator_input(cuda):
     torch.testing.assert_close(got.cpu().float(), want, rtol=2e-2, atol=2e-2)
 
 
+@pytest.mark.parametrize("dims", [(320, 384), (328, 344)])  # whole and ragged K steps / column tiles
 @pytest.mark.parametrize("swiglu", [False, True])
-def test_tile_modes_agree_bit_for_bit(cuda, swiglu):
+def test_tile_modes_agree_bit_for_bit(cuda, swiglu, dims):
     """One CTA per block and CTA pairs accumulate every output in the same order: identical results on sorted rows,
     with experts of 0, 1, 2, 3 and more blocks, with and without a scatter."""
     from triton_b200.triton_kernels.matmul import matmul, swiglu_activation
     from triton_b200.triton_kernels.tensor import make_ragged_tensor_metadata
     g = torch.Generator().manual_seed(17)
     sizes = torch.tensor([0, 100, 128, 129, 256, 300, 384, 385, 1, 700, 0, 513], dtype=torch.int32)
-    R, K, N = int(sizes.sum()), 320, 384
+    R, (K, N) = int(sizes.sum()), dims
     E = sizes.numel()
     x = torch.randn(R, K, generator=g).to(torch.bfloat16).to(cuda)
     w = (0.1 * torch.randn(E, K, N, generator=g)).to(torch.bfloat16).to(cuda)
