@@ -73,8 +73,15 @@ def attention_mxfp8_ref(q, k, v, q_scale, k_scale, v_scale, sm_scale: float, cau
     from . import mxfp8 as mx
     Z, H, N, D = q.shape
     Nk = k.shape[2]
-    qd = mx.dequantize(q.reshape(Z * H * N, D).cpu(), q_scale.reshape(-1).cpu()).reshape(Z, H, N, D)
-    kd = mx.dequantize(k.reshape(Z * H * Nk, D).cpu(), k_scale.reshape(-1).cpu()).reshape(Z, H, Nk, D)
+    def dq(x2d, atoms):  # the atoms cover the matrix padded to 128 rows x 4 blocks
+        rows, cols = x2d.shape
+        rp, bp = -(-rows // 128) * 128, -(-(cols // 32) // 4) * 4
+        xp = torch.zeros(rp, bp * 32, dtype=torch.float32)
+        xp[:rows, :cols] = x2d.float()
+        sc = mx.unswizzle_scales(atoms.reshape(-1).cpu().view(torch.uint8), rp, bp)
+        return (xp * mx.e8m0_to_float(sc).repeat_interleave(32, dim=1))[:rows, :cols]
+    qd = dq(q.reshape(Z * H * N, D).cpu(), q_scale).reshape(Z, H, N, D)
+    kd = dq(k.reshape(Z * H * Nk, D).cpu(), k_scale).reshape(Z, H, Nk, D)
     vt = v.reshape(Z * H * Nk, D).t().contiguous().cpu()            # [D, ZHN]: the matrix that was quantised
-    vd = mx.dequantize(vt, v_scale.reshape(-1).cpu()).t().reshape(Z, H, Nk, D)
+    vd = dq(vt, v_scale).t().reshape(Z, H, Nk, D)
     return attention_ref(qd, kd, vd, sm_scale, causal)

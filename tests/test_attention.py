@@ -31,6 +31,17 @@ def test_bf16_block_multiples(cuda, causal, S, D):
 
 
 @pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("D", [16, 32])
+def test_small_head_dims(cuda, causal, D):
+    """Head dims 16 and 32 of the reference's set (blackwell_fa_ws_pipelined_persistent.py:3291-3292) run zero-padded
+    through the 64-wide kernel."""
+    o, lse, ro, rl = _run(cuda, 2, 2, 300, D, causal)
+    assert o.shape[-1] == D
+    torch.testing.assert_close(o, ro, rtol=1e-2, atol=1e-2)
+    torch.testing.assert_close(lse, rl, rtol=0, atol=1e-3)
+
+
+@pytest.mark.parametrize("causal", [False, True])
 @pytest.mark.parametrize("S", [1, 77, 129, 1000])
 def test_ragged_sequence_lengths(cuda, causal, S):
     o, lse, ro, rl = _run(cuda, 1, 2, S, 128, causal)
@@ -105,7 +116,7 @@ def test_argument_checks(cuda):
     with pytest.raises(AssertionError):
         attention(q, q[..., :64].contiguous(), q, 1.0, False)
     with pytest.raises(NotImplementedError):
-        z = torch.zeros(1, 1, 128, 32, dtype=torch.bfloat16, device=cuda)
+        z = torch.zeros(1, 1, 128, 256, dtype=torch.bfloat16, device=cuda)
         attention(z, z, z, 1.0, False)
     with pytest.raises(RuntimeError):
         attention(q.cpu(), q.cpu(), q.cpu(), 1.0, False)

@@ -11,9 +11,8 @@ from oracle import attention as o_attn
 pytestmark = pytest.mark.gpu
 
 
-def _run(cuda, B, H, S, causal, dtype=torch.bfloat16, scale=None, seed=5, Skv=None, std=1.0):
+def _run(cuda, B, H, S, causal, dtype=torch.bfloat16, scale=None, seed=5, Skv=None, std=1.0, D=128):
     from triton_b200.tutorials.blackwell_fa_ws_pipelined_persistent import attention_backward, attention_with_lse
-    D = 128
     Skv = Skv or S
     g = torch.Generator().manual_seed(seed)
     q = (torch.randn(B, H, S, D, generator=g) * std).to(dtype)
@@ -40,6 +39,15 @@ def _check(got, ref, atol, rtol):
 @pytest.mark.parametrize("S", [64, 128, 256, 1024])
 def test_bf16_block_multiples(cuda, causal, S):
     got, ref = _run(cuda, 2, 2, S, causal)
+    _check(got, ref, 2e-2, 2e-2)
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("D", [32, 64])
+def test_smaller_head_dims(cuda, causal, D):
+    """Head dims below 128 run zero-padded through the 128-wide backward kernel."""
+    got, ref = _run(cuda, 1, 2, 320, causal, D=D)
+    assert got[0].shape[-1] == D
     _check(got, ref, 2e-2, 2e-2)
 
 
@@ -116,7 +124,7 @@ def test_linearity_in_do_at_config3_length(cuda):
 
 def test_argument_checks(cuda):
     from triton_b200.tutorials.blackwell_fa_ws_pipelined_persistent import attention_backward
-    q = torch.randn(1, 1, 64, 64, device=cuda, dtype=torch.bfloat16)
+    q = torch.randn(1, 1, 64, 256, device=cuda, dtype=torch.bfloat16)
     lse = torch.zeros(1, 1, 64, device=cuda)
     with pytest.raises(NotImplementedError):
         attention_backward(q, q, q, q, lse, q, 0.1, False)

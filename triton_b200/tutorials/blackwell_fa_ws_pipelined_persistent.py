@@ -3,12 +3,14 @@ flash-attention forward, ``third_party/tlx/tutorials/blackwell_fa_ws_pipelined_p
 
 q, k, v: ``[B, H, S, D]`` fp16 or bf16 CUDA tensors with equal head dims; returns ``o`` with the shape
 and dtype of ``q``. Like the reference (``_attention``, ``:3285-3488``) the call is an autograd Function
-when an input requires grad: ``backward`` runs the backward kernel (head_dim 128) and returns
+when an input requires grad: ``backward`` runs the backward kernel (built for head_dim 128; 16, 32 and 64 run
+zero-padded) and returns
 ``dq, dk, dv`` in the input dtype; ``attention_backward`` is the same step as a plain function.
 The reference keeps the row statistic ``M = m*sm_scale*log2(e) + log2(l)`` (base-2 log-sum-exp, ``:886-894``) internal;
 ``attention_with_lse`` returns it as a second fp32 ``[B, H, S]`` tensor without changing the
 signature of ``attention``. ``config`` is accepted for call compatibility (the tiling is fixed:
-256 query rows per CTA as two groups of 128, KV blocks of 128).
+256 query rows per CTA as two groups of 128, KV blocks of 128). Head dims: 64 and 128 natively, 16 and 32
+zero-padded to 64; 256 (the last of the reference's set, ``:3291-3292``) raises ``NotImplementedError``.
 """
 from __future__ import annotations
 
@@ -21,14 +23,23 @@ from .. import _lib
 _DT = {torch.bfloat16: _lib.BF16, torch.float16: _lib.F16}
 
 
+def _pad_head_dim(t, d):
+    return torch.nn.functional.pad(t, (0, d - t.shape[-1])) if t.shape[-1] < d else t
+
+
 def attention_with_lse(q, k, v, sm_scale, causal, config=None):
     HEAD_DIM_Q, HEAD_DIM_K, HEAD_DIM_V = q.shape[-1], k.shape[-1], v.shape[-1]
     assert HEAD_DIM_Q == HEAD_DIM_K and HEAD_DIM_K == HEAD_DIM_V
     assert HEAD_DIM_K in {16, 32, 64, 128, 256}
-    if HEAD_DIM_K not in (64, 128):
-        raise NotImplementedError(f"head_dim {HEAD_DIM_K}: this kernel is built for 64 and 128")
+    if HEAD_DIM_K == 256:
+        raise NotImplementedError("head_dim 256: the kernels are built for 64 and 128 (16 and 32 run zero-padded to 64)")
     if not q.is_cuda:
         raise RuntimeError("triton_b200 attention needs CUDA tensors (there is no CPU path)")
+    if HEAD_DIM_K < 64:
+        # zero columns add nothing to q k^T (sm_scale is the caller's) and give zero output columns: the 64-wide
+        # kernel serves head dims 16 and 32 at the cost of the padded work
+        o, M = attention_with_lse(_pad_head_dim(q, 64), _pad_head_dim(k, 64), _pad_head_dim(v, 64), sm_scale, causal)
+        return o[..., :HEAD_DIM_K].contiguous(), M
     assert q.dim() == 4 and k.dim() == 4 and v.dim() == 4
     assert q.dtype in _DT and k.dtype == q.dtype and v.dtype == q.dtype
     assert k.shape == v.shape and q.shape[:2] == k.shape[:2]
@@ -53,11 +64,19 @@ def attention_with_lse(q, k, v, sm_scale, causal, config=None):
 
 def attention_backward(q, k, v, o, lse, do, sm_scale, causal):
     """dq, dk, dv for ``o, lse = attention_with_lse(q, k, v, sm_scale, causal)`` and the output gradient
-    ``do`` (the reference's ``_attention.backward``, ``:3362``; head_dim 128)."""
+    ``do`` (the reference's ``_attention.backward``, ``:3362``). The kernel is built for head_dim 128; 16, 32 and 64
+    run zero-padded."""
     if not q.is_cuda:
         raise RuntimeError("triton_b200 attention needs CUDA tensors (there is no CPU path)")
-    if q.shape[-1] != 128:
-        raise NotImplementedError(f"attention backward: head_dim {q.shape[-1]} (the kernel is built for 128)")
+    if q.shape[-1] not in (16, 32, 64, 128):
+        raise NotImplementedError(f"attention backward: head_dim {q.shape[-1]} (16, 32, 64 and 128 are implemented)")
+    if q.shape[-1] < 128:
+        # the backward kernel is built for 128: smaller head dims run zero-padded (zero columns of q, k, v, o and do
+        # contribute nothing to the scores, to Delta or to the other columns' gradients)
+        d = q.shape[-1]
+        dq, dk, dv = attention_backward(*(_pad_head_dim(t, 128) for t in (q, k, v, o)), lse,
+                                        _pad_head_dim(do.to(q.dtype), 128), sm_scale, causal)
+        return dq[..., :d].contiguous(), dk[..., :d].contiguous(), dv[..., :d].contiguous()
     assert q.dtype in _DT and k.dtype == q.dtype and v.dtype == q.dtype and o.dtype == q.dtype
     assert o.shape == q.shape and do.shape == q.shape and k.shape == v.shape
     q, k, v, o = q.contiguous(), k.contiguous(), v.contiguous(), o.contiguous()

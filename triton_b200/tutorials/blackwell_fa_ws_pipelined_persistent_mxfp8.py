@@ -6,8 +6,8 @@ Same contract: ``q``, ``k``, ``v`` are ``[Z, H, N_CTX, HEAD_DIM]`` ``float8_e4m3
 is_swizzled_scales=True)`` and ``swizzled_to_tma_preshuffled`` (``:3290-3371``): Q and K quantised along
 ``HEAD_DIM``, V along the sequence (its transpose ``[HEAD_DIM, Z*H*N_CTX]`` is what was quantised). The scale tensors
 may have any shape (the reference's is ``[Z*H, blocks, 1, 2, 256]``) as long as their bytes are the atoms in
-``(batch*head, 128-row block)`` order. The result is a new bf16 tensor of ``q``'s shape. ``HEAD_DIM`` 128 and
-sequence lengths that are multiples of 128 are implemented (the reference's test runs 64 and 128).
+``(batch*head, 128-row block)`` order. The result is a new bf16 tensor of ``q``'s shape. ``HEAD_DIM`` 128 (and 64,
+zero-padded to 128: the reference's test runs both) and sequence lengths that are multiples of 128 are implemented.
 
 ``generate_attention_inputs(shape, device, dtype)`` mirrors the reference's helper of the same name (``:3320-3371``)
 with this library's own quantiser (``triton_kernels.numerics_details.mxfp.downcast_to_mxfp``, scale rounded up) in
@@ -23,10 +23,12 @@ from .. import _lib
 
 
 def swizzle_block_scales(scales: torch.Tensor) -> torch.Tensor:
-    """``[rows, blocks]`` e8m0 bytes (rows a multiple of 128, blocks a multiple of 4) -> the 512-byte atoms
+    """``[rows, blocks]`` e8m0 bytes (padded to a multiple of 128 rows and of 4 blocks) -> the 512-byte atoms
     ``[rows/128][blocks/4][row % 32][row / 32 % 4][block % 4]``, flat."""
     rows, cols = scales.shape
-    assert rows % 128 == 0 and cols % 4 == 0, "whole 128 x 4 atoms"
+    if rows % 128 or cols % 4:  # whole 128 x 4 atoms, zero bytes in the unused slots (what the reference's layout does)
+        scales = torch.nn.functional.pad(scales, (0, (-cols) % 4, 0, (-rows) % 128))
+        rows, cols = scales.shape
     t = scales.reshape(rows // 128, 4, 32, cols // 4, 4)  # [rb][row/32][row%32][cb][c%4]
     return t.permute(0, 3, 2, 1, 4).contiguous().reshape(-1)
 
@@ -60,6 +62,23 @@ def generate_attention_inputs(shape, device, dtype=torch.float8_e4m3fn):
     return tuple(out)
 
 
+def _attention_d64(q, k, v, q_scale, k_scale, v_scale, sm_scale, causal):
+    """Head dim 64 through the 128-wide kernel: zero value columns (they add nothing to q k^T and give zero output
+    columns) and scale 1.0 in the atoms' unused slots - blocks 2, 3 of every row for Q and K, rows 64..127 for V
+    (the reference's swizzled layout pads its atoms to 128 rows x 4 blocks, so the atom counts are the same)."""
+    Z, H, N, D = q.shape
+    Nk = k.shape[2]
+    pad = lambda t: torch.nn.functional.pad(t.view(torch.uint8), (0, 64)).view(torch.float8_e4m3fn)
+    qs, ks, vs = (t.contiguous().view(torch.uint8).reshape(-1, 32, 4, 4).clone() for t in (q_scale, k_scale, v_scale))
+    assert qs.shape[0] == Z * H * N // 128 and ks.shape[0] == Z * H * Nk // 128 and vs.shape[0] == Z * H * Nk // 128, \
+        "scale tensor: one 512-byte atom per 128 rows"
+    qs[:, :, :, 2:] = 127   # [row % 32][row / 32][block]: blocks 2, 3 cover head-dim columns 64..127
+    ks[:, :, :, 2:] = 127
+    vs[:, :, 2:, :] = 127   # rows = head-dim columns: 64..127 are padding
+    o = attention(pad(q), pad(k), pad(v), qs, ks, vs, sm_scale, causal)
+    return o[..., :64].contiguous()
+
+
 def attention(q, k, v, q_scale, k_scale, v_scale, sm_scale, causal, config=None):
     """MXFP8 flash-attention forward (``tb200_attention_mxfp8_fwd``); ``config`` is accepted and ignored (the tiling is
     the kernel's own)."""
@@ -69,8 +88,10 @@ def attention(q, k, v, q_scale, k_scale, v_scale, sm_scale, causal, config=None)
     assert q.dtype == k.dtype == v.dtype == torch.float8_e4m3fn, "MXFP8 attention takes float8_e4m3fn values"
     Z, H, N, D = q.shape
     Nk = k.shape[2]
+    if D == 64:
+        return _attention_d64(q, k, v, q_scale, k_scale, v_scale, sm_scale, causal)
     if D != 128:
-        raise NotImplementedError("MXFP8 attention: head dim 128 is implemented")
+        raise NotImplementedError("MXFP8 attention: head dims 64 and 128 are implemented")
     if N % 128 or Nk % 128:
         raise NotImplementedError("MXFP8 attention: sequence lengths must be multiples of 128 (whole scale atoms)")
     q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
