@@ -82,6 +82,9 @@ struct Mx4Smem {
   static constexpr int TOTAL = BAR_OFFSET + (2 * M4_STAGES + 2) * 8 + 16 + 1024;
 };
 
+// EXT: the instantiation with MX-scaled activations, MX-quantised output and flexpoint scales; the plain one compiles
+// them out, which keeps its producer and epilogue loops as short as they were before those existed (4-8 % of a layer).
+template <bool EXT>
 __global__ void __launch_bounds__(M4_THREADS, 1) moe_gemm_mx4_kernel(const __grid_constant__ Mx4Params p) {
   using L = Mx4Smem;
   constexpr int BN = M4_BN, STAGES = M4_STAGES;
@@ -140,7 +143,7 @@ __global__ void __launch_bounds__(M4_THREADS, 1) moe_gemm_mx4_kernel(const __gri
     // scale bytes of this K step for rows l, l + 32, l + 64, l + 96 (one step ahead, so the loads are in flight
     // while the warp waits for a free stage) and writes them as the 16 bytes of row l of a 512-byte atom
     // ([row % 32][row / 32][k]), the order tcgen05.cp.32x128b.warpx4 turns into the MMA's scale columns.
-    const uint8_t* const x_sf = p.x_sf;
+    const uint8_t* const x_sf = EXT ? p.x_sf : nullptr;
     if (lane == 0 || x_sf) {
       const uint64_t pol_x = policy_evict_normal();
       const uint64_t pol_w = policy_evict_first();  // a weight tile is read once per row block
@@ -207,7 +210,7 @@ __global__ void __launch_bounds__(M4_THREADS, 1) moe_gemm_mx4_kernel(const __gri
       const uint64_t sfdesc0 = make_smem_desc(smem_a + L::SF_OFFSET, 16, 128, SWIZZLE_NONE);
       const uint32_t tfull_a = smem_u32(tfull), tempty_a = smem_u32(tempty);
       const uint32_t t_sfa_one = tmem_base + SFA_COL;
-      const bool mx_x = p.x_sf != nullptr;
+      const bool mx_x = EXT && p.x_sf != nullptr;
       uint32_t s = 0, ph = 0, tcount = 0, kpar = 0;
       bool ok = true, ready = false;
       for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x) {
@@ -253,13 +256,13 @@ __global__ void __launch_bounds__(M4_THREADS, 1) moe_gemm_mx4_kernel(const __gri
     const int q = warp & 3;
     const int n = p.n, rows_y = p.rows_y;
     void* const y = p.y;
-    const float acc_scale = (p.x_scale ? __ldg(p.x_scale) : 1.f) * (p.w_flex ? __ldg(p.w_flex) : 1.f);
+    const float acc_scale = (p.x_scale ? __ldg(p.x_scale) : 1.f) * (EXT && p.w_flex ? __ldg(p.w_flex) : 1.f);
     MoeEpilogueExtra flex;
-    if (p.y_expected) {
+    if (EXT && p.y_expected) {
       flex.inv_expected = 1.f / __ldg(p.y_expected);
       if (p.saturate) flex.clip = p.out_kind == MOE_OUT_E5M2 ? 57344.f : p.out_kind == MOE_OUT_E4M3 ? 448.f : 65504.f;
     }
-    flex.track_absmax = p.y_actual != nullptr;
+    flex.track_absmax = EXT && p.y_actual != nullptr;
     const uint32_t tempty_a = smem_u32(tempty);
     uint32_t tcount = 0;
     for (int unit = blockIdx.x; unit < units; unit += gridDim.x) {
@@ -283,7 +286,7 @@ __global__ void __launch_bounds__(M4_THREADS, 1) moe_gemm_mx4_kernel(const __gri
       }
       const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16);
       const float* brow = p.bias ? p.bias + (long long)e * n : nullptr;
-      if (p.y_sf) {
+      if (EXT && p.y_sf) {
         // MX-quantised output: a block of 32 outputs is one chunk of 32 accumulator columns, or two with SwiGLU
         const int step = p.swiglu ? 64 : 32;
 #pragma unroll 1
@@ -319,7 +322,7 @@ __global__ void __launch_bounds__(M4_THREADS, 1) moe_gemm_mx4_kernel(const __gri
           absmax = fmaxf(absmax, moe_store_chunk(v, y, p.ldy, out_row, col, n, brow, p.swiglu, p.alpha, p.limit,
                                                  p.has_limit, gamma, p.out_kind, acc_scale, flex));
         }
-        if (p.y_actual) moe_flex_publish(absmax, p.y_actual, p.out_kind);
+        if (EXT && p.y_actual) moe_flex_publish(absmax, p.y_actual, p.out_kind);
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -359,6 +362,7 @@ struct Mx4SwapSmem {
 };
 static_assert(Mx4SwapSmem::TOTAL <= 232448, "shared memory budget");
 
+template <bool EXT>
 __global__ void __launch_bounds__(M4_THREADS, 1) moe_gemm_mx4_swap_kernel(const __grid_constant__ Mx4Params p) {
   using L = Mx4SwapSmem;
   constexpr int STAGES = S4_STAGES;
@@ -419,7 +423,7 @@ __global__ void __launch_bounds__(M4_THREADS, 1) moe_gemm_mx4_swap_kernel(const 
     // ------------------------------------------------------------- producer
     // With MX-scaled activations lane l also stages the four scale bytes of token row0 + l for each K step (row l of
     // a 512-byte atom, the other twelve bytes of the row are 1.0), fetched one step ahead.
-    const uint8_t* const x_sf = p.x_sf;
+    const uint8_t* const x_sf = EXT ? p.x_sf : nullptr;
     if (lane == 0 || x_sf) {
       const uint64_t pol_x = policy_evict_last();
       const uint64_t pol_w = policy_evict_first();
@@ -481,7 +485,7 @@ __global__ void __launch_bounds__(M4_THREADS, 1) moe_gemm_mx4_swap_kernel(const 
       const uint64_t sfdesc0 = make_smem_desc(smem_a + L::SF_OFFSET, 16, 128, SWIZZLE_NONE);
       const uint32_t tfull_a = smem_u32(tfull), tempty_a = smem_u32(tempty);
       const uint32_t t_sfb_one = tmem_base + SFB_COL;
-      const bool mx_x = p.x_sf != nullptr;
+      const bool mx_x = EXT && p.x_sf != nullptr;
       uint32_t s = 0, ph = 0, tcount = 0, kpar = 0;
       bool ok = true, ready = false;
       for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x) {
@@ -529,12 +533,12 @@ __global__ void __launch_bounds__(M4_THREADS, 1) moe_gemm_mx4_swap_kernel(const 
     const float alpha = p.alpha, limit = p.limit;
     void* const y = p.y;
     const long long ldy = p.ldy;
-    const float acc_scale = (p.x_scale ? __ldg(p.x_scale) : 1.f) * (p.w_flex ? __ldg(p.w_flex) : 1.f);
-    const float inv_expected = p.y_expected ? 1.f / __ldg(p.y_expected) : 1.f;
-    const float clip = (p.y_expected && p.saturate)
+    const float acc_scale = (p.x_scale ? __ldg(p.x_scale) : 1.f) * (EXT && p.w_flex ? __ldg(p.w_flex) : 1.f);
+    const float inv_expected = EXT && p.y_expected ? 1.f / __ldg(p.y_expected) : 1.f;
+    const float clip = (EXT && p.y_expected && p.saturate)
                            ? (out_kind == MOE_OUT_E5M2 ? 57344.f : out_kind == MOE_OUT_E4M3 ? 448.f : 65504.f) : 0.f;
-    float* const y_actual = p.y_actual;
-    uint8_t* const y_sf = p.y_sf;
+    float* const y_actual = EXT ? p.y_actual : nullptr;
+    uint8_t* const y_sf = EXT ? p.y_sf : nullptr;
     const long long ld_ysf = p.ld_ysf;
     const uint32_t tempty_a = smem_u32(tempty);
     uint32_t tcount = 0;
@@ -712,13 +716,14 @@ extern "C" int tb200_moe_gemm_mx4(const tb200_moe_gemm_mx4_args* a, void* stream
     p.idesc[k] = swap ? make_idesc_mx(wfmt, xfmt, S4_WROWS, S4_XROWS, k, k) : make_idesc_mx(xfmt, wfmt, M4_BM, M4_BN, k, k);
 
   const int grid = p.units < sms ? p.units : sms;
+  const bool ext = p.x_sf || p.y_sf || p.w_flex || p.y_expected || p.y_actual;
   if (swap) {
-    auto kfn = moe_gemm_mx4_swap_kernel;
+    auto kfn = ext ? moe_gemm_mx4_swap_kernel<true> : moe_gemm_mx4_swap_kernel<false>;
     if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, Mx4SwapSmem::TOTAL) != cudaSuccess)
       return TB200_ERR_CUDA;
     kfn<<<grid, M4_THREADS, Mx4SwapSmem::TOTAL, stream>>>(p);
   } else {
-    auto kfn = moe_gemm_mx4_kernel;
+    auto kfn = ext ? moe_gemm_mx4_kernel<true> : moe_gemm_mx4_kernel<false>;
     if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, Mx4Smem::TOTAL) != cudaSuccess)
       return TB200_ERR_CUDA;
     kfn<<<grid, M4_THREADS, Mx4Smem::TOTAL, stream>>>(p);
