@@ -127,7 +127,9 @@ struct MoeCfg {
   static constexpr int LOOKAHEAD = PAIR ? 3 : 2;
 };
 
-template <bool PAIR>
+// MXOUT: the instantiation whose epilogue can MX-quantise the output; the plain one compiles that branch out (it
+// cost the plain kernel spills at its 168-register cap).
+template <bool PAIR, bool MXOUT>
 __global__ void __launch_bounds__(MOE_THREADS, 1) moe_gemm_kernel(const __grid_constant__ MoeParams p) {
   using L = MoeCfg<PAIR>;
   constexpr int BN = MOE_BN;
@@ -542,7 +544,7 @@ __global__ void __launch_bounds__(MOE_THREADS, 1) moe_gemm_kernel(const __grid_c
         }
         continue;
       }
-      if (p.y_sf) {
+      if (MXOUT && p.y_sf) {
         // MX-quantised output: a block of 32 outputs is one chunk of 32 accumulator columns, or two with SwiGLU
         const int step = swiglu ? 64 : 32;
 #pragma unroll 1
@@ -596,7 +598,7 @@ __global__ void __launch_bounds__(MOE_THREADS, 1) moe_gemm_kernel(const __grid_c
 template <bool PAIR>
 static int launch_moe(const MoeParams& p, int sms, cudaStream_t stream) {
   using L = MoeCfg<PAIR>;
-  auto kfn = moe_gemm_kernel<PAIR>;
+  auto kfn = p.y_sf ? moe_gemm_kernel<PAIR, true> : moe_gemm_kernel<PAIR, false>;
   if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL) != cudaSuccess)
     return TB200_ERR_CUDA;
   const int workers_max = PAIR ? sms / 2 : sms;
