@@ -17,7 +17,8 @@
 // tensor memory with tcgen05.cp, four block-scaled MMAs of K = 32 per step. The activations carry no
 // block scales: their scale columns are written once with 1.0 (0x7f).
 // Work units are (block-schedule entry, N tile) as in the bf16 grouped kernel; one 128 x 256 accumulator
-// plus the scale columns fill tensor memory. Roles (192 threads): TMA warp, MMA warp, 4 epilogue warps.
+// plus the scale columns fill tensor memory. Roles (320 threads): TMA warp, MMA warp, 8 epilogue warps, which
+// take the accumulator into registers and hand tensor memory back before they compute and store.
 // With a few rows per expert (decode) this kernel streams the weights at 2.9 TB/s: per K step the four
 // 128 x 256 MMAs cost ~530 cycles however few rows are real, and the single accumulator serialises the
 // epilogue. A variant that moved the weights packed through an 8-deep ring and unpacked them with the
@@ -40,6 +41,7 @@
 namespace tb200 {
 
 static constexpr int M4_THREADS = 192;
+static constexpr int M4_BIG_THREADS = 320;  // the many-rows kernel: TMA warp, MMA warp, 8 epilogue warps
 static constexpr int M4_BM = 128;
 static constexpr int M4_BN = 256;
 static constexpr int M4_STAGES = 4;
@@ -85,7 +87,7 @@ struct Mx4Smem {
 // EXT: the instantiation with MX-scaled activations, MX-quantised output and flexpoint scales; the plain one compiles
 // them out, which keeps its producer and epilogue loops as short as they were before those existed (4-8 % of a layer).
 template <bool EXT>
-__global__ void __launch_bounds__(M4_THREADS, 1) moe_gemm_mx4_kernel(const __grid_constant__ Mx4Params p) {
+__global__ void __launch_bounds__(M4_BIG_THREADS, 1) moe_gemm_mx4_kernel(const __grid_constant__ Mx4Params p) {
   using L = Mx4Smem;
   constexpr int BN = M4_BN, STAGES = M4_STAGES;
   constexpr uint32_t SFA_COL = 256;       // four columns of 1.0 for the activations
@@ -109,7 +111,7 @@ __global__ void __launch_bounds__(M4_THREADS, 1) moe_gemm_mx4_kernel(const __gri
       mbar_init(&empty[s], 1);
     }
     mbar_init(tfull, 1);
-    mbar_init(tempty, 4);
+    mbar_init(tempty, 8);
     mbar_init_fence();
   }
   if (warp == 1) {
@@ -120,7 +122,7 @@ __global__ void __launch_bounds__(M4_THREADS, 1) moe_gemm_mx4_kernel(const __gri
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
-  if (warp >= 2) {  // activation scale columns: 1.0 in every byte, on all 128 lanes
+  if (warp >= 2 && warp < 6) {  // activation scale columns: 1.0 in every byte, on all 128 lanes
     const uint32_t one = 0x7f7f7f7fu;
     tmem_st_32x32b_x4(tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + SFA_COL, one, one, one, one);
     tmem_st_wait();
@@ -253,7 +255,11 @@ __global__ void __launch_bounds__(M4_THREADS, 1) moe_gemm_mx4_kernel(const __gri
     }
   } else {
     // ------------------------------------------------------------- epilogue
-    const int q = warp & 3;
+    // Eight warps: warp w reads lanes 32 (w % 4) .. of tensor memory, the first four take columns 0-127 of the tile,
+    // the other four 128-255. A thread first moves its 128 accumulator values to registers and releases the
+    // accumulator, so the next tile's MMAs run under the arithmetic and the stores of this one (with one accumulator
+    // in tensor memory and the epilogue done from there, a third of the layer's GEMM time was epilogue).
+    const int q = warp & 3, half = (warp - 2) >> 2;
     const int n = p.n, rows_y = p.rows_y;
     void* const y = p.y;
     const float acc_scale = (p.x_scale ? __ldg(p.x_scale) : 1.f) * (EXT && p.w_flex ? __ldg(p.w_flex) : 1.f);
@@ -264,18 +270,16 @@ __global__ void __launch_bounds__(M4_THREADS, 1) moe_gemm_mx4_kernel(const __gri
     }
     flex.track_absmax = EXT && p.y_actual != nullptr;
     const uint32_t tempty_a = smem_u32(tempty);
+    const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + (uint32_t)half * 128;
     uint32_t tcount = 0;
     for (int unit = blockIdx.x; unit < units; unit += gridDim.x) {
       const int si = unit / tiles_n;
       const int entry = __ldg(sched + si);
       if (entry < 0) continue;
       const int e = entry & 0xFFFF;
-      const int n0 = (unit - si * tiles_n) * BN;
+      const int n0 = (unit - si * tiles_n) * BN + half * 128;
       const int row0 = __ldg(slice_offs + e) + (entry >> 16) * M4_BM;
       const int row_end = slice_sizes ? __ldg(slice_offs + e) + __ldg(slice_sizes + e) : __ldg(slice_offs + e + 1);
-      if (!mbar_wait(tfull, tcount & 1, status, WAIT_TMEM_FULL)) break;
-      ++tcount;
-      tc_fence_after_sync();
       const int sr = row0 + q * 32 + lane;
       int out_row = -1;
       float gamma = 1.f;
@@ -284,49 +288,58 @@ __global__ void __launch_bounds__(M4_THREADS, 1) moe_gemm_mx4_kernel(const __gri
         if (out_row >= rows_y) out_row = -1;
         if (p.gammas) gamma = __ldg(p.gammas + sr);
       }
-      const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16);
       const float* brow = p.bias ? p.bias + (long long)e * n : nullptr;
-      if (EXT && p.y_sf) {
-        // MX-quantised output: a block of 32 outputs is one chunk of 32 accumulator columns, or two with SwiGLU
-        const int step = p.swiglu ? 64 : 32;
-#pragma unroll 1
-        for (int cc = 0; cc < BN; cc += step) {
-          uint32_t v0[32], v1[32];
-          tmem_ld_32x32b_x32(taddr + cc, v0);
-          if (p.swiglu) tmem_ld_32x32b_x32(taddr + cc + 32, v1);
-          tmem_ld_wait();
-          const int col = n0 + cc;
-          if (out_row < 0 || col >= n) continue;
-          float o[32];
-          moe_chunk_values<0>(v0, col, n, brow, p.swiglu, p.alpha, p.limit, p.has_limit, gamma, acc_scale,
-                              MoeEpilogueExtra(), o);
-          int ocol = col, cnt = min(32, n - col);
-          if (p.swiglu) {
-            moe_chunk_values<16>(v1, col + 32, n, brow, 1, p.alpha, p.limit, p.has_limit, gamma, acc_scale,
-                                 MoeEpilogueExtra(), o);
-            ocol = col >> 1;
-            cnt = min(32, (n - col) >> 1);
-          }
-          moe_store_mx_block(o, cnt, y, (long long)out_row * p.ldy + ocol, p.y_sf + (long long)out_row * p.ld_ysf + (ocol >> 5),
-                             p.out_kind);
-        }
-      } else {
-        float absmax = 0.f;
-#pragma unroll 1
-        for (int cc = 0; cc < BN; cc += 32) {
-          uint32_t v[32];
-          tmem_ld_32x32b_x32(taddr + cc, v);
-          tmem_ld_wait();
-          const int col = n0 + cc;
-          if (out_row < 0 || col >= n) continue;
-          absmax = fmaxf(absmax, moe_store_chunk(v, y, p.ldy, out_row, col, n, brow, p.swiglu, p.alpha, p.limit,
-                                                 p.has_limit, gamma, p.out_kind, acc_scale, flex));
-        }
-        if (EXT && p.y_actual) moe_flex_publish(absmax, p.y_actual, p.out_kind);
-      }
+      if (!mbar_wait(tfull, tcount & 1, status, WAIT_TMEM_FULL)) break;
+      ++tcount;
+      tc_fence_after_sync();
+      uint32_t v[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(taddr + c * 32, v[c]);
+      tmem_ld_wait();
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_a(tempty_a);
+      float absmax = 0.f;
+      if (out_row >= 0) {
+        if (EXT && p.y_sf) {
+          // MX-quantised output: a block of 32 outputs is one chunk of 32 accumulator columns, or two with SwiGLU
+          if (p.swiglu) {
+#pragma unroll
+            for (int c = 0; c < 4; c += 2) {
+              const int col = n0 + c * 32;
+              if (col >= n) break;
+              float o[32];
+              moe_chunk_values<0>(v[c], col, n, brow, 1, p.alpha, p.limit, p.has_limit, gamma, acc_scale,
+                                  MoeEpilogueExtra(), o);
+              moe_chunk_values<16>(v[c + 1], col + 32, n, brow, 1, p.alpha, p.limit, p.has_limit, gamma, acc_scale,
+                                   MoeEpilogueExtra(), o);
+              const int ocol = col >> 1;
+              moe_store_mx_block(o, min(32, (n - col) >> 1), y, (long long)out_row * p.ldy + ocol,
+                                 p.y_sf + (long long)out_row * p.ld_ysf + (ocol >> 5), p.out_kind);
+            }
+          } else {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              const int col = n0 + c * 32;
+              if (col >= n) break;
+              float o[32];
+              moe_chunk_values<0>(v[c], col, n, brow, 0, p.alpha, p.limit, p.has_limit, gamma, acc_scale,
+                                  MoeEpilogueExtra(), o);
+              moe_store_mx_block(o, min(32, n - col), y, (long long)out_row * p.ldy + col,
+                                 p.y_sf + (long long)out_row * p.ld_ysf + (col >> 5), p.out_kind);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const int col = n0 + c * 32;
+            if (col >= n) break;
+            absmax = fmaxf(absmax, moe_store_chunk(v[c], y, p.ldy, out_row, col, n, brow, p.swiglu, p.alpha, p.limit,
+                                                   p.has_limit, gamma, p.out_kind, acc_scale, flex));
+          }
+        }
+      }
+      if (EXT && p.y_actual && !p.y_sf) moe_flex_publish(absmax, p.y_actual, p.out_kind);
     }
   }
 
@@ -726,7 +739,7 @@ extern "C" int tb200_moe_gemm_mx4(const tb200_moe_gemm_mx4_args* a, void* stream
     auto kfn = ext ? moe_gemm_mx4_kernel<true> : moe_gemm_mx4_kernel<false>;
     if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, Mx4Smem::TOTAL) != cudaSuccess)
       return TB200_ERR_CUDA;
-    kfn<<<grid, M4_THREADS, Mx4Smem::TOTAL, stream>>>(p);
+    kfn<<<grid, M4_BIG_THREADS, Mx4Smem::TOTAL, stream>>>(p);
   }
   return cuda_err(cudaGetLastError());
 }
