@@ -265,7 +265,10 @@ static int launch_mx(const MxParams& p, int grid, cudaStream_t stream) {
 // Per CTA a K step lands 33.5 KB instead of 49.5 KB, which takes the TMA engine off the critical
 // path. Scales travel as 2-row boxes of a [atoms*2, 256]-byte tensor map so that, like the operand
 // loads, the peer's bytes can be counted on the leader's barrier. One 256-column accumulator plus
-// the scale columns fill tensor memory, so the epilogue is not overlapped with the next tile.
+// the scale columns fill tensor memory, so the epilogue is not overlapped with the next tile. (Eight epilogue warps
+// that take the accumulator into registers with four loads in flight and release it before storing - what brought
+// the fp8 x MXFP4 grouped kernel from 2.39 to 1.86 ms - change nothing here: 0.482 ms either way at 8192^3, the
+// drain of 14 tiles per cluster being ~2 % of 64 K steps each.)
 struct MxPairParams {
   CUtensorMap tma, tmb, tmsa, tmsb;
   void* c;
