@@ -350,7 +350,7 @@ def build_workload(name: str, rank: int, world: int, dev):
                         f"[{F},{D}], gate-weighted combine, seed 4", "moe_gemm_kernel",
                         "hbm" if name == "moe_decode" else "tensor", [x, logits], launches=9, cpu=cpu_moe,
                         footprint=(w1.numel() + w2.numel()) * 2)
-    if name in ("moe_mx4", "moe_mx4_decode", "moe_bf16_mx4"):
+    if name in ("moe_mx4", "moe_mx4_decode", "moe_bf16_mx4", "moe_fp8"):
         from triton_b200.triton_kernels.matmul import PrecisionConfig, matmul as moe_matmul, swiglu_activation
         from triton_b200.triton_kernels.numerics_details.mxfp import downcast_to_mxfp
         from triton_b200.triton_kernels.reduce import reduce
@@ -368,6 +368,9 @@ def build_workload(name: str, rank: int, world: int, dev):
             v, s = downcast_to_mxfp(w, torch.uint8, axis=1)
             return (convert_layout(wrap_torch_tensor(v, dtype=FP4), make_default_matmul_mxfp4_w_layout(mx_axis=1)),
                     convert_layout(wrap_torch_tensor(s), make_default_matmul_mxfp4_w_scale_layout(mx_axis=1)))
+        if name == "moe_fp8":  # plain fp8 weights, K contiguous (how the reference stores 8-bit weights)
+            def prep(w):
+                return w.to(torch.float8_e4m3fn).transpose(1, 2).contiguous().transpose(1, 2), None
         w1, s1 = prep(_dev_randn((E, D, 2 * F), dev, 6 + 1000 * rank, 0.02, bf))
         w2, s2 = prep(_dev_randn((E, F, D), dev, 7 + 1000 * rank, 0.02, bf))
         bf16_act = name == "moe_bf16_mx4"
@@ -393,11 +396,17 @@ def build_workload(name: str, rank: int, world: int, dev):
                             f"GEMM per call): {T} tokens, d_model {D}, E={E}, top-{k}, seed 4", "moe_gemm_kernel",
                             "tensor", [x, logits], launches=11)
         active = int((topk(logits, k).mask_metadata.col_sum > 0).sum().item())
+        if name == "moe_fp8":
+            by = active * (D * 2 * F + F * D) * 1.0 + R * (D + F) * 1.0 + R * (F * 1.0 + D * 2.0)
+            return Workload(step, fl, by, f"MoE layer, fp8 activations x fp8 weights: {T} tokens, d_model {D}, E={E}, "
+                            f"top-{k}, W1 [{D},{2*F}] SwiGLU W2 [{F},{D}], gate-weighted combine, seed 4",
+                            "moe_gemm_mx4_kernel", "tensor", [x, logits], dtype="e4m3", launches=9, peak="fp8",
+                            footprint=E * (D * 2 * F + F * D))
         by = active * (D * 2 * F + F * D) * (0.5 + 1.0 / 32) + R * (D + F) * 1.0 + R * (F * 1.0 + D * 2.0)
         return Workload(step, fl, by, f"MoE layer, fp8 activations x MXFP4 weights: {T} tokens, d_model {D}, E={E}, "
                         f"top-{k}, W1 [{D},{2*F}] SwiGLU W2 [{F},{D}], gate-weighted combine, seed 4",
                         "moe_gemm_mx4_kernel", "hbm" if name == "moe_mx4_decode" else "tensor", [x, logits], dtype="e4m3",
-                        launches=9, peak="fp8")
+                        launches=9, peak="fp8", footprint=int(E * (D * 2 * F + F * D) * (0.5 + 1.0 / 32)))
     if name == "mxfp4_upcast":
         from triton_b200.triton_kernels.matmul import upcast_mxfp4_weight
         from triton_b200.triton_kernels.tensor import FP4, convert_layout, wrap_torch_tensor
@@ -639,7 +648,7 @@ def run_single_workload(args, rank, local_rank, world):
     peaks = read_peaks()
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     wl_probe = args.workload
-    fp8_peak = measure_fp8_peak(dev) if wl_probe in ("fp8", "fp8_blockwise", "mxfp8", "moe_mx4", "moe_mx4_decode") else {}
+    fp8_peak = measure_fp8_peak(dev) if wl_probe in ("fp8", "fp8_blockwise", "mxfp8", "moe_mx4", "moe_mx4_decode", "moe_fp8") else {}
     sampler = ClockSampler(local_rank)
     sampler.start()
     res = measure_config(args.workload, rank, world, dev, max(args.steps, 1), max(args.warmup, 3), peaks, fp8_peak, flush,
@@ -750,7 +759,7 @@ def main():
     ap.add_argument("--configs", default="", help="comma-separated subset of the configs to measure")
     ap.add_argument("--workload", default="gemm",
                     help="gemm (headline + configs, default) | " + " | ".join(CONFIG_NAMES) + " | attn_bwd | attn_bwd_causal | "
-                         "attn_bwd_ref_shape[_causal] | fp8_blockwise | moe_mx4 | moe_mx4_decode | moe_bf16_mx4 | mxfp4_upcast | "
+                         "attn_bwd_ref_shape[_causal] | fp8_blockwise | moe_mx4 | moe_mx4_decode | moe_bf16_mx4 | moe_fp8 | mxfp4_upcast | "
                          "moe_ep_unfused | moe_ep_nccl | moe_small | attn_mxfp8 | attn_mxfp8_causal")
     args = ap.parse_args()
 

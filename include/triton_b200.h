@@ -663,7 +663,13 @@ typedef struct {
   const float* y_expected_scale;
   float* y_actual_scale;
   int32_t flexpoint_saturate_inf;
-  int32_t reserved0;
+  /* FP8 weights (the reference's float8 x float8 and float8 / mxfloat8 x mxfloat8 cases, tests/test_matmul.py:150,
+   * 193,214,254): w_dtype TB200_E4M3 or TB200_E5M2 makes w a byte matrix [E][N][K] with K contiguous (16-byte
+   * aligned, k % 16 == 0; n and k need not be multiples of 128). w_scale is then optional: NULL for plain fp8 weights
+   * (their tensor-wide scale goes in w_flex_scale), or the e8m0 atoms described above with ceil(N/128) and ceil(K/128)
+   * atoms per expert (bytes past N or K: 127) for MXFP8 weights; with x_mx_scale, ld_x_mx_scale >= 4 ceil(K/128).
+   * The 128-row schedule only. 0 = packed MXFP4 weights as described above. */
+  int32_t w_dtype;
 } tb200_moe_gemm_mx4_args;
 int tb200_moe_gemm_mx4(const tb200_moe_gemm_mx4_args* args, void* stream);
 

@@ -6,7 +6,7 @@ MoE path, executed here as they stand in the reference checkout given as argv[1]
   make_bitmatrix_metadata_torch         tensor_details/bitmatrix.py:157-168
   make_ragged_tensor_metadata_torch     tensor_details/ragged_tensor.py:217-253  (+ RaggedTensorMetadata :12-94)
   remap_ragged_tensor_metadata_torch    tensor_details/ragged_tensor.py:388-433
-  matmul_torch (+ apply_precision, scale)   matmul.py:755-914
+  matmul_torch (+ apply_precision, scale, compute_actual_scale)   matmul.py:755-914
   swiglu_torch                          swiglu.py:89-100
   reduce_torch                          reduce.py:1173-1206
 
@@ -253,6 +253,35 @@ wr = bf(torch.randn(Ktot, Nr, generator=g) * 0.2)
 rgk = make_ragged_tensor_metadata_torch(ks, Ktot)
 put("rk_a", ar), put("rk_w", wr), put("rk_sizes", ks)
 put("rk_y", matmul_torch(ar, wr, None, rgk, rgk, precision_config=PLAIN))
+
+# -- fp8 x fp8 with flexpoint scales, grouped (matmul.py:755-800: the operands are multiplied by lhs / rhs scale;
+#    :909-914: actual_scale = max |out| / max_finite(out dtype), the result divided by expected_scale)
+ns_num = {}
+for node in ast.parse(open(TK + "numerics.py").read()).body:
+    if isinstance(node, ast.Assign) and all(isinstance(t, ast.Name) and t.id.startswith("MAX_FINITE") for t in node.targets):
+        exec(compile(ast.Module(body=[node], type_ignores=[]), TK + "numerics.py", "exec"), {"torch": torch}, ns_num)
+tknum = types.ModuleType("triton_kernels.numerics")
+tknum.__dict__.update(ns_num)
+sys.modules["triton_kernels.numerics"] = tknum
+ns_cs = {"torch": torch}
+exec(cut(TK + "matmul.py", ["compute_actual_scale"]), ns_cs)
+ns_mm["compute_actual_scale"] = ns_cs["compute_actual_scale"]
+Ef, Kf, Nf = 3, 48, 40
+sizes_f = torch.tensor([9, 0, 22], dtype=torch.int32)
+Rf = int(sizes_f.sum())
+af = (torch.randn(Rf, Kf, generator=g)).to(torch.float8_e5m2)
+wf = (torch.randn(Ef, Kf, Nf, generator=g) * 0.5).to(torch.float8_e5m2)
+gam_f = torch.rand(Rf, generator=g)
+ls, rs, es = torch.tensor(0.5), torch.tensor(0.25), torch.tensor(0.03125)
+actual = torch.zeros(())
+FLEX = _Holder(flex_ctx=_Holder(lhs_data=_Holder(scale=ls), rhs_data=_Holder(scale=rs),
+                                out_data=_Holder(actual_scale=actual, expected_scale=es)),
+               a_mx_scale=None, b_mx_scale=None, out_dtype=torch.float8_e5m2)
+rgf = make_ragged_tensor_metadata_torch(sizes_f, Rf)
+put("f8_a", af.view(torch.uint8)), put("f8_w", wf.view(torch.uint8)), put("f8_sizes", sizes_f), put("f8_gammas", gam_f)
+put("f8_scales", torch.stack([ls, rs, es]))
+put("f8_y", matmul_torch(af, wf, None, rgf, gammas=gam_f, precision_config=FLEX))
+put("f8_actual", actual.reshape(1))
 
 np.savez_compressed(__file__.rsplit("/", 1)[0] + "/moe_cases.npz", **out)
 print("wrote", len(out), "arrays")

@@ -161,3 +161,34 @@ def test_ragged_k_matmul_matches_reference_twin(cuda, fx):
     bad = make_ragged_tensor_metadata(torch.tensor([5, K - 5], dtype=torch.int32, device=cuda), K)
     with pytest.raises(NotImplementedError):  # the second slice starts at element 5
         matmul(a.to(cuda), w.to(cuda), None, bad, bad)
+
+
+def test_fp8_flexpoint_matmul_matches_reference_twin(cuda, fx):
+    """float8_e5m2 x float8_e5m2, grouped, with lhs / rhs / expected scales and gate weights against matmul_torch's
+    output, and the actual_scale it computed. The kernel's output is e5m2 (2 mantissa bits): compared after
+    dequantisation within one rounding step of the twin's fp32 result."""
+    from triton_b200.triton_kernels.matmul import FlexCtx, PrecisionConfig, matmul
+    from triton_b200.triton_kernels.numerics import InFlexData, OutFlexData
+    from triton_b200.triton_kernels.tensor import make_ragged_tensor_metadata
+    d = fx
+    a = torch.from_numpy(d["f8_a"]).view(torch.float8_e5m2)
+    w = torch.from_numpy(d["f8_w"]).view(torch.float8_e5m2)
+    sizes = torch.from_numpy(d["f8_sizes"])
+    ls, rs, es = (torch.tensor(float(v), device=cuda) for v in d["f8_scales"])
+    actual = torch.zeros(1, device=cuda)
+    fc = FlexCtx(lhs_data=InFlexData(scale=ls), rhs_data=InFlexData(scale=rs),
+                 out_data=OutFlexData(expected_scale=es, actual_scale=actual))
+    md = make_ragged_tensor_metadata(sizes.to(cuda), int(sizes.sum()))
+    wk = w.transpose(1, 2).contiguous().transpose(1, 2).to(cuda)  # K contiguous, as the reference stores fp8 weights
+    y = matmul(a.to(cuda), wk, None, md, gammas=torch.from_numpy(d["f8_gammas"]).to(cuda),
+               precision_config=PrecisionConfig(flex_ctx=fc))
+    assert y.dtype == torch.float8_e5m2
+    ref = torch.from_numpy(d["f8_y"])
+    err = (y.cpu().float() - ref).abs()
+    assert float((err / ref.abs().clamp_min(2.0 ** -14)).max()) <= 0.126  # half an e5m2 step is 2^-3 relative
+    assert abs(float(actual) - float(d["f8_actual"][0])) <= 1e-5 * float(d["f8_actual"][0]) + 1e-30
+    # the same values with a bf16 output: the twin's tolerance for 16-bit outputs
+    fc16 = FlexCtx(lhs_data=InFlexData(scale=ls), rhs_data=InFlexData(scale=rs), out_data=OutFlexData(expected_scale=es))
+    y16 = matmul(a.to(cuda), wk, None, md, gammas=torch.from_numpy(d["f8_gammas"]).to(cuda),
+                 precision_config=PrecisionConfig(flex_ctx=fc16, out_dtype=torch.bfloat16))
+    torch.testing.assert_close(y16.cpu().float(), ref, rtol=2e-2, atol=2e-2)

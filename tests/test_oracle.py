@@ -279,3 +279,16 @@ def test_batched_and_ragged_k_oracles_match_reference_twin():
     y = o_moe.ragged_k_matmul_ref(t("rk_a"), t("rk_w"), d["rk_sizes"])
     torch.testing.assert_close(y, t("rk_y"), rtol=1e-5, atol=1e-5)
     assert float(y[1].abs().max()) == 0.0
+
+
+def test_grouped_oracle_matches_reference_twin_on_fp8_flexpoint():
+    """oracle.moe.grouped_matmul_ref on fp8 operands times their flexpoint scales, divided by expected_scale, and
+    flex_actual_scale_ref, against matmul_torch's output for the float8_e5m2 case in moe_cases.npz."""
+    d = np.load(os.path.join(GOLDEN, "moe_cases.npz"))
+    a = torch.from_numpy(d["f8_a"]).view(torch.float8_e5m2).float()
+    w = torch.from_numpy(d["f8_w"]).view(torch.float8_e5m2).float()
+    ls, rs, es = (float(v) for v in d["f8_scales"])
+    y = o_moe.grouped_matmul_ref(a * ls, w * rs, None, d["f8_sizes"], gammas=torch.from_numpy(d["f8_gammas"]),
+                                 out_dtype=torch.float32)
+    torch.testing.assert_close(y / es, torch.from_numpy(d["f8_y"]), rtol=1e-5, atol=1e-5)
+    assert abs(o_moe.flex_actual_scale_ref(y, torch.float8_e5m2) - float(d["f8_actual"][0])) <= 1e-6 * float(d["f8_actual"][0]) + 1e-29

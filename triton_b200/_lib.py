@@ -175,7 +175,7 @@ class MoeGemmMx4Args(Structure):
         ("swiglu_alpha", c_float), ("swiglu_limit", c_float), ("swiglu_has_limit", c_int32), ("block_rows", c_int32),
         ("x_mx_scale", c_void_p), ("ld_x_mx_scale", c_int64), ("y_mx_scale", c_void_p), ("ld_y_mx_scale", c_int64),
         ("w_flex_scale", c_void_p), ("y_expected_scale", c_void_p), ("y_actual_scale", c_void_p),
-        ("flexpoint_saturate_inf", c_int32), ("reserved0", c_int32),
+        ("flexpoint_saturate_inf", c_int32), ("w_dtype", c_int32),
     ]
 
 

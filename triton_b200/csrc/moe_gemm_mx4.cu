@@ -86,13 +86,16 @@ struct Mx4Smem {
 
 // EXT: the instantiation with MX-scaled activations, MX-quantised output and flexpoint scales; the plain one compiles
 // them out, which keeps its producer and epilogue loops as short as they were before those existed (4-8 % of a layer).
-template <bool EXT>
+// WF8: the weights are fp8 bytes ([E][N][K], K contiguous) behind a three-dimensional tensor map instead of packed
+// e2m1 blocks; their scale atoms are optional (none: plain fp8 weights, scale columns of 1.0; given: MXFP8 weights).
+template <bool EXT, bool WF8>
 __global__ void __launch_bounds__(M4_BIG_THREADS, 1) moe_gemm_mx4_kernel(const __grid_constant__ Mx4Params p) {
   using L = Mx4Smem;
   constexpr int BN = M4_BN, STAGES = M4_STAGES;
   constexpr uint32_t SFA_COL = 256;       // four columns of 1.0 for the activations
   constexpr uint32_t SFW_COL0 = 256 + 16; // two sets of 8 columns for the weight scales
   constexpr uint32_t SFX_COL0 = 256 + 32; // two sets of 4 columns for the activations' own block scales
+  constexpr uint32_t SFW_ONE = 256 + 48;  // eight columns of 1.0 for weights without block scales
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET);
@@ -125,6 +128,10 @@ __global__ void __launch_bounds__(M4_BIG_THREADS, 1) moe_gemm_mx4_kernel(const _
   if (warp >= 2 && warp < 6) {  // activation scale columns: 1.0 in every byte, on all 128 lanes
     const uint32_t one = 0x7f7f7f7fu;
     tmem_st_32x32b_x4(tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + SFA_COL, one, one, one, one);
+    if (WF8) {
+      tmem_st_32x32b_x4(tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + SFW_ONE, one, one, one, one);
+      tmem_st_32x32b_x4(tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + SFW_ONE + 4, one, one, one, one);
+    }
     tmem_st_wait();
   }
   tc_fence_before_sync();
@@ -188,13 +195,23 @@ __global__ void __launch_bounds__(M4_BIG_THREADS, 1) moe_gemm_mx4_kernel(const _
           }
           if (lane == 0) {
             const uint32_t bar = full_a + s * 8;
-            // the unpacking load of W reports the bytes it read (64 per row), not the 128 it writes
-            mbar_expect_tx_a(bar, L::A_BYTES + L::B_BYTES / 2 + nb_valid * 512);
             const uint32_t sa = smem_a + s * L::STAGE_BYTES;
-            tma_load_2d_a(sa, &p.tmx, bar, kb * 128, row0, pol_x);
-            tma_load_2d_a(sa + L::A_BYTES, &p.tmw, bar, 0, (((e * tiles_n + pid_n) * k_blocks) + kb) * BN, pol_w);
-            for (int j = 0; j < nb_valid; ++j)
-              bulk_load(sf + j * 512, atoms + ((size_t)j * k_blocks + kb) * 512, 512, &full[s]);
+            if (WF8) {
+              const bool w_scaled = p.sfw != nullptr;
+              mbar_expect_tx_a(bar, L::A_BYTES + L::B_BYTES + (w_scaled ? nb_valid * 512 : 0));
+              tma_load_2d_a(sa, &p.tmx, bar, kb * 128, row0, pol_x);
+              tma_load_3d(smem + s * L::STAGE_BYTES + L::A_BYTES, &p.tmw, &full[s], kb * 128, n0, e, pol_w);
+              if (w_scaled)
+                for (int j = 0; j < nb_valid; ++j)
+                  bulk_load(sf + j * 512, atoms + ((size_t)j * k_blocks + kb) * 512, 512, &full[s]);
+            } else {
+              // the unpacking load of W reports the bytes it read (64 per row), not the 128 it writes
+              mbar_expect_tx_a(bar, L::A_BYTES + L::B_BYTES / 2 + nb_valid * 512);
+              tma_load_2d_a(sa, &p.tmx, bar, kb * 128, row0, pol_x);
+              tma_load_2d_a(sa + L::A_BYTES, &p.tmw, bar, 0, (((e * tiles_n + pid_n) * k_blocks) + kb) * BN, pol_w);
+              for (int j = 0; j < nb_valid; ++j)
+                bulk_load(sf + j * 512, atoms + ((size_t)j * k_blocks + kb) * 512, 512, &full[s]);
+            }
           }
           if (x_sf && kb + 1 < k_blocks) load_sfx(kb + 1);
           if (++s == STAGES) {
@@ -213,6 +230,7 @@ __global__ void __launch_bounds__(M4_BIG_THREADS, 1) moe_gemm_mx4_kernel(const _
       const uint32_t tfull_a = smem_u32(tfull), tempty_a = smem_u32(tempty);
       const uint32_t t_sfa_one = tmem_base + SFA_COL;
       const bool mx_x = EXT && p.x_sf != nullptr;
+      const bool w_scaled = !WF8 || p.sfw != nullptr;
       uint32_t s = 0, ph = 0, tcount = 0, kpar = 0;
       bool ok = true, ready = false;
       for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x) {
@@ -229,10 +247,14 @@ __global__ void __launch_bounds__(M4_BIG_THREADS, 1) moe_gemm_mx4_kernel(const _
           tc_fence_after_sync();
           const uint32_t s1 = (s + 1 == STAGES) ? 0 : s + 1;
           ready = mbar_test_a(full_a + s1 * 8, s1 == 0 ? ph ^ 1 : ph);
-          const uint32_t t_sfw = tmem_base + SFW_COL0 + kpar * 8;
+          uint32_t t_sfw = tmem_base + SFW_COL0 + kpar * 8;
           const uint64_t sfd = sfdesc0 + (uint64_t)((s * L::SF_BYTES) >> 4);
-          tmem_cp_32x128b_warpx4(t_sfw, sfd);
-          tmem_cp_32x128b_warpx4(t_sfw + 4, sfd + (uint64_t)(512 >> 4));
+          if (WF8 && !w_scaled) {
+            t_sfw = tmem_base + SFW_ONE;
+          } else {
+            tmem_cp_32x128b_warpx4(t_sfw, sfd);
+            tmem_cp_32x128b_warpx4(t_sfw + 4, sfd + (uint64_t)(512 >> 4));
+          }
           uint32_t t_sfa = t_sfa_one;
           if (mx_x) {
             t_sfa = tmem_base + SFX_COL0 + kpar * 4;
@@ -634,23 +656,25 @@ __global__ void __launch_bounds__(M4_THREADS, 1) moe_gemm_mx4_swap_kernel(const 
 using namespace tb200;
 
 extern "C" int tb200_moe_gemm_mx4(const tb200_moe_gemm_mx4_args* a, void* stream_) {
-  if (!a || !a->x || !a->w || !a->w_scale || !a->y || !a->slice_offs || !a->block_schedule) return TB200_ERR_BAD_ARG;
+  if (!a || !a->x || !a->w || !a->y || !a->slice_offs || !a->block_schedule) return TB200_ERR_BAD_ARG;
+  const bool wf8 = a->w_dtype == TB200_E4M3 || a->w_dtype == TB200_E5M2;
+  if (!wf8 && (a->w_dtype != 0 || !a->w_scale)) return TB200_ERR_BAD_ARG;
   if (a->n_experts <= 0 || a->n_experts > 65535 || a->k <= 0 || a->n <= 0 || a->n_sched < 0) return TB200_ERR_BAD_ARG;
   if (a->rows_x < 0 || a->rows_y < 0) return TB200_ERR_BAD_ARG;
   if (a->x_dtype != TB200_E4M3 && a->x_dtype != TB200_E5M2) return TB200_ERR_UNSUPPORTED;
   if (a->out_dtype != TB200_BF16 && a->out_dtype != TB200_F16 && a->out_dtype != TB200_E4M3 &&
       a->out_dtype != TB200_E5M2)
     return TB200_ERR_UNSUPPORTED;
-  if ((a->k % 128) || (a->n % 128)) return TB200_ERR_UNSUPPORTED;
+  if (wf8 ? (a->k % 16) != 0 : ((a->k % 128) || (a->n % 128))) return TB200_ERR_UNSUPPORTED;
   if (a->swiglu && (a->n & 1)) return TB200_ERR_BAD_ARG;
   if ((a->ldx % 16) || a->ldx < a->k) return TB200_ERR_BAD_ARG;
-  if ((reinterpret_cast<uintptr_t>(a->x) & 15) || (reinterpret_cast<uintptr_t>(a->w) & 31) ||
+  if ((reinterpret_cast<uintptr_t>(a->x) & 15) || (reinterpret_cast<uintptr_t>(a->w) & (wf8 ? 15 : 31)) ||
       (reinterpret_cast<uintptr_t>(a->w_scale) & 15))
     return TB200_ERR_BAD_ARG;
   if (a->rows_x > INT32_MAX - 1 || a->rows_y > INT32_MAX || a->k > INT32_MAX || a->n > INT32_MAX)
     return TB200_ERR_UNSUPPORTED;
   if (a->x_mx_scale && ((reinterpret_cast<uintptr_t>(a->x_mx_scale) & 3) || (a->ld_x_mx_scale % 4) ||
-                        a->ld_x_mx_scale < a->k / 32))
+                        a->ld_x_mx_scale < (a->k + 127) / 128 * 4))
     return TB200_ERR_BAD_ARG;
   if (a->y_mx_scale) {
     const int64_t n_out = a->swiglu ? a->n / 2 : a->n;
@@ -664,6 +688,7 @@ extern "C" int tb200_moe_gemm_mx4(const tb200_moe_gemm_mx4_args* a, void* stream
 
   const bool swap = a->block_rows == S4_XROWS;
   if (!swap && a->block_rows != 0 && a->block_rows != M4_BM) return TB200_ERR_BAD_ARG;
+  if (swap && wf8) return TB200_ERR_UNSUPPORTED;  // fp8 weights: the 128-row schedule only
   // the swapped kernel quantises a warp's 32 columns as one block; with SwiGLU a block would span two warps
   if (swap && a->y_mx_scale && a->swiglu) return TB200_ERR_UNSUPPORTED;
   Mx4Params p;
@@ -675,7 +700,14 @@ extern "C" int tb200_moe_gemm_mx4(const tb200_moe_gemm_mx4_args* a, void* stream
     int rc = encode_tmap(&p.tmx, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a->x, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != TB200_OK) return rc;
   }
-  {
+  if (wf8) {
+    // fp8 weights [E][N][K]: rows past N and values past K read as zero
+    const uint64_t dims[3] = {(uint64_t)a->k, (uint64_t)a->n, (uint64_t)a->n_experts};
+    const uint64_t strides[2] = {(uint64_t)a->k, (uint64_t)a->k * (uint64_t)a->n};
+    const uint32_t box[3] = {128, (uint32_t)M4_BN, 1};
+    int rc = encode_tmap(&p.tmw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, a->w, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != TB200_OK) return rc;
+  } else {
     // blocked weights: one (expert, N tile, K step) block of 256 rows x 64 bytes after the other, so a tile
     // step is one contiguous 16 KB run of HBM
     const uint64_t tiles_n = (uint64_t)((a->n + M4_BN - 1) / M4_BN);
@@ -714,8 +746,8 @@ extern "C" int tb200_moe_gemm_mx4(const tb200_moe_gemm_mx4_args* a, void* stream
   if ((long long)p.n_sched * p.tiles_n > INT32_MAX) return TB200_ERR_UNSUPPORTED;
   p.units = p.n_sched * p.tiles_n;
   p.n = (int)a->n;
-  p.k_blocks = (int)(a->k / 128);
-  p.n_blocks = (int)(a->n / 128);
+  p.k_blocks = (int)((a->k + 127) / 128);
+  p.n_blocks = (int)((a->n + 127) / 128);
   p.rows_y = (int)a->rows_y;
   p.swiglu = a->swiglu ? 1 : 0;
   p.has_limit = a->swiglu_has_limit ? 1 : 0;
@@ -724,7 +756,7 @@ extern "C" int tb200_moe_gemm_mx4(const tb200_moe_gemm_mx4_args* a, void* stream
   p.out_kind = a->out_dtype == TB200_F16 ? MOE_OUT_F16 : a->out_dtype == TB200_E4M3 ? MOE_OUT_E4M3
                : a->out_dtype == TB200_E5M2 ? MOE_OUT_E5M2 : MOE_OUT_BF16;
   const uint32_t xfmt = a->x_dtype == TB200_E5M2 ? 1u : 0u;
-  const uint32_t wfmt = 5u;  // e2m1
+  const uint32_t wfmt = wf8 ? (a->w_dtype == TB200_E5M2 ? 1u : 0u) : 5u;  // 5 = e2m1
   for (uint32_t k = 0; k < 4; ++k)
     p.idesc[k] = swap ? make_idesc_mx(wfmt, xfmt, S4_WROWS, S4_XROWS, k, k) : make_idesc_mx(xfmt, wfmt, M4_BM, M4_BN, k, k);
 
@@ -736,7 +768,7 @@ extern "C" int tb200_moe_gemm_mx4(const tb200_moe_gemm_mx4_args* a, void* stream
       return TB200_ERR_CUDA;
     kfn<<<grid, M4_THREADS, Mx4SwapSmem::TOTAL, stream>>>(p);
   } else {
-    auto kfn = ext ? moe_gemm_mx4_kernel<true> : moe_gemm_mx4_kernel<false>;
+    auto kfn = wf8 ? moe_gemm_mx4_kernel<true, true> : ext ? moe_gemm_mx4_kernel<true, false> : moe_gemm_mx4_kernel<false, false>;
     if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, Mx4Smem::TOTAL) != cudaSuccess)
       return TB200_ERR_CUDA;
     kfn<<<grid, M4_BIG_THREADS, Mx4Smem::TOTAL, stream>>>(p);

@@ -155,6 +155,19 @@ def matmul(a, b, bias, a_ragged_metadata: RaggedTensorMetadata | None = None, b_
             raise NotImplementedError("matmul: MX-quantised output with c / c_acc_in is not implemented")
         if precision_config.c_microblock_size not in (None, 32):
             raise NotImplementedError("matmul: microblock size 32 (e8m0 scales) only")
+    fp8_w = isinstance(b, torch.Tensor) and b.dtype in _F8
+    if fp8_w and isinstance(a, torch.Tensor) and a.dtype in _F8 and (precision_config is None
+                                                                   or precision_config.b_mx_scale is None):
+        # fp8 x fp8 (tensor-wide flexpoint scales, or none): the block-scaled kernel with scale columns of 1.0
+        if precision_config is not None and precision_config.a_mx_scale is not None:
+            raise NotImplementedError("matmul: MX-scaled activations need an MX-scaled weight (b_mx_scale)")
+        if betas is not None or out_alpha is not None or c_acc_in is not None or fused_comm is not None or c is not None:
+            raise NotImplementedError("matmul (fp8 weights): betas / out_alpha / c_acc_in / fused_comm / a preallocated "
+                                      "output are not implemented")
+        if gather_indx is not None:
+            a = _gather_fp8_rows(a, gather_indx)
+        return _matmul_mx4(a, b, bias, a_ragged_metadata, scatter_indx, precision_config or PrecisionConfig(), gammas,
+                           fused_activation)
     if precision_config is not None and precision_config.a_mx_scale is not None:
         if precision_config.b_mx_scale is None or not isinstance(a, torch.Tensor) or a.dtype not in _F8:
             raise NotImplementedError("matmul: MX-scaled activations are implemented as MXFP8 x MXFP4 "
@@ -177,11 +190,7 @@ def matmul(a, b, bias, a_ragged_metadata: RaggedTensorMetadata | None = None, b_
             raise NotImplementedError("matmul (fp8 x MXFP4): a preallocated output is not implemented")
         if gather_indx is not None:
             # this kernel reads sorted rows only: indexed rows are gathered by a pass of their own first
-            if not isinstance(a, torch.Tensor) or a.ndim != 2 or not a.is_cuda:
-                raise NotImplementedError("matmul (fp8 x MXFP4): gather_indx needs a 2-D CUDA activation tensor")
-            if a.stride(1) != 1 or a.stride(0) % 16 or a.shape[1] % 16:
-                a = a.contiguous()
-            a = _gather_rows(a.view(torch.uint8), gather_indx).view(a.dtype)
+            a = _gather_fp8_rows(a, gather_indx)
             if precision_config.a_mx_scale is not None:  # the rows' block scales travel with them
                 import dataclasses
                 sc = _plain_scale(precision_config.a_mx_scale)
@@ -415,6 +424,42 @@ def _plain_scale(t):
     return t
 
 
+def _gather_fp8_rows(a, gather_indx):
+    """The fp8 kernels read sorted rows only: indexed rows are gathered by a pass of their own first."""
+    if not isinstance(a, torch.Tensor) or a.ndim != 2 or not a.is_cuda:
+        raise NotImplementedError("matmul (fp8 activations): gather_indx needs a 2-D CUDA activation tensor")
+    if a.stride(1) != 1 or a.stride(0) % 16 or a.shape[1] % 16:
+        a = a.contiguous()
+    return _gather_rows(a.view(torch.uint8), gather_indx).view(a.dtype)
+
+
+def _fp8_weight_kernel_layout(b, b_mx_scale, microblock):
+    """An fp8 weight [E, K, N] as the [E, N, K] byte matrix the kernel reads (no copy when K is the contiguous
+    dimension, which is how the reference lays fp8 weights out) and, for an MXFP8 weight, its [E, K/32, N] e8m0
+    scales as 512-byte atoms [E][ceil(N/128)][ceil(K/128)][n % 32][n / 32 % 4][k / 32 % 4] (127 past N and K)."""
+    if microblock not in (None, 32):
+        raise NotImplementedError("matmul (MXFP8 weight): microblock size 32 (e8m0 scales) only")
+    if b.ndim == 2:
+        b = b.unsqueeze(0)
+    E, K, N = b.shape
+    if K % 16:
+        raise NotImplementedError("matmul (fp8 weights): K must be a multiple of 16")
+    w = b.transpose(1, 2)
+    if not w.is_contiguous():
+        w = w.contiguous()
+    atoms = None
+    if b_mx_scale is not None:
+        sc = _plain_scale(b_mx_scale)
+        if sc.ndim == 2:
+            sc = sc.unsqueeze(0)
+        assert sc.shape == (E, (K + 31) // 32, N), "b_mx_scale: [E, ceil(K / 32), N] e8m0 bytes"
+        kb, nb = (K + 127) // 128, (N + 127) // 128
+        full = torch.full((E, kb * 4, nb * 128), 127, dtype=torch.uint8, device=sc.device)
+        full[:, :sc.shape[1], :N] = sc
+        atoms = full.view(E, kb, 4, nb, 4, 32).permute(0, 3, 1, 5, 4, 2).contiguous()
+    return w, atoms, (E, K, N)
+
+
 def _gather_scale_rows(sc, gather_indx):
     if sc.stride(1) == 1 and sc.shape[1] % 16 == 0 and sc.stride(0) % 16 == 0:
         return _gather_rows(sc, gather_indx)
@@ -476,8 +521,13 @@ def _matmul_mx4(a, b, bias, a_ragged_metadata, scatter_indx, pc: PrecisionConfig
         raise RuntimeError("triton_b200 matmul needs CUDA tensors (there is no CPU path)")
     if a.ndim != 2:
         raise NotImplementedError("matmul: batched input is not implemented")
-    w, ws = _mx4_kernel_layout(b, pc.b_mx_scale, pc.b_microblock_size)
-    E, K, N = w.shape
+    w_fp8 = isinstance(b, torch.Tensor) and b.dtype in _F8
+    if w_fp8:
+        w_bytes, ws_bytes, (E, K, N) = _fp8_weight_kernel_layout(b, pc.b_mx_scale, pc.b_microblock_size)
+    else:
+        w, ws = _mx4_kernel_layout(b, pc.b_mx_scale, pc.b_microblock_size)
+        E, K, N = w.shape
+        w_bytes, ws_bytes = w.data, ws.data
     assert a.shape[1] == K, "inner dimensions differ"
     dev = a.device
     if a.stride(1) != 1 or a.stride(0) % 16:
@@ -497,7 +547,7 @@ def _matmul_mx4(a, b, bias, a_ragged_metadata, scatter_indx, pc: PrecisionConfig
     md = a_ragged_metadata
     # few rows per expert (decode): the 32-row schedule and the kernel with swapped operand roles (which cannot
     # quantise a SwiGLU output: a block of 32 outputs would span two of its warps)
-    block_rows = 32 if R <= 32 * E and not (swiglu and pc.c_mx_scale is not None) else 128
+    block_rows = 32 if R <= 32 * E and not w_fp8 and not (swiglu and pc.c_mx_scale is not None) else 128
     sched = md.block_schedule(block_rows)
     rows_y = R if scatter_indx is None else scatter_indx.shape[0]
     out_dtype = pc.out_dtype or a.dtype  # as the reference: the activation dtype (fp8) unless asked otherwise
@@ -508,7 +558,10 @@ def _matmul_mx4(a, b, bias, a_ragged_metadata, scatter_indx, pc: PrecisionConfig
     a_sf = c_sf = None
     if pc.a_mx_scale is not None:
         a_sf = _plain_scale(pc.a_mx_scale)
-        assert a_sf.shape == (R, K // 32), "a_mx_scale: one e8m0 byte per 32 values of K, [rows, K/32]"
+        assert a_sf.shape == (R, (K + 31) // 32), "a_mx_scale: one e8m0 byte per 32 values of K, [rows, K/32]"
+        k_steps4 = (K + 127) // 128 * 4
+        if a_sf.shape[1] < k_steps4:  # the kernel reads four bytes per 128 values of K: pad the last step with 1.0
+            a_sf = torch.nn.functional.pad(a_sf, (0, k_steps4 - a_sf.shape[1]), value=127)
         if a_sf.stride(1) != 1 or a_sf.stride(0) % 4 or a_sf.data_ptr() % 4:
             a_sf = a_sf.contiguous()
     if pc.c_mx_scale is not None:
@@ -536,7 +589,9 @@ def _matmul_mx4(a, b, bias, a_ragged_metadata, scatter_indx, pc: PrecisionConfig
         if out_dtype not in _F8 and out_dtype != torch.float16:
             raise NotImplementedError("matmul: actual_scale needs an fp8 or fp16 output")
     args = _lib.MoeGemmMx4Args()
-    args.x, args.w, args.w_scale, args.y = a.data_ptr(), w.data.data_ptr(), ws.data.data_ptr(), c.data_ptr()
+    args.x, args.w, args.y = a.data_ptr(), w_bytes.data_ptr(), c.data_ptr()
+    args.w_scale = ws_bytes.data_ptr() if ws_bytes is not None else None
+    args.w_dtype = _F8[b.dtype] if w_fp8 else 0
     args.x_scale = xs.data_ptr() if xs is not None else None
     args.bias = bs.data_ptr() if bs is not None else None
     args.slice_offs, args.slice_sizes, args.block_schedule = (md.slice_offs.data_ptr(), md.slice_sizes.data_ptr(),
