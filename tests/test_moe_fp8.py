@@ -163,6 +163,23 @@ def test_mxfp8_weights(cuda, mx_act, shape):
     torch.testing.assert_close(out.cpu().float(), ref, rtol=1e-2, atol=2e-2)
 
 
+def test_bf16_x_mxfp8_weights(cuda):
+    """bfloat16 x mxfloat8 (tests/test_matmul.py:177): the weight is upcast to bf16, then the 16-bit kernel runs."""
+    from triton_b200.triton_kernels.matmul import PrecisionConfig, matmul
+    from triton_b200.triton_kernels.tensor import make_ragged_tensor_metadata
+    E, K, N = 3, 416, 400
+    g = torch.Generator().manual_seed(8)
+    cnt = torch.tensor([200, 0, 100], dtype=torch.int32)
+    rg = make_ragged_tensor_metadata(cnt.to(cuda), 300)
+    wv, ws = downcast_to_mxfp((0.3 * torch.randn(E, K, N, generator=g)).to(torch.bfloat16), torch.float8_e4m3fn, axis=1)
+    wdq = upcast_from_mxfp(wv, ws, torch.float32, axis=1)
+    x = torch.randn(300, K, generator=g).to(torch.bfloat16)
+    out = matmul(x.to(cuda), wv.to(cuda), None, rg, precision_config=PrecisionConfig(b_mx_scale=ws.to(cuda)))
+    ref = o.grouped_matmul_ref(x.float(), wdq, None, cnt.numpy(), out_dtype=torch.float32)
+    assert out.dtype == torch.bfloat16
+    torch.testing.assert_close(out.cpu().float(), ref, rtol=2e-2, atol=2e-2)
+
+
 def test_argument_checks(cuda):
     from triton_b200.triton_kernels.matmul import PrecisionConfig, matmul
     x = torch.zeros(64, 72, device=cuda).to(torch.float8_e4m3fn)

@@ -180,8 +180,16 @@ def matmul(a, b, bias, a_ragged_metadata: RaggedTensorMetadata | None = None, b_
                 raise NotImplementedError("matmul: flexpoint scales are implemented for fp8 activations x MXFP4 weights")
             # 16-bit activations: the weight is upcast to the activation dtype (what the reference's
             # tl.dot_scaled(x, None, "bf16", w, w_scales, "e2m1") computes), then the 16-bit grouped GEMM runs
-            w16 = upcast_mxfp4_weight(b, precision_config.b_mx_scale, a.dtype,
-                                      precision_config.b_microblock_size)
+            if fp8_w:  # MXFP8 weight (bfloat16 x mxfloat8 in the reference's test list): upcast with torch ops
+                from .numerics_details.mxfp import upcast_from_mxfp
+                if precision_config.b_microblock_size not in (None, 32):
+                    raise NotImplementedError("matmul (MXFP8 weight): microblock size 32 (e8m0 scales) only")
+                b3 = b if b.ndim == 3 else b.unsqueeze(0)
+                sc = _plain_scale(precision_config.b_mx_scale)
+                w16 = upcast_from_mxfp(b3, sc if sc.ndim == 3 else sc.unsqueeze(0), a.dtype, axis=1)
+            else:
+                w16 = upcast_mxfp4_weight(b, precision_config.b_mx_scale, a.dtype,
+                                          precision_config.b_microblock_size)
             pc16 = PrecisionConfig(out_dtype=precision_config.out_dtype, c_mx_scale=precision_config.c_mx_scale,
                                    c_microblock_size=precision_config.c_microblock_size)
             return matmul(a, w16, bias, a_ragged_metadata, None, gather_indx, scatter_indx, pc16, None, gammas,
