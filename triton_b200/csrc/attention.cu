@@ -73,6 +73,7 @@ struct AttnSmem {
 
 struct AttnTile {
   int bh, q0, nkv;
+  int nkv0;  // KV blocks the first 128-row group needs: one fewer than nkv when the last block lies wholly above its diagonal
 };
 
 // Heaviest tiles first (largest query block = most KV blocks under a causal mask), all heads of one query
@@ -88,7 +89,11 @@ __device__ __forceinline__ AttnTile attn_tile(const AttnParams& p, int unit) {
   t.bh = unit % p.bh;
   t.q0 = qb * 2 * ATT_BM;
   int nkv = (p.s_kv + ATT_BN - 1) / ATT_BN;
-  if (p.causal) nkv = min(nkv, (t.q0 + 2 * ATT_BM + ATT_BN - 1) / ATT_BN);
+  t.nkv0 = nkv;
+  if (p.causal) {
+    t.nkv0 = min(nkv, (t.q0 + ATT_BM + ATT_BN - 1) / ATT_BN);
+    nkv = min(nkv, (t.q0 + 2 * ATT_BM + ATT_BN - 1) / ATT_BN);
+  }
   t.nkv = nkv;
   return t;
 }
@@ -200,7 +205,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_fwd_kernel(const __g
       const uint64_t kdesc0 = make_smem_desc(smem_a + L::KV_OFFSET, 16, 1024, SWIZZLE_128B);
       const uint64_t vdesc0 = make_smem_desc(smem_a + L::KV_OFFSET, BOX_BYTES, 1024, SWIZZLE_128B);
       uint32_t kvs = 0, kvph = 0;  // ring position of the next unconsumed KV tile
-      uint32_t it = 0;             // kv iterations issued so far (phase source for s/p/pv barriers)
+      uint32_t it0 = 0, it1 = 0;   // kv iterations issued so far per group (phase source for the s / p barriers)
       uint32_t tcount = 0;
       bool ok = true;
 
@@ -260,42 +265,48 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_fwd_kernel(const __g
         tc_fence_after_sync();
         issue_qk(1, kcur);
         umma_commit(&kv_empty[kcur]);
-        if (t.nkv == 1) {
-          umma_commit(&q_empty[0]);
-          umma_commit(&q_empty[1]);
-        }
-        for (int j = 0; j < t.nkv; ++j, ++it) {
-          const uint32_t iph = it & 1;
+        // Under a causal mask the last KV block of a tile can lie wholly above the first group's diagonal: that group
+        // then runs one block fewer (n0 = n1 - 1) and the last iteration serves the second group alone.
+        const int n0 = t.nkv0, n1 = t.nkv;
+        if (n0 == 1) umma_commit(&q_empty[0]);
+        if (n1 == 1) umma_commit(&q_empty[1]);
+        for (int j = 0; j < n1; ++j, ++it1) {
+          const uint32_t iph0 = it0 & 1, iph1 = it1 & 1;
+          const bool act0 = j < n0, more0 = j + 1 < n0, more1 = j + 1 < n1;
           const uint32_t vcur = kvs, vcur_ph = kvph;
           advance();
-          const bool more = j + 1 < t.nkv;
           uint32_t knext = 0, knext_ph = 0;
-          if (more) {
+          if (more1) {
             knext = kvs;
             knext_ph = kvph;
             advance();
           }
           // PV0(j)
           if (!mbar_wait(&kv_full[vcur], vcur_ph, status, WAIT_SMEM_FULL)) { ok = false; break; }
-          if (j == 0 && !mbar_wait(&o_free[0], tph ^ 1, status, WAIT_ATTN)) { ok = false; break; }
-          bool k_ready = more && mbar_test(&kv_full[knext], knext_ph);
-          if (!issue_pv(0, vcur, j > 0 ? 1u : 0u, iph, mbar_test(&p_full[4 / ATT_PV_SLICES - 1], iph), !more)) { ok = false; break; }
+          bool k_ready = more1 && mbar_test(&kv_full[knext], knext_ph);
+          if (act0) {
+            if (j == 0 && !mbar_wait(&o_free[0], tph ^ 1, status, WAIT_ATTN)) { ok = false; break; }
+            if (!issue_pv(0, vcur, j > 0 ? 1u : 0u, iph0, mbar_test(&p_full[4 / ATT_PV_SLICES - 1], iph0), !more0)) { ok = false; break; }
+            ++it0;
+          }
           bool p1_ready = false;
-          if (more) {
+          if (more1) {
             if (!k_ready && !mbar_wait(&kv_full[knext], knext_ph, status, WAIT_SMEM_FULL)) { ok = false; break; }
             tc_fence_after_sync();
-            p1_ready = mbar_test(&p_full[4 + 4 / ATT_PV_SLICES - 1], iph);
-            issue_qk(0, knext);
-            if (j + 2 == t.nkv) umma_commit(&q_empty[0]);
+            p1_ready = mbar_test(&p_full[4 + 4 / ATT_PV_SLICES - 1], iph1);
+            if (more0) {
+              issue_qk(0, knext);
+              if (j + 2 == n0) umma_commit(&q_empty[0]);
+            }
           }
           // PV1(j)
           if (j == 0 && !mbar_wait(&o_free[1], tph ^ 1, status, WAIT_ATTN)) { ok = false; break; }
-          if (!issue_pv(1, vcur, j > 0 ? 1u : 0u, iph, p1_ready, !more)) { ok = false; break; }
+          if (!issue_pv(1, vcur, j > 0 ? 1u : 0u, iph1, p1_ready, !more1)) { ok = false; break; }
           umma_commit(&kv_empty[vcur]);
-          if (more) {
+          if (more1) {
             issue_qk(1, knext);
             umma_commit(&kv_empty[knext]);
-            if (j + 2 == t.nkv) umma_commit(&q_empty[1]);
+            if (j + 2 == n1) umma_commit(&q_empty[1]);
           }
         }
       }
@@ -319,7 +330,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_fwd_kernel(const __g
       const AttnTile t = attn_tile(p, unit);
       const int qrow = t.q0 + g * ATT_BM + row_in_group;  // position in the sequence
       float m = -INFINITY, l = 0.f;
-      for (int j = 0; j < t.nkv; ++j, ++it) {
+      const int nkv_g = g == 0 ? t.nkv0 : t.nkv;
+      for (int j = 0; j < nkv_g; ++j, ++it) {
         const uint32_t iph = it & 1;
         if (!mbar_wait(&s_full[g], iph, status, WAIT_ATTN)) { ok = false; break; }
         tc_fence_after_sync();
