@@ -283,9 +283,41 @@ def pointer_array(ptrs):
     return (c_void_p * len(ptrs))(*[int(p) for p in ptrs])
 
 
-def current_stream_ptr(device=None) -> int:
+def _device_index(device) -> int:
     import torch
-    return torch.cuda.current_stream(device).cuda_stream
+    if device is None:
+        return torch.cuda.current_device()
+    if isinstance(device, int):
+        return device
+    idx = torch.device(device).index if not isinstance(device, torch.device) else device.index
+    return torch.cuda.current_device() if idx is None else idx
+
+
+def current_stream_ptr(device=None) -> int:
+    """The raw cudaStream_t of torch's current stream on `device` (the stream every entry point is launched on)."""
+    import torch
+    return torch._C._cuda_getCurrentRawStream(_device_index(device))
+
+
+class _NoGuard:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_GUARD = _NoGuard()
+
+
+def device_guard(device):
+    """``torch.cuda.device(device)`` when `device` is not the current one, else a context manager that does nothing
+    (switching devices costs a few microseconds per call, which matters for launch-bound shapes)."""
+    import torch
+    idx = _device_index(device)
+    if idx == torch.cuda.current_device():
+        return _NO_GUARD
+    return torch.cuda.device(idx)
 
 
 def sync_check(device=None) -> None:

@@ -167,7 +167,7 @@ class _Handle:
         if arr is None:
             arr = _lib.pointer_array([b + channel * self.CHANNEL_BYTES for b in pool.base_ptrs])
             self._arrays[channel] = arr
-        with torch.cuda.device(pool.device):
+        with _lib.device_guard(pool.device):
             rc = _lib.lib().tb200_symm_barrier(arr, pool.mesh.local_rank, pool.mesh.world_size, limit_ns or self.LIMIT_NS,
                                                ctypes.c_void_p(_lib.current_stream_ptr(pool.device)))
         _lib.check(rc, "tb200_symm_barrier")
@@ -216,7 +216,7 @@ class SymmetricMemoryPool:
         self.size = max(self.SIGNAL_BYTES, max((r.base + r.size for r in self.regions.values()), default=0))
         l = _lib.lib()
         world, rank = self.mesh.world_size, self.mesh.local_rank
-        with torch.cuda.device(device):
+        with _lib.device_guard(device):
             own = ctypes.c_void_p()
             _lib.check(l.tb200_symm_alloc(self.size, ctypes.byref(own)), "tb200_symm_alloc")
             self._own_ptr = own.value
@@ -286,7 +286,7 @@ class SymmetricMemoryPool:
         if not self._is_initialized:
             return
         l = _lib.lib()
-        with torch.cuda.device(self.device):
+        with _lib.device_guard(self.device):
             torch.cuda.synchronize()
             if self.mesh.world_size > 1:
                 dist.barrier(group=self.mesh.process_group)
@@ -346,7 +346,7 @@ def _move_rows(src: torch.Tensor, dst: torch.Tensor, indx: torch.Tensor, scatter
     assert src.stride(1) == 1 and dst.stride(1) == 1 and src.shape[1] == dst.shape[1] and src.dtype == dst.dtype
     indx = indx.to(torch.int32).contiguous()
     esz = src.element_size()
-    with torch.cuda.device(src.device):
+    with _lib.device_guard(src.device):
         rc = _lib.lib().tb200_move_rows(src.data_ptr(), src.stride(0) * esz, dst.data_ptr(), dst.stride(0) * esz,
                                         indx.data_ptr(), indx.numel(), src.shape[1] * esz, 1 if scatter else 0,
                                         dst.shape[0] if scatter else src.shape[0],
@@ -393,7 +393,7 @@ def all_gather_topk(x_local: torch.Tensor, k: int, ep, apply_softmax: bool = Tru
         all_vals = ep.make_empty((world * n, k), vals.dtype, region="topk")
         all_indx = ep.make_empty((world * n, k), torch.int16, region="topk", region_offset=world * n * k * 4)
         l = _lib.lib()
-        with torch.cuda.device(dev):
+        with _lib.device_guard(dev):
             stream = ctypes.c_void_p(_lib.current_stream_ptr(dev))
             for src, bufs, esz in ((vals, all_vals, vb), (indx, all_indx, 2)):
                 slots = _lib.pointer_array([b.data_ptr() + rank * n * k * esz for b in bufs])
@@ -441,7 +441,7 @@ def convert_dp_to_ep(src, expt_assignment: ExptAssignment, expt_indx, gate_indx,
         args.dst_pitch_bytes, args.dst_rows, args.row_bytes = d * esz, n_global * k, d * esz
         args.n_tokens_local, args.token_offset = n_local, rank * n_local
         args.k, args.n_experts, args.world = k, owner.shape[0], world
-        with torch.cuda.device(dev):
+        with _lib.device_guard(dev):
             rc = _lib.lib().tb200_ep_dispatch(ctypes.byref(args), ctypes.c_void_p(_lib.current_stream_ptr(dev)))
         _lib.check(rc, "tb200_ep_dispatch")
         pool.hdl.barrier(channel=0)
@@ -484,7 +484,7 @@ def convert_ep_to_dp(src, expt_assignment: ExptAssignment, expt_indx, topk_indx,
         args.dst_pitch_bytes, args.row_bytes = d * esz, d * esz
         args.n_rows, args.rows_per_rank = src.shape[0], rows_per_rank
         args.n_experts, args.world, args.rank = owner.shape[0], world, rank
-        with torch.cuda.device(dev):
+        with _lib.device_guard(dev):
             rc = _lib.lib().tb200_ep_combine(ctypes.byref(args), ctypes.c_void_p(_lib.current_stream_ptr(dev)))
         _lib.check(rc, "tb200_ep_combine")
         pool.hdl.barrier(channel=0)

@@ -321,7 +321,7 @@ def matmul(a, b, bias, a_ragged_metadata: RaggedTensorMetadata | None = None, b_
     args.moe_tile_mode = int(_tile_mode)  # extension: 0 choose, 1 one CTA per block, 2 CTA pair per two blocks
     # extension: gammas holds one value per OUTPUT row (e.g. the top-k values in (token, slot) order) instead of per sorted row
     args.gammas_by_out_row = 1 if _gammas_by_out_row else 0
-    with torch.cuda.device(dev):
+    with _lib.device_guard(dev):
         rc = _lib.lib().tb200_moe_gemm(ctypes.byref(args), ctypes.c_void_p(_lib.current_stream_ptr(dev)))
     _lib.check(rc, "tb200_moe_gemm")
     return c if peers is None else fused_comm.out_handles
@@ -337,7 +337,7 @@ def _gather_rows(a, gather_indx):
     gi = gather_indx.to(torch.int32).contiguous()
     out = torch.empty((gi.shape[0], a.shape[1]), dtype=a.dtype, device=a.device)
     esz = a.element_size()
-    with torch.cuda.device(a.device):
+    with _lib.device_guard(a.device):
         rc = _lib.lib().tb200_gather_rows(a.data_ptr(), a.stride(0) * esz, a.shape[0], out.data_ptr(), out.stride(0) * esz,
                                           gi.data_ptr(), gi.numel(), a.shape[1] * esz,
                                           ctypes.c_void_p(_lib.current_stream_ptr(a.device)))
@@ -512,7 +512,7 @@ def upcast_mxfp4_weight(b, b_mx_scale, dtype, microblock=None):
         args.w, args.w_scale, args.out = w.data.data_ptr(), ws.data.data_ptr(), out.data_ptr()
         args.n_experts, args.k, args.n = E, K, N
         args.out_dtype = _DT[dtype]
-        with torch.cuda.device(dev):
+        with _lib.device_guard(dev):
             rc = _lib.lib().tb200_mxfp4_upcast(ctypes.byref(args), ctypes.c_void_p(_lib.current_stream_ptr(dev)))
         _lib.check(rc, "tb200_mxfp4_upcast")
     return out.transpose(1, 2)
@@ -627,7 +627,7 @@ def _matmul_mx4(a, b, bias, a_ragged_metadata, scatter_indx, pc: PrecisionConfig
         args.x_mx_scale, args.ld_x_mx_scale = a_sf.data_ptr(), a_sf.stride(0)
     if c_sf is not None:
         args.y_mx_scale, args.ld_y_mx_scale = c_sf.data_ptr(), c_sf.stride(0)
-    with torch.cuda.device(dev):
+    with _lib.device_guard(dev):
         rc = _lib.lib().tb200_moe_gemm_mx4(ctypes.byref(args), ctypes.c_void_p(_lib.current_stream_ptr(dev)))
     _lib.check(rc, "tb200_moe_gemm_mx4")
     return c

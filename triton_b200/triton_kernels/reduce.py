@@ -41,7 +41,7 @@ def reduce(x: torch.Tensor, dim: int, mask=None, scale=None, x_mxscale=None, x_f
     args.scale = s.data_ptr() if s is not None else None
     args.row_indx = ri.data_ptr() if ri is not None else None
     args.n_tokens, args.d, args.k, args.dtype = T, d, k, _DT[x.dtype]
-    with torch.cuda.device(x.device):
+    with _lib.device_guard(x.device):
         rc = _lib.lib().tb200_reduce_k(ctypes.byref(args), ctypes.c_void_p(_lib.current_stream_ptr(x.device)))
     _lib.check(rc, "tb200_reduce_k")
     return y, None

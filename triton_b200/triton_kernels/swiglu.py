@@ -38,7 +38,7 @@ def swiglu(a: torch.Tensor, alpha: float, precision_config: PrecisionConfig = Pr
     args.limit = float(limit) if limit is not None else 0.0
     args.has_limit = 1 if limit is not None else 0
     args.dtype = _DT[a.dtype]
-    with torch.cuda.device(a.device):
+    with _lib.device_guard(a.device):
         rc = _lib.lib().tb200_swiglu(ctypes.byref(args), ctypes.c_void_p(_lib.current_stream_ptr(a.device)))
     _lib.check(rc, "tb200_swiglu")
     return out.view(a.shape[:-1] + out.shape[-1:])

@@ -51,7 +51,7 @@ def make_bitmatrix_metadata(nonzero_indx: torch.Tensor, bitmatrix: Bitmatrix) ->
     args.workspace, args.workspace_bytes = ws.data_ptr(), need
     args.n_entries, args.n_cols = n, n_cols
     args.indx_is_int16 = 1 if nonzero_indx.dtype == torch.int16 else 0
-    with torch.cuda.device(dev):
+    with _lib.device_guard(dev):
         rc = l.tb200_bitmatrix_metadata(ctypes.byref(args), ctypes.c_void_p(_lib.current_stream_ptr(dev)))
     _lib.check(rc, "tb200_bitmatrix_metadata")
     return BitmatrixMetadata(col_sum=col_sum, col_sorted_indx=col_sorted, row_sorted_indx=row_sorted)
@@ -119,7 +119,7 @@ def make_ragged_tensor_metadata(slice_sizes: torch.Tensor, n_total_rows: int) ->
     args.slice_sizes, args.slice_offs = slice_sizes.data_ptr(), slice_offs.data_ptr()
     args.block_offs, args.block_schedule = block_offs.data_ptr(), block_schedule.data_ptr()
     args.n_slices, args.max_n_blocks = n_slices, max_n_blocks
-    with torch.cuda.device(dev):
+    with _lib.device_guard(dev):
         rc = _lib.lib().tb200_ragged_metadata(ctypes.byref(args), ctypes.c_void_p(_lib.current_stream_ptr(dev)))
     _lib.check(rc, "tb200_ragged_metadata")
     return RaggedTensorMetadata(slice_sizes, slice_offs, block_offs, block_schedule)
@@ -147,7 +147,7 @@ def remap_ragged_tensor_metadata(md: RaggedTensorMetadata, slice_map: torch.Tens
     args.out_slice_sizes, args.out_slice_offs = o_ss.data_ptr(), o_so.data_ptr()
     args.out_block_offs, args.out_block_schedule = o_bo.data_ptr(), o_bs.data_ptr()
     args.n_slices, args.max_n_blocks = n_slices, bs.shape[1]
-    with torch.cuda.device(dev):
+    with _lib.device_guard(dev):
         rc = _lib.lib().tb200_remap_ragged_metadata(ctypes.byref(args), ctypes.c_void_p(_lib.current_stream_ptr(dev)))
     _lib.check(rc, "tb200_remap_ragged_metadata")
     return RaggedTensorMetadata(o_ss, o_so, o_bo, o_bs)

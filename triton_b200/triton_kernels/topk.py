@@ -48,7 +48,7 @@ def topk_forward(x, k, apply_softmax=True, dim=1, y_indx=None, n_rows=None, all_
     args.k, args.dtype = k, _DT[x.dtype]
     args.apply_softmax = 1 if apply_softmax else 0
     args.use_provided_indx = 1 if use_provided else 0
-    with torch.cuda.device(dev):
+    with _lib.device_guard(dev):
         rc = _lib.lib().tb200_topk(ctypes.byref(args), ctypes.c_void_p(_lib.current_stream_ptr(dev)))
     _lib.check(rc, "tb200_topk")
     bitmatrix = Bitmatrix(bits, shape=[n_valid, n_cols], shape_max=[rows, None])

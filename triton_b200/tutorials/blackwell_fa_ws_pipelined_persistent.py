@@ -56,7 +56,7 @@ def attention_with_lse(q, k, v, sm_scale, causal, config=None):
     args.dtype = _DT[q.dtype]
     args.causal = 1 if causal else 0
     args.sm_scale = float(sm_scale)
-    with torch.cuda.device(q.device):
+    with _lib.device_guard(q.device):
         rc = _lib.lib().tb200_attention_fwd(ctypes.byref(args), ctypes.c_void_p(_lib.current_stream_ptr(q.device)))
     _lib.check(rc, "tb200_attention_fwd")
     return o, M
@@ -99,7 +99,7 @@ def attention_backward(q, k, v, o, lse, do, sm_scale, causal):
     need = _lib.lib().tb200_attention_bwd_workspace_bytes(ctypes.byref(args))
     ws = torch.empty(max(need, 16), dtype=torch.uint8, device=q.device)
     args.workspace, args.workspace_bytes = ws.data_ptr(), need
-    with torch.cuda.device(q.device):
+    with _lib.device_guard(q.device):
         rc = _lib.lib().tb200_attention_bwd(ctypes.byref(args), ctypes.c_void_p(_lib.current_stream_ptr(q.device)))
     _lib.check(rc, "tb200_attention_bwd")
     return dq, dk, dv

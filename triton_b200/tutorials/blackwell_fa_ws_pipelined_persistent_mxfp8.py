@@ -109,7 +109,7 @@ def attention(q, k, v, q_scale, k_scale, v_scale, sm_scale, causal, config=None)
     args.lse = None
     args.batch, args.heads, args.seq_q, args.seq_kv = Z, H, N, Nk
     args.head_dim, args.causal, args.sm_scale = D, int(bool(causal)), float(sm_scale)
-    with torch.cuda.device(q.device):
+    with _lib.device_guard(q.device):
         rc = _lib.lib().tb200_attention_mxfp8_fwd(ctypes.byref(args), ctypes.c_void_p(_lib.current_stream_ptr(q.device)))
     _lib.check(rc, "tb200_attention_mxfp8_fwd")
     return o

@@ -86,7 +86,7 @@ def matmul(a: torch.Tensor, b: torch.Tensor, config=None, out: torch.Tensor | No
         if int(config.get("NUM_CTAS", 1) or 1) == 2:
             args.block_n = 512  # CTA pair: 256 x 256 tile per 2-CTA cluster
     l = _lib.lib()
-    with torch.cuda.device(a.device):
+    with _lib.device_guard(a.device):
         need = l.tb200_gemm_workspace_bytes(ctypes.byref(args))
         ws = None
         if need:

@@ -54,7 +54,7 @@ def matmul(a: torch.Tensor, b: torch.Tensor, a_scale: torch.Tensor, b_scale: tor
     args.block_n = bn if bn in (128, 256, 512) else 0
     if config and int(config.get("NUM_CTAS", 1) or 1) == 2:
         args.block_n = 512  # CTA pair, 256 x 256 tile per cluster
-    with torch.cuda.device(a.device):
+    with _lib.device_guard(a.device):
         rc = _lib.lib().tb200_gemm_mxfp8(ctypes.byref(args), ctypes.c_void_p(_lib.current_stream_ptr(a.device)))
     _lib.check(rc, "tb200_gemm_mxfp8")
     return out

@@ -51,7 +51,7 @@ def blackwell_scaled_mm_ws(a, b, scale_a, scale_b, out_dtype=torch.bfloat16, BLO
         bargs.scale_a, bargs.scale_b = sa.data_ptr(), sb.data_ptr()
         bargs.m, bargs.n, bargs.k, bargs.ldc = M, N, K, c.stride(0)
         bargs.in_dtype, bargs.out_dtype = _IN[a.dtype], _OUT[out_dtype]
-        with torch.cuda.device(a.device):
+        with _lib.device_guard(a.device):
             rc = _lib.lib().tb200_gemm_fp8_blockwise(ctypes.byref(bargs),
                                                      ctypes.c_void_p(_lib.current_stream_ptr(a.device)))
         _lib.check(rc, "tb200_gemm_fp8_blockwise")
@@ -79,7 +79,7 @@ def blackwell_scaled_mm_ws(a, b, scale_a, scale_b, out_dtype=torch.bfloat16, BLO
     args.block_n = (1024 if BLOCK_N == 512 else 512) if NUM_CTAS == 2 else 0
     args.scale_a, args.scale_b = scale_a.data_ptr(), scale_b.data_ptr()
     args.scale_mode = 1 if scale_mode == "rowwise" else 0
-    with torch.cuda.device(a.device):
+    with _lib.device_guard(a.device):
         rc = _lib.lib().tb200_gemm(ctypes.byref(args), ctypes.c_void_p(_lib.current_stream_ptr(a.device)))
     _lib.check(rc, "tb200_gemm")
     return c
