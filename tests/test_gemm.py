@@ -213,3 +213,24 @@ def test_in_cluster_split_k_fp16_and_default_plan(cuda):
         w = torch.randn(N, K).to(dt)
         c = _mm()(a.to(cuda), w.to(cuda).T)
         _check(c, o_gemm.gemm_ref(a, w.T))
+
+
+def test_tensors_on_another_device_than_the_current_one(cuda):
+    """Operands on cuda:1 while cuda:0 is current: the wrappers switch devices for the call (and only then) and launch
+    on that device's current stream. Needs two GPUs."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from triton_b200 import _lib
+    from triton_b200.triton_kernels.matmul import matmul as moe_matmul
+    other = torch.device("cuda:1")
+    torch.manual_seed(14)
+    a = (torch.randn(256, 512) / 512 ** 0.5).to(torch.bfloat16)
+    w = torch.randn(384, 512).to(torch.bfloat16)
+    with torch.cuda.device(cuda):
+        c = _mm()(a.to(other), w.to(other).T)
+        assert c.device == other and torch.cuda.current_device() == 0
+        _check(c, o_gemm.gemm_ref(a, w.T))
+        y = moe_matmul(a.to(other), w.t().contiguous().unsqueeze(0).to(other), None)
+        assert y.device == other
+        _check(y, o_gemm.gemm_ref(a, w.T))
+        _lib.sync_check(other)
