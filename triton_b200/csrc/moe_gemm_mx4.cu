@@ -19,6 +19,10 @@
 // Work units are (block-schedule entry, N tile) as in the bf16 grouped kernel; one 128 x 256 accumulator
 // plus the scale columns fill tensor memory. Roles (320 threads): TMA warp, MMA warp, 8 epilogue warps, which
 // take the accumulator into registers and hand tensor memory back before they compute and store.
+// (Handing the accumulator over in two 128-column halves, as the dense wide tile does - the first and last one or
+// two K steps of a tile issued as N = 128 MMAs on one half while the other half is drained - measured equal with one
+// split step each end and 4 % slower with two: the split steps read the activation tile twice and copy more scales,
+// which costs what the shorter hand-over saves.)
 // With a few rows per expert (decode) this kernel streams the weights at 2.9 TB/s: per K step the four
 // 128 x 256 MMAs cost ~530 cycles however few rows are real, and the single accumulator serialises the
 // epilogue. A variant that moved the weights packed through an 8-deep ring and unpacked them with the
