@@ -163,6 +163,59 @@ def test_mxfp8_weights(cuda, mx_act, shape):
     torch.testing.assert_close(out.cpu().float(), ref, rtol=1e-2, atol=2e-2)
 
 
+def test_batched_fp8_x_mxfp8_weights(cuda):
+    """float8_e5m2 x mxfloat8_e4m3fn, batched (tests/test_matmul.py:196)."""
+    from triton_b200.triton_kernels.matmul import PrecisionConfig, matmul
+    B, M, K, N = 2, 300, 416, 400
+    g = torch.Generator().manual_seed(9)
+    wv, ws = downcast_to_mxfp((0.3 * torch.randn(B, K, N, generator=g)).to(torch.bfloat16), torch.float8_e4m3fn, axis=1)
+    wdq = upcast_from_mxfp(wv, ws, torch.float32, axis=1)
+    x = (torch.randn(B, M, K, generator=g) * 0.5).to(torch.float8_e5m2)
+    out = matmul(x.to(cuda), _col_major(wv).to(cuda), None,
+                 precision_config=PrecisionConfig(b_mx_scale=ws.to(cuda), out_dtype=torch.bfloat16))
+    torch.testing.assert_close(out.cpu().float(), torch.bmm(x.float(), wdq), rtol=1e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("swiglu", [False, True])
+def test_mxfp8_x_mxfp8_moe_call_with_quantised_output(cuda, swiglu):
+    """The whole MoE call on MXFP8 operands: rows (and their block scales) gathered per expert, (SwiGLU), gate
+    weights, scatter, MX-quantised output; compared as the reference compares quantised outputs (dequantise both
+    sides, maxtol 4e-1, rmstol 4e-2, tests/test_matmul.py:604-625)."""
+    from triton_b200.triton_kernels.matmul import Epilogue, FnName, FnSpecs, PrecisionConfig, matmul, swiglu_activation
+    from triton_b200.triton_kernels.numerics_details.mxfp import quantize_mxfp8_fn
+    from triton_b200.triton_kernels.tensor import make_ragged_tensor_metadata
+    from triton_b200.triton_kernels.topk import topk
+    T, E, k, K, N = 200, 8, 2, 256, 512
+    g = torch.Generator().manual_seed(10)
+    sm = topk(torch.randn(T, E, generator=g).to(cuda), k)
+    mm = sm.mask_metadata
+    R = T * k
+    rg = make_ragged_tensor_metadata(mm.col_sum, R)
+    combine = mm.col_sorted_indx
+    gather = torch.div(combine, k, rounding_mode="trunc")
+    xv, xs = downcast_to_mxfp(torch.randn(T, K, generator=g).to(torch.bfloat16), torch.float8_e4m3fn, axis=1)
+    wv, ws = downcast_to_mxfp((0.3 * torch.randn(E, K, N, generator=g)).to(torch.bfloat16), torch.float8_e4m3fn, axis=1)
+    xdq, wdq = upcast_from_mxfp(xv, xs, torch.float32, axis=1), upcast_from_mxfp(wv, ws, torch.float32, axis=1)
+    gam = torch.rand(R, generator=g)
+    n_out = N // 2 if swiglu else N
+    c_scale = torch.zeros((R, n_out // 32), dtype=torch.uint8, device=cuda)
+    pc = PrecisionConfig(a_mx_scale=xs.to(cuda), a_microblock_size=32, b_mx_scale=ws.to(cuda), b_microblock_size=32,
+                         c_mx_scale=c_scale)
+    epi = Epilogue(FnSpecs(FnName.QUANTIZE_MXFP8.name, quantize_mxfp8_fn, (), ()), tuple(), tuple(), 6.0)
+    out = matmul(xv.to(cuda), _col_major(wv).to(cuda), None, rg, gather_indx=gather, scatter_indx=combine,
+                 gammas=gam.to(cuda), precision_config=pc, fused_activation=swiglu_activation(1.1, 7.0) if swiglu else None,
+                 epilogue=epi)
+    assert out.dtype == torch.float8_e4m3fn and out.shape == (R, n_out)
+    ref = o.grouped_matmul_ref(xdq, wdq, None, mm.col_sum.cpu().numpy(), gather_indx=gather.cpu().numpy(),
+                               scatter_indx=combine.cpu().numpy(), gammas=gam, swiglu=(1.1, 7.0) if swiglu else None,
+                               out_dtype=torch.float32)
+    got = o.dequantize_mxfp8_ref(out.cpu(), c_scale.cpu())
+    q_ref, s_ref = o.quantize_mxfp8_ref(ref)
+    want = o.dequantize_mxfp8_ref(q_ref, s_ref)
+    assert float((got - want).abs().max() / want.abs().max().clamp_min(1e-6)) <= 4e-1
+    assert float(torch.sqrt(((got - want) ** 2).mean()) / torch.sqrt((want ** 2).mean()).clamp_min(1e-6)) <= 4e-2
+
+
 def test_bf16_x_mxfp8_weights(cuda):
     """bfloat16 x mxfloat8 (tests/test_matmul.py:177): the weight is upcast to bf16, then the 16-bit kernel runs."""
     from triton_b200.triton_kernels.matmul import PrecisionConfig, matmul
