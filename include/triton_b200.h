@@ -609,11 +609,12 @@ int tb200_moe_gemm(const tb200_moe_gemm_args* args, void* stream);
  * x: [rows_x, k] TB200_E4M3 or TB200_E5M2, row-major (ldx bytes between rows, multiple of 16), rows sorted
  *    by expert (no gather index); x_scale: one float or NULL (1).
  * w: uint8, two e2m1 values per byte along K (even index in the low nibble), blocked as
- *    [E][ceil(N/256)][K/128][256][64]: block (e, t, s) holds rows 256 t .. 256 t + 255 of expert e (zero
- *    rows past N) and values 128 s .. 128 s + 127 of each; 32-byte aligned.
+ *    [E][ceil(N/256)][ceil(K/128)][256][64]: block (e, t, s) holds rows 256 t .. 256 t + 255 of expert e (zero
+ *    rows past N) and values 128 s .. 128 s + 127 of each (zero codes past K); 32-byte aligned.
  * w_scale: uint8 e8m0, one per 32 values of K, per expert in 512-byte atoms
- *    [E][N/128][K/128][n%32][n/32%4][k/32%4]   (the layout tb200_gemm_mxfp8 uses for its scales).
- * k % 128 == 0, n % 128 == 0. Output TB200_BF16, TB200_F16, or TB200_E4M3 / TB200_E5M2 (round to nearest even,
+ *    [E][ceil(N/128)][ceil(K/128)][n%32][n/32%4][k/32%4]   (the layout tb200_gemm_mxfp8 uses for its scales; 127 past
+ *    N and K).
+ * k % 32 == 0 (whole scale blocks); n is free. Output TB200_BF16, TB200_F16, or TB200_E4M3 / TB200_E5M2 (round to nearest even,
  * saturating to the largest finite value: the conversion of the reference's kernels when the output tensor is
  * fp8, which is what matmul.py:243 allocates for fp8 activations unless precision_config.out_dtype says otherwise).
  * ldy in elements of the output type. Other fields as in tb200_moe_gemm_args.

@@ -27,7 +27,10 @@ def _prepared(v, s, cuda):
 
 
 @pytest.mark.parametrize("shape", [(128, 256, 128), (300, 384, 512), (64, 128, 1024), (1024, 1024, 2048),
-                                   (16, 384, 512), (32, 256, 4096), (1, 128, 128)])
+                                   (16, 384, 512), (32, 256, 4096), (1, 128, 128),
+                                   # K and N that are no multiples of 128 (the reference's 300 x 400 x 832 and
+                                   # 1000 x 704 x 800, tests/test_matmul.py:194,210), on both kernels
+                                   (300, 400, 832), (1000, 704, 800), (24, 400, 416), (5, 48, 96)])
 @pytest.mark.parametrize("prepared", [True, False])
 def test_dense_fp8_x_mx4(cuda, shape, prepared):
     from triton_b200.triton_kernels.matmul import PrecisionConfig, matmul

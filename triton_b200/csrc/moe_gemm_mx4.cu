@@ -620,7 +620,7 @@ __global__ void __launch_bounds__(M4_THREADS, 1) moe_gemm_mx4_swap_kernel(const 
           const float max_finite = out_kind == MOE_OUT_E5M2 ? 57344.f : 448.f;
           const uint32_t bits = (__float_as_uint(__fdiv_rn(amax, max_finite)) + 0x007FFFFFu) & 0x7F800000u;
           const float inv = bits == 0u ? 0.f : __frcp_rn(__uint_as_float(bits));
-          if (out_row >= 0) {
+          if (out_row >= 0 && col < n) {
             moe_store_one(y, (long long)out_row * ldy + col, o * inv, out_kind);
             if (lane == 0) y_sf[(long long)out_row * ld_ysf + (col >> 5)] = (uint8_t)(bits >> 23);
           }
@@ -669,7 +669,7 @@ extern "C" int tb200_moe_gemm_mx4(const tb200_moe_gemm_mx4_args* a, void* stream
   if (a->out_dtype != TB200_BF16 && a->out_dtype != TB200_F16 && a->out_dtype != TB200_E4M3 &&
       a->out_dtype != TB200_E5M2)
     return TB200_ERR_UNSUPPORTED;
-  if (wf8 ? (a->k % 16) != 0 : ((a->k % 128) || (a->n % 128))) return TB200_ERR_UNSUPPORTED;
+  if (wf8 ? (a->k % 16) != 0 : (a->k % 32) != 0) return TB200_ERR_UNSUPPORTED;
   if (a->swiglu && (a->n & 1)) return TB200_ERR_BAD_ARG;
   if ((a->ldx % 16) || a->ldx < a->k) return TB200_ERR_BAD_ARG;
   if ((reinterpret_cast<uintptr_t>(a->x) & 15) || (reinterpret_cast<uintptr_t>(a->w) & (wf8 ? 15 : 31)) ||
@@ -715,7 +715,7 @@ extern "C" int tb200_moe_gemm_mx4(const tb200_moe_gemm_mx4_args* a, void* stream
     // blocked weights: one (expert, N tile, K step) block of 256 rows x 64 bytes after the other, so a tile
     // step is one contiguous 16 KB run of HBM
     const uint64_t tiles_n = (uint64_t)((a->n + M4_BN - 1) / M4_BN);
-    const uint64_t rows = (uint64_t)a->n_experts * tiles_n * (uint64_t)(a->k / 128) * M4_BN;
+    const uint64_t rows = (uint64_t)a->n_experts * tiles_n * (uint64_t)((a->k + 127) / 128) * M4_BN;
     if (rows > (1ull << 31)) return TB200_ERR_UNSUPPORTED;
     const uint64_t dims[2] = {128, rows};  // in 4-bit values
     const uint64_t strides[1] = {64};
@@ -746,7 +746,7 @@ extern "C" int tb200_moe_gemm_mx4(const tb200_moe_gemm_mx4_args* a, void* stream
   p.status = status_ptr();
   if (!p.status) return TB200_ERR_CUDA;
   p.n_sched = (int)a->n_sched;
-  p.tiles_n = swap ? (int)(a->n / S4_WROWS) : (int)((a->n + M4_BN - 1) / M4_BN);
+  p.tiles_n = swap ? (int)((a->n + S4_WROWS - 1) / S4_WROWS) : (int)((a->n + M4_BN - 1) / M4_BN);
   if ((long long)p.n_sched * p.tiles_n > INT32_MAX) return TB200_ERR_UNSUPPORTED;
   p.units = p.n_sched * p.tiles_n;
   p.n = (int)a->n;

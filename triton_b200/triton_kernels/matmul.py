@@ -494,7 +494,7 @@ def _mx4_kernel_layout(b, b_mx_scale, microblock):
     if not isinstance(ws.layout, BlackwellMXScaleLayout):
         ws = convert_layout(ws, make_default_matmul_mxfp4_w_scale_layout(mx_axis=1))
     E, K, N = w.shape
-    assert ws.shape == (E, K // 32, N), "scale shape does not match the weight"
+    assert ws.shape == (E, (K + 31) // 32, N), "scale shape does not match the weight"
     return w, ws
 
 
@@ -503,6 +503,8 @@ def upcast_mxfp4_weight(b, b_mx_scale, dtype, microblock=None):
     bf16 / fp16 view with K contiguous (``tb200_mxfp4_upcast``)."""
     w, ws = _mx4_kernel_layout(b, b_mx_scale, microblock)
     E, K, N = w.shape
+    if K % 128 or N % 128:
+        raise NotImplementedError("matmul (16-bit activations x MXFP4): K and N must be multiples of 128")
     dev = w.data.device
     if not w.data.is_cuda:
         raise RuntimeError("triton_b200 matmul needs CUDA tensors (there is no CPU path)")

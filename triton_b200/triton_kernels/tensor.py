@@ -212,19 +212,21 @@ def convert_layout(t: Tensor, layout) -> Tensor:
     if isinstance(layout, BlackwellMX4ValueLayout):
         assert t.dtype is FP4 and d.dtype == torch.uint8
         E, K2, N = d.shape
-        assert (2 * K2) % 128 == 0 and N % 128 == 0, "K and N must be multiples of 128"
+        assert (2 * K2) % 32 == 0, "K must be a multiple of the 32-value scale block"
         nk = d.transpose(1, 2)                                   # [E, N, K/2]
-        tiles = (N + 255) // 256
-        if tiles * 256 != N:
-            nk = torch.nn.functional.pad(nk, (0, 0, 0, tiles * 256 - N))
+        tiles, ksteps = (N + 255) // 256, (K2 + 63) // 64
+        if tiles * 256 != N or ksteps * 64 != K2:                # zero rows past N, zero codes (+0.0) past K
+            nk = torch.nn.functional.pad(nk, (0, ksteps * 64 - K2, 0, tiles * 256 - N))
         # blocked: [E][N/256][K/128][256 rows][64 bytes] - one tile step is one contiguous 16 KB run
-        out = nk.reshape(E, tiles, 256, K2 // 64, 64).permute(0, 1, 3, 2, 4).contiguous()
+        out = nk.reshape(E, tiles, 256, ksteps, 64).permute(0, 1, 3, 2, 4).contiguous()
         return Tensor(out, FP4, (E, 2 * K2, N), layout)
     if isinstance(layout, BlackwellMXScaleLayout):
         assert d.dtype == torch.uint8
         E, KB, N = d.shape  # KB = K / 32
-        assert KB % 4 == 0 and N % 128 == 0, "K and N must be multiples of 128"
-        s = d.transpose(1, 2).reshape(E, N // 128, 4, 32, KB // 4, 4)  # e, n/128, n/32%4, n%32, k/128, k/32%4
+        nb, ksteps = (N + 127) // 128, (KB + 3) // 4
+        if nb * 128 != N or ksteps * 4 != KB:                          # scale 1.0 past N and K
+            d = torch.nn.functional.pad(d, (0, nb * 128 - N, 0, ksteps * 4 - KB), value=127)
+        s = d.transpose(1, 2).reshape(E, nb, 4, 32, ksteps, 4)          # e, n/128, n/32%4, n%32, k/128, k/32%4
         out = s.permute(0, 1, 4, 3, 2, 5).contiguous()                 # e, n/128, k/128, n%32, n/32%4, k/32%4
         return Tensor(out, torch.uint8, (E, KB, N), layout)
     raise NotImplementedError(f"convert_layout: {layout!r}")
