@@ -216,6 +216,25 @@ def test_mxfp8_x_mxfp8_moe_call_with_quantised_output(cuda, swiglu):
     assert float(torch.sqrt(((got - want) ** 2).mean()) / torch.sqrt((want ** 2).mean()).clamp_min(1e-6)) <= 4e-2
 
 
+@pytest.mark.parametrize("wdtype", [torch.bfloat16, torch.float16])
+def test_mxfp8_activations_x_16bit_weights(cuda, wdtype):
+    """mxfloat8 x bfloat16 / float16 (tests/test_matmul.py:217-224): the activations are upcast to the weights' dtype and the
+    16-bit kernel runs; the output has that dtype."""
+    from triton_b200.triton_kernels.matmul import PrecisionConfig, matmul
+    from triton_b200.triton_kernels.tensor import make_ragged_tensor_metadata
+    E, K, N = 3, 96, 128
+    g = torch.Generator().manual_seed(11)
+    cnt = torch.tensor([40, 0, 24], dtype=torch.int32)
+    rg = make_ragged_tensor_metadata(cnt.to(cuda), 64)
+    xv, xs = downcast_to_mxfp(torch.randn(64, K, generator=g).to(torch.bfloat16), torch.float8_e4m3fn, axis=1)
+    xdq = upcast_from_mxfp(xv, xs, torch.float32, axis=1)
+    w = (0.3 * torch.randn(E, K, N, generator=g)).to(wdtype)
+    out = matmul(xv.to(cuda), w.to(cuda), None, rg, precision_config=PrecisionConfig(a_mx_scale=xs.to(cuda)))
+    assert out.dtype == wdtype
+    ref = o.grouped_matmul_ref(xdq, w.float(), None, cnt.numpy(), out_dtype=torch.float32)
+    torch.testing.assert_close(out.cpu().float(), ref, rtol=2e-2, atol=2e-2)
+
+
 def test_bf16_x_mxfp8_weights(cuda):
     """bfloat16 x mxfloat8 (tests/test_matmul.py:177): the weight is upcast to bf16, then the 16-bit kernel runs."""
     from triton_b200.triton_kernels.matmul import PrecisionConfig, matmul

@@ -168,6 +168,18 @@ def matmul(a, b, bias, a_ragged_metadata: RaggedTensorMetadata | None = None, b_
             a = _gather_fp8_rows(a, gather_indx)
         return _matmul_mx4(a, b, bias, a_ragged_metadata, scatter_indx, precision_config or PrecisionConfig(), gammas,
                            fused_activation)
+    if precision_config is not None and precision_config.a_mx_scale is not None and precision_config.b_mx_scale is None \
+            and isinstance(a, torch.Tensor) and a.dtype in _F8 and isinstance(b, torch.Tensor) and b.dtype in _DT:
+        # mxfloat8 activations x 16-bit weights (tests/test_matmul.py:217-224 in the reference): the activations are
+        # upcast to the weight dtype with torch ops, then the 16-bit grouped GEMM runs
+        import dataclasses
+        from .numerics_details.mxfp import upcast_from_mxfp
+        if precision_config.a_microblock_size not in (None, 32):
+            raise NotImplementedError("matmul: microblock size 32 (e8m0 scales) only")
+        a16 = upcast_from_mxfp(a, _plain_scale(precision_config.a_mx_scale), b.dtype, axis=a.ndim - 1)
+        pc16 = dataclasses.replace(precision_config, a_mx_scale=None, a_microblock_size=None)
+        return matmul(a16, b, bias, a_ragged_metadata, b_ragged_metadata, gather_indx, scatter_indx, pc16, betas, gammas,
+                      out_alpha, c, fused_comm, fused_activation, epilogue, c_acc_in, _tile_mode, _gammas_by_out_row)
     if precision_config is not None and precision_config.a_mx_scale is not None:
         if precision_config.b_mx_scale is None or not isinstance(a, torch.Tensor) or a.dtype not in _F8:
             raise NotImplementedError("matmul: MX-scaled activations are implemented as MXFP8 x MXFP4 "
