@@ -336,3 +336,23 @@ def test_tile_modes_agree_bit_for_bit(cuda, swiglu, dims):
     ref = o.grouped_matmul_ref(x.cpu(), w.cpu(), None, sizes.numpy(), scatter_indx=scat.cpu().numpy(), gammas=gam.cpu(),
                                swiglu=(1.0, None) if swiglu else None)
     torch.testing.assert_close(outs[1].cpu().float(), ref.float(), rtol=2e-2, atol=2e-2)
+
+
+def test_transposed_operands_and_output(cuda):
+    """The reference's transpose / permute cases (tests/test_matmul.py:257-266): column-major activations, weights and
+    output buffer give the same product."""
+    from triton_b200.triton_kernels.matmul import matmul
+    g = torch.Generator().manual_seed(31)
+    B, M, K, N = 2, 320, 400, 400
+    a = torch.randn(B, M, K, generator=g).to(torch.float16)
+    w = (0.1 * torch.randn(B, K, N, generator=g)).to(torch.float16)
+    ref = torch.bmm(a.float(), w.float())
+    tr = lambda t: t.transpose(-1, -2).contiguous().transpose(-1, -2)
+    for a_tr, b_tr in ((False, False), (True, False), (False, True), (True, True)):
+        y = matmul((tr(a) if a_tr else a).to(cuda), (tr(w) if b_tr else w).to(cuda), None)
+        torch.testing.assert_close(y.cpu().float(), ref, rtol=2e-2, atol=2e-2)
+    # column-major output buffer (2-D ragged call with one slice)
+    buf = torch.empty(N, M, dtype=torch.float16, device=cuda).t()
+    out = matmul(a[0].to(cuda), w[0].to(cuda), None, c=buf)
+    assert out.data_ptr() == buf.data_ptr() and buf.stride(0) == 1
+    torch.testing.assert_close(buf.cpu().float(), ref[0], rtol=2e-2, atol=2e-2)

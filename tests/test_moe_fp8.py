@@ -94,6 +94,20 @@ def test_grouped_fp8_gather_scatter(cuda, dtype, swiglu):
     torch.testing.assert_close(out.cpu().float(), ref, rtol=1e-2, atol=2e-2)
 
 
+def test_preallocated_output(cuda):
+    """``c=``: the product lands in the caller's buffer (a row-strided view here) and that tensor is returned."""
+    from triton_b200.triton_kernels.matmul import PrecisionConfig, matmul
+    g = torch.Generator().manual_seed(12)
+    x = (torch.randn(96, 128, generator=g) * 0.5).to(torch.float8_e4m3fn)
+    w = (torch.randn(128, 144, generator=g) * 0.5).to(torch.float8_e4m3fn)
+    buf = torch.full((96, 160), 7.0, dtype=torch.bfloat16, device=cuda)
+    out = matmul(x.to(cuda), _col_major(w).to(cuda), None, precision_config=PrecisionConfig(out_dtype=torch.bfloat16),
+                 c=buf[:, :144])
+    assert out.data_ptr() == buf.data_ptr()
+    torch.testing.assert_close(buf[:, :144].cpu().float(), x.float() @ w.float(), rtol=1e-2, atol=1e-2)
+    assert float((buf[:, 144:].float() - 7.0).abs().max()) == 0.0
+
+
 def test_batched_fp8(cuda):
     from triton_b200.triton_kernels.matmul import PrecisionConfig, matmul
     B, M, K, N = 3, 300, 416, 400

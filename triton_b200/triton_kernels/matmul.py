@@ -118,6 +118,14 @@ def matmul(a, b, bias, a_ragged_metadata: RaggedTensorMetadata | None = None, b_
            gather_indx=None, scatter_indx=None, precision_config: PrecisionConfig | None = None, betas=None,
            gammas=None, out_alpha=None, c=None, fused_comm=None, fused_activation: FusedActivation | None = None,
            epilogue: Epilogue | None = None, c_acc_in=None, _tile_mode: int = 0, _gammas_by_out_row: bool = False):
+    if isinstance(c, torch.Tensor) and c.ndim >= 2 and c.stride(-1) != 1 and fused_comm is None:
+        # a transposed (column-major) output buffer, as the reference's c_transpose cases pass: the kernels write
+        # rows, so the product is formed in a row-major temporary and copied over
+        out = matmul(a, b, bias, a_ragged_metadata, b_ragged_metadata, gather_indx, scatter_indx, precision_config, betas,
+                     gammas, out_alpha, None, None, fused_activation, epilogue, c_acc_in, _tile_mode, _gammas_by_out_row)
+        assert out.shape == c.shape and out.dtype == c.dtype, "c does not match the product's shape or dtype"
+        c.copy_(out)
+        return c
     if b_ragged_metadata is not None:
         if (gather_indx is not None or scatter_indx is not None or fused_comm is not None or c_acc_in is not None
                 or (fused_activation is not None and fused_activation.specs.name != "dflt")
@@ -161,13 +169,12 @@ def matmul(a, b, bias, a_ragged_metadata: RaggedTensorMetadata | None = None, b_
         # fp8 x fp8 (tensor-wide flexpoint scales, or none): the block-scaled kernel with scale columns of 1.0
         if precision_config is not None and precision_config.a_mx_scale is not None:
             raise NotImplementedError("matmul: MX-scaled activations need an MX-scaled weight (b_mx_scale)")
-        if betas is not None or out_alpha is not None or c_acc_in is not None or fused_comm is not None or c is not None:
-            raise NotImplementedError("matmul (fp8 weights): betas / out_alpha / c_acc_in / fused_comm / a preallocated "
-                                      "output are not implemented")
+        if betas is not None or out_alpha is not None or c_acc_in is not None or fused_comm is not None:
+            raise NotImplementedError("matmul (fp8 weights): betas / out_alpha / c_acc_in / fused_comm are not implemented")
         if gather_indx is not None:
             a = _gather_fp8_rows(a, gather_indx)
         return _matmul_mx4(a, b, bias, a_ragged_metadata, scatter_indx, precision_config or PrecisionConfig(), gammas,
-                           fused_activation)
+                           fused_activation, c)
     if precision_config is not None and precision_config.a_mx_scale is not None and precision_config.b_mx_scale is None \
             and isinstance(a, torch.Tensor) and a.dtype in _F8 and isinstance(b, torch.Tensor) and b.dtype in _DT:
         # mxfloat8 activations x 16-bit weights (tests/test_matmul.py:217-224 in the reference): the activations are
@@ -206,8 +213,6 @@ def matmul(a, b, bias, a_ragged_metadata: RaggedTensorMetadata | None = None, b_
                                    c_microblock_size=precision_config.c_microblock_size)
             return matmul(a, w16, bias, a_ragged_metadata, None, gather_indx, scatter_indx, pc16, None, gammas,
                           None, c, None, fused_activation, epilogue, None, _tile_mode)
-        if c is not None:
-            raise NotImplementedError("matmul (fp8 x MXFP4): a preallocated output is not implemented")
         if gather_indx is not None:
             # this kernel reads sorted rows only: indexed rows are gathered by a pass of their own first
             a = _gather_fp8_rows(a, gather_indx)
@@ -215,7 +220,7 @@ def matmul(a, b, bias, a_ragged_metadata: RaggedTensorMetadata | None = None, b_
                 import dataclasses
                 sc = _plain_scale(precision_config.a_mx_scale)
                 precision_config = dataclasses.replace(precision_config, a_mx_scale=_gather_scale_rows(sc, gather_indx))
-        return _matmul_mx4(a, b, bias, a_ragged_metadata, scatter_indx, precision_config, gammas, fused_activation)
+        return _matmul_mx4(a, b, bias, a_ragged_metadata, scatter_indx, precision_config, gammas, fused_activation, c)
     if precision_config is not None and _flex_in_use(precision_config.flex_ctx):
         raise NotImplementedError("matmul: flexpoint scales are implemented for fp8 activations x MXFP4 weights")
     if not isinstance(a, torch.Tensor) or not isinstance(b, torch.Tensor):
@@ -532,7 +537,7 @@ def upcast_mxfp4_weight(b, b_mx_scale, dtype, microblock=None):
     return out.transpose(1, 2)
 
 
-def _matmul_mx4(a, b, bias, a_ragged_metadata, scatter_indx, pc: PrecisionConfig, gammas, fused_activation):
+def _matmul_mx4(a, b, bias, a_ragged_metadata, scatter_indx, pc: PrecisionConfig, gammas, fused_activation, c=None):
     """FP8 activations x MXFP4 weights (the reference's Blackwell "fp8 x mx4" MoE configuration,
     bench/bench_mlp.py:253-279). ``b`` / ``pc.b_mx_scale`` are either what ``downcast_to_mxfp(w, torch.uint8,
     axis=1)`` returned ([E, K/2, N] and [E, K/32, N] uint8: re-laid here on every call) or the Tensors
@@ -576,7 +581,15 @@ def _matmul_mx4(a, b, bias, a_ragged_metadata, scatter_indx, pc: PrecisionConfig
     out_codes = {**_DT, **_F8}
     if out_dtype not in out_codes:
         raise NotImplementedError("matmul (MXFP4 weight): bf16 / fp16 / fp8 output")
-    c = (torch.zeros if scatter_indx is not None else torch.empty)((rows_y, n_out), dtype=out_dtype, device=dev)
+    if c is not None:  # the caller's output buffer (rows a scatter index does not name are zeroed, as in a fresh one)
+        if pc.c_mx_scale is not None:
+            raise NotImplementedError("matmul: MX-quantised output with c / c_acc_in is not implemented")
+        assert c.shape == (rows_y, n_out) and c.dtype == out_dtype and c.device == dev and c.stride(1) == 1, \
+            "c must be a [rows, n_out] tensor of the output dtype with unit column stride"
+        if scatter_indx is not None:
+            c.zero_()
+    else:
+        c = (torch.zeros if scatter_indx is not None else torch.empty)((rows_y, n_out), dtype=out_dtype, device=dev)
     a_sf = c_sf = None
     if pc.a_mx_scale is not None:
         a_sf = _plain_scale(pc.a_mx_scale)
