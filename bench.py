@@ -246,12 +246,15 @@ def build_workload(name: str, rank: int, world: int, dev):
         from triton_b200.tutorials.blackwell_fa_ws_pipelined_persistent import attention_with_lse
         causal = name.endswith("causal")
         B, H, S, D = (32, 32, 1024, 128) if "short" in name else (4, 32, 8192, 128)
+        if "d256" in name:  # head dim 256 with the same flop count: half the heads
+            H, D = H // 2, 256
         q, k, v = (_dev_randn((B, H, S, D), dev, 2 + 1000 * rank + i, dtype=bf) for i in range(3))
         sc = 1.0 / math.sqrt(D)
         fl = 4.0 * B * H * D * (S * (S + 1) / 2 if causal else S * S)
         return Workload(lambda: attention_with_lse(q, k, v, sc, causal)[0], fl, 4.0 * B * H * S * D * 2,
                         f"flash-attention fwd bf16 [B={B},H={H},S={S},D={D}] causal={causal}, seed 2",
-                        "attention_fwd_kernel<128>", "tensor", [q, k, v], cpu=lambda: cpu_attn(causal))
+                        f"attention_fwd_kernel<{D}>", "tensor", [q, k, v],
+                        cpu=None if D == 256 else (lambda: cpu_attn(causal)))
     if name in ("attn_bwd", "attn_bwd_causal", "attn_bwd_ref_shape", "attn_bwd_ref_shape_causal"):
         from triton_b200.tutorials.blackwell_fa_ws_pipelined_persistent import attention_backward, attention_with_lse
         causal = name.endswith("causal")
@@ -759,7 +762,7 @@ def main():
     ap.add_argument("--configs", default="", help="comma-separated subset of the configs to measure")
     ap.add_argument("--workload", default="gemm",
                     help="gemm (headline + configs, default) | " + " | ".join(CONFIG_NAMES) + " | attn_bwd | attn_bwd_causal | "
-                         "attn_bwd_ref_shape[_causal] | fp8_blockwise | moe_mx4 | moe_mx4_decode | moe_bf16_mx4 | moe_fp8 | mxfp4_upcast | "
+                         "attn_d256[_causal] | attn_bwd_ref_shape[_causal] | fp8_blockwise | moe_mx4 | moe_mx4_decode | moe_bf16_mx4 | moe_fp8 | mxfp4_upcast | "
                          "moe_ep_unfused | moe_ep_nccl | moe_small | attn_mxfp8 | attn_mxfp8_causal")
     args = ap.parse_args()
 

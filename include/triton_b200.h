@@ -179,7 +179,7 @@ int tb200_gemm_fp8_blockwise(const tb200_gemm_fp8_blockwise_args* args, void* st
  * Stands behind: third_party/tlx/tutorials/blackwell_fa_ws_pipelined_persistent.py:3491
  *   attention(q, k, v, sm_scale, causal, config=None)   (kernel _attn_fwd_ws :600, forward :3288).
  * q, o: [batch, heads, seq_q, head_dim] contiguous; k, v: [batch, heads, seq_kv, head_dim]
- * contiguous; dtype TB200_BF16 or TB200_F16; head_dim 64 or 128; lse (may be NULL):
+ * contiguous; dtype TB200_BF16 or TB200_F16; head_dim 64, 128 or 256; lse (may be NULL):
  * float [batch, heads, seq_q]. causal requires seq_q == seq_kv (as in the reference).
  * Any sequence length >= 1 is accepted (the tail is masked). Base pointers 16-byte aligned.
  */

@@ -22,6 +22,10 @@
 //                of the warp), otherwise the stale max stays the reference point and the final
 //                O / l is unchanged. P (bf16) is written over the first half of S's columns.
 // Tensor memory (512 columns): S0 | S1 | O0 | O1 with P_g aliasing S_g.
+// Head dim 256 (a 128-row tile is 64 KB, an output accumulator 256 columns): the same kernel with one query group per
+// CTA - Q | a two-deep K / V ring in shared memory, S0 | O0 in tensor memory, the second softmax warpgroup idle; the
+// softmax of a block then runs with the tensor pipe idle, which weighs less here because a block carries twice the
+// MMA work per score (measured 905 / 920 TFLOP/s at [4, 16, 8192, 256] non-causal / causal).
 // In-order execution of one thread's tcgen05.mma stream gives the S/P write-after-read order
 // (QK_g(j+1) is issued after PV_g(j)) and makes PV_g(j-1) complete before S_g(j) is signalled, so
 // only the last PV of a tile carries a completion barrier of its own. The issuing thread probes
@@ -61,12 +65,15 @@ struct AttnParams {
   float scale_log2;  // sm_scale * log2(e)
 };
 
-template <int D>
+// G = query groups per CTA: 2 (256 query rows, the groups' MMAs and softmax passes interleaved), or 1 for head dim 256,
+// where a tile is 64 KB and tensor memory holds one 128 x 256 output besides the scores: one group, a two-deep K / V ring.
+template <int D, int G>
 struct AttnSmem {
   static constexpr int TILE_BYTES = 128 * D * 2;  // one 128-row tile of Q, K or V
+  static constexpr int KV_STAGES = G == 2 ? ATT_KV_STAGES : 2;
   static constexpr int Q_OFFSET = 0;
-  static constexpr int KV_OFFSET = 2 * TILE_BYTES;
-  static constexpr int BAR_OFFSET = KV_OFFSET + ATT_KV_STAGES * TILE_BYTES;
+  static constexpr int KV_OFFSET = G * TILE_BYTES;
+  static constexpr int BAR_OFFSET = KV_OFFSET + KV_STAGES * TILE_BYTES;
   static constexpr int NUM_BARS = 4 + 2 * ATT_KV_STAGES + 14;
   static constexpr int TOTAL = BAR_OFFSET + NUM_BARS * 8 + 16 + 1024;
 };
@@ -83,24 +90,27 @@ struct AttnTile {
 // Measured again with groups of heads sized to 16 / 32 MB of K + V, alternating with this order in one process
 // (five rounds): [4, 32, 8192, 128] 999 / 992 against 1044 TFLOP/s non-causal and 930 / 931 against 967 causal;
 // [32, 32, 1024, 128] 901 / 917 against 890 and 596 / 585 against 609.
+template <int G>
 __device__ __forceinline__ AttnTile attn_tile(const AttnParams& p, int unit) {
   AttnTile t;
   const int qb = p.q_tiles - 1 - unit / p.bh;
   t.bh = unit % p.bh;
-  t.q0 = qb * 2 * ATT_BM;
+  t.q0 = qb * G * ATT_BM;
   int nkv = (p.s_kv + ATT_BN - 1) / ATT_BN;
   t.nkv0 = nkv;
   if (p.causal) {
     t.nkv0 = min(nkv, (t.q0 + ATT_BM + ATT_BN - 1) / ATT_BN);
-    nkv = min(nkv, (t.q0 + 2 * ATT_BM + ATT_BN - 1) / ATT_BN);
+    nkv = min(nkv, (t.q0 + G * ATT_BM + ATT_BN - 1) / ATT_BN);
   }
   t.nkv = nkv;
   return t;
 }
 
-template <int D, bool F16>
+template <int D, bool F16, int G>
 __global__ void __launch_bounds__(ATT_THREADS, 1) attention_fwd_kernel(const __grid_constant__ AttnParams p) {
-  using L = AttnSmem<D>;
+  using L = AttnSmem<D, G>;
+  constexpr bool TWO = G == 2;
+  constexpr int KV_STAGES = L::KV_STAGES;
   constexpr int DBOX = D / 64;                 // 64-column TMA boxes per tile
   constexpr int BOX_BYTES = 128 * 128;         // 128 rows x 128 bytes
   constexpr uint32_t S_COLS = 128;
@@ -173,20 +183,22 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_fwd_kernel(const __g
       auto load_kv = [&](const CUtensorMap* tm, int row, int bh) -> bool {
         if (!mbar_wait(&kv_empty[kvs], kvph ^ 1, status, WAIT_SMEM_EMPTY)) return false;
         load_tile(tm, smem_a + L::KV_OFFSET + kvs * L::TILE_BYTES, &kv_full[kvs], row, bh, pol_kv);
-        if (++kvs == ATT_KV_STAGES) {
+        if (++kvs == KV_STAGES) {
           kvs = 0;
           kvph ^= 1;
         }
         return true;
       };
       for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x, ++tcount) {
-        const AttnTile t = attn_tile(p, unit);
+        const AttnTile t = attn_tile<G>(p, unit);
         const uint32_t qph = (tcount & 1) ^ 1;
         if (!mbar_wait(&q_empty[0], qph, status, WAIT_SMEM_EMPTY)) break;
         load_tile(&p.tmq, smem_a + L::Q_OFFSET, &q_full[0], t.q0, t.bh, pol_q);
         if (!load_kv(&p.tmk, 0, t.bh)) break;
-        if (!mbar_wait(&q_empty[1], qph, status, WAIT_SMEM_EMPTY)) break;
-        load_tile(&p.tmq, smem_a + L::Q_OFFSET + L::TILE_BYTES, &q_full[1], t.q0 + ATT_BM, t.bh, pol_q);
+        if constexpr (TWO) {
+          if (!mbar_wait(&q_empty[1], qph, status, WAIT_SMEM_EMPTY)) break;
+          load_tile(&p.tmq, smem_a + L::Q_OFFSET + L::TILE_BYTES, &q_full[1], t.q0 + ATT_BM, t.bh, pol_q);
+        }
         if (!load_kv(&p.tmv, 0, t.bh)) break;
         for (int j = 1; j < t.nkv && ok; ++j) {
           ok = load_kv(&p.tmk, j * ATT_BN, t.bh) && load_kv(&p.tmv, j * ATT_BN, t.bh);
@@ -245,14 +257,14 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_fwd_kernel(const __g
         return true;
       };
       auto advance = [&]() {
-        if (++kvs == ATT_KV_STAGES) {
+        if (++kvs == KV_STAGES) {
           kvs = 0;
           kvph ^= 1;
         }
       };
 
       for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x, ++tcount) {
-        const AttnTile t = attn_tile(p, unit);
+        const AttnTile t = attn_tile<G>(p, unit);
         const uint32_t tph = tcount & 1;
         // prologue: S_g(0) = Q_g K(0)^T
         uint32_t kcur = kvs, kcur_ph = kvph;
@@ -261,15 +273,17 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_fwd_kernel(const __g
         if (!mbar_wait(&kv_full[kcur], kcur_ph, status, WAIT_SMEM_FULL)) break;
         tc_fence_after_sync();
         issue_qk(0, kcur);
-        if (!mbar_wait(&q_full[1], tph, status, WAIT_ATTN)) break;
-        tc_fence_after_sync();
-        issue_qk(1, kcur);
+        if constexpr (TWO) {
+          if (!mbar_wait(&q_full[1], tph, status, WAIT_ATTN)) break;
+          tc_fence_after_sync();
+          issue_qk(1, kcur);
+        }
         umma_commit(&kv_empty[kcur]);
         // Under a causal mask the last KV block of a tile can lie wholly above the first group's diagonal: that group
         // then runs one block fewer (n0 = n1 - 1) and the last iteration serves the second group alone.
-        const int n0 = t.nkv0, n1 = t.nkv;
+        const int n0 = t.nkv0, n1 = TWO ? t.nkv : t.nkv0;  // one group: the loop is the first group's
         if (n0 == 1) umma_commit(&q_empty[0]);
-        if (n1 == 1) umma_commit(&q_empty[1]);
+        if (TWO && n1 == 1) umma_commit(&q_empty[1]);
         for (int j = 0; j < n1; ++j, ++it1) {
           const uint32_t iph0 = it0 & 1, iph1 = it1 & 1;
           const bool act0 = j < n0, more0 = j + 1 < n0, more1 = j + 1 < n1;
@@ -293,20 +307,22 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_fwd_kernel(const __g
           if (more1) {
             if (!k_ready && !mbar_wait(&kv_full[knext], knext_ph, status, WAIT_SMEM_FULL)) { ok = false; break; }
             tc_fence_after_sync();
-            p1_ready = mbar_test(&p_full[4 + 4 / ATT_PV_SLICES - 1], iph1);
+            if constexpr (TWO) p1_ready = mbar_test(&p_full[4 + 4 / ATT_PV_SLICES - 1], iph1);
             if (more0) {
               issue_qk(0, knext);
               if (j + 2 == n0) umma_commit(&q_empty[0]);
             }
           }
           // PV1(j)
-          if (j == 0 && !mbar_wait(&o_free[1], tph ^ 1, status, WAIT_ATTN)) { ok = false; break; }
-          if (!issue_pv(1, vcur, j > 0 ? 1u : 0u, iph1, p1_ready, !more1)) { ok = false; break; }
+          if constexpr (TWO) {
+            if (j == 0 && !mbar_wait(&o_free[1], tph ^ 1, status, WAIT_ATTN)) { ok = false; break; }
+            if (!issue_pv(1, vcur, j > 0 ? 1u : 0u, iph1, p1_ready, !more1)) { ok = false; break; }
+          }
           umma_commit(&kv_empty[vcur]);
           if (more1) {
-            issue_qk(1, knext);
+            if constexpr (TWO) issue_qk(1, knext);
             umma_commit(&kv_empty[knext]);
-            if (j + 2 == n1) umma_commit(&q_empty[1]);
+            if (TWO && j + 2 == n1) umma_commit(&q_empty[1]);
           }
         }
       }
@@ -326,8 +342,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_fwd_kernel(const __g
     const int s_kv = p.s_kv, s_q = p.s_q, causal = p.causal;
     uint32_t it = 0, tcount = 0;
     bool ok = true;
-    for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x, ++tcount) {
-      const AttnTile t = attn_tile(p, unit);
+    for (int unit = blockIdx.x; unit < units && ok && (TWO || g == 0); unit += gridDim.x, ++tcount) {
+      const AttnTile t = attn_tile<G>(p, unit);
       const int qrow = t.q0 + g * ATT_BM + row_in_group;  // position in the sequence
       float m = -INFINITY, l = 0.f;
       const int nkv_g = g == 0 ? t.nkv0 : t.nkv;
@@ -476,10 +492,11 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attention_fwd_kernel(const __g
   }
 }
 
-template <int D>
+template <int D, int G>
 static int launch_attn(const AttnParams& p, int grid, cudaStream_t stream) {
-  using L = AttnSmem<D>;
-  auto kfn = p.out_f16 ? attention_fwd_kernel<D, true> : attention_fwd_kernel<D, false>;
+  using L = AttnSmem<D, G>;
+  static_assert(L::TOTAL <= 232448, "shared memory budget");
+  auto kfn = p.out_f16 ? attention_fwd_kernel<D, true, G> : attention_fwd_kernel<D, false, G>;
   if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL) != cudaSuccess)
     return TB200_ERR_CUDA;
   kfn<<<grid, ATT_THREADS, L::TOTAL, stream>>>(p);
@@ -493,7 +510,7 @@ using namespace tb200;
 extern "C" int tb200_attention_fwd(const tb200_attention_args* a, void* stream_) {
   if (!a || !a->q || !a->k || !a->v || !a->o) return TB200_ERR_BAD_ARG;
   if (a->batch < 0 || a->heads < 0 || a->seq_q < 0 || a->seq_kv < 0) return TB200_ERR_BAD_ARG;
-  if (a->head_dim != 64 && a->head_dim != 128) return TB200_ERR_UNSUPPORTED;
+  if (a->head_dim != 64 && a->head_dim != 128 && a->head_dim != 256) return TB200_ERR_UNSUPPORTED;
   if (a->dtype != TB200_BF16 && a->dtype != TB200_F16) return TB200_ERR_UNSUPPORTED;
   if (a->causal && a->seq_q != a->seq_kv) return TB200_ERR_UNSUPPORTED;
   if (!(a->sm_scale > 0.f)) return TB200_ERR_BAD_ARG;
@@ -535,11 +552,13 @@ extern "C" int tb200_attention_fwd(const tb200_attention_args* a, void* stream_)
   p.bh = (int)bh;
   p.s_q = (int)a->seq_q;
   p.s_kv = (int)a->seq_kv;
-  p.q_tiles = (int)((a->seq_q + 2 * ATT_BM - 1) / (2 * ATT_BM));
+  const int tile_rows = (D == 256 ? 1 : 2) * ATT_BM;
+  p.q_tiles = (int)((a->seq_q + tile_rows - 1) / tile_rows);
   p.units = p.q_tiles * p.bh;
   p.causal = a->causal ? 1 : 0;
   p.out_f16 = a->dtype == TB200_F16 ? 1 : 0;
   p.scale_log2 = a->sm_scale * 1.4426950408889634f;
   const int grid = p.units < sms ? p.units : sms;
-  return D == 128 ? launch_attn<128>(p, grid, stream) : launch_attn<64>(p, grid, stream);
+  return D == 256 ? launch_attn<256, 1>(p, grid, stream)
+         : D == 128 ? launch_attn<128, 2>(p, grid, stream) : launch_attn<64, 2>(p, grid, stream);
 }

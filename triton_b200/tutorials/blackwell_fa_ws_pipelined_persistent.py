@@ -9,8 +9,9 @@ zero-padded) and returns
 The reference keeps the row statistic ``M = m*sm_scale*log2(e) + log2(l)`` (base-2 log-sum-exp, ``:886-894``) internal;
 ``attention_with_lse`` returns it as a second fp32 ``[B, H, S]`` tensor without changing the
 signature of ``attention``. ``config`` is accepted for call compatibility (the tiling is fixed:
-256 query rows per CTA as two groups of 128, KV blocks of 128). Head dims: 64 and 128 natively, 16 and 32
-zero-padded to 64; 256 (the last of the reference's set, ``:3291-3292``) raises ``NotImplementedError``.
+256 query rows per CTA as two groups of 128, KV blocks of 128; head dim 256: one group of 128 rows). Head dims of the
+reference's set (``:3291-3292``): 64, 128 and 256 natively in the forward pass, 16 and 32 zero-padded to 64; the
+backward pass serves up to 128.
 """
 from __future__ import annotations
 
@@ -31,8 +32,6 @@ def attention_with_lse(q, k, v, sm_scale, causal, config=None):
     HEAD_DIM_Q, HEAD_DIM_K, HEAD_DIM_V = q.shape[-1], k.shape[-1], v.shape[-1]
     assert HEAD_DIM_Q == HEAD_DIM_K and HEAD_DIM_K == HEAD_DIM_V
     assert HEAD_DIM_K in {16, 32, 64, 128, 256}
-    if HEAD_DIM_K == 256:
-        raise NotImplementedError("head_dim 256: the kernels are built for 64 and 128 (16 and 32 run zero-padded to 64)")
     if not q.is_cuda:
         raise RuntimeError("triton_b200 attention needs CUDA tensors (there is no CPU path)")
     if HEAD_DIM_K < 64:
