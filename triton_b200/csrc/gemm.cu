@@ -848,7 +848,7 @@ static int launch_gemm(const GemmParams& p, const GemmPlan& plan, int sms, cudaS
   const int grid = p.units < sms ? p.units : sms;
   switch (plan.bn) {
     case 256: return launch_one<256, 4, false, F8>(p, grid, stream);
-    case 128: return launch_one<128, 6, false, F8>(p, grid, stream);
+    case 128: return launch_one<128, 7, false, F8>(p, grid, stream);
     default: return launch_one<64, 8, false, F8>(p, grid, stream);
   }
 }
