@@ -94,6 +94,16 @@ def test_grouped_fp8_gather_scatter(cuda, dtype, swiglu):
     torch.testing.assert_close(out.cpu().float(), ref, rtol=1e-2, atol=2e-2)
 
 
+def test_more_tiles_than_sms(cuda):
+    """Several tiles per CTA with fp8 weights: 5000 rows x 1280 columns = 200 work units on 148 CTAs."""
+    from triton_b200.triton_kernels.matmul import PrecisionConfig, matmul
+    g = torch.Generator().manual_seed(13)
+    x = (torch.randn(5000, 272, generator=g) * 0.5).to(torch.float8_e4m3fn)
+    w = (torch.randn(272, 1280, generator=g) * 0.5).to(torch.float8_e4m3fn)
+    out = matmul(x.to(cuda), _col_major(w).to(cuda), None, precision_config=PrecisionConfig(out_dtype=torch.bfloat16))
+    torch.testing.assert_close(out.cpu().float(), x.float() @ w.float(), rtol=1e-2, atol=1e-2)
+
+
 def test_preallocated_output(cuda):
     """``c=``: the product lands in the caller's buffer (a row-strided view here) and that tensor is returned."""
     from triton_b200.triton_kernels.matmul import PrecisionConfig, matmul

@@ -240,3 +240,30 @@ def test_argument_checks(cuda):
     s = torch.full((1, 8, 128), 127, device=cuda, dtype=torch.uint8)
     with pytest.raises(NotImplementedError):
         matmul(x, v, None, precision_config=PrecisionConfig(b_mx_scale=s))  # fp32 activations
+
+
+@pytest.mark.parametrize("swiglu", [False, True])
+def test_more_tiles_than_sms(cuda, swiglu):
+    """Several tiles per CTA (the persistent loop: the accumulator handed from one tile's epilogue to the next tile's
+    MMAs): 6000 rows on 8 experts x 1024 columns = about 200 work units on 148 CTAs, every output checked."""
+    from triton_b200.triton_kernels.matmul import PrecisionConfig, matmul, swiglu_activation
+    from triton_b200.triton_kernels.tensor import make_ragged_tensor_metadata
+    E, K, N = 8, 384, 1024
+    g = torch.Generator().manual_seed(21)
+    cnt = torch.tensor([900, 0, 1300, 128, 1, 1671, 1000, 1000], dtype=torch.int32)
+    R = int(cnt.sum())
+    rg = make_ragged_tensor_metadata(cnt.to(cuda), R)
+    x = (torch.randn(R, K, generator=g) * 0.5).to(torch.float8_e4m3fn)
+    v, s_, wdq = _quantise(0.3 * torch.randn(E, K, N, generator=g))
+    gam = torch.rand(R, generator=g)
+    out = matmul(x.to(cuda), v.to(cuda), None, rg, gammas=gam.to(cuda),
+                 precision_config=PrecisionConfig(b_mx_scale=s_.to(cuda), out_dtype=torch.bfloat16),
+                 fused_activation=swiglu_activation(1.1, 7.0) if swiglu else None)
+    ref = o.grouped_matmul_ref(x.float(), wdq, None, cnt.numpy(), gammas=gam, swiglu=(1.1, 7.0) if swiglu else None,
+                               out_dtype=torch.float32)
+    torch.testing.assert_close(out.cpu().float(), ref, rtol=1e-2, atol=2e-2)
+    # the same call twice: identical bits (no dependence on which CTA got which tile)
+    out2 = matmul(x.to(cuda), v.to(cuda), None, rg, gammas=gam.to(cuda),
+                  precision_config=PrecisionConfig(b_mx_scale=s_.to(cuda), out_dtype=torch.bfloat16),
+                  fused_activation=swiglu_activation(1.1, 7.0) if swiglu else None)
+    assert torch.equal(out, out2)

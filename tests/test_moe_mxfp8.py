@@ -76,7 +76,7 @@ def _check_like_reference(out, scale, ref32, maxtol=4e-1, rmstol=4e-2):
     assert int((scale.cpu().int() - s_ref.int()).abs().max()) <= 1
 
 
-@pytest.mark.parametrize("T,E,k", [(64, 8, 2), (777, 16, 4), (32, 16, 2)])
+@pytest.mark.parametrize("T,E,k", [(64, 8, 2), (777, 16, 4), (32, 16, 2), (5000, 8, 2)])  # the last: more work units than SMs
 @pytest.mark.parametrize("swiglu", [False, True])
 def test_grouped_mxfp8_x_mx4_quantised_output(cuda, T, E, k, swiglu):
     """MXFP8 activations x MXFP4 weights -> (SwiGLU) -> gammas -> scatter -> MXFP8 output, grouped by expert."""
