@@ -228,6 +228,94 @@ __global__ void bm_rank_kernel(const void* __restrict__ indx, int is16, long lon
   }
 }
 
+// The same two steps for up to BM_SMALL_COLS columns (the expert counts of MoE layers), shaped for latency: the routing
+// chain runs on every rank of an expert-parallel layer whatever the number of ranks. The scan spreads its columns
+// over blocks (a warp per column); the rank kernel derives the column offsets from the column sums itself, counts
+// per warp with match.any and prefixes the 32 warps' counts per column - three block barriers instead of one per
+// warp - and also writes the -1 entries the caller would otherwise have to memset (rows that name no column, the
+// tail of the column-sorted list).
+static constexpr int BM_SMALL_COLS = 256;
+
+__global__ void bm_scan_cols_kernel(int* __restrict__ partial, int n_blocks, int n_cols, int* __restrict__ col_sum) {
+  const int lane = threadIdx.x & 31;
+  const int c = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (c >= n_cols) return;
+  int carry = 0;
+  for (int b0 = 0; b0 < n_blocks; b0 += 32) {
+    const int b = b0 + lane;
+    const int v = b < n_blocks ? partial[(long long)b * n_cols + c] : 0;
+    int incl = v;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, incl, off);
+      if (lane >= off) incl += t;
+    }
+    if (b < n_blocks) partial[(long long)b * n_cols + c] = carry + incl - v;
+    carry += __shfl_sync(0xffffffffu, incl, 31);
+  }
+  if (lane == 0) col_sum[c] = carry;
+}
+
+__global__ void bm_rank_small_kernel(const void* __restrict__ indx, int is16, long long n, int n_cols,
+                                     const int* __restrict__ partial, const int* __restrict__ col_sum,
+                                     int* __restrict__ col_sorted, int* __restrict__ row_sorted) {
+  extern __shared__ int sm[];
+  int* offs = sm;                  // [n_cols] exclusive scan of col_sum
+  int* wc = sm + n_cols;           // [32][n_cols] per-warp counts, then their exclusive prefix over the warps
+  __shared__ int warp_tot[BM_SMALL_COLS / 32];
+  __shared__ int total_sh;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int j = threadIdx.x; j < 32 * n_cols; j += blockDim.x) wc[j] = 0;
+  int v = 0, incl = 0;
+  if (threadIdx.x < BM_SMALL_COLS) {
+    v = threadIdx.x < n_cols ? col_sum[threadIdx.x] : 0;
+    incl = v;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, incl, off);
+      if (lane >= off) incl += t;
+    }
+    if (lane == 31) warp_tot[warp] = incl;
+  }
+  __syncthreads();
+  if (threadIdx.x < BM_SMALL_COLS) {
+    int base = 0;
+    for (int w = 0; w < warp; ++w) base += warp_tot[w];
+    if (threadIdx.x < n_cols) offs[threadIdx.x] = base + incl - v;
+    if (threadIdx.x == BM_SMALL_COLS - 1) total_sh = base + incl;
+  }
+  const long long i = (long long)blockIdx.x * BM_BLOCK + threadIdx.x;
+  int e = -1;
+  if (i < n) {
+    e = load_indx(indx, is16, i);
+    if (e >= n_cols) e = -1;
+  }
+  const unsigned peers = __match_any_sync(0xffffffffu, e);
+  const int lane_rank = __popc(peers & ((1u << lane) - 1u));
+  if (e >= 0 && lane == __ffs(peers) - 1) wc[warp * n_cols + e] = __popc(peers);
+  __syncthreads();
+  if (threadIdx.x < n_cols) {
+    int running = 0;
+    for (int w = 0; w < 32; ++w) {
+      const int t = wc[w * n_cols + threadIdx.x];
+      wc[w * n_cols + threadIdx.x] = running;
+      running += t;
+    }
+  }
+  __syncthreads();
+  if (i < n) {
+    if (e >= 0) {
+      const int pos = offs[e] + partial[(long long)blockIdx.x * n_cols + e] + wc[warp * n_cols + e] + lane_rank;
+      row_sorted[i] = pos;
+      col_sorted[pos] = (int)i;
+    } else {
+      row_sorted[i] = -1;
+    }
+  }
+  if (blockIdx.x == 0)  // positions no entry maps to
+    for (long long j = total_sh + threadIdx.x; j < n; j += blockDim.x) col_sorted[j] = -1;
+}
+
 // --------------------------------------------------------------------------- ragged metadata
 
 // blockIdx.x == 0: slice_offs; blockIdx.x = 1 + s: block_offs[s] and block_schedule[s] for block
@@ -502,6 +590,14 @@ int bitmatrix_metadata_launch(const void* indx, int is16, long long n, int n_col
   const int n_blocks = (int)((n + BM_BLOCK - 1) / BM_BLOCK);
   int* partial = scratch;
   int* col_offs = scratch + (long long)n_blocks * n_cols;
+  if (n_cols <= BM_SMALL_COLS) {
+    if (n_blocks > 0) bm_hist_kernel<<<n_blocks, BM_BLOCK, n_cols * sizeof(int), stream>>>(indx, is16, n, n_cols, partial);
+    bm_scan_cols_kernel<<<(n_cols + 7) / 8, 256, 0, stream>>>(partial, n_blocks, n_cols, col_sum);
+    if (n_blocks > 0)
+      bm_rank_small_kernel<<<n_blocks, BM_BLOCK, 33 * n_cols * sizeof(int), stream>>>(indx, is16, n, n_cols, partial, col_sum,
+                                                                                    col_sorted, row_sorted);
+    return cuda_err(cudaGetLastError());
+  }
   if (n > 0) {
     cudaError_t e = cudaMemsetAsync(col_sorted, 0xFF, (size_t)n * sizeof(int), stream);
     if (e != cudaSuccess) return TB200_ERR_CUDA;
